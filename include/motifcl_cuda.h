@@ -1,0 +1,127 @@
+/* motifcl_cuda.h -- C ABI of the B200 (sm_100a) counter-synapse linear path.
+ *
+ * This is the boundary a MotifCL maintainer binds to: plain pointers and sizes, no C++ or
+ * framework types.  Each entry point names the MotifCL interface it replaces (paths are
+ * relative to the MotifCL source tree).  All data pointers are DEVICE pointers on the
+ * context's device unless a parameter is called *_host.  Tensors are dense row-major.
+ *
+ * Conventions
+ *   - Every function returns 0 on success or an MCL_CUDA_E* code; the human-readable reason
+ *     is kept per context (or per thread when no context exists yet) and read with
+ *     mcl_cuda_last_error().  Nothing throws, aborts, exits or traps.
+ *   - Work is enqueued on the context's stream in call order and the call returns without
+ *     waiting, like the reference's in-order queue; mcl_cuda_finish() and
+ *     mcl_cuda_download() wait.  A context is used from one host thread at a time.
+ *   - Counter-state layout: uint8 [out, in/4, 3], four 6-bit codes per 3 bytes
+ *     (kernels/compact_counter.cl:2-3,25-36).  scale, v: float [out].
+ *   - Argument checks mirror the reference's wrappers
+ *     (src/runtime/vulkan_backend.cpp:8497-8521,8615-8648,8676-8710,8741-8784): zero sizes,
+ *     in % 4 != 0, C == 0 or 3*(2C-1) > 64, non-finite lr / lr_scale / rms_beta, negative or
+ *     non-finite rms_eps, out*in beyond 32-bit element indexing are all refused.
+ *   - Float inputs must be finite; the update is defined for |counter + tick| < 2^31.
+ */
+#ifndef MOTIFCL_CUDA_H
+#define MOTIFCL_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MCL_CUDA_OK 0
+#define MCL_CUDA_EINVAL 1      /* refused argument (message says which) */
+#define MCL_CUDA_ECUDA 2       /* a CUDA runtime call failed */
+#define MCL_CUDA_EUNSUPPORTED 3 /* valid request this build cannot serve (message says why) */
+#define MCL_CUDA_ENOMEM 4
+#define MCL_CUDA_ENODEVICE 5
+
+typedef struct mcl_cuda_ctx mcl_cuda_ctx;
+
+/* ---- context / buffers: replaces VulkanRuntime::create, device_name, finish and
+ * VulkanRuntime::create_buffer / VulkanBuffer::upload / download
+ * (include/motifcl/runtime/vulkan_backend.hpp:156-243, 80-154). ---- */
+int mcl_cuda_device_count(void);   /* 0 when no usable CUDA device: callers skip like probe_vulkan_runtime() */
+int mcl_cuda_create(int device, mcl_cuda_ctx** out_ctx);
+/* Same, but enqueue on a stream the caller owns (a cudaStream_t passed as void*). */
+int mcl_cuda_create_on_stream(int device, void* cuda_stream, mcl_cuda_ctx** out_ctx);
+void mcl_cuda_destroy(mcl_cuda_ctx* ctx);
+const char* mcl_cuda_last_error(mcl_cuda_ctx* ctx);   /* ctx may be NULL */
+const char* mcl_cuda_device_name(mcl_cuda_ctx* ctx);
+int mcl_cuda_sm_count(mcl_cuda_ctx* ctx);
+int mcl_cuda_finish(mcl_cuda_ctx* ctx);
+int mcl_cuda_alloc(mcl_cuda_ctx* ctx, size_t bytes, void** out_dptr);
+int mcl_cuda_free(mcl_cuda_ctx* ctx, void* dptr);
+int mcl_cuda_upload(mcl_cuda_ctx* ctx, void* dst, const void* src_host, size_t bytes);
+int mcl_cuda_download(mcl_cuda_ctx* ctx, void* dst_host, const void* src, size_t bytes);
+/* Number of kernels this library has launched on the context so far. */
+uint64_t mcl_cuda_launch_count(mcl_cuda_ctx* ctx);
+
+/* ---- decode: replaces run_vulkan_compact_counter_decode_weight
+ * (include/motifcl/runtime/vulkan_backend.hpp:713-719; kernels/compact_counter.cl:39-55).
+ * weight[out,in] = scale[row] * t. ---- */
+int mcl_cuda_counter_decode_weight(mcl_cuda_ctx* ctx, const uint8_t* state, const float* scale,
+                                   float* weight, size_t in_features, size_t out_features, size_t C);
+
+/* ---- 2-bit pack (no reference counterpart in code; layout of
+ * docs/BITNET_TERNARY_VULKAN_PLAN.md:97): packed2 uint32 [out, in/16], weight m of a row in
+ * bits [2(m%16)+1 : 2(m%16)] of word m/16, field = t + 1.  Requires in % 16 == 0. ---- */
+int mcl_cuda_counter_pack2(mcl_cuda_ctx* ctx, const uint8_t* state, uint32_t* packed2,
+                           size_t in_features, size_t out_features, size_t C);
+
+/* ---- forward: replaces run_vulkan_compact_counter_forward_u8
+ * (vulkan_backend.hpp:722-730; kernels/vulkan/counter_forward_f32_rb4.comp; OpenCL path
+ * src/nn/compact_counter.cpp:287-293).  y[batch,out] = x[batch,in] * (scale . t)^T. ---- */
+int mcl_cuda_counter_forward(mcl_cuda_ctx* ctx, const float* x, const uint8_t* state,
+                             const float* scale, float* y, size_t batch, size_t in_features,
+                             size_t out_features, size_t C);
+
+/* ---- backward to input: replaces run_vulkan_compact_counter_backward_input_u8
+ * (vulkan_backend.hpp:752-760; kernels/compact_counter.cl:248-269).
+ * grad_x[batch,in] = (grad_out . scale) * t. ---- */
+int mcl_cuda_counter_backward_input(mcl_cuda_ctx* ctx, const uint8_t* state, const float* scale,
+                                    const float* grad_out, float* grad_x, size_t batch,
+                                    size_t in_features, size_t out_features, size_t C);
+
+/* ---- dense fused update: replaces CounterStateLinear::apply_update_seed, i.e. the three
+ * launches counter_row_stats_f32 + counter_apply_update_f32 + copy_f32
+ * (src/nn/compact_counter.cpp:113-156; kernels/compact_counter.cl:59-139).
+ * One kernel: reads state and grad_w[rows,in] once; writes state, scale, v in place and, when
+ * packed2_out != NULL (needs in % 16 == 0), the 2-bit weights of the NEW state.
+ * `rows` rows are updated; they are rows [row_offset, row_offset+rows) of the full matrix for
+ * the purpose of the per-element random stream, so a row shard updates exactly like the same
+ * rows of the whole layer.  All pointers address the shard's first row. ---- */
+int mcl_cuda_counter_update_dense(mcl_cuda_ctx* ctx, uint8_t* state, float* scale, float* v,
+                                  const float* grad_w, uint32_t* packed2_out, size_t C,
+                                  size_t in_features, size_t rows, size_t row_offset, float lr,
+                                  float lr_scale, float rms_beta, float rms_eps, uint32_t seed);
+
+/* ---- memory-native fused update: replaces run_vulkan_compact_counter_apply_update_fused
+ * (vulkan_backend.hpp:731-751; src/nn/compact_counter.cpp:158-231).  grad_w = grad_out^T x is
+ * formed in row tiles inside a bounded workspace of the context -- never as a whole
+ * [out,in] tensor -- and each tile is consumed by the dense update above.  The two scratch
+ * pointers exist for signature parity with the reference and may be NULL (unused).
+ * packed2_out may be NULL. ---- */
+int mcl_cuda_counter_update_fused(mcl_cuda_ctx* ctx, uint8_t* state, float* scale, float* v,
+                                  const float* grad_out, const float* x, float* scale_new_scratch,
+                                  float* denom_scratch, uint32_t* packed2_out, size_t C,
+                                  size_t in_features, size_t out_features, size_t batch, float lr,
+                                  float lr_scale, float rms_beta, float rms_eps, uint32_t seed);
+
+/* ---- generic fp32 matmul: replaces matmul / matmul_transpose_a / matmul_transpose_b
+ * (src/ops/matmul.cpp:1131-1233; kernels/matmul.cl:55-129,413-563).
+ * c[M,N] = op(a) op(b); trans_a: a stored [K,M]; trans_b: b stored [N,K]. ---- */
+int mcl_cuda_matmul_f32(mcl_cuda_ctx* ctx, const float* a, const float* b, float* c, size_t M,
+                        size_t K, size_t N, int trans_a, int trans_b);
+
+/* ---- ternary decode GEMV, M <= 16 (no reference kernel; semantics of the forward above
+ * applied to 2-bit weights).  y[M,out] = x[M,in] * (scale . t)^T.  Requires in % 16 == 0. ---- */
+int mcl_cuda_ternary_gemv(mcl_cuda_ctx* ctx, const float* x, const uint32_t* packed2,
+                          const float* scale, float* y, size_t M, size_t in_features,
+                          size_t out_features);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOTIFCL_CUDA_H */

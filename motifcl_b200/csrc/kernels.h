@@ -1,0 +1,42 @@
+// Internal launch interface between the C-ABI layer (abi.cu) and the kernel files.
+// Every launcher enqueues on `stream` and returns the launch status; none synchronises.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace mcl {
+
+// counter_update.cu
+cudaError_t launch_counter_update_dense(uint8_t* state, float* scale, float* v, const float* grad_w,
+                                        uint32_t* packed2, int C, int in_features, int rows,
+                                        int row_offset, float lr, float lr_scale, float rms_beta,
+                                        float rms_eps, uint32_t seed, int sm_count, size_t max_smem,
+                                        cudaStream_t stream);
+cudaError_t launch_decode_weight(const uint8_t* state, const float* scale, float* w, int C,
+                                 int in_features, int out_features, int sm_count, cudaStream_t stream);
+cudaError_t launch_pack2(const uint8_t* state, uint32_t* packed2, int C, int in_features,
+                         int out_features, int sm_count, cudaStream_t stream);
+
+// simt_gemm.cu -- fp32 CUDA-core contractions (any shape; exact fp32 FMA accumulation)
+cudaError_t launch_simt_matmul_f32(const float* a, const float* b, float* c, int M, int K, int N,
+                                   int transA, int transB, cudaStream_t stream);
+cudaError_t launch_simt_counter_forward(const float* x, const uint8_t* state, const float* scale,
+                                        float* y, int batch, int in_features, int out_features, int C,
+                                        cudaStream_t stream);
+cudaError_t launch_simt_counter_backward_input(const uint8_t* state, const float* scale,
+                                               const float* grad_out, float* grad_x, int batch,
+                                               int in_features, int out_features, int C,
+                                               cudaStream_t stream);
+// dW rows [row0, row0+rows) of dY^T X into grad_w[rows, in]
+cudaError_t launch_simt_grad_w(const float* grad_out, const float* x, float* grad_w, int batch,
+                               int in_features, int out_features, int row0, int rows,
+                               cudaStream_t stream);
+
+// gemv.cu
+cudaError_t launch_ternary_gemv(const float* x, const uint32_t* packed2, const float* scale, float* y,
+                                int M, int in_features, int out_features, int sm_count,
+                                cudaStream_t stream);
+
+}  // namespace mcl

@@ -1,0 +1,124 @@
+"""Python face of the C ABI: a `Context` owns one mcl_cuda_ctx and forwards calls.
+
+Device buffers are torch CUDA tensors (or raw integer device pointers); torch is used only
+for device memory and streams.  Every method enqueues on the context's stream and raises
+MotifclCudaError when the C call refuses or fails.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+from ._lib import MotifclCudaError, lib
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    return t.data_ptr()
+
+
+class Context:
+    """One device + one in-order stream, like the reference's Backend
+    (MotifCL include/motifcl/runtime/backend.hpp:43-81)."""
+
+    def __init__(self, device: int = 0, stream: int | None = None):
+        self._lib = lib()
+        self._ctx = C.c_void_p()
+        if stream is None:
+            rc = self._lib.mcl_cuda_create(device, C.byref(self._ctx))
+        else:
+            rc = self._lib.mcl_cuda_create_on_stream(device, C.c_void_p(stream), C.byref(self._ctx))
+        if rc != 0:
+            raise MotifclCudaError(rc, self._lib.mcl_cuda_last_error(None).decode())
+        self.device = device
+
+    @classmethod
+    def on_torch_stream(cls, device: int = 0) -> "Context":
+        import torch
+        return cls(device, torch.cuda.current_stream(device).cuda_stream)
+
+    def close(self):
+        if self._ctx:
+            self._lib.mcl_cuda_destroy(self._ctx)
+            self._ctx = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int):
+        if rc != 0:
+            raise MotifclCudaError(rc, self._lib.mcl_cuda_last_error(self._ctx).decode())
+
+    # -- context -------------------------------------------------------------------------
+    @property
+    def device_name(self) -> str:
+        return self._lib.mcl_cuda_device_name(self._ctx).decode()
+
+    @property
+    def sm_count(self) -> int:
+        return self._lib.mcl_cuda_sm_count(self._ctx)
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.mcl_cuda_launch_count(self._ctx))
+
+    def finish(self):
+        self._check(self._lib.mcl_cuda_finish(self._ctx))
+
+    def alloc(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        self._check(self._lib.mcl_cuda_alloc(self._ctx, nbytes, C.byref(p)))
+        return p.value
+
+    def free(self, dptr: int):
+        self._check(self._lib.mcl_cuda_free(self._ctx, dptr))
+
+    def upload(self, dst, src_host_ptr: int, nbytes: int):
+        self._check(self._lib.mcl_cuda_upload(self._ctx, _ptr(dst), src_host_ptr, nbytes))
+
+    def download(self, dst_host_ptr: int, src, nbytes: int):
+        self._check(self._lib.mcl_cuda_download(self._ctx, dst_host_ptr, _ptr(src), nbytes))
+
+    # -- counter path --------------------------------------------------------------------
+    def counter_decode_weight(self, state, scale, weight, in_features, out_features, C_):
+        self._check(self._lib.mcl_cuda_counter_decode_weight(
+            self._ctx, _ptr(state), _ptr(scale), _ptr(weight), in_features, out_features, C_))
+
+    def counter_pack2(self, state, packed2, in_features, out_features, C_):
+        self._check(self._lib.mcl_cuda_counter_pack2(
+            self._ctx, _ptr(state), _ptr(packed2), in_features, out_features, C_))
+
+    def counter_forward(self, x, state, scale, y, batch, in_features, out_features, C_):
+        self._check(self._lib.mcl_cuda_counter_forward(
+            self._ctx, _ptr(x), _ptr(state), _ptr(scale), _ptr(y), batch, in_features, out_features, C_))
+
+    def counter_backward_input(self, state, scale, grad_out, grad_x, batch, in_features, out_features, C_):
+        self._check(self._lib.mcl_cuda_counter_backward_input(
+            self._ctx, _ptr(state), _ptr(scale), _ptr(grad_out), _ptr(grad_x), batch, in_features,
+            out_features, C_))
+
+    def counter_update_dense(self, state, scale, v, grad_w, packed2_out, C_, in_features, rows,
+                             row_offset, lr, lr_scale, rms_beta, rms_eps, seed):
+        self._check(self._lib.mcl_cuda_counter_update_dense(
+            self._ctx, _ptr(state), _ptr(scale), _ptr(v), _ptr(grad_w), _ptr(packed2_out), C_,
+            in_features, rows, row_offset, lr, lr_scale, rms_beta, rms_eps, seed & 0xFFFFFFFF))
+
+    def counter_update_fused(self, state, scale, v, grad_out, x, packed2_out, C_, in_features,
+                             out_features, batch, lr, lr_scale, rms_beta, rms_eps, seed):
+        self._check(self._lib.mcl_cuda_counter_update_fused(
+            self._ctx, _ptr(state), _ptr(scale), _ptr(v), _ptr(grad_out), _ptr(x), None, None,
+            _ptr(packed2_out), C_, in_features, out_features, batch, lr, lr_scale, rms_beta, rms_eps,
+            seed & 0xFFFFFFFF))
+
+    def matmul_f32(self, a, b, c, M, K, N, trans_a=False, trans_b=False):
+        self._check(self._lib.mcl_cuda_matmul_f32(self._ctx, _ptr(a), _ptr(b), _ptr(c), M, K, N,
+                                                  int(trans_a), int(trans_b)))
+
+    def ternary_gemv(self, x, packed2, scale, y, M, in_features, out_features):
+        self._check(self._lib.mcl_cuda_ternary_gemv(self._ctx, _ptr(x), _ptr(packed2), _ptr(scale),
+                                                    _ptr(y), M, in_features, out_features))

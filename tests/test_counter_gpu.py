@@ -1,0 +1,278 @@
+"""GPU parity tests of the counter-linear path.  Every call goes through the C ABI
+(libmotifcl_cuda.so via ctypes); the CPU oracle and the golden file are the checkers.
+
+Bars: bit-exact for state bytes, 2-bit words, scale and v after the update given identical
+fp32 gradients; abs 2e-5 on the reference tests' small shapes and relative L2 1e-5 elsewhere
+for forward / grad_x / grad_w (tolerances of MotifCL tests/test_vulkan_counter_fused.cpp:107-118
+and tests/test_memory_truth_gate.cpp:86-97)."""
+import numpy as np
+import pytest
+import torch
+
+from cases import all_cases
+from motifcl_b200 import MotifclCudaError, codec, synth
+
+pytestmark = pytest.mark.gpu
+CASES = {c["name"]: c for c in all_cases()}
+DEV = "cuda:0"
+
+
+def _hy(c):
+    return c["lr"], c["lr_scale"], c["beta"], c["eps"], c["seed"]
+
+
+def _t(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def _bits(a):
+    return np.ascontiguousarray(a).view(np.uint32)
+
+
+def rel_l2(a, ref):
+    a, ref = a.astype(np.float64), ref.astype(np.float64)
+    return float(np.linalg.norm(a - ref) / max(np.linalg.norm(ref), 1e-30))
+
+
+def run_dense(ctx, c, gw, rows=None, row_offset=0, want_p2=True):
+    I, C = c["I"], c["C"]
+    rows = c["O"] if rows is None else rows
+    rb = I // 4 * 3
+    st = _t(c["state"][row_offset * rb:(row_offset + rows) * rb])
+    sc = _t(c["scale"][row_offset:row_offset + rows])
+    v = _t(c["v"][row_offset:row_offset + rows])
+    g = _t(gw[row_offset:row_offset + rows])
+    p2 = torch.zeros(rows, I // 16, dtype=torch.int32, device=DEV) if (want_p2 and I % 16 == 0) else None
+    ctx.counter_update_dense(st, sc, v, g, p2, C, I, rows, row_offset, *_hy(c))
+    ctx.finish()
+    return (st.cpu().numpy(), sc.cpu().numpy(), v.cpu().numpy(),
+            None if p2 is None else p2.cpu().numpy().view(np.uint32))
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_dense_update_bit_exact_vs_golden_and_oracle(name, ctx, orc, golden):
+    c = CASES[name]
+    gw = orc.grad_w(c["dy"], c["x"])
+    st, sc, v, p2 = run_dense(ctx, c, gw)
+    assert np.array_equal(st, golden[f"{name}/dense_state"])
+    assert np.array_equal(_bits(sc), _bits(golden[f"{name}/dense_scale"]))
+    assert np.array_equal(_bits(v), _bits(golden[f"{name}/dense_v"]))
+    o = orc.update_dense(c["state"], c["scale"], c["v"], gw, c["C"], c["I"], c["O"], 0, *_hy(c))
+    assert np.array_equal(st, o[0])
+    if p2 is not None:
+        assert np.array_equal(p2, o[3])
+
+
+def test_dense_update_row_shard_matches_full(ctx, orc):
+    c = CASES["wide"]
+    gw = orc.grad_w(c["dy"], c["x"])
+    full = orc.update_dense(c["state"], c["scale"], c["v"], gw, c["C"], c["I"], c["O"], 0, *_hy(c))
+    rb = c["I"] // 4 * 3
+    for r0, nr in [(0, 7), (7, 20), (27, 13)]:
+        st, sc, v, p2 = run_dense(ctx, c, gw, rows=nr, row_offset=r0)
+        assert np.array_equal(st, full[0][r0 * rb:(r0 + nr) * rb])
+        assert np.array_equal(_bits(sc), _bits(full[1][r0:r0 + nr]))
+        assert np.array_equal(_bits(v), _bits(full[2][r0:r0 + nr]))
+        assert np.array_equal(p2, full[3][r0:r0 + nr])
+
+
+@pytest.mark.parametrize("O,I,C,lr,lr_scale", [
+    (5, 4, 3, 1.0, 0.05),          # one group per row
+    (3, 16, 11, 0.5, 0.0),         # one 2-bit word per row
+    (130, 64, 11, 3e-3, 0.0),      # 16-byte aligned state rows, ragged row batches
+    (33, 2048, 11, 0.2, 0.05),     # eight lane sweeps, q path
+    (9, 14336, 11, 3e-3, 0.0),     # the longest row of the 8B-scale configuration
+    (6, 5632, 11, 1.0, 0.01),
+    (70, 260, 5, 2.0, 0.1),        # in % 16 != 0: byte path, no 2-bit output
+])
+def test_dense_update_shapes_bit_exact(ctx, orc, O, I, C, lr, lr_scale):
+    rng = np.random.default_rng(O * 100003 + I)
+    ncodes = 64 if C == 11 else 3 * (2 * C - 1)
+    state = codec.pack_codes(rng.integers(0, ncodes, size=(O, I)).astype(np.uint8)).reshape(-1)
+    c = dict(I=I, O=O, C=C, state=state, scale=rng.uniform(0.02, 0.2, O).astype(np.float32),
+             v=rng.uniform(1e-4, 1e-2, O).astype(np.float32), lr=lr, lr_scale=lr_scale, beta=0.9,
+             eps=1e-3, seed=int(rng.integers(0, 2 ** 32)))
+    gw = (0.3 * rng.standard_normal((O, I))).astype(np.float32)
+    gw[0, :4] = [0.0, -0.0, 1e-30, -1e3]     # zero, negative zero, tiny, huge gradient
+    o = orc.update_dense(state, c["scale"], c["v"], gw, C, I, O, 0, *_hy(c))
+    st, sc, v, p2 = run_dense(ctx, c, gw)
+    assert np.array_equal(st, o[0])
+    assert np.array_equal(_bits(sc), _bits(o[1]))
+    assert np.array_equal(_bits(v), _bits(o[2]))
+    if I % 16 == 0:
+        assert np.array_equal(p2, o[3])
+
+
+def test_two_updates_in_a_row_stay_exact(ctx, orc):
+    c = dict(CASES["cfg1_rebase"])
+    gw = orc.grad_w(c["dy"], c["x"])
+    st, sc, v = c["state"], c["scale"], c["v"]
+    dst, dsc, dv = _t(st), _t(sc), _t(v)
+    for step in range(3):
+        hy = (c["lr"], c["lr_scale"], c["beta"], c["eps"], c["seed"] + step)
+        st, sc, v, _ = orc.update_dense(st, sc, v, gw, c["C"], c["I"], c["O"], 0, *hy)
+        ctx.counter_update_dense(dst, dsc, dv, _t(gw), None, c["C"], c["I"], c["O"], 0, *hy)
+    ctx.finish()
+    assert np.array_equal(dst.cpu().numpy(), st)
+    assert np.array_equal(_bits(dsc.cpu().numpy()), _bits(sc))
+    assert np.array_equal(_bits(dv.cpu().numpy()), _bits(v))
+
+
+@pytest.mark.parametrize("name", ["fused_witness", "cross_backend"])
+def test_decode_forward_grad_x_on_reference_test_shapes(name, ctx, orc, golden):
+    c = CASES[name]
+    N, I, O, C = c["N"], c["I"], c["O"], c["C"]
+    st, sc = _t(c["state"]), _t(c["scale"])
+    w = torch.empty(O, I, dtype=torch.float32, device=DEV)
+    ctx.counter_decode_weight(st, sc, w, I, O, C)
+    assert np.array_equal(w.cpu().numpy(), golden[f"{name}/weight"])     # one multiply: exact
+    y = torch.empty(N, O, dtype=torch.float32, device=DEV)
+    ctx.counter_forward(_t(c["x"]), st, sc, y, N, I, O, C)
+    y_ref = orc.forward(c["x"], c["state"], c["scale"], C, O)
+    assert np.abs(y.cpu().numpy() - y_ref).max() <= 2e-5
+    gx = torch.empty(N, I, dtype=torch.float32, device=DEV)
+    ctx.counter_backward_input(st, sc, _t(c["dy"]), gx, N, I, O, C)
+    assert np.abs(gx.cpu().numpy() - golden[f"{name}/grad_x"]).max() <= 2e-5
+
+
+def test_known_answer_vectors_through_the_abi(ctx):
+    """MotifCL tests/test_vulkan_runtime_standalone.cpp:579-640."""
+    C = 3
+    tern = np.array([[1, 0, -1, 1], [0, 1, 1, -1]])
+    st = _t(codec.pack_codes(codec.encode(tern, np.zeros_like(tern), C)).reshape(-1))
+    sc = _t(np.array([0.5, 2.0], np.float32))
+    w = torch.empty(2, 4, dtype=torch.float32, device=DEV)
+    ctx.counter_decode_weight(st, sc, w, 4, 2, C)
+    assert w.cpu().numpy().tolist() == [[0.5, 0.0, -0.5, 0.5], [0.0, 2.0, 2.0, -2.0]]
+    go = np.array([[1.0, 2.0], [-1.0, 0.5]], np.float32)
+    gx = torch.empty(2, 4, dtype=torch.float32, device=DEV)
+    ctx.counter_backward_input(st, sc, _t(go), gx, 2, 4, 2, C)
+    expect = go[:, :1] * 0.5 * tern[0] + go[:, 1:] * 2.0 * tern[1]
+    assert np.allclose(gx.cpu().numpy(), expect, atol=1e-6)
+
+
+def test_cfg1_forward_backward_grad_w_within_tolerance(ctx, orc):
+    c = CASES["cfg1"]
+    N, I, O, C = c["N"], c["I"], c["O"], c["C"]
+    st, sc = _t(c["state"]), _t(c["scale"])
+    y = torch.empty(N, O, dtype=torch.float32, device=DEV)
+    ctx.counter_forward(_t(c["x"]), st, sc, y, N, I, O, C)
+    assert rel_l2(y.cpu().numpy(), orc.forward(c["x"], c["state"], c["scale"], C, O)) <= 1e-5
+    gx = torch.empty(N, I, dtype=torch.float32, device=DEV)
+    ctx.counter_backward_input(st, sc, _t(c["dy"]), gx, N, I, O, C)
+    assert rel_l2(gx.cpu().numpy(), orc.backward_input(c["dy"], c["state"], c["scale"], C, I)) <= 1e-5
+    gw = torch.empty(O, I, dtype=torch.float32, device=DEV)
+    ctx.matmul_f32(_t(c["dy"]), _t(c["x"]), gw, O, N, I, trans_a=True)
+    assert rel_l2(gw.cpu().numpy(), orc.grad_w(c["dy"], c["x"])) <= 1e-5
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True)])
+def test_matmul_f32_multi_tile_odd_shapes(ctx, orc, ta, tb):
+    """48 x 40 x 33 as in MotifCL tests/test_vulkan_runtime_standalone.cpp (multi-tile,
+    non-multiples); tolerance 1e-4 abs of tests/test_matmul.cpp."""
+    M, K, N = 48, 40, 33
+    rng = np.random.default_rng(3)
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    a = A.T.copy() if ta else A
+    b = B.T.copy() if tb else B
+    c = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ctx.matmul_f32(_t(a), _t(b), c, M, K, N, ta, tb)
+    assert np.abs(c.cpu().numpy() - orc.matmul(a, b, M, K, N, ta, tb)).max() <= 1e-4
+
+
+@pytest.mark.parametrize("name", ["fused_witness", "cross_backend", "cfg1_rebase"])
+def test_fused_update_through_layer_api(name, ctx, orc, golden):
+    """The autograd-order transaction of MotifCL src/nn/compact_counter.cpp:40-50: grad_x from
+    the pre-update state, then the memory-native update.  State/scale/v must equal the
+    compiled reference's exactly when the in-library grad_w equals the r-ascending fp32 sum
+    bit for bit."""
+    c = CASES[name]
+    N, I, O, C = c["N"], c["I"], c["O"], c["C"]
+    st, sc, v = _t(c["state"]), _t(c["scale"]), _t(c["v"])
+    p2 = torch.zeros(O, max(I // 16, 1), dtype=torch.int32, device=DEV) if I % 16 == 0 else None
+    ctx.counter_update_fused(st, sc, v, _t(c["dy"]), _t(c["x"]), p2, C, I, O, N, *_hy(c))
+    ctx.finish()
+    got = codec.unpack_codes(st.cpu().numpy().reshape(O, -1), I)
+    want = codec.unpack_codes(golden[f"{name}/dense_state"].reshape(O, -1), I)
+    # these shapes take the exact CUDA-core contraction (k ascending, unfused multiply-add),
+    # so the whole transaction is bit-identical, as MotifCL tests/test_vulkan_counter_fused.cpp:120-133 asks
+    assert np.array_equal(got, want)
+    assert np.array_equal(_bits(sc.cpu().numpy()), _bits(golden[f"{name}/dense_scale"]))
+    assert np.array_equal(_bits(v.cpu().numpy()), _bits(golden[f"{name}/dense_v"]))
+    if p2 is not None:
+        t, _ = codec.decode(got, C)
+        assert np.array_equal(codec.unpack2(p2.cpu().numpy().view(np.uint32), I), (t + 1).astype(np.uint8))
+
+
+def test_pack2_matches_oracle(ctx, orc):
+    c = CASES["cfg1"]
+    p2 = torch.empty(c["O"], c["I"] // 16, dtype=torch.int32, device=DEV)
+    ctx.counter_pack2(_t(c["state"]), p2, c["I"], c["O"], c["C"])
+    assert np.array_equal(p2.cpu().numpy().view(np.uint32), orc.pack2(c["state"], c["C"], c["I"], c["O"]))
+
+
+@pytest.mark.parametrize("M", [1, 3, 4, 16])
+@pytest.mark.parametrize("O,I", [(288, 288), (96, 2048), (40, 5632)])
+def test_ternary_gemv_vs_oracle(ctx, orc, M, O, I):
+    rng = np.random.default_rng(M * 7 + O)
+    st = synth.counters(5, O % 97, O, I).reshape(-1)
+    p2 = orc.pack2(st, 11, I, O)
+    scale = rng.uniform(0.02, 0.2, O).astype(np.float32)
+    x = rng.standard_normal((M, I)).astype(np.float32)
+    y = torch.empty(M, O, dtype=torch.float32, device=DEV)
+    ctx.ternary_gemv(_t(x), _t(p2.view(np.int32)), _t(scale), y, M, I, O)
+    ref64 = orc.ternary_gemv(x, p2, scale, f64=True)
+    assert rel_l2(y.cpu().numpy(), ref64) <= 1e-5
+    assert rel_l2(y.cpu().numpy(), orc.forward(x, st, scale, 11, O)) <= 1e-5
+
+
+def test_argument_checks_mirror_the_reference(ctx):
+    """Refusals of MotifCL src/runtime/vulkan_backend.cpp:8497-8521."""
+    st = torch.zeros(48, dtype=torch.uint8, device=DEV)
+    f = torch.zeros(64, dtype=torch.float32, device=DEV)
+    good = dict(C_=3, in_features=8, rows=2, row_offset=0, lr=0.1, lr_scale=0.0, rms_beta=0.9, rms_eps=1e-3, seed=1)
+
+    def call(**kw):
+        a = dict(good, **kw)
+        ctx.counter_update_dense(st, f, f, f, None, a["C_"], a["in_features"], a["rows"], a["row_offset"],
+                                 a["lr"], a["lr_scale"], a["rms_beta"], a["rms_eps"], a["seed"])
+
+    call()
+    for bad, frag in [(dict(in_features=6), "in_features % 4"), (dict(C_=0), "non-zero"),
+                      (dict(C_=12), "C too large"), (dict(rows=0), "non-zero"),
+                      (dict(lr=float("nan")), "finite lr"), (dict(lr_scale=float("inf")), "finite lr_scale"),
+                      (dict(rms_beta=float("nan")), "finite rms_beta"), (dict(rms_eps=-1.0), "rms_eps")]:
+        with pytest.raises(MotifclCudaError) as e:
+            call(**bad)
+        assert e.value.code == 1 and frag in e.value.message
+    with pytest.raises(MotifclCudaError):
+        ctx.ternary_gemv(f, st, f, f, 17, 16, 2)
+    ctx.finish()    # the context stays usable after refusals
+    call()
+    ctx.finish()
+
+
+def test_layer_mirror_teacher_recovery(ctx):
+    """Statistical witness of MotifCL tests/test_counter_state.cpp:17-90 (16x16 teacher, N 256,
+    C 11, lr 5e-3, 800 steps of forward + MSE + backward): final MSE <= 5e-3, ternary accuracy
+    >= 0.9.  MSE gradient formed with torch; everything else through the library."""
+    from motifcl_b200 import CounterStateLinear
+    g = torch.Generator(device="cpu").manual_seed(0)
+    teacher_t = torch.randint(-1, 2, (16, 16), generator=g).float()
+    s0 = float(np.sqrt(3.0 / 32.0))
+    teacher = (teacher_t * s0).to(DEV)
+    layer = CounterStateLinear(ctx, 16, 16, C=11, lr=5e-3, seed=12345)
+    mse = None
+    for step in range(800):
+        x = torch.randn(256, 16, generator=g).to(DEV)
+        y = layer.forward(x)
+        target = x @ teacher.T
+        diff = y - target
+        mse = float((diff * diff).mean())
+        grad_out = (2.0 / diff.numel()) * diff
+        layer.backward(x, grad_out, layer.next_seed(), need_grad_x=False)
+    codes = codec.unpack_codes(layer.state.cpu().numpy().reshape(16, -1), 16)
+    t, _ = codec.decode(codes, 11)
+    acc = float((t == teacher_t.numpy().astype(np.int64)).mean())
+    assert mse <= 5e-3 and acc >= 0.9, (mse, acc)

@@ -109,46 +109,47 @@ def measured_peaks():
     return 6650.0, 1400.0, "fallback"
 
 
-def cpu_reference_rate(wl, seconds_budget: float = 12.0):
+def cpu_reference_rate(wl, min_seconds: float = 10.0, max_tokens: int = 8192):
     """Times the CPU checker (restatement of the reference kernels, all host cores) on a
-    bounded sample of the workload: whole linears of the workload at a reduced token count,
-    scaled to tokens/s by tokens * weights (every term of the step is linear in tokens except
-    the update, which is timed in full)."""
+    bounded sample of the workload: one linear of every distinct shape, at up to `max_tokens`
+    tokens, repeated until `min_seconds` of CPU work; scaled to the full workload by
+    tokens * weights for the three contractions and by weights for the update."""
     import oracle
     from motifcl_b200 import synth
     cores = len(os.sched_getaffinity(0))
     oracle.port.set_threads(cores)
     cfg, sigma = wl["cfg"], wl["sigma"]
-    n_s = min(wl["tokens"], 256)
-    t_gemm = t_upd = 0.0
-    w_done = 0
+    n_s = min(wl["tokens"], max_tokens)
     shapes = {}
     for idx, l in enumerate(wl["linears"]):
         shapes.setdefault((l.out_features, l.in_features), idx)
-    t0 = time.perf_counter()
+    data = []
     for (O, I), idx in shapes.items():
-        st = synth.counters(cfg, idx, O, I).reshape(-1)
         sc, v = synth.scale_v(cfg, idx, O, I)
-        x = synth.activations(cfg, idx, n_s, I)
-        dy = synth.upstream_grad(cfg, idx, n_s, O, sigma)
-        a = time.perf_counter()
-        oracle.port.forward(x, st, sc, 11, O)
-        oracle.port.backward_input(dy, st, sc, 11, I)
-        gw = oracle.port.grad_w(dy, x)
-        b = time.perf_counter()
-        oracle.port.update_dense(st, sc, v, gw, 11, I, O, 0, 3e-3, 0.0, 0.9, 1e-3, 12345)
-        c = time.perf_counter()
-        t_gemm += b - a
-        t_upd += c - b
-        w_done += O * I
-        if time.perf_counter() - t0 > seconds_budget:
-            break
+        data.append((O, I, synth.counters(cfg, idx, O, I).reshape(-1), sc, v,
+                     synth.activations(cfg, idx, n_s, I), synth.upstream_grad(cfg, idx, n_s, O, sigma)))
+    t_gemm = t_upd = 0.0
+    reps = 0
+    t0 = time.perf_counter()
+    while reps == 0 or time.perf_counter() - t0 < min_seconds:
+        for O, I, st, sc, v, x, dy in data:
+            a = time.perf_counter()
+            oracle.port.forward(x, st, sc, 11, O)
+            oracle.port.backward_input(dy, st, sc, 11, I)
+            gw = oracle.port.grad_w(dy, x)
+            b = time.perf_counter()
+            oracle.port.update_dense(st, sc, v, gw, 11, I, O, 0, 3e-3, 0.0, 0.9, 1e-3, 12345)
+            c = time.perf_counter()
+            t_gemm += b - a
+            t_upd += c - b
+        reps += 1
+    w_done = sum(d[0] * d[1] for d in data)
     alg = algorithmic(wl)
-    # seconds for the full workload: GEMM part scales with tokens*weights, update with weights
-    full = t_gemm * (wl["tokens"] / n_s) * (alg["weights"] / w_done) + t_upd * (alg["weights"] / w_done)
+    full = (t_gemm / reps) * (wl["tokens"] / n_s) * (alg["weights"] / w_done) + (t_upd / reps) * (alg["weights"] / w_done)
     return dict(value=wl["tokens"] / full, unit=UNIT, cores=cores, kind="port",
-                sample=f"{len(shapes)} distinct linear shapes ({w_done} weights) at {n_s} tokens, "
-                       f"scaled by tokens*weights (update by weights) to the full workload"), full
+                sample=f"{len(data)} distinct linear shapes ({w_done} weights) at {n_s} tokens, {reps} repetitions "
+                       f"({time.perf_counter() - t0:.1f} s of CPU work); scaled by tokens*weights "
+                       f"(update by weights) to the full workload"), full
 
 
 def run_reference(args, wl):
@@ -158,7 +159,7 @@ def run_reference(args, wl):
     times = []
     base = None
     for i in range(args.warmup + args.steps):
-        base, full = cpu_reference_rate(wl, seconds_budget=8.0)
+        base, full = cpu_reference_rate(wl, min_seconds=0.0, max_tokens=2048)
         if i >= args.warmup:
             times.append(full)
     t = float(np.mean(times))

@@ -109,6 +109,35 @@ int mcl_cuda_counter_update_fused(mcl_cuda_ctx* ctx, uint8_t* state, float* scal
                                   size_t in_features, size_t out_features, size_t batch, float lr,
                                   float lr_scale, float rms_beta, float rms_eps, uint32_t seed);
 
+/* ---- how the three contractions are computed (no reference counterpart: the reference has one
+ * fp32 path).  mode MCL_CUDA_GEMM_AUTO: tensor cores (tcgen05, bf16 term splitting) for shapes
+ * that are large and aligned enough, the exact CUDA-core kernels otherwise;
+ * MCL_CUDA_GEMM_EXACT: always the CUDA-core kernels, whose every output equals the reference's
+ * k-ascending fp32 sum bit for bit; MCL_CUDA_GEMM_TENSOR: tensor cores whenever the shape
+ * allows.  act_terms (2 or 3) = bf16 terms per fp32 activation in Y and dX; grad_terms (3 or 6)
+ * = term products in dW = dY^T X.  Defaults: AUTO, 3, 6 (error of every product below 1e-5
+ * relative L2 against the fp32 reference sum; 2 / 3 also meet that bound and cost 7/12 of the
+ * tensor-core time). ---- */
+#define MCL_CUDA_GEMM_AUTO 0
+#define MCL_CUDA_GEMM_EXACT 1
+#define MCL_CUDA_GEMM_TENSOR 2
+int mcl_cuda_set_gemm_mode(mcl_cuda_ctx* ctx, int mode, int act_terms, int grad_terms);
+
+/* ---- one whole training step of one counter linear (what MotifCL's autograd does around
+ * CounterStateLinear, src/nn/compact_counter.cpp:40-50,266-300, with the dense update of
+ * :113-156): y = x W^T; grad_x = (grad_out . scale) T from the PRE-update state; grad_w =
+ * grad_out^T x; then the fused update of `rows` rows starting at `row_offset` (pass rows =
+ * out_features, row_offset = 0 for the whole layer).  Shares the operand splits between the
+ * three products.  y, grad_x and packed2_out may be NULL to skip that output; grad_w must hold
+ * out*in floats.  With update_rows == 0 the update is skipped (the caller reduces grad_w
+ * across ranks first and then calls mcl_cuda_counter_update_dense on its shard). ---- */
+int mcl_cuda_counter_linear_step(mcl_cuda_ctx* ctx, const float* x, const float* grad_out,
+                                 uint8_t* state, float* scale, float* v, float* y, float* grad_x,
+                                 float* grad_w, uint32_t* packed2_out, size_t C, size_t in_features,
+                                 size_t out_features, size_t batch, size_t update_rows,
+                                 size_t row_offset, float lr, float lr_scale, float rms_beta,
+                                 float rms_eps, uint32_t seed);
+
 /* ---- generic fp32 matmul: replaces matmul / matmul_transpose_a / matmul_transpose_b
  * (src/ops/matmul.cpp:1131-1233; kernels/matmul.cl:55-129,413-563).
  * c[M,N] = op(a) op(b); trans_a: a stored [K,M]; trans_b: b stored [N,K]. ---- */

@@ -21,6 +21,11 @@ struct mcl_cuda_ctx {
     // grow-only workspace used by entry points that need scratch (row tiles of grad_w, ...)
     void* ws = nullptr;
     size_t ws_bytes = 0;
+    // how the contractions run (mcl_cuda_set_gemm_mode)
+    int gemm_mode = MCL_CUDA_GEMM_AUTO;
+    int act_terms = 3;
+    int grad_terms = 6;
+    int* err_word = nullptr;     // device word the tensor-core kernels set when a bounded wait gives up
 };
 
 namespace {
@@ -128,7 +133,77 @@ int create_impl(int device, cudaStream_t stream, bool own, mcl_cuda_ctx** out_ct
     } else {
         ctx->stream = stream;
     }
+    e = cudaMalloc(reinterpret_cast<void**>(&ctx->err_word), sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->err_word, 0, sizeof(int));
+    if (e != cudaSuccess) {
+        if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        return fail_cuda(nullptr, "context setup", e);
+    }
     *out_ctx = ctx;
+    return MCL_CUDA_OK;
+}
+
+// Reads (after the stream has drained) whether a tensor-core kernel abandoned a wait.
+int check_device_error(mcl_cuda_ctx* ctx) {
+    int w = 0;
+    cudaError_t e = cudaMemcpy(&w, ctx->err_word, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail_cuda(ctx, "error-word read", e);
+    if (w != 0) {
+        cudaMemset(ctx->err_word, 0, sizeof(int));
+        const char* who = w == 1 ? "TMA producer (slot never released)" : w == 2 ? "MMA issuer (tile never arrived)"
+                                                                                 : "epilogue (accumulator never completed)";
+        return fail(ctx, MCL_CUDA_ECUDA, std::string("tensor-core kernel gave up a bounded wait: ") + who +
+                                             "; results of that call are invalid");
+    }
+    return MCL_CUDA_OK;
+}
+
+struct Carver {
+    char* base = nullptr;
+    size_t off = 0;
+    size_t reserve(size_t bytes) { off = (off + 1023) & ~size_t(1023); const size_t at = off; off += bytes; return at; }
+};
+
+inline int up8(size_t x) { return (int)((x + 7) & ~size_t(7)); }
+
+bool tc_wanted(const mcl_cuda_ctx* ctx, size_t M, size_t N, size_t K) {
+    if (ctx->gemm_mode == MCL_CUDA_GEMM_EXACT) return false;
+    if (N % 4 != 0) return false;                       // 128-bit stores of the output tile
+    if (M > 0x7fffffffull / 2 || N > 0x7fffffffull / 2 || K > 0x7fffffffull / 2) return false;
+    if (ctx->gemm_mode == MCL_CUDA_GEMM_TENSOR) return true;
+    return (double)M * (double)N * (double)K >= (double)(1u << 22);
+}
+
+// term lists: product of plane pa of A with plane pb of B, smallest contributions first
+void act_term_list(int act_terms, int* pa, int* pb, int* n) {
+    *n = act_terms;
+    for (int t = 0; t < act_terms; ++t) { pa[t] = act_terms - 1 - t; pb[t] = 0; }
+}
+void grad_term_list(int grad_terms, int* pa, int* pb, int* n, int* planes) {
+    if (grad_terms >= 6) {
+        const int a[6] = {2, 0, 1, 1, 0, 0}, b[6] = {0, 2, 1, 0, 1, 0};
+        for (int t = 0; t < 6; ++t) { pa[t] = a[t]; pb[t] = b[t]; }
+        *n = 6; *planes = 3;
+    } else {
+        const int a[3] = {1, 0, 0}, b[3] = {0, 1, 0};
+        for (int t = 0; t < 3; ++t) { pa[t] = a[t]; pb[t] = b[t]; }
+        *n = 3; *planes = 2;
+    }
+}
+
+#define MCL_CU(ctx, what, call) do { cudaError_t _e = (call); if (_e != cudaSuccess) return fail_cuda(ctx, what, _e); } while (0)
+
+// One tensor-core product on prepared planes (adds the split-K workspace to the carve).
+int tc_product(mcl_cuda_ctx* ctx, const void* a, int a_planes, int lda, size_t a_stride, const void* b,
+               int b_planes, int ldb, size_t b_stride, float* c, int ldc, int M, int N, int K, const int* pa,
+               const int* pb, int nterms, const float* col_scale, float* splitk_ws, int splits) {
+    int launches = 0;
+    cudaError_t e = mcl::launch_tc_gemm(a, a_planes, lda, a_stride, b, b_planes, ldb, b_stride, c, ldc, M, N, K,
+                                        pa, pb, nterms, col_scale, splitk_ws, splits, ctx->err_word,
+                                        ctx->max_smem, ctx->stream, &launches);
+    ctx->launches += launches;
+    if (e != cudaSuccess) return fail_cuda(ctx, "tensor-core contraction", e);
     return MCL_CUDA_OK;
 }
 
@@ -150,6 +225,7 @@ void mcl_cuda_destroy(mcl_cuda_ctx* ctx) {
     DeviceGuard guard(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->ws) cudaFree(ctx->ws);
+    if (ctx->err_word) cudaFree(ctx->err_word);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -163,6 +239,16 @@ int mcl_cuda_finish(mcl_cuda_ctx* ctx) {
     DeviceGuard guard(ctx->device);
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) return fail_cuda(ctx, "finish", e);
+    return check_device_error(ctx);
+}
+
+int mcl_cuda_set_gemm_mode(mcl_cuda_ctx* ctx, int mode, int act_terms, int grad_terms) {
+    MCL_NEED_CTX(ctx);
+    if (mode != MCL_CUDA_GEMM_AUTO && mode != MCL_CUDA_GEMM_EXACT && mode != MCL_CUDA_GEMM_TENSOR)
+        return fail(ctx, MCL_CUDA_EINVAL, "set_gemm_mode: unknown mode");
+    if (act_terms != 2 && act_terms != 3) return fail(ctx, MCL_CUDA_EINVAL, "set_gemm_mode: act_terms must be 2 or 3");
+    if (grad_terms != 3 && grad_terms != 6) return fail(ctx, MCL_CUDA_EINVAL, "set_gemm_mode: grad_terms must be 3 or 6");
+    ctx->gemm_mode = mode; ctx->act_terms = act_terms; ctx->grad_terms = grad_terms;
     return MCL_CUDA_OK;
 }
 int mcl_cuda_alloc(mcl_cuda_ctx* ctx, size_t bytes, void** out_dptr) {
@@ -255,6 +341,27 @@ int mcl_cuda_counter_forward(mcl_cuda_ctx* ctx, const float* x, const uint8_t* s
     MCL_TRY(check_ptr(ctx, op, "scale", scale, 4));
     MCL_TRY(check_ptr(ctx, op, "y", y, 4));
     DeviceGuard guard(ctx->device);
+    if (tc_wanted(ctx, batch, out_features, in_features)) {
+        const int ta = ctx->act_terms, ldi = up8(in_features);
+        int splits = 1;
+        const size_t sk = mcl::tc_splitk_workspace_bytes((int)batch, (int)out_features, (int)in_features,
+                                                         ctx->sm_count, &splits);
+        Carver cv;
+        const size_t o_x = cv.reserve((size_t)ta * batch * ldi * 2), o_t = cv.reserve(out_features * (size_t)ldi * 2),
+                     o_k = cv.reserve(sk);
+        void* wsp = nullptr;
+        MCL_TRY(ws_reserve(ctx, cv.off, &wsp));
+        char* w = static_cast<char*>(wsp);
+        MCL_LAUNCH(ctx, op, mcl::launch_split_planes(x, (int)batch, (int)in_features, nullptr, w + o_x, ldi, ta,
+                                                     nullptr, 0, 0, ctx->stream));
+        MCL_LAUNCH(ctx, op, mcl::launch_expand_ternary(state, (int)C, (int)out_features, (int)in_features,
+                                                       w + o_t, ldi, nullptr, 0, ctx->stream));
+        int pa[6], pb[6], nt;
+        act_term_list(ta, pa, pb, &nt);
+        return tc_product(ctx, w + o_x, ta, ldi, batch * (size_t)ldi, w + o_t, 1, ldi, out_features * (size_t)ldi, y,
+                          (int)out_features, (int)batch, (int)out_features, (int)in_features, pa, pb, nt, scale,
+                          reinterpret_cast<float*>(w + o_k), splits);
+    }
     MCL_LAUNCH(ctx, op, mcl::launch_simt_counter_forward(x, state, scale, y, (int)batch, (int)in_features,
                                                          (int)out_features, (int)C, ctx->stream));
     return MCL_CUDA_OK;
@@ -272,6 +379,27 @@ int mcl_cuda_counter_backward_input(mcl_cuda_ctx* ctx, const uint8_t* state, con
     MCL_TRY(check_ptr(ctx, op, "grad_out", grad_out, 4));
     MCL_TRY(check_ptr(ctx, op, "grad_x", grad_x, 4));
     DeviceGuard guard(ctx->device);
+    if (tc_wanted(ctx, batch, in_features, out_features)) {
+        const int ta = ctx->act_terms, ldo = up8(out_features);
+        int splits = 1;
+        const size_t sk = mcl::tc_splitk_workspace_bytes((int)batch, (int)in_features, (int)out_features,
+                                                         ctx->sm_count, &splits);
+        Carver cv;
+        const size_t o_g = cv.reserve((size_t)ta * batch * ldo * 2), o_t = cv.reserve(in_features * (size_t)ldo * 2),
+                     o_k = cv.reserve(sk);
+        void* wsp = nullptr;
+        MCL_TRY(ws_reserve(ctx, cv.off, &wsp));
+        char* w = static_cast<char*>(wsp);
+        MCL_LAUNCH(ctx, op, mcl::launch_split_planes(grad_out, (int)batch, (int)out_features, scale, w + o_g, ldo, ta,
+                                                     nullptr, 0, 0, ctx->stream));
+        MCL_LAUNCH(ctx, op, mcl::launch_expand_ternary(state, (int)C, (int)out_features, (int)in_features,
+                                                       nullptr, 0, w + o_t, ldo, ctx->stream));
+        int pa[6], pb[6], nt;
+        act_term_list(ta, pa, pb, &nt);
+        return tc_product(ctx, w + o_g, ta, ldo, batch * (size_t)ldo, w + o_t, 1, ldo, in_features * (size_t)ldo,
+                          grad_x, (int)in_features, (int)batch, (int)in_features, (int)out_features, pa, pb, nt,
+                          nullptr, reinterpret_cast<float*>(w + o_k), splits);
+    }
     MCL_LAUNCH(ctx, op, mcl::launch_simt_counter_backward_input(state, scale, grad_out, grad_x, (int)batch,
                                                                 (int)in_features, (int)out_features,
                                                                 (int)C, ctx->stream));
@@ -325,29 +453,129 @@ int mcl_cuda_counter_update_fused(mcl_cuda_ctx* ctx, uint8_t* state, float* scal
     if (packed2_out && in_features % 16 != 0)
         return fail(ctx, MCL_CUDA_EINVAL, "counter update: packed2 output requires in_features % 16 == 0");
     // Row tile of grad_w: at most 1/8 of the dense [out,in] gradient (and at most 32 MiB),
-    // at least one row; rounded to a multiple of 64 rows when that fits.
+    // at least one row; rounded to a multiple of 128 rows when that fits.
     const size_t row_b = in_features * sizeof(float);
     size_t budget = out_features * row_b / 8;
     if (budget > (32u << 20)) budget = 32u << 20;
     size_t tile_rows = budget / row_b;
     if (tile_rows < 1) tile_rows = 1;
-    if (tile_rows > 64) tile_rows &= ~size_t(63);
+    if (tile_rows > 128) tile_rows &= ~size_t(127);
     if (tile_rows > out_features) tile_rows = out_features;
-    void* wsp = nullptr;
     DeviceGuard guard(ctx->device);
-    MCL_TRY(ws_reserve(ctx, tile_rows * row_b, &wsp));
-    float* gw = static_cast<float*>(wsp);
     const size_t state_row = in_features / 4 * 3;
+    const bool tc = tc_wanted(ctx, tile_rows, in_features, batch) && tile_rows >= 64;
+    int pa[6], pb[6], nt = 0, planes = 0, splits = 1;
+    const int ldn = up8(batch);
+    Carver cv;
+    const size_t o_gw = cv.reserve(tile_rows * row_b);
+    size_t o_a = 0, o_b = 0, o_k = 0;
+    if (tc) {
+        grad_term_list(ctx->grad_terms, pa, pb, &nt, &planes);
+        const size_t sk = mcl::tc_splitk_workspace_bytes((int)tile_rows, (int)in_features, (int)batch,
+                                                         ctx->sm_count, &splits);
+        o_a = cv.reserve((size_t)planes * out_features * ldn * 2);   // dY^T term planes (activation-sized)
+        o_b = cv.reserve((size_t)planes * in_features * ldn * 2);    // X^T term planes
+        o_k = cv.reserve(sk);
+    }
+    void* wsp = nullptr;
+    MCL_TRY(ws_reserve(ctx, cv.off, &wsp));
+    char* w = static_cast<char*>(wsp);
+    float* gw = reinterpret_cast<float*>(w + o_gw);
+    if (tc) {
+        MCL_LAUNCH(ctx, op, mcl::launch_split_planes(grad_out, (int)batch, (int)out_features, nullptr, nullptr, 0, 0,
+                                                     w + o_a, ldn, planes, ctx->stream));
+        MCL_LAUNCH(ctx, op, mcl::launch_split_planes(x, (int)batch, (int)in_features, nullptr, nullptr, 0, 0,
+                                                     w + o_b, ldn, planes, ctx->stream));
+    }
     for (size_t r0 = 0; r0 < out_features; r0 += tile_rows) {
         const size_t nr = (out_features - r0 < tile_rows) ? out_features - r0 : tile_rows;
-        MCL_LAUNCH(ctx, "counter update (grad_w tile)",
-                   mcl::launch_simt_grad_w(grad_out, x, gw, (int)batch, (int)in_features,
-                                           (int)out_features, (int)r0, (int)nr, ctx->stream));
+        if (tc) {
+            int sp = splits;
+            MCL_TRY(tc_product(ctx, w + o_a + r0 * (size_t)ldn * 2, planes, ldn, out_features * (size_t)ldn,
+                               w + o_b, planes, ldn, in_features * (size_t)ldn, gw, (int)in_features, (int)nr,
+                               (int)in_features, (int)batch, pa, pb, nt, nullptr,
+                               reinterpret_cast<float*>(w + o_k), sp));
+        } else {
+            MCL_LAUNCH(ctx, "counter update (grad_w tile)",
+                       mcl::launch_simt_grad_w(grad_out, x, gw, (int)batch, (int)in_features,
+                                               (int)out_features, (int)r0, (int)nr, ctx->stream));
+        }
         int rc = mcl_cuda_counter_update_dense(ctx, state + r0 * state_row, scale + r0, v + r0, gw,
                                                packed2_out ? packed2_out + r0 * (in_features / 16) : nullptr,
                                                C, in_features, nr, r0, lr, lr_scale, rms_beta, rms_eps, seed);
         if (rc != MCL_CUDA_OK) return rc;
     }
+    return MCL_CUDA_OK;
+}
+
+int mcl_cuda_counter_linear_step(mcl_cuda_ctx* ctx, const float* x, const float* grad_out,
+                                 uint8_t* state, float* scale, float* v, float* y, float* grad_x,
+                                 float* grad_w, uint32_t* packed2_out, size_t C, size_t in_features,
+                                 size_t out_features, size_t batch, size_t update_rows,
+                                 size_t row_offset, float lr, float lr_scale, float rms_beta,
+                                 float rms_eps, uint32_t seed) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "counter linear step";
+    MCL_TRY(check_counter_dims(ctx, op, C, in_features, out_features));
+    if (batch == 0 || batch > 0x7fffffffull) return fail(ctx, MCL_CUDA_EINVAL, "counter linear step requires 0 < batch < 2^31");
+    MCL_TRY(check_hypers(ctx, op, lr, lr_scale, rms_beta, rms_eps));
+    MCL_TRY(check_ptr(ctx, op, "x", x, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_out", grad_out, 4));
+    MCL_TRY(check_ptr(ctx, op, "state", state, 1));
+    MCL_TRY(check_ptr(ctx, op, "scale", scale, 4));
+    MCL_TRY(check_ptr(ctx, op, "v", v, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_w", grad_w, 16));
+    if (row_offset + update_rows > out_features)
+        return fail(ctx, MCL_CUDA_EINVAL, "counter linear step: update rows exceed out_features");
+    const size_t state_row = in_features / 4 * 3;
+    const size_t O = out_features, I = in_features, Nt = batch;
+    DeviceGuard guard(ctx->device);
+    const bool tc = tc_wanted(ctx, Nt, O, I) && tc_wanted(ctx, Nt, I, O) && tc_wanted(ctx, O, I, Nt);
+    if (!tc) {
+        if (y) MCL_TRY(mcl_cuda_counter_forward(ctx, x, state, scale, y, Nt, I, O, C));
+        if (grad_x) MCL_TRY(mcl_cuda_counter_backward_input(ctx, state, scale, grad_out, grad_x, Nt, I, O, C));
+        MCL_TRY(mcl_cuda_matmul_f32(ctx, grad_out, x, grad_w, O, Nt, I, 1, 0));
+    } else {
+        const int ta = ctx->act_terms;
+        int pa[6], pb[6], nt, gp;
+        grad_term_list(ctx->grad_terms, pa, pb, &nt, &gp);
+        const int ldi = up8(I), ldo = up8(O), ldn = up8(Nt);
+        int s_y = 1, s_x = 1, s_w = 1;
+        const size_t k_y = mcl::tc_splitk_workspace_bytes((int)Nt, (int)O, (int)I, ctx->sm_count, &s_y);
+        const size_t k_x = mcl::tc_splitk_workspace_bytes((int)Nt, (int)I, (int)O, ctx->sm_count, &s_x);
+        const size_t k_w = mcl::tc_splitk_workspace_bytes((int)O, (int)I, (int)Nt, ctx->sm_count, &s_w);
+        size_t k_max = k_y > k_x ? k_y : k_x;
+        if (k_w > k_max) k_max = k_w;
+        Carver cv;
+        const size_t o_xp = cv.reserve((size_t)ta * Nt * ldi * 2);    // X terms        [ta][N][I]
+        const size_t o_xt = cv.reserve((size_t)gp * I * ldn * 2);     // X^T terms      [gp][I][N]
+        const size_t o_gp = cv.reserve((size_t)ta * Nt * ldo * 2);    // (dY.s) terms   [ta][N][O]
+        const size_t o_gt = cv.reserve((size_t)gp * O * ldn * 2);     // dY^T terms     [gp][O][N]
+        const size_t o_t = cv.reserve(O * (size_t)ldi * 2);           // T   [O][I]
+        const size_t o_tt = cv.reserve(I * (size_t)ldo * 2);          // T^T [I][O]
+        const size_t o_k = cv.reserve(k_max);
+        void* wsp = nullptr;
+        MCL_TRY(ws_reserve(ctx, cv.off, &wsp));
+        char* w = static_cast<char*>(wsp);
+        float* kws = reinterpret_cast<float*>(w + o_k);
+        // X: terms in both orientations from one read (planes use the first ta / gp terms)
+        MCL_LAUNCH(ctx, op, mcl::launch_split_planes(x, (int)Nt, (int)I, nullptr, w + o_xp, ldi, ta, w + o_xt, ldn, gp, ctx->stream));
+        MCL_LAUNCH(ctx, op, mcl::launch_expand_ternary(state, (int)C, (int)O, (int)I, w + o_t, ldi, w + o_tt, ldo, ctx->stream));
+        MCL_LAUNCH(ctx, op, mcl::launch_split_planes(grad_out, (int)Nt, (int)O, scale, w + o_gp, ldo, ta, w + o_gt, ldn, gp, ctx->stream));
+        int qa[6], qb[6], qn;
+        act_term_list(ta, qa, qb, &qn);
+        if (y) MCL_TRY(tc_product(ctx, w + o_xp, ta, ldi, Nt * (size_t)ldi, w + o_t, 1, ldi, O * (size_t)ldi, y, (int)O,
+                                  (int)Nt, (int)O, (int)I, qa, qb, qn, scale, kws, s_y));
+        if (grad_x) MCL_TRY(tc_product(ctx, w + o_gp, ta, ldo, Nt * (size_t)ldo, w + o_tt, 1, ldo, I * (size_t)ldo, grad_x,
+                                       (int)I, (int)Nt, (int)I, (int)O, qa, qb, qn, nullptr, kws, s_x));
+        MCL_TRY(tc_product(ctx, w + o_gt, gp, ldn, O * (size_t)ldn, w + o_xt, gp, ldn, I * (size_t)ldn, grad_w, (int)I,
+                           (int)O, (int)I, (int)Nt, pa, pb, nt, nullptr, kws, s_w));
+    }
+    if (update_rows > 0)
+        return mcl_cuda_counter_update_dense(ctx, state + row_offset * state_row, scale + row_offset, v + row_offset,
+                                             grad_w + row_offset * I,
+                                             packed2_out ? packed2_out + row_offset * (I / 16) : nullptr, C, I,
+                                             update_rows, row_offset, lr, lr_scale, rms_beta, rms_eps, seed);
     return MCL_CUDA_OK;
 }
 
@@ -362,6 +590,27 @@ int mcl_cuda_matmul_f32(mcl_cuda_ctx* ctx, const float* a, const float* b, float
     MCL_TRY(check_ptr(ctx, op, "b", b, 4));
     MCL_TRY(check_ptr(ctx, op, "c", c, 4));
     DeviceGuard guard(ctx->device);
+    if (tc_wanted(ctx, M, N, K)) {
+        int pa[6], pb[6], nt, planes;
+        grad_term_list(ctx->grad_terms, pa, pb, &nt, &planes);
+        const int ldk = up8(K);
+        int splits = 1;
+        const size_t sk = mcl::tc_splitk_workspace_bytes((int)M, (int)N, (int)K, ctx->sm_count, &splits);
+        Carver cv;
+        const size_t o_a = cv.reserve((size_t)planes * M * ldk * 2), o_b = cv.reserve((size_t)planes * N * ldk * 2),
+                     o_k = cv.reserve(sk);
+        void* wsp = nullptr;
+        MCL_TRY(ws_reserve(ctx, cv.off, &wsp));
+        char* w = static_cast<char*>(wsp);
+        // A logical [M,K]: stored [M,K] -> planes as is; stored [K,M] (trans_a) -> transposed planes
+        if (!trans_a) MCL_LAUNCH(ctx, op, mcl::launch_split_planes(a, (int)M, (int)K, nullptr, w + o_a, ldk, planes, nullptr, 0, 0, ctx->stream));
+        else MCL_LAUNCH(ctx, op, mcl::launch_split_planes(a, (int)K, (int)M, nullptr, nullptr, 0, 0, w + o_a, ldk, planes, ctx->stream));
+        // B logical [K,N], needed as [N,K]: stored [N,K] (trans_b) -> as is; stored [K,N] -> transposed planes
+        if (trans_b) MCL_LAUNCH(ctx, op, mcl::launch_split_planes(b, (int)N, (int)K, nullptr, w + o_b, ldk, planes, nullptr, 0, 0, ctx->stream));
+        else MCL_LAUNCH(ctx, op, mcl::launch_split_planes(b, (int)K, (int)N, nullptr, nullptr, 0, 0, w + o_b, ldk, planes, ctx->stream));
+        return tc_product(ctx, w + o_a, planes, ldk, M * (size_t)ldk, w + o_b, planes, ldk, N * (size_t)ldk, c, (int)N,
+                          (int)M, (int)N, (int)K, pa, pb, nt, nullptr, reinterpret_cast<float*>(w + o_k), splits);
+    }
     MCL_LAUNCH(ctx, op, mcl::launch_simt_matmul_f32(a, b, c, (int)M, (int)K, (int)N, trans_a, trans_b, ctx->stream));
     return MCL_CUDA_OK;
 }

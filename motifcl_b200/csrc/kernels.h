@@ -34,6 +34,23 @@ cudaError_t launch_simt_grad_w(const float* grad_out, const float* x, float* gra
                                int in_features, int out_features, int row0, int rows,
                                cudaStream_t stream);
 
+// tc_gemm.cu -- tcgen05 / TMEM / TMA contractions on bf16 term planes (see the file header)
+int tc_pick_bn(int N);
+size_t tc_splitk_workspace_bytes(int M, int N, int K, int sm_count, int* splits_out);
+// C[M,N] (+= over terms) A_pa[M,K] . B_pb[N,K]^T ; planes are bf16 [P][rows][ld], plane stride in elements
+cudaError_t launch_tc_gemm(const void* a_planes, int a_nplanes, int lda, size_t a_plane_stride,
+                           const void* b_planes, int b_nplanes, int ldb, size_t b_plane_stride, float* c,
+                           int ldc, int M, int N, int K, const int* pa, const int* pb, int nterms,
+                           const float* col_scale, float* splitk_ws, int splits, int* err_word,
+                           size_t max_smem, cudaStream_t stream, int* launches);
+// fp32 [R,Cc] -> bf16 term planes [t][R][ld_n] of (src * col_scale) and/or transposed planes
+// [t][Cc][ld_t] of src
+cudaError_t launch_split_planes(const float* src, int R, int Cc, const float* col_scale, void* planes, int ld_n,
+                                int nterms, void* planes_t, int ld_t, int nterms_t, cudaStream_t stream);
+// packed 6-bit state -> bf16 ternary digits T [O][ld_i] and/or T^T [I][ld_o]
+cudaError_t launch_expand_ternary(const uint8_t* state, int C, int O, int I, void* T, int ld_i, void* Tt, int ld_o,
+                                  cudaStream_t stream);
+
 // gemv.cu
 cudaError_t launch_ternary_gemv(const float* x, const uint32_t* packed2, const float* scale, float* y,
                                 int M, int in_features, int out_features, int sm_count,

@@ -1,0 +1,486 @@
+// Tensor-core contractions of the counter-linear path for sm_100a: tcgen05.mma with fp32
+// accumulators in tensor memory (TMEM), operands staged in shared memory by TMA.
+//
+// One kernel serves the three products of a training step (MotifCL
+// src/nn/compact_counter.cpp:233-300 and kernels/matmul.cl:413-563 compute them with fp32
+// scalar FMAs):
+//     Y  [tokens,out] = X  . T^T          A = planes of X  [tokens,in],   B = T   [out,in]
+//     dX [tokens,in ] = (dY.s) . T        A = planes of dY.s [tokens,out], B = T^T [in,out]
+//     dW [out,in]     = dY^T . X          A = planes of dY^T [out,tokens], B = planes of X^T [in,tokens]
+// Every operand is K-major bf16 ("NT" form), produced by the pre-pass kernels below:
+//   * an fp32 tensor is split into bf16 terms a = a1 + a2 (+ a3), a1 = bf16(a),
+//     a2 = bf16(a - a1), a3 = bf16(a - a1 - a2); products of terms are accumulated in fp32
+//     in TMEM, so fp32 activations keep (nearly) fp32 accuracy on bf16 tensor cores;
+//   * ternary weights {-1,0,1,(2)} are exact in bf16 and are expanded from the packed 6-bit
+//     state, in both orientations.
+// The kernel computes  C[M,N] = sum over a list of (plane of A, plane of B) pairs of
+// A_p[M,K] . B_q[N,K]^T, optionally scaled per column, or writes split-K partial sums that a
+// fixed-order reduction kernel adds up (deterministic).
+//
+// Structure of a CTA (128 threads, one 128 x BN output tile, BN a multiple of 32 up to 256):
+//   warp 0 lane 0   TMA producer: cp.async.bulk.tensor (3-D tile {64 k, rows, plane}, 128-byte
+//                   swizzle) into a ring of `stages` shared-memory slots, mbarrier complete_tx
+//   warp 1 lane 0   MMA issuer: four tcgen05.mma (K = 16 each) per slot, tcgen05.commit to
+//                   release the slot, final commit to signal the accumulator
+//   warp 2          allocates / frees the TMEM columns
+//   all warps       epilogue: tcgen05.ld 32 lanes x 32 columns, scale, 128-bit stores
+// Every mbarrier wait is bounded: on time-out the kernel records an error word, skips the
+// rest of its work, frees its TMEM and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "counter_codec.cuh"
+#include "kernels.h"
+
+namespace mcl {
+namespace {
+
+constexpr int BM = 128;          // UMMA M
+constexpr int BK = 64;           // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kMaxStages = 8;
+constexpr int kATileBytes = BM * BK * 2;   // 16 KiB
+constexpr unsigned long long kWaitCycles = 1000000000ull;   // ~0.5 s at 2 GHz
+
+struct TcParams {
+    float* C;                 // output [M, ldc] (or split-K partials [splits][M][ldc])
+    const float* col_scale;   // optional, applied when splits == 1
+    int M, N, K, ldc;
+    int BN, stages;
+    int nterms;
+    int pa[6], pb[6];
+    int ktiles_per_split, splits;
+    int* err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait; returns false after ~0.5 s or as soon as another role has flagged an abort.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = clock64();
+    unsigned spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 0x3FFu) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitCycles) return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
+                                            int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accum) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_c), "l"(da), "l"(db), "r"(idesc), "r"(accum) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major bf16 tile stored as rows of 128 bytes with the
+// 128-byte swizzle (what the TMA box {64, rows} writes): start address / 16, leading byte
+// offset 16 B (unused for swizzled K-major), stride byte offset 1024 B (8 rows),
+// descriptor version 1, layout type 2 = SWIZZLE_128B.
+__device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor, kind::f16: D = f32 (bits 4-5 = 1), A = B = bf16 (bits 7-9, 10-12 = 1),
+// both K-major (bits 15, 16 = 0), N >> 3 at bit 17, M >> 4 at bit 24.
+__device__ __forceinline__ uint32_t idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(128) tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                      const __grid_constant__ CUtensorMap tmB,
+                                                      const TcParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 1];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int BN = p.BN, S = p.stages;
+    const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t stage_bytes = kATileBytes + (uint32_t)BN * BK * 2;
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
+    const uint32_t accum_bar = bar0 + 8u * (2 * kMaxStages);
+    uint32_t tmem_cols = 32;
+    while ((int)tmem_cols < BN) tmem_cols <<= 1;
+
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, split = blockIdx.z;
+    const int ktiles = (p.K + BK - 1) / BK;
+    const int kt0 = split * p.ktiles_per_split;
+    const int my_kt = min(p.ktiles_per_split, ktiles - kt0);
+    const int total = p.nterms * my_kt;
+
+    if (threadIdx.x == 0) {
+        abort_flag = (*reinterpret_cast<volatile int*>(p.err) != 0);   // an earlier CTA gave up: do not wait at all
+        for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_slot)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer ------------------------------------------------------------------
+        for (int it = 0; it < total; ++it) {
+            const int s = it % S;
+            const uint32_t ph = (uint32_t)(it / S) & 1u;
+            if (!mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 1); break; }
+            const int term = it / my_kt, kt = kt0 + it % my_kt;
+            const uint32_t a_dst = tiles + (uint32_t)s * stage_bytes;
+            mbar_expect_tx(full_bar(s), stage_bytes);
+            tma_load_3d(a_dst, &tmA, full_bar(s), kt * BK, m0, p.pa[term]);
+            tma_load_3d(a_dst + kATileBytes, &tmB, full_bar(s), kt * BK, n0, p.pb[term]);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer --------------------------------------------------------------------
+        const uint32_t idesc = idesc_bf16(BM, BN);
+        bool ok = true;
+        for (int it = 0; it < total; ++it) {
+            const int s = it % S;
+            const uint32_t ph = (uint32_t)(it / S) & 1u;
+            if (!mbar_wait(full_bar(s), ph, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 2); ok = false; break; }
+            tc_fence_after();
+            const uint32_t a_addr = tiles + (uint32_t)s * stage_bytes;
+            const uint64_t da = smem_desc_k_sw128(a_addr), db = smem_desc_k_sw128(a_addr + kATileBytes);
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk)   // 16 bf16 = 32 bytes = +2 in the address field
+                umma_bf16(tmem_base, da + 2u * kk, db + 2u * kk, idesc, (it | kk) != 0 ? 1u : 0u);
+            umma_commit(empty_bar(s));
+        }
+        if (ok) umma_commit(accum_bar);
+    }
+    __syncwarp();
+
+    // ---- epilogue: TMEM -> registers -> global ---------------------------------------------
+    bool have_acc = total > 0;
+    if (have_acc) {
+        if (!mbar_wait(accum_bar, 0, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 3); have_acc = false; }
+    }
+    have_acc = __all_sync(0xffffffffu, have_acc);
+    tc_fence_after();
+    const int row = m0 + warp * 32 + lane;
+    float* crow = p.C + ((size_t)split * p.M + row) * p.ldc;
+    const bool scale = (p.col_scale != nullptr) && p.splits == 1;
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= p.N) break;
+        uint32_t r[32];
+        if (have_acc) {
+            tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+            tmem_ld_wait();
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (row < p.M) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                const int col = n0 + c0 + j;
+                if (col >= p.N) break;
+                float4 o = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                       __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                if (scale) {
+                    const float4 sc = __ldg(reinterpret_cast<const float4*>(p.col_scale + col));
+                    o.x *= sc.x; o.y *= sc.y; o.z *= sc.z; o.w *= sc.w;
+                }
+                *reinterpret_cast<float4*>(crow + col) = o;    // N % 4 == 0, ldc % 4 == 0
+            }
+        }
+    }
+    if (abort_flag) {
+        // gave up: let copies that are still in flight land before the shared memory is released
+        const unsigned long long t0 = clock64();
+        while (clock64() - t0 < 2000000ull) {}
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+}
+
+// C[m,n] = scale[n] * sum_z partial[z][m][n], z ascending (deterministic split-K reduction).
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, float* __restrict__ C,
+                                     const float* __restrict__ col_scale, int M, int N, int ldc, int splits) {
+    const size_t n4 = (size_t)M * (N / 4);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const int m = (int)(i / (N / 4)), c = (int)(i % (N / 4)) * 4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int z = 0; z < splits; ++z) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(partial + ((size_t)z * M + m) * N + c));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        if (col_scale) {
+            const float4 s = __ldg(reinterpret_cast<const float4*>(col_scale + c));
+            acc.x *= s.x; acc.y *= s.y; acc.z *= s.z; acc.w *= s.w;
+        }
+        *reinterpret_cast<float4*>(C + (size_t)m * ldc + c) = acc;
+    }
+}
+
+// ---- pre-pass: fp32 -> bf16 term planes (optionally column-scaled, optionally transposed) ----
+// src [R, Cc] fp32.  Writes, for t < nterms:
+//   planes   [t][R ][ld_n]  = term t of (src * col_scale), t < nterms    (when planes   != null)
+//   planes_t [t][Cc][ld_t]  = term t of  src (unscaled), transposed, t < nterms_t (when planes_t != null)
+// 64 x 64 tiles through shared memory so that both outputs are written with coalesced rows.
+__device__ __forceinline__ void split3(float v, __nv_bfloat16 (&h)[3]) {
+    h[0] = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(h[0]);
+    h[1] = __float2bfloat16_rn(r1);
+    const float r2 = r1 - __bfloat162float(h[1]);
+    h[2] = __float2bfloat16_rn(r2);
+}
+
+__global__ void __launch_bounds__(256) split_planes_kernel(const float* __restrict__ src, int R, int Cc,
+                                                           const float* __restrict__ col_scale,
+                                                           __nv_bfloat16* __restrict__ planes, int ld_n,
+                                                           __nv_bfloat16* __restrict__ planes_t, int ld_t,
+                                                           int nterms, int nterms_t) {
+    __shared__ float tile[64][65];
+    const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;    // 64 x 4
+    for (int rr = ty; rr < 64; rr += 4) {
+        const int r = r0 + rr, c = c0 + tx;
+        float v = 0.0f;
+        if (r < R && c < Cc) v = __ldg(src + (size_t)r * Cc + c);
+        tile[rr][tx] = v;
+        if (planes != nullptr && r < R && c < Cc) {
+            const float sv = col_scale ? __fmul_rn(v, __ldg(col_scale + c)) : v;
+            __nv_bfloat16 h[3];
+            split3(sv, h);
+            for (int t = 0; t < nterms; ++t) planes[((size_t)t * R + r) * ld_n + c] = h[t];
+        }
+    }
+    if (planes_t == nullptr) return;
+    __syncthreads();
+    for (int cc = ty; cc < 64; cc += 4) {
+        const int c = c0 + cc, r = r0 + tx;
+        if (c < Cc && r < R) {
+            __nv_bfloat16 h[3];
+            split3(tile[tx][cc], h);
+            for (int t = 0; t < nterms_t; ++t) planes_t[((size_t)t * Cc + c) * ld_t + r] = h[t];
+        }
+    }
+}
+
+// ---- pre-pass: packed 6-bit state -> bf16 ternary digits, both orientations ------------------
+//   T  [O][ld_i] (when T  != null),  Tt [I][ld_o] (when Tt != null)
+__global__ void __launch_bounds__(256) expand_ternary_kernel(const uint8_t* __restrict__ state, int C,
+                                                             int O, int I, __nv_bfloat16* __restrict__ T,
+                                                             int ld_i, __nv_bfloat16* __restrict__ Tt, int ld_o) {
+    __shared__ DecodeLut lut;
+    __shared__ __nv_bfloat16 tile[64][66];
+    build_decode_lut(&lut, C, threadIdx.x, blockDim.x);
+    __syncthreads();
+    const int o0 = blockIdx.y * 64, i0 = blockIdx.x * 64;
+    const int gpr = I >> 2;
+    // 64 rows x 16 groups per tile; thread handles one group (4 weights) at a time
+    for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+        const int oo = e >> 4, g = (i0 >> 2) + (e & 15);
+        const int o = o0 + oo;
+        if (o < O && g < gpr) {
+            const uint8_t* s = state + ((size_t)o * gpr + g) * 3;
+            const uint32_t w = (uint32_t)__ldg(s) | ((uint32_t)__ldg(s + 1) << 8) | ((uint32_t)__ldg(s + 2) << 16);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const __nv_bfloat16 t = __float2bfloat16_rn(lut.e[(w >> (6 * k)) & 63u].x);
+                tile[oo][(e & 15) * 4 + k] = t;
+                if (T != nullptr) T[(size_t)o * ld_i + g * 4 + k] = t;
+            }
+        }
+    }
+    if (Tt == nullptr) return;
+    __syncthreads();
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+    for (int ii = ty; ii < 64; ii += 4) {
+        const int i = i0 + ii, o = o0 + tx;
+        if (i < I && o < O) Tt[(size_t)i * ld_o + o] = tile[tx][ii];
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 3-D map over bf16 planes [P][rows][ld]: dims {K, rows, P}, box {64, box_rows, 1}, 128-byte swizzle.
+// Reads beyond K or rows return zeros, so ragged edges need no padding in memory.
+bool make_map(CUtensorMap* map, const void* base, int K, int rows, int planes, int ld, size_t plane_stride,
+              int box_rows) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)planes};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)plane_stride * 2};
+    cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+int tc_pick_bn(int N) {
+    // widest tile that wastes least: N = 288 -> 96 x 3, 768 -> 256 x 3, 1024.. -> 256
+    int best = 256, best_waste = 1 << 30;
+    for (int bn = 256; bn >= 64; bn -= 32) {
+        const int tiles = (N + bn - 1) / bn;
+        const int waste = tiles * bn - N;
+        if (waste < best_waste) { best_waste = waste; best = bn; }
+    }
+    return best;
+}
+
+size_t tc_splitk_workspace_bytes(int M, int N, int K, int sm_count, int* splits_out) {
+    const int bn = tc_pick_bn(N);
+    const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+    const int ktiles = (K + BK - 1) / BK;
+    int splits = 1;
+    if (tiles < sm_count && ktiles >= 8) {
+        splits = (2 * sm_count + tiles - 1) / tiles;
+        if (splits > ktiles / 4) splits = ktiles / 4;
+        if (splits > 32) splits = 32;
+        if (splits < 1) splits = 1;
+    }
+    *splits_out = splits;
+    return splits > 1 ? (size_t)splits * M * N * sizeof(float) : 0;
+}
+
+cudaError_t launch_tc_gemm(const void* a_planes, int a_nplanes, int lda, size_t a_plane_stride,
+                           const void* b_planes, int b_nplanes, int ldb, size_t b_plane_stride, float* c,
+                           int ldc, int M, int N, int K, const int* pa, const int* pb,
+                           int nterms, const float* col_scale, float* splitk_ws, int splits, int* err_word,
+                           size_t max_smem, cudaStream_t stream, int* launches) {
+    if (nterms < 1 || nterms > 6 || (N & 3) || (ldc & 3) || (lda & 7) || (ldb & 7)) return cudaErrorInvalidValue;
+    const int bn = tc_pick_bn(N);
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, a_planes, K, M, a_nplanes, lda, a_plane_stride, BM)) return cudaErrorInvalidValue;
+    if (!make_map(&mb, b_planes, K, N, b_nplanes, ldb, b_plane_stride, bn)) return cudaErrorInvalidValue;
+    TcParams p;
+    p.col_scale = col_scale;
+    p.M = M; p.N = N; p.K = K;
+    p.BN = bn;
+    const size_t stage_bytes = (size_t)kATileBytes + (size_t)bn * BK * 2;
+    const int ktiles = (K + BK - 1) / BK;
+    int stages = (int)((max_smem - 2048) / stage_bytes);
+    if (stages > kMaxStages) stages = kMaxStages;
+    const int want = nterms * ((ktiles + splits - 1) / splits);   // slots one CTA ever fills
+    if (want <= 32) {
+        // short main loops: leave room for two resident CTAs, so that the epilogue of one
+        // overlaps the main loop of the other
+        const int half = (int)((((max_smem - 4096) / 2) - 1024) / stage_bytes);
+        if (half >= 3 && half < stages) stages = half;
+    }
+    if (stages > want) stages = want;
+    if (stages < 2) stages = 2;
+    if ((size_t)stages * stage_bytes + 1024 > max_smem) return cudaErrorInvalidConfiguration;
+    if (stages < 2) return cudaErrorInvalidConfiguration;
+    p.stages = stages;
+    p.nterms = nterms;
+    for (int t = 0; t < 6; ++t) { p.pa[t] = t < nterms ? pa[t] : 0; p.pb[t] = t < nterms ? pb[t] : 0; }
+    p.splits = splits;
+    p.ktiles_per_split = (ktiles + splits - 1) / splits;
+    // drop empty trailing splits
+    p.splits = splits = (ktiles + p.ktiles_per_split - 1) / p.ktiles_per_split;
+    p.err = err_word;
+    p.C = splits > 1 ? splitk_ws : c;
+    p.ldc = splits > 1 ? N : ldc;
+    const size_t smem = (size_t)stages * stage_bytes + 1024;
+    cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    dim3 grid((N + bn - 1) / bn, (M + BM - 1) / BM, splits);
+    tc_gemm_kernel<<<grid, 128, smem, stream>>>(ma, mb, p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    ++*launches;
+    if (splits > 1) {
+        const size_t n4 = (size_t)M * (N / 4);
+        int blocks = (int)((n4 + 255) / 256);
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(splitk_ws, c, col_scale, M, N, ldc, splits);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        ++*launches;
+    }
+    return cudaSuccess;
+}
+
+cudaError_t launch_split_planes(const float* src, int R, int Cc, const float* col_scale, void* planes, int ld_n,
+                                int nterms, void* planes_t, int ld_t, int nterms_t, cudaStream_t stream) {
+    dim3 grid((Cc + 63) / 64, (R + 63) / 64);
+    split_planes_kernel<<<grid, 256, 0, stream>>>(src, R, Cc, col_scale, static_cast<__nv_bfloat16*>(planes), ld_n,
+                                                  static_cast<__nv_bfloat16*>(planes_t), ld_t, nterms, nterms_t);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_expand_ternary(const uint8_t* state, int C, int O, int I, void* T, int ld_i, void* Tt, int ld_o,
+                                  cudaStream_t stream) {
+    dim3 grid((I + 63) / 64, (O + 63) / 64);
+    expand_ternary_kernel<<<grid, 256, 0, stream>>>(state, C, O, I, static_cast<__nv_bfloat16*>(T), ld_i,
+                                                    static_cast<__nv_bfloat16*>(Tt), ld_o);
+    return cudaGetLastError();
+}
+
+}  // namespace mcl

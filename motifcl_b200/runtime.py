@@ -115,6 +115,20 @@ class Context:
             _ptr(packed2_out), C_, in_features, out_features, batch, lr, lr_scale, rms_beta, rms_eps,
             seed & 0xFFFFFFFF))
 
+    GEMM_MODES = {"auto": 0, "exact": 1, "tensor": 2}
+
+    def set_gemm_mode(self, mode: str = "auto", act_terms: int = 3, grad_terms: int = 6):
+        """auto | exact (CUDA cores, bit-equal to the reference sums) | tensor (tcgen05)."""
+        self._check(self._lib.mcl_cuda_set_gemm_mode(self._ctx, self.GEMM_MODES[mode], act_terms, grad_terms))
+
+    def counter_linear_step(self, x, grad_out, state, scale, v, y, grad_x, grad_w, packed2_out, C_,
+                            in_features, out_features, batch, update_rows, row_offset, lr, lr_scale,
+                            rms_beta, rms_eps, seed):
+        self._check(self._lib.mcl_cuda_counter_linear_step(
+            self._ctx, _ptr(x), _ptr(grad_out), _ptr(state), _ptr(scale), _ptr(v), _ptr(y), _ptr(grad_x),
+            _ptr(grad_w), _ptr(packed2_out), C_, in_features, out_features, batch, update_rows, row_offset,
+            lr, lr_scale, rms_beta, rms_eps, seed & 0xFFFFFFFF))
+
     def matmul_f32(self, a, b, c, M, K, N, trans_a=False, trans_b=False):
         self._check(self._lib.mcl_cuda_matmul_f32(self._ctx, _ptr(a), _ptr(b), _ptr(c), M, K, N,
                                                   int(trans_a), int(trans_b)))

@@ -191,11 +191,15 @@ def test_fused_update_through_layer_api(name, ctx, orc, golden):
     N, I, O, C = c["N"], c["I"], c["O"], c["C"]
     st, sc, v = _t(c["state"]), _t(c["scale"]), _t(c["v"])
     p2 = torch.zeros(O, max(I // 16, 1), dtype=torch.int32, device=DEV) if I % 16 == 0 else None
-    ctx.counter_update_fused(st, sc, v, _t(c["dy"]), _t(c["x"]), p2, C, I, O, N, *_hy(c))
-    ctx.finish()
+    ctx.set_gemm_mode("exact")
+    try:
+        ctx.counter_update_fused(st, sc, v, _t(c["dy"]), _t(c["x"]), p2, C, I, O, N, *_hy(c))
+        ctx.finish()
+    finally:
+        ctx.set_gemm_mode("auto")
     got = codec.unpack_codes(st.cpu().numpy().reshape(O, -1), I)
     want = codec.unpack_codes(golden[f"{name}/dense_state"].reshape(O, -1), I)
-    # these shapes take the exact CUDA-core contraction (k ascending, unfused multiply-add),
+    # exact mode = the CUDA-core contraction (k ascending, unfused multiply-add),
     # so the whole transaction is bit-identical, as MotifCL tests/test_vulkan_counter_fused.cpp:120-133 asks
     assert np.array_equal(got, want)
     assert np.array_equal(_bits(sc.cpu().numpy()), _bits(golden[f"{name}/dense_scale"]))
@@ -276,3 +280,118 @@ def test_layer_mirror_teacher_recovery(ctx):
     t, _ = codec.decode(codes, 11)
     acc = float((t == teacher_t.numpy().astype(np.int64)).mean())
     assert mse <= 5e-3 and acc >= 0.9, (mse, acc)
+
+
+# ---- tensor-core (tcgen05) contractions -----------------------------------------------------
+
+TC_SHAPES = [(256, 288, 288), (512, 768, 288), (300, 288, 768), (1000, 2048, 512), (129, 96, 1032), (4096, 1024, 1024)]
+
+
+@pytest.mark.parametrize("terms", [(3, 6), (2, 3)])
+@pytest.mark.parametrize("N,I,O", TC_SHAPES)
+def test_tensor_core_contractions_vs_oracle(ctx, orc, N, I, O, terms):
+    """Y, dX and dW on tcgen05 against the fp32 reference sums (relative L2 <= 1e-5, the bound
+    the path is specified to) and against float64 accumulation."""
+    rng = np.random.default_rng(N + I + O)
+    st = synth.counters(7, (N + O) % 89, O, I).reshape(-1)
+    scale = rng.uniform(0.02, 0.2, O).astype(np.float32)
+    x = rng.standard_normal((N, I)).astype(np.float32)
+    dy = (0.02 * rng.standard_normal((N, O))).astype(np.float32)
+    ctx.set_gemm_mode("tensor", *terms)
+    try:
+        d_st, d_sc, d_x, d_dy = _t(st), _t(scale), _t(x), _t(dy)
+        y = torch.empty(N, O, dtype=torch.float32, device=DEV)
+        gx = torch.empty(N, I, dtype=torch.float32, device=DEV)
+        gw = torch.empty(O, I, dtype=torch.float32, device=DEV)
+        ctx.counter_forward(d_x, d_st, d_sc, y, N, I, O, 11)
+        ctx.counter_backward_input(d_st, d_sc, d_dy, gx, N, I, O, 11)
+        ctx.matmul_f32(d_dy, d_x, gw, O, N, I, trans_a=True)
+        ctx.finish()
+    finally:
+        ctx.set_gemm_mode("auto")
+    w = orc.decode_weight(st, scale, 11, I, O)
+    small = N * I * O <= 300 * 768 * 768
+    if small:
+        assert rel_l2(y.cpu().numpy(), orc.forward(x, st, scale, 11, O)) <= 1e-5
+        assert rel_l2(gx.cpu().numpy(), orc.backward_input(dy, st, scale, 11, I)) <= 1e-5
+        assert rel_l2(gw.cpu().numpy(), orc.grad_w(dy, x)) <= 1e-5
+    y64 = x.astype(np.float64) @ w.astype(np.float64).T
+    gx64 = dy.astype(np.float64) @ w.astype(np.float64)
+    gw64 = dy.astype(np.float64).T @ x.astype(np.float64)
+    assert rel_l2(y.cpu().numpy(), y64) <= 1e-5
+    assert rel_l2(gx.cpu().numpy(), gx64) <= 1e-5
+    assert rel_l2(gw.cpu().numpy(), gw64) <= 1e-5
+
+
+def test_tensor_core_matmul_all_transposes(ctx, orc):
+    M, K, N = 200, 520, 136
+    rng = np.random.default_rng(17)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = rng.standard_normal((K, N)).astype(np.float32)
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    ctx.set_gemm_mode("tensor")
+    try:
+        for ta, tb in [(False, False), (True, False), (False, True), (True, True)]:
+            a = A.T.copy() if ta else A
+            b = B.T.copy() if tb else B
+            c = torch.empty(M, N, dtype=torch.float32, device=DEV)
+            ctx.matmul_f32(_t(a), _t(b), c, M, K, N, ta, tb)
+            ctx.finish()
+            assert rel_l2(c.cpu().numpy(), ref) <= 1e-5, (ta, tb)
+    finally:
+        ctx.set_gemm_mode("auto")
+
+
+@pytest.mark.parametrize("mode", ["tensor", "exact"])
+def test_linear_step_matches_separate_calls_and_oracle(ctx, orc, mode):
+    """The one-call step: y and grad_x from the PRE-update state, then the dense update fed by
+    the step's own grad_w; the update must be bit-exact given that gradient."""
+    c = CASES["cfg1_rebase"]
+    N, I, O, C = c["N"], c["I"], c["O"], c["C"]
+    st, sc, v = _t(c["state"]), _t(c["scale"]), _t(c["v"])
+    y = torch.empty(N, O, dtype=torch.float32, device=DEV)
+    gx = torch.empty(N, I, dtype=torch.float32, device=DEV)
+    gw = torch.empty(O, I, dtype=torch.float32, device=DEV)
+    p2 = torch.zeros(O, I // 16, dtype=torch.int32, device=DEV)
+    ctx.set_gemm_mode(mode)
+    try:
+        ctx.counter_linear_step(_t(c["x"]), _t(c["dy"]), st, sc, v, y, gx, gw, p2, C, I, O, N, O, 0, *_hy(c))
+        ctx.finish()
+    finally:
+        ctx.set_gemm_mode("auto")
+    assert rel_l2(y.cpu().numpy(), orc.forward(c["x"], c["state"], c["scale"], C, O)) <= 1e-5
+    assert rel_l2(gx.cpu().numpy(), orc.backward_input(c["dy"], c["state"], c["scale"], C, I)) <= 1e-5
+    gw_h = gw.cpu().numpy()
+    assert rel_l2(gw_h, orc.grad_w(c["dy"], c["x"])) <= 1e-5
+    o = orc.update_dense(c["state"], c["scale"], c["v"], gw_h, C, I, O, 0, *_hy(c))
+    assert np.array_equal(st.cpu().numpy(), o[0])
+    assert np.array_equal(_bits(sc.cpu().numpy()), _bits(o[1]))
+    assert np.array_equal(_bits(v.cpu().numpy()), _bits(o[2]))
+    assert np.array_equal(p2.cpu().numpy().view(np.uint32), o[3])
+    if mode == "exact":   # and then the whole transaction equals the reference's
+        e = orc.update_fused(c["state"], c["scale"], c["v"], c["dy"], c["x"], C, *_hy(c))
+        assert np.array_equal(st.cpu().numpy(), e[0])
+
+
+def test_tensor_core_fused_update_flip_rate(ctx, orc):
+    """Memory-native update with grad_w formed on tensor cores: grad_w differs from the fp32
+    reference sum in its last bits, so a few stochastic roundings may fall the other way.  The
+    rate is measured here and must stay small; scale and v agree to 1e-6 as the reference's own
+    cross-backend rule asks (MotifCL tests/test_vulkan_backend.cpp:1208-1219)."""
+    c = CASES["cfg1_rebase"]
+    N, I, O, C = c["N"], c["I"], c["O"], c["C"]
+    st, sc, v = _t(c["state"]), _t(c["scale"]), _t(c["v"])
+    ctx.set_gemm_mode("tensor")
+    try:
+        ctx.counter_update_fused(st, sc, v, _t(c["dy"]), _t(c["x"]), None, C, I, O, N, *_hy(c))
+        ctx.finish()
+    finally:
+        ctx.set_gemm_mode("auto")
+    e = orc.update_fused(c["state"], c["scale"], c["v"], c["dy"], c["x"], C, *_hy(c))
+    got = codec.unpack_codes(st.cpu().numpy().reshape(O, -1), I)
+    want = codec.unpack_codes(e[0].reshape(O, -1), I)
+    flips = float((got != want).mean())
+    print(f"tensor-core fused update: code flip rate {flips:.2e}")
+    assert flips <= 1e-3
+    assert np.allclose(sc.cpu().numpy(), e[1], rtol=0, atol=1e-6)
+    assert np.allclose(v.cpu().numpy(), e[2], rtol=1e-5, atol=1e-9)

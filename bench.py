@@ -183,6 +183,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="do not record the step into one batch (for per-kernel profiling)")
     args = ap.parse_args()
     wl = workload(args.workload)
     if args.impl == "reference":
@@ -203,6 +204,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
+    torch.cuda.set_stream(torch.cuda.Stream(device=local))   # a recordable (non-default) stream
     ctx = Context.on_torch_stream(local)
     cfg, T, sigma = wl["cfg"], wl["tokens"], wl["sigma"]
 
@@ -246,7 +248,7 @@ def main():
 
     # ---- device-resident throughput ------------------------------------------------------
     with ClockSampler(local) as clk:
-        ms_step, launches = timed(lambda: stack.step(xs, dys), args.steps, max(args.warmup, 3))
+        ms_step, launches = timed(lambda: stack.step(xs, dys, recorded=not args.eager), args.steps, max(args.warmup, 3))
     clocks = clk.summary()
 
     # ---- roofline of the dominant kernel: timed alone on the launching stream ---------------
@@ -289,7 +291,7 @@ def main():
         for i in range(len(xs)):
             xs[i].copy_(xs_h[i], non_blocking=True)
             dys[i].copy_(dys_h[i], non_blocking=True)
-        stack.step(xs, dys)
+        stack.step(xs, dys, recorded=not args.eager)
         for l, o in zip(stack.linears, out_h):
             o[0].copy_(l.state, non_blocking=True)
             o[1].copy_(l.packed2, non_blocking=True)

@@ -58,6 +58,24 @@ int mcl_cuda_download(mcl_cuda_ctx* ctx, void* dst_host, const void* src, size_t
 /* Number of kernels this library has launched on the context so far. */
 uint64_t mcl_cuda_launch_count(mcl_cuda_ctx* ctx);
 
+/* ---- batch recording: replaces VulkanRuntime::batch_begin / batch_end, which wrap a training
+ * step into one command-buffer submit (include/motifcl/runtime/vulkan_backend.hpp:174-178;
+ * tools/train_ternary15m.cpp:371,381).  Between begin and end, calls on the context are
+ * recorded instead of run (CUDA stream capture); batch_end returns a replayable batch that
+ * mcl_cuda_batch_launch enqueues as ONE graph launch.  The recorded calls must already have run
+ * once unrecorded with the same shapes, so that the context's workspace has its final size;
+ * finish, download, upload, alloc and free are refused while recording. ---- */
+typedef struct mcl_cuda_batch mcl_cuda_batch;
+/* Optional device word whose value is added to the seed of every counter update enqueued
+ * afterwards (NULL = none).  A recorded batch bakes its scalar arguments in; bumping this word
+ * between replays gives each step its own seed, as CounterStateLinear::next_seed() does
+ * (include/motifcl/nn/compact_counter.hpp:34). */
+int mcl_cuda_set_seed_offset(mcl_cuda_ctx* ctx, const uint32_t* device_word);
+int mcl_cuda_batch_begin(mcl_cuda_ctx* ctx);
+int mcl_cuda_batch_end(mcl_cuda_ctx* ctx, mcl_cuda_batch** out_batch);
+int mcl_cuda_batch_launch(mcl_cuda_ctx* ctx, mcl_cuda_batch* batch);
+void mcl_cuda_batch_destroy(mcl_cuda_batch* batch);
+
 /* ---- decode: replaces run_vulkan_compact_counter_decode_weight
  * (include/motifcl/runtime/vulkan_backend.hpp:713-719; kernels/compact_counter.cl:39-55).
  * weight[out,in] = scale[row] * t. ---- */

@@ -75,6 +75,12 @@ def lib() -> C.CDLL:
         L.mcl_cuda_counter_update_dense.argtypes = [vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, f, f, f, f, u32]
         L.mcl_cuda_counter_update_fused.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, sz, sz, sz,
                                                     f, f, f, f, u32]
+        L.mcl_cuda_batch_begin.argtypes = [vp]
+        L.mcl_cuda_batch_end.argtypes = [vp, C.POINTER(vp)]
+        L.mcl_cuda_batch_launch.argtypes = [vp, vp]
+        L.mcl_cuda_batch_destroy.argtypes = [vp]
+        L.mcl_cuda_batch_destroy.restype = None
+        L.mcl_cuda_set_seed_offset.argtypes = [vp, vp]
         L.mcl_cuda_set_gemm_mode.argtypes = [vp, i, i, i]
         L.mcl_cuda_counter_linear_step.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, sz, sz,
                                                    f, f, f, f, u32]

@@ -26,6 +26,15 @@ struct mcl_cuda_ctx {
     int act_terms = 3;
     int grad_terms = 6;
     int* err_word = nullptr;     // device word the tensor-core kernels set when a bounded wait gives up
+    const uint32_t* seed_offset = nullptr;   // device word added to every update seed (mcl_cuda_set_seed_offset)
+    bool recording = false;      // between mcl_cuda_batch_begin and mcl_cuda_batch_end
+    uint64_t recorded_launches = 0;
+};
+
+struct mcl_cuda_batch {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t kernels = 0;        // kernel launches one replay stands for
 };
 
 namespace {
@@ -82,6 +91,8 @@ int check_hypers(mcl_cuda_ctx* ctx, const char* op, float lr, float lr_scale, fl
 
 int ws_reserve(mcl_cuda_ctx* ctx, size_t bytes, void** out) {
     if (bytes > ctx->ws_bytes) {
+        if (ctx->recording)
+            return fail(ctx, MCL_CUDA_EINVAL, "workspace would grow while recording a batch: run the same calls once unrecorded first");
         cudaError_t e = cudaStreamSynchronize(ctx->stream);
         if (e != cudaSuccess) return fail_cuda(ctx, "workspace sync", e);
         if (ctx->ws) cudaFree(ctx->ws);
@@ -100,6 +111,7 @@ int ws_reserve(mcl_cuda_ctx* ctx, size_t bytes, void** out) {
 
 #define MCL_TRY(expr) do { int _rc = (expr); if (_rc != MCL_CUDA_OK) return _rc; } while (0)
 #define MCL_NEED_CTX(ctx) do { if (!(ctx)) return fail(nullptr, MCL_CUDA_EINVAL, "context is NULL"); } while (0)
+#define MCL_NOT_RECORDING(ctx, what) do { if ((ctx)->recording) return fail(ctx, MCL_CUDA_EINVAL, what " is not allowed while recording a batch"); } while (0)
 #define MCL_LAUNCH(ctx, what, call) do { cudaError_t _e = (call); if (_e != cudaSuccess) return fail_cuda(ctx, what, _e); ++(ctx)->launches; } while (0)
 
 int create_impl(int device, cudaStream_t stream, bool own, mcl_cuda_ctx** out_ctx) {
@@ -234,12 +246,71 @@ const char* mcl_cuda_device_name(mcl_cuda_ctx* ctx) { return ctx ? ctx->name.c_s
 int mcl_cuda_sm_count(mcl_cuda_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
 uint64_t mcl_cuda_launch_count(mcl_cuda_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
+int mcl_cuda_batch_begin(mcl_cuda_ctx* ctx) {
+    MCL_NEED_CTX(ctx);
+    if (ctx->recording) return fail(ctx, MCL_CUDA_EINVAL, "batch_begin: already recording");
+    if (ctx->stream == nullptr || ctx->stream == cudaStreamLegacy || ctx->stream == cudaStreamPerThread)
+        return fail(ctx, MCL_CUDA_EUNSUPPORTED, "batch_begin: the context runs on a default stream, which cannot be recorded; "
+                                              "create the context with its own stream");
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) return fail_cuda(ctx, "batch_begin", e);
+    ctx->recording = true;
+    ctx->recorded_launches = ctx->launches;
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_batch_end(mcl_cuda_ctx* ctx, mcl_cuda_batch** out_batch) {
+    MCL_NEED_CTX(ctx);
+    if (!out_batch) return fail(ctx, MCL_CUDA_EINVAL, "batch_end: out_batch is NULL");
+    *out_batch = nullptr;
+    if (!ctx->recording) return fail(ctx, MCL_CUDA_EINVAL, "batch_end without batch_begin");
+    DeviceGuard guard(ctx->device);
+    ctx->recording = false;
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+    if (e != cudaSuccess || graph == nullptr) { cudaGetLastError(); return fail_cuda(ctx, "batch_end", e); }
+    mcl_cuda_batch* b = new (std::nothrow) mcl_cuda_batch();
+    if (!b) { cudaGraphDestroy(graph); return fail(ctx, MCL_CUDA_ENOMEM, "out of host memory"); }
+    b->graph = graph;
+    b->kernels = ctx->launches - ctx->recorded_launches;
+    ctx->launches = ctx->recorded_launches;     // recorded, not run
+    e = cudaGraphInstantiate(&b->exec, graph, 0);
+    if (e != cudaSuccess) { cudaGraphDestroy(graph); delete b; return fail_cuda(ctx, "batch_end (instantiate)", e); }
+    *out_batch = b;
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_batch_launch(mcl_cuda_ctx* ctx, mcl_cuda_batch* batch) {
+    MCL_NEED_CTX(ctx);
+    if (!batch || !batch->exec) return fail(ctx, MCL_CUDA_EINVAL, "batch_launch: batch is NULL");
+    MCL_NOT_RECORDING(ctx, "batch_launch");
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = cudaGraphLaunch(batch->exec, ctx->stream);
+    if (e != cudaSuccess) return fail_cuda(ctx, "batch_launch", e);
+    ctx->launches += batch->kernels;
+    return MCL_CUDA_OK;
+}
+void mcl_cuda_batch_destroy(mcl_cuda_batch* batch) {
+    if (!batch) return;
+    if (batch->exec) cudaGraphExecDestroy(batch->exec);
+    if (batch->graph) cudaGraphDestroy(batch->graph);
+    delete batch;
+}
+
 int mcl_cuda_finish(mcl_cuda_ctx* ctx) {
     MCL_NEED_CTX(ctx);
+    MCL_NOT_RECORDING(ctx, "finish");
     DeviceGuard guard(ctx->device);
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) return fail_cuda(ctx, "finish", e);
     return check_device_error(ctx);
+}
+
+int mcl_cuda_set_seed_offset(mcl_cuda_ctx* ctx, const uint32_t* device_word) {
+    MCL_NEED_CTX(ctx);
+    if (device_word && reinterpret_cast<uintptr_t>(device_word) % 4 != 0)
+        return fail(ctx, MCL_CUDA_EINVAL, "set_seed_offset: pointer must be 4-byte aligned");
+    ctx->seed_offset = device_word;
+    return MCL_CUDA_OK;
 }
 
 int mcl_cuda_set_gemm_mode(mcl_cuda_ctx* ctx, int mode, int act_terms, int grad_terms) {
@@ -253,6 +324,7 @@ int mcl_cuda_set_gemm_mode(mcl_cuda_ctx* ctx, int mode, int act_terms, int grad_
 }
 int mcl_cuda_alloc(mcl_cuda_ctx* ctx, size_t bytes, void** out_dptr) {
     MCL_NEED_CTX(ctx);
+    MCL_NOT_RECORDING(ctx, "alloc");
     if (!out_dptr) return fail(ctx, MCL_CUDA_EINVAL, "alloc: out_dptr is NULL");
     *out_dptr = nullptr;
     if (bytes == 0) return fail(ctx, MCL_CUDA_EINVAL, "alloc: zero-size buffer");
@@ -266,6 +338,7 @@ int mcl_cuda_alloc(mcl_cuda_ctx* ctx, size_t bytes, void** out_dptr) {
 }
 int mcl_cuda_free(mcl_cuda_ctx* ctx, void* dptr) {
     MCL_NEED_CTX(ctx);
+    MCL_NOT_RECORDING(ctx, "free");
     if (!dptr) return MCL_CUDA_OK;
     DeviceGuard guard(ctx->device);
     // Work that still uses the buffer may be queued: wait for the stream first, which keeps
@@ -278,6 +351,7 @@ int mcl_cuda_free(mcl_cuda_ctx* ctx, void* dptr) {
 }
 int mcl_cuda_upload(mcl_cuda_ctx* ctx, void* dst, const void* src_host, size_t bytes) {
     MCL_NEED_CTX(ctx);
+    MCL_NOT_RECORDING(ctx, "upload");
     if (bytes == 0) return MCL_CUDA_OK;
     if (!dst || !src_host) return fail(ctx, MCL_CUDA_EINVAL, "upload: NULL pointer");
     DeviceGuard guard(ctx->device);
@@ -291,6 +365,7 @@ int mcl_cuda_upload(mcl_cuda_ctx* ctx, void* dst, const void* src_host, size_t b
 }
 int mcl_cuda_download(mcl_cuda_ctx* ctx, void* dst_host, const void* src, size_t bytes) {
     MCL_NEED_CTX(ctx);
+    MCL_NOT_RECORDING(ctx, "download");
     if (bytes == 0) return MCL_CUDA_OK;
     if (!dst_host || !src) return fail(ctx, MCL_CUDA_EINVAL, "download: NULL pointer");
     DeviceGuard guard(ctx->device);
@@ -427,8 +502,8 @@ int mcl_cuda_counter_update_dense(mcl_cuda_ctx* ctx, uint8_t* state, float* scal
     DeviceGuard guard(ctx->device);
     cudaError_t e = mcl::launch_counter_update_dense(state, scale, v, grad_w, packed2_out, (int)C,
                                                      (int)in_features, (int)rows, (int)row_offset, lr,
-                                                     lr_scale, rms_beta, rms_eps, seed, ctx->sm_count,
-                                                     ctx->max_smem, ctx->stream);
+                                                     lr_scale, rms_beta, rms_eps, seed, ctx->seed_offset,
+                                                     ctx->sm_count, ctx->max_smem, ctx->stream);
     if (e == cudaErrorInvalidConfiguration)
         return fail(ctx, MCL_CUDA_EUNSUPPORTED, "counter update: in_features too large for one row in shared memory");
     if (e != cudaSuccess) return fail_cuda(ctx, op, e);

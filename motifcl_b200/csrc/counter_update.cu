@@ -41,6 +41,7 @@ struct UpdParams {
     int state_align;         // 16, 4 or 1: widest access every state / packed2 row start allows
     float lr, lr_scale, rms_beta, rms_eps;
     uint32_t seed;
+    const uint32_t* seed_offset;   // optional device word added to seed (a step counter for recorded batches)
 };
 
 struct RowConst {
@@ -78,6 +79,7 @@ counter_update_dense_kernel(const UpdParams p) {
     const int lv = 2 * p.C - 1;
     const float Cf = (float)p.C;
     const float neg_lr = -p.lr;
+    const uint32_t seed = p.seed + (p.seed_offset ? __ldg(p.seed_offset) : 0u);
     const bool aligned16 = p.state_align >= 16;   // state rows start and end on 16-byte boundaries
     const bool aligned4 = p.state_align >= 4;     // ... on 4-byte boundaries
 
@@ -206,7 +208,7 @@ counter_update_dense_kernel(const UpdParams p) {
                     const float2 tc = lut->e[(w >> (6 * k)) & 63u];
                     uint32_t fld;
                     const uint32_t code =
-                        counter_tick(gwv[k], tc.x, tc.y, elem_row + (uint32_t)(g * 4 + k), p.seed,
+                        counter_tick(gwv[k], tc.x, tc.y, elem_row + (uint32_t)(g * 4 + k), seed,
                                      neg_lr, rc.dn, rc.k_tick, rc.k_reb, Cf, p.C, lv, &fld);
                     nw |= (code & 0x3Fu) << (6 * k);
                     fields |= (fld & 3u) << (2 * k);
@@ -309,11 +311,26 @@ __global__ void pack2_kernel(const uint8_t* __restrict__ state, uint32_t* __rest
 
 }  // namespace
 
+// Opt a kernel in to the device's full dynamic shared memory, once per device and kernel slot.
+cudaError_t ensure_dynamic_smem(const void* kern, int slot, size_t max_smem) {
+    static bool done[64][4] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && slot < 4 && done[dev][slot]) return cudaSuccess;
+    cudaFuncAttributes fa;
+    cudaError_t e = cudaFuncGetAttributes(&fa, kern);
+    if (e != cudaSuccess) return e;
+    // the opt-in limit covers static + dynamic shared memory
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(max_smem - fa.sharedSizeBytes));
+    if (e == cudaSuccess && dev >= 0 && dev < 64 && slot < 4) done[dev][slot] = true;
+    return e;
+}
+
 cudaError_t launch_counter_update_dense(uint8_t* state, float* scale, float* v, const float* grad_w,
                                         uint32_t* packed2, int C, int in_features, int rows,
                                         int row_offset, float lr, float lr_scale, float rms_beta,
-                                        float rms_eps, uint32_t seed, int sm_count, size_t max_smem,
-                                        cudaStream_t stream) {
+                                        float rms_eps, uint32_t seed, const uint32_t* seed_offset, int sm_count,
+                                        size_t max_smem, cudaStream_t stream) {
     const bool with_q = (lr_scale != 0.0f);
     int R = kMaxRowsPerBatch;
     while (R > 1 && upd_smem_bytes(in_features, R, with_q) > max_smem / 2) --R;
@@ -326,7 +343,7 @@ cudaError_t launch_counter_update_dense(uint8_t* state, float* scale, float* v, 
     const uintptr_t sp = reinterpret_cast<uintptr_t>(state), pp = reinterpret_cast<uintptr_t>(packed2);
     p.state_align = (in_features % 64 == 0 && sp % 16 == 0 && pp % 16 == 0) ? 16
                     : (in_features % 16 == 0 && sp % 4 == 0) ? 4 : 1;
-    p.lr = lr; p.lr_scale = lr_scale; p.rms_beta = rms_beta; p.rms_eps = rms_eps; p.seed = seed;
+    p.lr = lr; p.lr_scale = lr_scale; p.rms_beta = rms_beta; p.rms_eps = rms_eps; p.seed = seed; p.seed_offset = seed_offset;
     const int nbatches = (rows + R - 1) / R;
     int ctas_per_sm = (int)(max_smem / smem);
     if (ctas_per_sm > 2048 / kUpdThreads) ctas_per_sm = 2048 / kUpdThreads;
@@ -334,7 +351,7 @@ cudaError_t launch_counter_update_dense(uint8_t* state, float* scale, float* v, 
     int grid = sm_count * ctas_per_sm;
     if (grid > nbatches) grid = nbatches;
     auto kern = with_q ? counter_update_dense_kernel<true> : counter_update_dense_kernel<false>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), with_q ? 0 : 1, max_smem);
     if (e != cudaSuccess) return e;
     kern<<<grid, kUpdThreads, smem, stream>>>(p);
     return cudaGetLastError();

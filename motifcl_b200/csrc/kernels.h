@@ -9,11 +9,12 @@
 namespace mcl {
 
 // counter_update.cu
+cudaError_t ensure_dynamic_smem(const void* kern, int slot, size_t max_smem);
 cudaError_t launch_counter_update_dense(uint8_t* state, float* scale, float* v, const float* grad_w,
                                         uint32_t* packed2, int C, int in_features, int rows,
                                         int row_offset, float lr, float lr_scale, float rms_beta,
-                                        float rms_eps, uint32_t seed, int sm_count, size_t max_smem,
-                                        cudaStream_t stream);
+                                        float rms_eps, uint32_t seed, const uint32_t* seed_offset, int sm_count,
+                                        size_t max_smem, cudaStream_t stream);
 cudaError_t launch_decode_weight(const uint8_t* state, const float* scale, float* w, int C,
                                  int in_features, int out_features, int sm_count, cudaStream_t stream);
 cudaError_t launch_pack2(const uint8_t* state, uint32_t* packed2, int C, int in_features,

@@ -448,7 +448,7 @@ cudaError_t launch_tc_gemm(const void* a_planes, int a_nplanes, int lda, size_t 
     p.C = splits > 1 ? splitk_ws : c;
     p.ldc = splits > 1 ? N : ldc;
     const size_t smem = (size_t)stages * stage_bytes + 1024;
-    cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(tc_gemm_kernel), 2, max_smem);
     if (e != cudaSuccess) return e;
     dim3 grid((N + bn - 1) / bn, (M + BM - 1) / BM, splits);
     tc_gemm_kernel<<<grid, 128, smem, stream>>>(ma, mb, p);

@@ -84,6 +84,18 @@ class Context:
     def download(self, dst_host_ptr: int, src, nbytes: int):
         self._check(self._lib.mcl_cuda_download(self._ctx, dst_host_ptr, _ptr(src), nbytes))
 
+    # -- batch recording (one graph launch per recorded step) -------------------------------
+    def batch_begin(self):
+        self._check(self._lib.mcl_cuda_batch_begin(self._ctx))
+
+    def batch_end(self) -> "Batch":
+        b = C.c_void_p()
+        self._check(self._lib.mcl_cuda_batch_end(self._ctx, C.byref(b)))
+        return Batch(self, b)
+
+    def set_seed_offset(self, device_word):
+        self._check(self._lib.mcl_cuda_set_seed_offset(self._ctx, _ptr(device_word)))
+
     # -- counter path --------------------------------------------------------------------
     def counter_decode_weight(self, state, scale, weight, in_features, out_features, C_):
         self._check(self._lib.mcl_cuda_counter_decode_weight(
@@ -136,3 +148,24 @@ class Context:
     def ternary_gemv(self, x, packed2, scale, y, M, in_features, out_features):
         self._check(self._lib.mcl_cuda_ternary_gemv(self._ctx, _ptr(x), _ptr(packed2), _ptr(scale),
                                                     _ptr(y), M, in_features, out_features))
+
+
+class Batch:
+    """A recorded sequence of calls (Context.batch_begin ... batch_end), replayed with launch()."""
+
+    def __init__(self, ctx: Context, handle):
+        self._ctx, self._h = ctx, handle
+
+    def launch(self):
+        self._ctx._check(self._ctx._lib.mcl_cuda_batch_launch(self._ctx._ctx, self._h))
+
+    def close(self):
+        if self._h:
+            self._ctx._lib.mcl_cuda_batch_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

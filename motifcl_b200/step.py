@@ -75,22 +75,57 @@ class CounterStack:
             if self.world > 1:
                 l.gw_shard = torch.empty(max(l.rows, 1), l.shape.in_features, dtype=torch.float32, device=dev)
         self.step_index = 0
+        self._batch = None
+        self._batch_key = None
+        self._step_word = torch.zeros(1, dtype=torch.int32, device=dev)
 
-    def step(self, xs, dys, base_seed: int = 12345):
-        """xs[i]: [tokens, in_i], dys[i]: [tokens, out_i] device tensors.  One full step."""
+    def step(self, xs, dys, base_seed: int = 12345, recorded: bool = False):
+        """xs[i]: [tokens, in_i], dys[i]: [tokens, out_i] device tensors.  One full step.
+
+        recorded=True (single GPU): the first call runs eagerly (sizing the workspace), the
+        second records the same calls into one batch, later ones replay it -- one graph launch
+        per step, as the reference submits one command buffer per step.  The per-step seed then
+        comes from a device word that is bumped after every replay."""
+        if recorded and self.world == 1:
+            return self._step_recorded(xs, dys, base_seed)
+        self._step_eager(xs, dys, (base_seed + self.step_index) & 0xFFFFFFFF)
+        self.step_index += 1
+
+    def _step_recorded(self, xs, dys, base_seed):
+        key = (tuple(t.data_ptr() for t in xs), tuple(t.data_ptr() for t in dys), base_seed)
+        if self._batch is None or self._batch_key != key:
+            if self._batch is not None:
+                self._batch.close()
+                self._batch = None
+            self._step_word.fill_(self.step_index)
+            self.ctx.set_seed_offset(self._step_word)
+            try:
+                self._step_eager(xs, dys, base_seed)          # this call's step; also sizes the workspace
+                self._step_word.add_(1)
+                self.step_index += 1
+                self.ctx.finish()
+                self.ctx.batch_begin()
+                try:
+                    self._step_eager(xs, dys, base_seed)      # recorded, not run
+                finally:
+                    self._batch = self.ctx.batch_end()
+            finally:
+                self.ctx.set_seed_offset(None)
+            self._batch_key = key
+            return
+        self._batch.launch()
+        self._step_word.add_(1)
+        self.step_index += 1
+
+    def _step_eager(self, xs, dys, seed):
         ctx, h = self.ctx, self.h
-        seed = (base_seed + self.step_index) & 0xFFFFFFFF
         for l, x, dy in zip(self.linears, xs, dys):
             O, I = l.shape.out_features, l.shape.in_features
-            ctx.counter_forward(x, l.state, l.scale, l.y, self.tokens, I, O, h.C)
-            ctx.counter_backward_input(l.state, l.scale, dy, l.dx, self.tokens, I, O, h.C)
-            ctx.matmul_f32(dy, x, l.grad_w, O, self.tokens, I, trans_a=True)
-            if self.world == 1:
-                ctx.counter_update_dense(l.state, l.scale, l.v, l.grad_w, l.packed2, h.C, I, O, 0,
-                                         h.lr, h.lr_scale, h.rms_beta, h.rms_eps, seed)
-            else:
+            upd = O if self.world == 1 else 0     # data parallel: reduce grad_w first, then update the shard
+            ctx.counter_linear_step(x, dy, l.state, l.scale, l.v, l.y, l.dx, l.grad_w, l.packed2, h.C, I, O,
+                                    self.tokens, upd, 0, h.lr, h.lr_scale, h.rms_beta, h.rms_eps, seed)
+            if self.world > 1:
                 self._dp_update(l, seed)
-        self.step_index += 1
 
     def _dp_update(self, l: CounterLinearState, seed: int):
         import torch.distributed as dist

@@ -33,6 +33,10 @@ def ctx():
     from motifcl_b200 import Context
     assert torch.cuda.is_available(), "GPU test started without a CUDA device"
     torch.cuda.set_device(0)
+    # a side stream made current for the whole session: torch's copies and the library's
+    # kernels then share one in-order stream that can also be recorded into a batch
+    side = torch.cuda.Stream(device=0)
+    torch.cuda.set_stream(side)
     c = Context.on_torch_stream(0)
     yield c
     c.finish()

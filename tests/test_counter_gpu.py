@@ -395,3 +395,32 @@ def test_tensor_core_fused_update_flip_rate(ctx, orc):
     assert flips <= 1e-3
     assert np.allclose(sc.cpu().numpy(), e[1], rtol=0, atol=1e-6)
     assert np.allclose(v.cpu().numpy(), e[2], rtol=1e-5, atol=1e-9)
+
+
+def test_recorded_batch_replays_the_step_with_a_per_step_seed(ctx, orc):
+    """Two steps replayed from one recorded batch equal two eager steps: the seed of step k is
+    base + k through the device seed word (as CounterStateLinear::next_seed() advances,
+    MotifCL include/motifcl/nn/compact_counter.hpp:34)."""
+    from motifcl_b200.step import CounterLinearState, CounterStack, Hyper
+    c = CASES["cfg1"]
+    N, I, O = c["N"], c["I"], c["O"]
+    shape = synth.LinearShape("l", O, I)
+    x, dy = _t(c["x"]), _t(c["dy"])
+    results = []
+    for recorded in (False, True):
+        lin = CounterLinearState(shape, c["state"], c["scale"], c["v"], torch.device(DEV))
+        stack = CounterStack(ctx, [lin], Hyper(lr=0.05), N)
+        for _ in range(4):
+            stack.step([x], [dy], base_seed=100, recorded=recorded)
+        ctx.finish()
+        results.append((lin.state.cpu().numpy(), lin.scale.cpu().numpy(), lin.v.cpu().numpy(),
+                        lin.packed2.cpu().numpy()))
+    for a, b in zip(*results):
+        assert np.array_equal(a, b)
+    # and the first step's update is bit-exact against the checker given the step's own gradient
+    lin = CounterLinearState(shape, c["state"], c["scale"], c["v"], torch.device(DEV))
+    stack = CounterStack(ctx, [lin], Hyper(lr=0.05), N)
+    stack.step([x], [dy], base_seed=100)
+    ctx.finish()
+    o = orc.update_dense(c["state"], c["scale"], c["v"], lin.grad_w.cpu().numpy(), 11, I, O, 0, 0.05, 0.0, 0.9, 1e-3, 100)
+    assert np.array_equal(lin.state.cpu().numpy(), o[0])

@@ -183,6 +183,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--lanes", type=int, default=8, help="contexts (streams) that independent linears are spread over")
     ap.add_argument("--eager", action="store_true", help="do not record the step into one batch (for per-kernel profiling)")
     args = ap.parse_args()
     wl = workload(args.workload)
@@ -217,7 +218,7 @@ def main():
         # every rank draws its own tokens (data parallel): offset the linear index by rank
         xs_h.append(torch.from_numpy(synth.activations(cfg, idx + 100 * rank, T, I)).pin_memory())
         dys_h.append(torch.from_numpy(synth.upstream_grad(cfg, idx + 100 * rank, T, O, sigma)).pin_memory())
-    stack = CounterStack(ctx, lin_states, Hyper(), T, group)
+    stack = CounterStack(ctx, lin_states, Hyper(), T, group, lanes=args.lanes)
     xs = [t.to(dev, non_blocking=True) for t in xs_h]
     dys = [t.to(dev, non_blocking=True) for t in dys_h]
     torch.cuda.synchronize()

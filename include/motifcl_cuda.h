@@ -74,6 +74,14 @@ int mcl_cuda_set_seed_offset(mcl_cuda_ctx* ctx, const uint32_t* device_word);
 int mcl_cuda_batch_begin(mcl_cuda_ctx* ctx);
 int mcl_cuda_batch_end(mcl_cuda_ctx* ctx, mcl_cuda_batch** out_batch);
 int mcl_cuda_batch_launch(mcl_cuda_ctx* ctx, mcl_cuda_batch* batch);
+/* Lanes (no reference counterpart: the reference has one queue).  Independent linears can run
+ * side by side on further contexts of the same device, each with its own stream and workspace.
+ * fork makes everything enqueued on `lane` from now on wait for what `ctx` has enqueued so
+ * far; join makes `ctx` wait for what `lane` has enqueued.  Inside a recording on `ctx`, fork
+ * pulls the lane's stream into the recording (its calls become parallel branches of the
+ * batch) and join must follow before batch_end. */
+int mcl_cuda_lane_fork(mcl_cuda_ctx* ctx, mcl_cuda_ctx* lane);
+int mcl_cuda_lane_join(mcl_cuda_ctx* ctx, mcl_cuda_ctx* lane);
 void mcl_cuda_batch_destroy(mcl_cuda_batch* batch);
 
 /* ---- decode: replaces run_vulkan_compact_counter_decode_weight

@@ -80,6 +80,8 @@ def lib() -> C.CDLL:
         L.mcl_cuda_batch_launch.argtypes = [vp, vp]
         L.mcl_cuda_batch_destroy.argtypes = [vp]
         L.mcl_cuda_batch_destroy.restype = None
+        L.mcl_cuda_lane_fork.argtypes = [vp, vp]
+        L.mcl_cuda_lane_join.argtypes = [vp, vp]
         L.mcl_cuda_set_seed_offset.argtypes = [vp, vp]
         L.mcl_cuda_set_gemm_mode.argtypes = [vp, i, i, i]
         L.mcl_cuda_counter_linear_step.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, sz, sz,

@@ -27,6 +27,8 @@ struct mcl_cuda_ctx {
     int grad_terms = 6;
     int* err_word = nullptr;     // device word the tensor-core kernels set when a bounded wait gives up
     const uint32_t* seed_offset = nullptr;   // device word added to every update seed (mcl_cuda_set_seed_offset)
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    uint64_t lane_mark = 0;      // launches at the last lane_fork (when this context is a lane)
     bool recording = false;      // between mcl_cuda_batch_begin and mcl_cuda_batch_end
     uint64_t recorded_launches = 0;
 };
@@ -147,6 +149,8 @@ int create_impl(int device, cudaStream_t stream, bool own, mcl_cuda_ctx** out_ct
     }
     e = cudaMalloc(reinterpret_cast<void**>(&ctx->err_word), sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->err_word, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_join, cudaEventDisableTiming);
     if (e != cudaSuccess) {
         if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
         delete ctx;
@@ -238,6 +242,8 @@ void mcl_cuda_destroy(mcl_cuda_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->err_word) cudaFree(ctx->err_word);
+    if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
+    if (ctx->ev_join) cudaEventDestroy(ctx->ev_join);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -294,6 +300,31 @@ void mcl_cuda_batch_destroy(mcl_cuda_batch* batch) {
     if (batch->exec) cudaGraphExecDestroy(batch->exec);
     if (batch->graph) cudaGraphDestroy(batch->graph);
     delete batch;
+}
+
+int mcl_cuda_lane_fork(mcl_cuda_ctx* ctx, mcl_cuda_ctx* lane) {
+    MCL_NEED_CTX(ctx);
+    if (!lane || lane == ctx) return fail(ctx, MCL_CUDA_EINVAL, "lane_fork: lane must be another context");
+    if (lane->device != ctx->device) return fail(ctx, MCL_CUDA_EINVAL, "lane_fork: lane is on another device");
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = cudaEventRecord(lane->ev_fork, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(lane->stream, lane->ev_fork, 0);
+    if (e != cudaSuccess) return fail_cuda(ctx, "lane_fork", e);
+    lane->recording = ctx->recording;
+    lane->lane_mark = lane->launches;
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_lane_join(mcl_cuda_ctx* ctx, mcl_cuda_ctx* lane) {
+    MCL_NEED_CTX(ctx);
+    if (!lane || lane == ctx) return fail(ctx, MCL_CUDA_EINVAL, "lane_join: lane must be another context");
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = cudaEventRecord(lane->ev_join, lane->stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->stream, lane->ev_join, 0);
+    if (e != cudaSuccess) return fail_cuda(ctx, "lane_join", e);
+    lane->recording = false;
+    ctx->launches += lane->launches - lane->lane_mark;    // account the lane's kernels to the owner
+    lane->launches = lane->lane_mark;
+    return MCL_CUDA_OK;
 }
 
 int mcl_cuda_finish(mcl_cuda_ctx* ctx) {

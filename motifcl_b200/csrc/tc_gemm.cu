@@ -313,6 +313,65 @@ __global__ void __launch_bounds__(256) split_planes_kernel(const float* __restri
     }
 }
 
+// Vectorised form of the same pre-pass for Cc % 4 == 0, R % 4 == 0 and 16-byte aligned src:
+// 128-bit loads, 64-bit stores of four bf16 in both orientations.
+__device__ __forceinline__ uint2 pack4(const __nv_bfloat16 a, const __nv_bfloat16 b, const __nv_bfloat16 c,
+                                       const __nv_bfloat16 d) {
+    uint2 o;
+    o.x = (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+    o.y = (uint32_t)__bfloat16_as_ushort(c) | ((uint32_t)__bfloat16_as_ushort(d) << 16);
+    return o;
+}
+
+__global__ void __launch_bounds__(256) split_planes_vec_kernel(const float* __restrict__ src, int R, int Cc,
+                                                               const float* __restrict__ col_scale,
+                                                               __nv_bfloat16* __restrict__ planes, int ld_n,
+                                                               __nv_bfloat16* __restrict__ planes_t, int ld_t,
+                                                               int nterms, int nterms_t) {
+    __shared__ float tile[64][65];
+    const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;    // 16 column quads x 16 rows
+    const int c = c0 + tx * 4;
+    float4 sc4 = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (col_scale != nullptr && c < Cc) sc4 = __ldg(reinterpret_cast<const float4*>(col_scale + c));
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+        const int rr = pass * 16 + ty, r = r0 + rr;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < R && c < Cc) v = __ldg(reinterpret_cast<const float4*>(src + (size_t)r * Cc + c));
+        tile[rr][tx * 4 + 0] = v.x; tile[rr][tx * 4 + 1] = v.y; tile[rr][tx * 4 + 2] = v.z; tile[rr][tx * 4 + 3] = v.w;
+        if (planes != nullptr && r < R && c < Cc) {
+            if (col_scale != nullptr) {
+                v.x = __fmul_rn(v.x, sc4.x); v.y = __fmul_rn(v.y, sc4.y);
+                v.z = __fmul_rn(v.z, sc4.z); v.w = __fmul_rn(v.w, sc4.w);
+            }
+            __nv_bfloat16 h0[3], h1[3], h2[3], h3[3];
+            split3(v.x, h0); split3(v.y, h1); split3(v.z, h2); split3(v.w, h3);
+#pragma unroll
+            for (int t = 0; t < 3; ++t)
+                if (t < nterms)
+                    *reinterpret_cast<uint2*>(planes + ((size_t)t * R + r) * ld_n + c) = pack4(h0[t], h1[t], h2[t], h3[t]);
+        }
+    }
+    if (planes_t == nullptr) return;
+    __syncthreads();
+    // transposed: thread owns 4 consecutive source rows (= 4 consecutive output columns) of one source column
+    const int rq = threadIdx.x & 15, cl = threadIdx.x >> 4;
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+        const int cc = pass * 16 + cl, cg = c0 + cc, r = r0 + rq * 4;
+        if (cg < Cc && r < R) {
+            __nv_bfloat16 h0[3], h1[3], h2[3], h3[3];
+            split3(tile[rq * 4 + 0][cc], h0); split3(tile[rq * 4 + 1][cc], h1);
+            split3(tile[rq * 4 + 2][cc], h2); split3(tile[rq * 4 + 3][cc], h3);
+#pragma unroll
+            for (int t = 0; t < 3; ++t)
+                if (t < nterms_t)
+                    *reinterpret_cast<uint2*>(planes_t + ((size_t)t * Cc + cg) * ld_t + r) = pack4(h0[t], h1[t], h2[t], h3[t]);
+        }
+    }
+}
+
 // ---- pre-pass: packed 6-bit state -> bf16 ternary digits, both orientations ------------------
 //   T  [O][ld_i] (when T  != null),  Tt [I][ld_o] (when Tt != null)
 __global__ void __launch_bounds__(256) expand_ternary_kernel(const uint8_t* __restrict__ state, int C,
@@ -470,6 +529,13 @@ cudaError_t launch_tc_gemm(const void* a_planes, int a_nplanes, int lda, size_t 
 cudaError_t launch_split_planes(const float* src, int R, int Cc, const float* col_scale, void* planes, int ld_n,
                                 int nterms, void* planes_t, int ld_t, int nterms_t, cudaStream_t stream) {
     dim3 grid((Cc + 63) / 64, (R + 63) / 64);
+    if ((Cc & 3) == 0 && (R & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+        (col_scale == nullptr || (reinterpret_cast<uintptr_t>(col_scale) & 15) == 0)) {
+        split_planes_vec_kernel<<<grid, 256, 0, stream>>>(src, R, Cc, col_scale, static_cast<__nv_bfloat16*>(planes),
+                                                          ld_n, static_cast<__nv_bfloat16*>(planes_t), ld_t, nterms,
+                                                          nterms_t);
+        return cudaGetLastError();
+    }
     split_planes_kernel<<<grid, 256, 0, stream>>>(src, R, Cc, col_scale, static_cast<__nv_bfloat16*>(planes), ld_n,
                                                   static_cast<__nv_bfloat16*>(planes_t), ld_t, nterms, nterms_t);
     return cudaGetLastError();

@@ -93,6 +93,12 @@ class Context:
         self._check(self._lib.mcl_cuda_batch_end(self._ctx, C.byref(b)))
         return Batch(self, b)
 
+    def lane_fork(self, lane: "Context"):
+        self._check(self._lib.mcl_cuda_lane_fork(self._ctx, lane._ctx))
+
+    def lane_join(self, lane: "Context"):
+        self._check(self._lib.mcl_cuda_lane_join(self._ctx, lane._ctx))
+
     def set_seed_offset(self, device_word):
         self._check(self._lib.mcl_cuda_set_seed_offset(self._ctx, _ptr(device_word)))
 

@@ -63,8 +63,12 @@ class CounterLinearState:
 
 class CounterStack:
     def __init__(self, ctx: Context, linears: list[CounterLinearState], hyper: Hyper, tokens: int,
-                 group=None):
+                 group=None, lanes: int = 1):
+        """lanes > 1: the linears of a step are independent, so they are spread round-robin over
+        `lanes` contexts (own stream, own workspace) that run side by side between a fork and a
+        join on `ctx`."""
         self.ctx, self.linears, self.h, self.tokens = ctx, linears, hyper, tokens
+        self.lanes = [ctx] + [Context(ctx.device) for _ in range(max(0, lanes - 1))]
         self.group = group
         self.world = 1 if group is None else torch.distributed.get_world_size(group)
         self.rank = 0 if group is None else torch.distributed.get_rank(group)
@@ -98,7 +102,8 @@ class CounterStack:
                 self._batch.close()
                 self._batch = None
             self._step_word.fill_(self.step_index)
-            self.ctx.set_seed_offset(self._step_word)
+            for lane in self.lanes:
+                lane.set_seed_offset(self._step_word)
             try:
                 self._step_eager(xs, dys, base_seed)          # this call's step; also sizes the workspace
                 self._step_word.add_(1)
@@ -110,7 +115,8 @@ class CounterStack:
                 finally:
                     self._batch = self.ctx.batch_end()
             finally:
-                self.ctx.set_seed_offset(None)
+                for lane in self.lanes:
+                    lane.set_seed_offset(None)
             self._batch_key = key
             return
         self._batch.launch()
@@ -119,13 +125,19 @@ class CounterStack:
 
     def _step_eager(self, xs, dys, seed):
         ctx, h = self.ctx, self.h
-        for l, x, dy in zip(self.linears, xs, dys):
+        nl = len(self.lanes) if self.world == 1 else 1      # collectives stay on the main stream
+        for lane in self.lanes[1:nl]:
+            ctx.lane_fork(lane)
+        for i, (l, x, dy) in enumerate(zip(self.linears, xs, dys)):
             O, I = l.shape.out_features, l.shape.in_features
             upd = O if self.world == 1 else 0     # data parallel: reduce grad_w first, then update the shard
-            ctx.counter_linear_step(x, dy, l.state, l.scale, l.v, l.y, l.dx, l.grad_w, l.packed2, h.C, I, O,
-                                    self.tokens, upd, 0, h.lr, h.lr_scale, h.rms_beta, h.rms_eps, seed)
+            self.lanes[i % nl].counter_linear_step(x, dy, l.state, l.scale, l.v, l.y, l.dx, l.grad_w, l.packed2,
+                                                   h.C, I, O, self.tokens, upd, 0, h.lr, h.lr_scale, h.rms_beta,
+                                                   h.rms_eps, seed)
             if self.world > 1:
                 self._dp_update(l, seed)
+        for lane in self.lanes[1:nl]:
+            ctx.lane_join(lane)
 
     def _dp_update(self, l: CounterLinearState, seed: int):
         import torch.distributed as dist

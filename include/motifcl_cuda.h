@@ -176,6 +176,29 @@ int mcl_cuda_ternary_gemv(mcl_cuda_ctx* ctx, const float* x, const uint32_t* pac
                           const float* scale, float* y, size_t M, size_t in_features,
                           size_t out_features);
 
+/* ---- memory-native fused update that allocates nothing (it has no counterpart in the
+ * reference).  For callers that may not call cudaMalloc / cudaFree while they run: a host that
+ * gave all device memory to its own arena at start-up, a plugin inside a latency-critical loop
+ * where an allocation would stall the device, or code that owns only a stream and its buffers
+ * and no library context.  Same arithmetic and results as mcl_cuda_counter_update_fused in
+ * MCL_CUDA_GEMM_EXACT mode, but the grad_w row tile lives in a 4 MiB array built into the
+ * library (every GPU that loads the library holds it until the process exits) instead of a
+ * workspace grown on demand.  No context: work is enqueued on `cuda_stream` of the CURRENT
+ * device.  Limits and rules:
+ *   - in_features <= mcl_cuda_static_scratch_floats() (1,048,576): one gradient row must fit;
+ *     larger shapes are refused with a message (mcl_cuda_static_last_error()).
+ *   - all calls on a device share the array: calls that overlap on the GPU race; keep them on
+ *     one stream.  The array is not cleared between calls and nothing relies on its contents.
+ *   - the first call on a device resolves the array's device address (cudaGetSymbolAddress);
+ *     make that first call before any stream capture. ---- */
+int mcl_cuda_counter_update_fused_static(void* cuda_stream, uint8_t* state, float* scale, float* v,
+                                         const float* grad_out, const float* x, uint32_t* packed2_out,
+                                         size_t C, size_t in_features, size_t out_features, size_t batch,
+                                         float lr, float lr_scale, float rms_beta, float rms_eps,
+                                         uint32_t seed);
+size_t mcl_cuda_static_scratch_floats(void);
+const char* mcl_cuda_static_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -88,5 +88,8 @@ def lib() -> C.CDLL:
                                                    f, f, f, f, u32]
         L.mcl_cuda_matmul_f32.argtypes = [vp, vp, vp, vp, sz, sz, sz, i, i]
         L.mcl_cuda_ternary_gemv.argtypes = [vp, vp, vp, vp, vp, sz, sz, sz]
+        L.mcl_cuda_counter_update_fused_static.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, f, f, f, f, u32]
+        L.mcl_cuda_static_scratch_floats.restype = C.c_size_t
+        L.mcl_cuda_static_last_error.restype = C.c_char_p
         _lib = L
     return _lib

@@ -175,6 +175,93 @@ def run_reference(args, wl):
     print(json.dumps(line))
 
 
+def run_micro(args):
+    """Single-kernel timing at an HBM-resident size, for roofline figures and profiler captures:
+        --micro update:ROWSxIN[:lr_scale]   fused counter update (5.75 B/weight + 16 B/row)
+        --micro gemv:OUTxIN:M               ternary GEMV (out*in/4 + 4*out + 4*M*(in+out) bytes)
+        --micro step:TOKENSxINxOUT          one linear step (6*tokens*in*out flop)
+    Buffers are rotated so that consecutive launches never touch the same memory (sets larger
+    than L2 in total)."""
+    import torch
+    from motifcl_b200 import Context
+    torch.cuda.set_device(0)
+    torch.cuda.set_stream(torch.cuda.Stream(device=0))
+    ctx = Context.on_torch_stream(0)
+    dev = "cuda:0"
+    kind, shape, *rest = args.micro.split(":")
+    dims = [int(v) for v in shape.split("x")]
+    hbm_peak, tf_peak, peak_kind = measured_peaks()
+    g = torch.Generator(device=dev).manual_seed(1)
+
+    def timed(fn, iters, warm):
+        for i in range(warm):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            fn(warm + i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    with ClockSampler(0) as clk:
+        if kind == "update":
+            O, I = dims
+            lrs = float(rest[0]) if rest else 0.0
+            per_set = O * I * 4.75
+            nsets = max(2, int(300e6 // per_set) + 1)
+            sets = []
+            for _ in range(nsets):
+                codes = torch.randint(0, 63, (O, I // 4, 4), device=dev, generator=g, dtype=torch.int32)
+                w = codes[..., 0] | (codes[..., 1] << 6) | (codes[..., 2] << 12) | (codes[..., 3] << 18)
+                st = torch.stack([w & 255, (w >> 8) & 255, (w >> 16) & 255], -1).to(torch.uint8).reshape(-1).contiguous()
+                sets.append((st, torch.full((O,), 0.05, device=dev), torch.full((O,), 1e-3, device=dev),
+                             torch.randn(O, I, device=dev, generator=g) * 0.5,
+                             torch.zeros(O, I // 16, dtype=torch.int32, device=dev)))
+            def fn(i):
+                st, sc, v, gw, p2 = sets[i % nsets]
+                ctx.counter_update_dense(st, sc, v, gw, p2, 11, I, O, 0, 3e-3, lrs, 0.9, 1e-3, 12345 + i)
+            ms = timed(fn, args.steps, max(args.warmup, 3))
+            nbytes = 5.75 * O * I + 16.0 * O
+            out = {"kernel": "counter_update_dense_kernel", "bound": "hbm", "achieved": nbytes / ms / 1e6,
+                   "peak": hbm_peak, "unit": "GB/s", "bytes_per_launch": nbytes}
+        elif kind == "gemv":
+            O, I = dims
+            M = int(rest[0]) if rest else 1
+            nsets = max(2, int(300e6 // (O * I / 4)) + 1)
+            p2s = [torch.randint(-2 ** 31, 2 ** 31 - 1, (O, I // 16), dtype=torch.int32, device=dev, generator=g)
+                   for _ in range(nsets)]
+            sc = torch.full((O,), 0.05, device=dev)
+            x = torch.randn(M, I, device=dev, generator=g)
+            y = torch.empty(M, O, device=dev)
+            ms = timed(lambda i: ctx.ternary_gemv(x, p2s[i % nsets], sc, y, M, I, O), args.steps, max(args.warmup, 3))
+            nbytes = O * I / 4 + 4 * O + 4 * M * (I + O)
+            out = {"kernel": "ternary_gemv_kernel", "bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": hbm_peak,
+                   "unit": "GB/s", "bytes_per_launch": nbytes, "tokens_per_s": M / (ms * 1e-3)}
+        elif kind == "step":
+            T, I, O = dims
+            x = torch.randn(T, I, device=dev, generator=g)
+            dy = torch.randn(T, O, device=dev, generator=g) * 0.02
+            st = torch.randint(0, 255, (O * I // 4 * 3,), dtype=torch.uint8, device=dev, generator=g)
+            sc, v = torch.full((O,), 0.05, device=dev), torch.zeros(O, device=dev)
+            y, dx = torch.empty(T, O, device=dev), torch.empty(T, I, device=dev)
+            gw, p2 = torch.empty(O, I, device=dev), torch.zeros(O, I // 16, dtype=torch.int32, device=dev)
+            if rest:
+                a, b = rest[0].split("/")
+                ctx.set_gemm_mode("tensor", int(a), int(b))
+            ms = timed(lambda i: ctx.counter_linear_step(x, dy, st, sc, v, y, dx, gw, p2, 11, I, O, T, O, 0, 3e-3,
+                                                         0.0, 0.9, 1e-3, i), args.steps, max(args.warmup, 3))
+            fl = 6.0 * T * I * O
+            out = {"kernel": "linear step (split, expand, 3 contractions, update)", "bound": "tensor",
+                   "achieved": fl / ms / 1e9, "peak": tf_peak, "unit": "TFLOP/s", "flop_per_launch": fl}
+        else:
+            raise SystemExit("unknown --micro kind")
+    out.update({"frac": out["achieved"] / out["peak"], "peak_kind": peak_kind, "ms": ms, "micro": args.micro,
+                "steps": args.steps, "clocks": clk.summary(), "gpu_launches": ctx.launch_count})
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -185,7 +272,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--lanes", type=int, default=8, help="contexts (streams) that independent linears are spread over")
     ap.add_argument("--eager", action="store_true", help="do not record the step into one batch (for per-kernel profiling)")
+    ap.add_argument("--micro", default=None, help="single-kernel timing, see run_micro()")
     args = ap.parse_args()
+    if args.micro:
+        return run_micro(args)
     wl = workload(args.workload)
     if args.impl == "reference":
         return run_reference(args, wl)

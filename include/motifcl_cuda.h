@@ -164,6 +164,14 @@ int mcl_cuda_counter_linear_step(mcl_cuda_ctx* ctx, const float* x, const float*
                                  size_t row_offset, float lr, float lr_scale, float rms_beta,
                                  float rms_eps, uint32_t seed);
 
+/* ---- the three products of one linear from the 2-bit packed weights (no reference counterpart;
+ * same arithmetic as the forward / backward-to-input / weight-gradient entries above with the
+ * ternary digit read from packed2).  This is what a data-parallel rank runs for layers whose
+ * counter state lives on other ranks: y, grad_x, grad_w (any may be NULL), no update. ---- */
+int mcl_cuda_ternary_linear_products(mcl_cuda_ctx* ctx, const float* x, const float* grad_out,
+                                     const uint32_t* packed2, const float* scale, float* y, float* grad_x,
+                                     float* grad_w, size_t in_features, size_t out_features, size_t batch);
+
 /* ---- generic fp32 matmul: replaces matmul / matmul_transpose_a / matmul_transpose_b
  * (src/ops/matmul.cpp:1131-1233; kernels/matmul.cl:55-129,413-563).
  * c[M,N] = op(a) op(b); trans_a: a stored [K,M]; trans_b: b stored [N,K]. ---- */

@@ -614,6 +614,68 @@ int mcl_cuda_counter_update_fused(mcl_cuda_ctx* ctx, uint8_t* state, float* scal
     return MCL_CUDA_OK;
 }
 
+// Y, dX and dW of one linear; the ternary digits come from the packed 6-bit state or, when
+// state == NULL, from the 2-bit packed weights.
+static int linear_products(mcl_cuda_ctx* ctx, const char* op, const float* x, const float* grad_out,
+                           const uint8_t* state, const uint32_t* packed2, const float* scale, float* y,
+                           float* grad_x, float* grad_w, size_t C, size_t I, size_t O, size_t Nt) {
+    const bool tc = tc_wanted(ctx, Nt, O, I) && tc_wanted(ctx, Nt, I, O) && tc_wanted(ctx, O, I, Nt);
+    if (!tc) {
+        if (state) {
+            if (y) MCL_TRY(mcl_cuda_counter_forward(ctx, x, state, scale, y, Nt, I, O, C));
+            if (grad_x) MCL_TRY(mcl_cuda_counter_backward_input(ctx, state, scale, grad_out, grad_x, Nt, I, O, C));
+        } else {
+            if (y) MCL_LAUNCH(ctx, op, mcl::launch_simt_ternary_forward(x, packed2, scale, y, (int)Nt, (int)I, (int)O, ctx->stream));
+            if (grad_x) MCL_LAUNCH(ctx, op, mcl::launch_simt_ternary_backward_input(packed2, scale, grad_out, grad_x, (int)Nt,
+                                                                                 (int)I, (int)O, ctx->stream));
+        }
+        if (grad_w) MCL_TRY(mcl_cuda_matmul_f32(ctx, grad_out, x, grad_w, O, Nt, I, 1, 0));
+        return MCL_CUDA_OK;
+    }
+    const int ta = ctx->act_terms;
+    int pa[6], pb[6], nt, gp;
+    grad_term_list(ctx->grad_terms, pa, pb, &nt, &gp);
+    const int ldi = up8(I), ldo = up8(O), ldn = up8(Nt);
+    int s_y = 1, s_x = 1, s_w = 1;
+    const size_t k_y = mcl::tc_splitk_workspace_bytes((int)Nt, (int)O, (int)I, ctx->sm_count, &s_y);
+    const size_t k_x = mcl::tc_splitk_workspace_bytes((int)Nt, (int)I, (int)O, ctx->sm_count, &s_x);
+    const size_t k_w = mcl::tc_splitk_workspace_bytes((int)O, (int)I, (int)Nt, ctx->sm_count, &s_w);
+    size_t k_max = k_y > k_x ? k_y : k_x;
+    if (k_w > k_max) k_max = k_w;
+    Carver cv;
+    const size_t o_xp = cv.reserve((size_t)ta * Nt * ldi * 2);    // X terms        [ta][N][I]
+    const size_t o_xt = cv.reserve((size_t)gp * I * ldn * 2);     // X^T terms      [gp][I][N]
+    const size_t o_gp = cv.reserve((size_t)ta * Nt * ldo * 2);    // (dY.s) terms   [ta][N][O]
+    const size_t o_gt = cv.reserve((size_t)gp * O * ldn * 2);     // dY^T terms     [gp][O][N]
+    const size_t o_t = cv.reserve(O * (size_t)ldi * 2);           // T   [O][I]
+    const size_t o_tt = cv.reserve(I * (size_t)ldo * 2);          // T^T [I][O]
+    const size_t o_k = cv.reserve(k_max);
+    void* wsp = nullptr;
+    MCL_TRY(ws_reserve(ctx, cv.off, &wsp));
+    char* w = static_cast<char*>(wsp);
+    float* kws = reinterpret_cast<float*>(w + o_k);
+    // each fp32 tensor is read once and written as terms in the orientations its products need
+    MCL_LAUNCH(ctx, op, mcl::launch_split_planes(x, (int)Nt, (int)I, nullptr, y ? w + o_xp : nullptr, ldi, ta,
+                                                 grad_w ? w + o_xt : nullptr, ldn, gp, ctx->stream));
+    if (state)
+        MCL_LAUNCH(ctx, op, mcl::launch_expand_ternary(state, (int)C, (int)O, (int)I, y ? w + o_t : nullptr, ldi,
+                                                       grad_x ? w + o_tt : nullptr, ldo, ctx->stream));
+    else
+        MCL_LAUNCH(ctx, op, mcl::launch_expand_ternary_p2(packed2, (int)O, (int)I, y ? w + o_t : nullptr, ldi,
+                                                          grad_x ? w + o_tt : nullptr, ldo, ctx->stream));
+    MCL_LAUNCH(ctx, op, mcl::launch_split_planes(grad_out, (int)Nt, (int)O, scale, grad_x ? w + o_gp : nullptr, ldo, ta,
+                                                 grad_w ? w + o_gt : nullptr, ldn, gp, ctx->stream));
+    int qa[6], qb[6], qn;
+    act_term_list(ta, qa, qb, &qn);
+    if (y) MCL_TRY(tc_product(ctx, w + o_xp, ta, ldi, Nt * (size_t)ldi, w + o_t, 1, ldi, O * (size_t)ldi, y, (int)O,
+                              (int)Nt, (int)O, (int)I, qa, qb, qn, scale, kws, s_y));
+    if (grad_x) MCL_TRY(tc_product(ctx, w + o_gp, ta, ldo, Nt * (size_t)ldo, w + o_tt, 1, ldo, I * (size_t)ldo, grad_x,
+                                   (int)I, (int)Nt, (int)I, (int)O, qa, qb, qn, nullptr, kws, s_x));
+    if (grad_w) MCL_TRY(tc_product(ctx, w + o_gt, gp, ldn, O * (size_t)ldn, w + o_xt, gp, ldn, I * (size_t)ldn, grad_w,
+                                   (int)I, (int)O, (int)I, (int)Nt, pa, pb, nt, nullptr, kws, s_w));
+    return MCL_CUDA_OK;
+}
+
 int mcl_cuda_counter_linear_step(mcl_cuda_ctx* ctx, const float* x, const float* grad_out,
                                  uint8_t* state, float* scale, float* v, float* y, float* grad_x,
                                  float* grad_w, uint32_t* packed2_out, size_t C, size_t in_features,
@@ -634,55 +696,37 @@ int mcl_cuda_counter_linear_step(mcl_cuda_ctx* ctx, const float* x, const float*
     if (row_offset + update_rows > out_features)
         return fail(ctx, MCL_CUDA_EINVAL, "counter linear step: update rows exceed out_features");
     const size_t state_row = in_features / 4 * 3;
-    const size_t O = out_features, I = in_features, Nt = batch;
+    const size_t I = in_features;
     DeviceGuard guard(ctx->device);
-    const bool tc = tc_wanted(ctx, Nt, O, I) && tc_wanted(ctx, Nt, I, O) && tc_wanted(ctx, O, I, Nt);
-    if (!tc) {
-        if (y) MCL_TRY(mcl_cuda_counter_forward(ctx, x, state, scale, y, Nt, I, O, C));
-        if (grad_x) MCL_TRY(mcl_cuda_counter_backward_input(ctx, state, scale, grad_out, grad_x, Nt, I, O, C));
-        MCL_TRY(mcl_cuda_matmul_f32(ctx, grad_out, x, grad_w, O, Nt, I, 1, 0));
-    } else {
-        const int ta = ctx->act_terms;
-        int pa[6], pb[6], nt, gp;
-        grad_term_list(ctx->grad_terms, pa, pb, &nt, &gp);
-        const int ldi = up8(I), ldo = up8(O), ldn = up8(Nt);
-        int s_y = 1, s_x = 1, s_w = 1;
-        const size_t k_y = mcl::tc_splitk_workspace_bytes((int)Nt, (int)O, (int)I, ctx->sm_count, &s_y);
-        const size_t k_x = mcl::tc_splitk_workspace_bytes((int)Nt, (int)I, (int)O, ctx->sm_count, &s_x);
-        const size_t k_w = mcl::tc_splitk_workspace_bytes((int)O, (int)I, (int)Nt, ctx->sm_count, &s_w);
-        size_t k_max = k_y > k_x ? k_y : k_x;
-        if (k_w > k_max) k_max = k_w;
-        Carver cv;
-        const size_t o_xp = cv.reserve((size_t)ta * Nt * ldi * 2);    // X terms        [ta][N][I]
-        const size_t o_xt = cv.reserve((size_t)gp * I * ldn * 2);     // X^T terms      [gp][I][N]
-        const size_t o_gp = cv.reserve((size_t)ta * Nt * ldo * 2);    // (dY.s) terms   [ta][N][O]
-        const size_t o_gt = cv.reserve((size_t)gp * O * ldn * 2);     // dY^T terms     [gp][O][N]
-        const size_t o_t = cv.reserve(O * (size_t)ldi * 2);           // T   [O][I]
-        const size_t o_tt = cv.reserve(I * (size_t)ldo * 2);          // T^T [I][O]
-        const size_t o_k = cv.reserve(k_max);
-        void* wsp = nullptr;
-        MCL_TRY(ws_reserve(ctx, cv.off, &wsp));
-        char* w = static_cast<char*>(wsp);
-        float* kws = reinterpret_cast<float*>(w + o_k);
-        // X: terms in both orientations from one read (planes use the first ta / gp terms)
-        MCL_LAUNCH(ctx, op, mcl::launch_split_planes(x, (int)Nt, (int)I, nullptr, w + o_xp, ldi, ta, w + o_xt, ldn, gp, ctx->stream));
-        MCL_LAUNCH(ctx, op, mcl::launch_expand_ternary(state, (int)C, (int)O, (int)I, w + o_t, ldi, w + o_tt, ldo, ctx->stream));
-        MCL_LAUNCH(ctx, op, mcl::launch_split_planes(grad_out, (int)Nt, (int)O, scale, w + o_gp, ldo, ta, w + o_gt, ldn, gp, ctx->stream));
-        int qa[6], qb[6], qn;
-        act_term_list(ta, qa, qb, &qn);
-        if (y) MCL_TRY(tc_product(ctx, w + o_xp, ta, ldi, Nt * (size_t)ldi, w + o_t, 1, ldi, O * (size_t)ldi, y, (int)O,
-                                  (int)Nt, (int)O, (int)I, qa, qb, qn, scale, kws, s_y));
-        if (grad_x) MCL_TRY(tc_product(ctx, w + o_gp, ta, ldo, Nt * (size_t)ldo, w + o_tt, 1, ldo, I * (size_t)ldo, grad_x,
-                                       (int)I, (int)Nt, (int)I, (int)O, qa, qb, qn, nullptr, kws, s_x));
-        MCL_TRY(tc_product(ctx, w + o_gt, gp, ldn, O * (size_t)ldn, w + o_xt, gp, ldn, I * (size_t)ldn, grad_w, (int)I,
-                           (int)O, (int)I, (int)Nt, pa, pb, nt, nullptr, kws, s_w));
-    }
+    MCL_TRY(linear_products(ctx, op, x, grad_out, state, nullptr, scale, y, grad_x, grad_w, C, in_features,
+                            out_features, batch));
     if (update_rows > 0)
         return mcl_cuda_counter_update_dense(ctx, state + row_offset * state_row, scale + row_offset, v + row_offset,
                                              grad_w + row_offset * I,
                                              packed2_out ? packed2_out + row_offset * (I / 16) : nullptr, C, I,
                                              update_rows, row_offset, lr, lr_scale, rms_beta, rms_eps, seed);
     return MCL_CUDA_OK;
+}
+
+int mcl_cuda_ternary_linear_products(mcl_cuda_ctx* ctx, const float* x, const float* grad_out,
+                                     const uint32_t* packed2, const float* scale, float* y, float* grad_x,
+                                     float* grad_w, size_t in_features, size_t out_features, size_t batch) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "ternary linear products";
+    if (in_features == 0 || out_features == 0 || batch == 0)
+        return fail(ctx, MCL_CUDA_EINVAL, "ternary linear products requires non-zero dimensions");
+    if (in_features % 16 != 0) return fail(ctx, MCL_CUDA_EINVAL, "ternary linear products requires in_features % 16 == 0");
+    if (in_features > 0x7fffffffull || out_features > 0x7fffffffull || batch > 0x7fffffffull ||
+        in_features * out_features > 0x7fffffffull)
+        return fail(ctx, MCL_CUDA_EINVAL, "ternary linear products: dimension exceeds 32-bit indexing");
+    MCL_TRY(check_ptr(ctx, op, "x", x, 4));
+    MCL_TRY(check_ptr(ctx, op, "packed2", packed2, 4));
+    MCL_TRY(check_ptr(ctx, op, "scale", scale, 4));
+    if (grad_x || grad_w) MCL_TRY(check_ptr(ctx, op, "grad_out", grad_out, 4));
+    if (grad_w) MCL_TRY(check_ptr(ctx, op, "grad_w", grad_w, 16));
+    DeviceGuard guard(ctx->device);
+    return linear_products(ctx, op, x, grad_out, nullptr, packed2, scale, y, grad_x, grad_w, 11, in_features,
+                           out_features, batch);
 }
 
 int mcl_cuda_matmul_f32(mcl_cuda_ctx* ctx, const float* a, const float* b, float* c, size_t M,

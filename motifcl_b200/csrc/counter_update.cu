@@ -15,8 +15,12 @@
 //          rounded multiply and add, then the 32,16,...,1 tree (first step through shared
 //          memory, the rest by warp shuffles).  Lane 0 finishes v, denom and the new scale.
 //   tick   all threads run the stochastic-rounding tick, one packed group (4 weights) per
-//          thread-iteration, rewriting the state bytes in shared memory and emitting one
-//          byte of 2-bit fields per group.
+//          thread-iteration, writing the new state bytes to shared memory and emitting one
+//          byte of 2-bit fields per group.  The part of the tick after the stochastic
+//          rounding -- carry into the ternary digit, clamp, re-encode -- is a function of the
+//          old ternary digit and the (small, integer) rounded counter only, so it is read
+//          from a table built once per CTA with the reference's own float formulas; values
+//          outside the table's range take the formulas directly.
 //   store  all threads copy the new state and the 2-bit words back with wide stores.
 // HBM traffic per weight: 0.75 B state in, 4 B gradient in, 0.75 B state out, 0.25 B
 // packed weights out = 5.75 B.
@@ -48,12 +52,24 @@ struct RowConst {
     float dn, k_tick, k_reb, pad;
 };
 
+// Tail table: new 6-bit code and 2-bit field for (old ternary digit t in {-1,0,1,2}, rounded
+// counter ccv in [-kTailK, kTailK]); entry = code | field << 8.
+constexpr int kTailK = 32;
+constexpr int kTailRow = 2 * kTailK + 1;
+
+// Per-row table indexed by the OLD code: x = float(c) * (s_old / s_new) (the rebased counter),
+// y = index of the tail-table row of the code's ternary digit, pre-offset by kTailK.
+struct RowEntry {
+    float creb;
+    int tail_base;
+};
+
 // Shared-memory carve-up (per CTA), all offsets 16-byte aligned:
 //   lut[64] float2 | rowc[R] RowConst | part[R][2][32] float | gw[R][I] float |
 //   q[R][I] float (only WITH_Q) | st[R][sb] bytes (sb = state row bytes rounded up to 16, +16)
 //   | so[R][sb] bytes (new state) | p2[R][I/4 rounded to 16] bytes
 template <bool WITH_Q>
-__global__ void __launch_bounds__(kUpdThreads)
+__global__ void __launch_bounds__(kUpdThreads, 3)
 counter_update_dense_kernel(const UpdParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int I = p.in_features;
@@ -66,7 +82,9 @@ counter_update_dense_kernel(const UpdParams p) {
     DecodeLut* lut = reinterpret_cast<DecodeLut*>(smem);
     RowConst* rowc = reinterpret_cast<RowConst*>(smem + sizeof(DecodeLut));
     float* part = reinterpret_cast<float*>(rowc + kMaxRowsPerBatch);
-    float* gw_s = part + kMaxRowsPerBatch * 64;
+    RowEntry* rowtab = reinterpret_cast<RowEntry*>(part + kMaxRowsPerBatch * 64);     // [R][64]
+    unsigned short* tail = reinterpret_cast<unsigned short*>(rowtab + kMaxRowsPerBatch * 64);   // [4][kTailRow]
+    float* gw_s = reinterpret_cast<float*>(tail + ((4 * kTailRow + 7) & ~7));
     float* q_s = gw_s + (size_t)R * I;
     unsigned char* st_s = reinterpret_cast<unsigned char*>(WITH_Q ? q_s + (size_t)R * I : q_s);
     unsigned char* so_s = st_s + (size_t)R * sb;
@@ -79,11 +97,26 @@ counter_update_dense_kernel(const UpdParams p) {
     const int lv = 2 * p.C - 1;
     const float Cf = (float)p.C;
     const float neg_lr = -p.lr;
+    const bool check_t = 4 * lv < 64;      // some code values decode to a ternary digit the tail table lacks
     const uint32_t seed = p.seed + (p.seed_offset ? __ldg(p.seed_offset) : 0u);
     const bool aligned16 = p.state_align >= 16;   // state rows start and end on 16-byte boundaries
     const bool aligned4 = p.state_align >= 4;     // ... on 4-byte boundaries
 
     build_decode_lut(lut, p.C, tid, kUpdThreads);
+    // tail table, evaluated with the reference's formulas (kernels/compact_counter.cl:129-136)
+    for (int e = tid; e < 4 * kTailRow; e += kUpdThreads) {
+        const int t = e / kTailRow - 1;
+        const float ccv = (float)(e % kTailRow - kTailK);
+        const float carry = truncf(__fdiv_rn(ccv, Cf));
+        float rem = __fsub_rn(ccv, __fmul_rn(carry, Cf));
+        const int nt = t + (int)carry;
+        const int ct = nt < -1 ? -1 : (nt > 1 ? 1 : nt);
+        if (ct != nt) rem = __fmul_rn(ccv > 0.0f ? 1.0f : (ccv < 0.0f ? -1.0f : 0.0f), __fsub_rn(Cf, 1.0f));
+        int ri = (int)rem;
+        ri = ri < -(p.C - 1) ? -(p.C - 1) : (ri > p.C - 1 ? p.C - 1 : ri);
+        const unsigned code = (unsigned)((ct + 1) * lv + (ri + (p.C - 1))) & 0x3Fu;
+        tail[e] = (unsigned short)(code | ((unsigned)(ct + 1) << 8));
+    }
     __syncthreads();
 
     const int nbatches = (p.rows + R - 1) / R;
@@ -189,6 +222,17 @@ counter_update_dense_kernel(const UpdParams p) {
             }
         }
         __syncthreads();
+        // per-row table of rebased counters (one entry per old code value)
+        if (pair < nrows) {
+            const float k_reb = rowc[pair].k_reb;
+            const float2 tc = lut->e[vlane];
+            RowEntry re;
+            re.creb = __fmul_rn(tc.y, k_reb);
+            const int ti = (int)tc.x + 1;                       // 0..3 for every code the tail table covers
+            re.tail_base = (ti >= 0 && ti < 4) ? ti * kTailRow + kTailK : -(1 << 20);
+            rowtab[pair * 64 + vlane] = re;
+        }
+        __syncthreads();
 
         // ---- tick: one packed group per thread-iteration --------------------------------
         for (int r = 0; r < nrows; ++r) {
@@ -198,20 +242,43 @@ counter_update_dense_kernel(const UpdParams p) {
             unsigned char* so = so_s + (size_t)r * sb;
             unsigned char* p2 = p2_s + (size_t)r * pb;
             const uint32_t elem_row = (uint32_t)(p.row_offset + row0 + r) * (uint32_t)I;
+            const RowEntry* rt = rowtab + r * 64;
             for (int g = tid; g < gpr; g += kUpdThreads) {
                 const uint32_t w = load_group24(raw, (uint32_t)g * 3u);
                 const float4 gw = g4[g];
                 const float gwv[4] = {gw.x, gw.y, gw.z, gw.w};
                 uint32_t nw = 0, fields = 0;
+                // first round of the element hash: the four indices of a group differ only in
+                // their two low bits, so x >> 16 is shared (kernels/compact_counter.cl:17-21)
+                const uint32_t e0 = elem_row + (uint32_t)(g * 4);
+                const uint32_t e0x = e0 ^ (e0 >> 16);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const float2 tc = lut->e[(w >> (6 * k)) & 63u];
-                    uint32_t fld;
-                    const uint32_t code =
-                        counter_tick(gwv[k], tc.x, tc.y, elem_row + (uint32_t)(g * 4 + k), seed,
-                                     neg_lr, rc.dn, rc.k_tick, rc.k_reb, Cf, p.C, lv, &fld);
-                    nw |= (code & 0x3Fu) << (6 * k);
-                    fields |= (fld & 3u) << (2 * k);
+                    const uint32_t code_old = (w >> (6 * k)) & 63u;
+                    const RowEntry re = rt[code_old];
+                    const float tick = __fmul_rn(__fmul_rn(neg_lr, __fdiv_rn(gwv[k], rc.dn)), rc.k_tick);
+                    const float val = __fadd_rn(re.creb, tick);
+                    const float f = floorf(val);
+                    uint32_t x = (e0x ^ (uint32_t)k) * 0x7feb352du;     // (e0 + k) ^ ((e0 + k) >> 16), e0 % 4 == 0
+                    x ^= x >> 15; x *= 0x846ca68bu;
+                    x = seed ^ x ^ (x >> 16);
+                    const uint32_t h = cc_hash_u32(x) & 0x00ffffffu;
+                    const float rnd = __fmul_rn((float)h, 1.0f / 16777216.0f);
+                    const int iccv = __float2int_rn(f) + ((rnd < __fsub_rn(val, f)) ? 1 : 0);
+                    uint32_t code, fld;
+                    // |val| < K-1 bounds floor(val) + {0,1} to the table's range
+                    if (fabsf(val) < (float)(kTailK - 1) && (!check_t || re.tail_base >= 0)) {
+                        const unsigned e = tail[re.tail_base + iccv];
+                        code = e & 0x3Fu;
+                        fld = e >> 8;
+                    } else {
+                        const float2 tc = lut->e[code_old];
+                        code = counter_tick(gwv[k], tc.x, tc.y, e0 + (uint32_t)k, seed, neg_lr, rc.dn, rc.k_tick,
+                                            rc.k_reb, Cf, p.C, lv, &fld) & 0x3Fu;
+                        fld &= 3u;
+                    }
+                    nw += code << (6 * k);
+                    fields += fld << (2 * k);
                 }
                 so[g * 3 + 0] = (unsigned char)(nw & 0xFFu);
                 so[g * 3 + 1] = (unsigned char)((nw >> 8) & 0xFFu);
@@ -253,11 +320,313 @@ counter_update_dense_kernel(const UpdParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Fast variant for in_features % 16 == 0 (every benchmark shape): same phases, but
+//   * a batch holds up to kMaxRowsU16 rows, so narrow layers still give each CTA thousands of
+//     weights between barriers; a warp pair walks its rows of the batch one after another and
+//     pairs meet on their own named barrier, not a CTA-wide one;
+//   * the tick works on units of 16 weights = 3 aligned state words in, 3 state words + one
+//     2-bit word out, all 32-bit shared-memory accesses; units of all rows of the batch are
+//     flattened over the threads;
+//   * the gradient tile in shared memory is XOR-swizzled at 16-byte granularity so that the
+//     unit-strided 128-bit reads are bank-conflict free;
+//   * the right shifts of the integer hash are issued as mul.hi (FMA pipe) because the ALU
+//     pipe is the busiest one in this kernel.
+constexpr int kMaxRowsU16 = 64;
+constexpr int kPairs = kUpdThreads / 64;
+
+__device__ __forceinline__ int swz4(int f) {          // float4 index -> swizzled float4 index
+    return (f & ~3) | ((f & 3) ^ ((f >> 3) & 3));
+}
+__device__ __forceinline__ uint32_t shr_mulhi(uint32_t x, uint32_t pow2) {   // x >> (32 - log2(pow2))
+    uint32_t r;
+    asm("mul.hi.u32 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(pow2));
+    return r;
+}
+
+struct U16Layout {
+    int sb, off_tailc, off_tailf, off_rowc, off_part, off_rowtab, off_gw, off_q, off_st, off_so, off_p2;
+    size_t total;
+};
+__host__ __device__ inline U16Layout u16_layout(int I, int R, bool with_q) {
+    U16Layout L;
+    const int row_bytes = (I >> 2) * 3;
+    L.sb = (row_bytes + 15) & ~15;
+    size_t o = sizeof(DecodeLut);
+    L.off_tailc = (int)o; o += (4 * kTailRow + 15) & ~15;
+    L.off_tailf = (int)o; o += (4 * kTailRow + 15) & ~15;
+    L.off_rowc = (int)o; o += sizeof(RowConst) * R;
+    L.off_part = (int)o; o += sizeof(float) * 64 * kPairs;
+    L.off_rowtab = (int)o; o += sizeof(RowEntry) * 64 * (size_t)R;
+    L.off_gw = (int)o; o += sizeof(float) * (size_t)R * I;
+    L.off_q = (int)o; if (with_q) o += sizeof(float) * (size_t)R * I;
+    L.off_st = (int)o; o += (size_t)R * L.sb + 16;
+    L.off_so = (int)o; o += (size_t)R * L.sb + 16;
+    L.off_p2 = (int)o; o += (size_t)R * (I >> 2);
+    L.total = (o + 15) & ~size_t(15);
+    return L;
+}
+
+template <bool WITH_Q>
+__global__ void __launch_bounds__(kUpdThreads, 4)
+counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const uint32_t pow16, const uint32_t pow17) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int I = p.in_features;
+    const int gpr = I >> 2;               // packed groups (float4s) per row
+    const int upr = I >> 4;               // 16-weight units per row
+    const int row_bytes = gpr * 3;
+    const int R = p.rows_per_batch;
+    const U16Layout L = u16_layout(I, R, WITH_Q);
+
+    DecodeLut* lut = reinterpret_cast<DecodeLut*>(smem);
+    unsigned char* tail_code = smem + L.off_tailc;
+    unsigned char* tail_field = smem + L.off_tailf;
+    RowConst* rowc = reinterpret_cast<RowConst*>(smem + L.off_rowc);
+    float* part = reinterpret_cast<float*>(smem + L.off_part);
+    RowEntry* rowtab = reinterpret_cast<RowEntry*>(smem + L.off_rowtab);
+    float4* gw_s = reinterpret_cast<float4*>(smem + L.off_gw);
+    float4* q_s = reinterpret_cast<float4*>(smem + L.off_q);
+    unsigned char* st_s = smem + L.off_st;
+    unsigned char* so_s = smem + L.off_so;
+    uint32_t* p2_s = reinterpret_cast<uint32_t*>(smem + L.off_p2);
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int pair = tid >> 6;
+    const int vlane = tid & 63;
+    const int lv = 2 * p.C - 1;
+    const float Cf = (float)p.C;
+    const float neg_lr = -p.lr;
+    const bool check_t = 4 * lv < 64;
+    const uint32_t seed = p.seed + (p.seed_offset ? __ldg(p.seed_offset) : 0u);
+    const bool aligned16 = p.state_align >= 16;
+
+    build_decode_lut(lut, p.C, tid, kUpdThreads);
+    for (int e = tid; e < 4 * kTailRow; e += kUpdThreads) {     // kernels/compact_counter.cl:129-136
+        const int t = e / kTailRow - 1;
+        const float ccv = (float)(e % kTailRow - kTailK);
+        const float carry = truncf(__fdiv_rn(ccv, Cf));
+        float rem = __fsub_rn(ccv, __fmul_rn(carry, Cf));
+        const int nt = t + (int)carry;
+        const int ct = nt < -1 ? -1 : (nt > 1 ? 1 : nt);
+        if (ct != nt) rem = __fmul_rn(ccv > 0.0f ? 1.0f : (ccv < 0.0f ? -1.0f : 0.0f), __fsub_rn(Cf, 1.0f));
+        int ri = (int)rem;
+        ri = ri < -(p.C - 1) ? -(p.C - 1) : (ri > p.C - 1 ? p.C - 1 : ri);
+        tail_code[e] = (unsigned char)(((ct + 1) * lv + (ri + (p.C - 1))) & 0x3F);
+        tail_field[e] = (unsigned char)(ct + 1);
+    }
+    __syncthreads();
+
+    const int nbatches = (p.rows + R - 1) / R;
+    for (int batch = blockIdx.x; batch < nbatches; batch += gridDim.x) {
+        const int row0 = batch * R;
+        const int nrows = min(R, p.rows - row0);
+
+        // ---- load: the batch's rows are contiguous in global memory ------------------------
+        {
+            const uint8_t* src = p.state + (size_t)row0 * row_bytes;
+            if (aligned16) {        // row_bytes % 16 == 0: one flat copy, smem row stride == row_bytes
+                const uint4* s4 = reinterpret_cast<const uint4*>(src);
+                uint4* d4 = reinterpret_cast<uint4*>(st_s);
+                for (int i = tid; i < nrows * (row_bytes >> 4); i += kUpdThreads) d4[i] = __ldg(s4 + i);
+            } else {                // rows are 4-byte aligned; smem rows padded to L.sb
+                const uint32_t* s1 = reinterpret_cast<const uint32_t*>(src);
+                const int wpr = row_bytes >> 2;
+                for (int i = tid; i < nrows * wpr; i += kUpdThreads) {
+                    const int r = i / wpr, w = i - r * wpr;
+                    reinterpret_cast<uint32_t*>(st_s + (size_t)r * L.sb)[w] = __ldg(s1 + i);
+                }
+            }
+        }
+        if (WITH_Q) __syncthreads();
+        {
+            const float4* src = reinterpret_cast<const float4*>(p.grad_w + (size_t)row0 * I);
+            for (int i = tid; i < nrows * gpr; i += kUpdThreads) {
+                const float4 gw = __ldg(src + i);
+                const int r = i / gpr, g = i - r * gpr;
+                const int at = r * gpr + swz4(g);
+                gw_s[at] = gw;
+                if (WITH_Q) {
+                    const uint32_t* raw = reinterpret_cast<const uint32_t*>(st_s + (size_t)r * L.sb);
+                    const uint32_t w = load_group24(raw, (uint32_t)g * 3u);
+                    float4 q;
+                    q.x = __fmul_rn(gw.x, lut->e[w & 63u].x);
+                    q.y = __fmul_rn(gw.y, lut->e[(w >> 6) & 63u].x);
+                    q.z = __fmul_rn(gw.z, lut->e[(w >> 12) & 63u].x);
+                    q.w = __fmul_rn(gw.w, lut->e[(w >> 18) & 63u].x);
+                    q_s[at] = q;
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- stats: warp pair `pair` walks rows pair, pair + kPairs, ... ---------------------
+        for (int r = pair; r < nrows; r += kPairs) {
+            float a = 0.0f, b = 0.0f;
+            const float4* g4 = gw_s + r * gpr;
+            const float4* q4 = q_s + r * gpr;
+            for (int g = vlane; g < gpr; g += 64) {
+                const float4 gw = g4[swz4(g)];
+                a = __fadd_rn(a, __fmul_rn(gw.x, gw.x));
+                a = __fadd_rn(a, __fmul_rn(gw.y, gw.y));
+                a = __fadd_rn(a, __fmul_rn(gw.z, gw.z));
+                a = __fadd_rn(a, __fmul_rn(gw.w, gw.w));
+                if (WITH_Q) {
+                    const float4 q = q4[swz4(g)];
+                    b = __fadd_rn(b, q.x);
+                    b = __fadd_rn(b, q.y);
+                    b = __fadd_rn(b, q.z);
+                    b = __fadd_rn(b, q.w);
+                }
+            }
+            if (vlane >= 32) {
+                part[pair * 64 + lane] = a;
+                part[pair * 64 + 32 + lane] = b;
+            }
+            asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory");
+            if (vlane < 32) {
+                a = __fadd_rn(a, part[pair * 64 + lane]);
+                b = __fadd_rn(b, part[pair * 64 + 32 + lane]);
+#pragma unroll
+                for (int s = 16; s > 0; s >>= 1) {
+                    a = __fadd_rn(a, __shfl_down_sync(0xffffffffu, a, s));
+                    b = __fadd_rn(b, __shfl_down_sync(0xffffffffu, b, s));
+                }
+                if (lane == 0) {                  // kernels/compact_counter.cl:92-99
+                    const int row = row0 + r;
+                    const float gsq = __fdiv_rn(a, (float)I);
+                    const float s_old = p.scale[row];
+                    float s_new = s_old;
+                    if (WITH_Q) {
+                        const float gs = __fdiv_rn(b, __fsqrt_rn((float)I));
+                        s_new = __fsub_rn(s_old, __fmul_rn(p.lr_scale, gs));
+                    }
+                    s_new = fminf(fmaxf(s_new, 1e-5f), 10.0f);
+                    const float vv = __fadd_rn(__fmul_rn(p.rms_beta, p.v[row]),
+                                               __fmul_rn(__fsub_rn(1.0f, p.rms_beta), gsq));
+                    p.v[row] = vv;
+                    RowConst rc;
+                    rc.dn = fmaxf(__fsqrt_rn(vv), p.rms_eps);
+                    rc.k_tick = __fdiv_rn(Cf, s_new);
+                    rc.k_reb = __fdiv_rn(s_old, s_new);
+                    rc.pad = 0.0f;
+                    rowc[r] = rc;
+                    p.scale[row] = s_new;
+                }
+            }
+            asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory");
+            {   // per-row table of rebased counters, one entry per old code value
+                const float2 tc = lut->e[vlane];
+                RowEntry re;
+                re.creb = __fmul_rn(tc.y, rowc[r].k_reb);
+                const int ti = (int)tc.x + 1;
+                re.tail_base = (ti >= 0 && ti < 4) ? ti * kTailRow + kTailK : -(1 << 20);
+                rowtab[r * 64 + vlane] = re;
+            }
+        }
+        __syncthreads();
+
+        // ---- tick: 16 weights per thread-iteration, units of the whole batch flattened --------
+        const int nunits = nrows * upr;
+        for (int u = tid; u < nunits; u += kUpdThreads) {
+            const int r = unit_magic ? (int)__umulhi((uint32_t)u, unit_magic) : u;       // u / upr (magic 0: upr == 1)
+            const int j = u - r * upr;
+            const RowConst rc = rowc[r];
+            const RowEntry* rt = rowtab + r * 64;
+            const uint32_t* sw = reinterpret_cast<const uint32_t*>(st_s + (size_t)r * L.sb) + 3 * j;
+            const uint32_t s0 = sw[0], s1 = sw[1], s2 = sw[2];
+            const uint32_t gwd[4] = {s0 & 0xFFFFFFu, (s0 >> 24) | ((s1 & 0xFFFFu) << 8),
+                                     (s1 >> 16) | ((s2 & 0xFFu) << 16), s2 >> 8};
+            const float4* g4 = gw_s + r * gpr + 4 * j;
+            const int jsw = (j >> 1) & 3;
+            const uint32_t e_unit = (uint32_t)(p.row_offset + row0 + r) * (uint32_t)I + (uint32_t)(16 * j);
+            uint32_t nwd[4], fields = 0;
+#pragma unroll
+            for (int gg = 0; gg < 4; ++gg) {
+                const float4 gw = g4[gg ^ jsw];
+                const float gwv[4] = {gw.x, gw.y, gw.z, gw.w};
+                const uint32_t w = gwd[gg];
+                const uint32_t e0 = e_unit + 4u * gg;
+                const uint32_t e0x = e0 ^ shr_mulhi(e0, pow16);
+                uint32_t nw = 0;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t code_old = (w >> (6 * k)) & 63u;
+                    const RowEntry re = rt[code_old];
+                    const float tick = __fmul_rn(__fmul_rn(neg_lr, __fdiv_rn(gwv[k], rc.dn)), rc.k_tick);
+                    const float val = __fadd_rn(re.creb, tick);
+                    uint32_t x = (e0x ^ (uint32_t)k) * 0x7feb352du;
+                    x ^= shr_mulhi(x, pow17);            // x >> 15
+                    x *= 0x846ca68bu;
+                    x = seed ^ x ^ shr_mulhi(x, pow16);  // seed ^ hash(elem)
+                    x ^= shr_mulhi(x, pow16);
+                    x *= 0x7feb352du;
+                    x ^= shr_mulhi(x, pow17);
+                    x *= 0x846ca68bu;
+                    const uint32_t h = (x ^ shr_mulhi(x, pow16)) & 0x00ffffffu;
+                    uint32_t code, fld;
+                    if (fabsf(val) < (float)(kTailK - 1) && (!check_t || re.tail_base >= 0)) {
+                        const float f = floorf(val);
+                        const float rnd = __fmul_rn((float)h, 1.0f / 16777216.0f);
+                        const float up = (rnd < __fsub_rn(val, f)) ? 1.0f : 0.0f;
+                        const int idx = re.tail_base + __float2int_rn(__fadd_rn(f, up));
+                        code = tail_code[idx];
+                        fld = tail_field[idx];
+                    } else {
+                        const float2 tc = lut->e[code_old];
+                        code = counter_tick(gwv[k], tc.x, tc.y, e0 + (uint32_t)k, seed, neg_lr, rc.dn, rc.k_tick,
+                                            rc.k_reb, Cf, p.C, lv, &fld) & 0x3Fu;
+                        fld &= 3u;
+                    }
+                    nw += code << (6 * k);
+                    fields += fld << (2 * (4 * gg + k));
+                }
+                nwd[gg] = nw;
+            }
+            uint32_t* so = reinterpret_cast<uint32_t*>(so_s + (size_t)r * L.sb) + 3 * j;
+            so[0] = nwd[0] | (nwd[1] << 24);
+            so[1] = (nwd[1] >> 8) | (nwd[2] << 16);
+            so[2] = (nwd[2] >> 16) | (nwd[3] << 8);
+            p2_s[r * upr + j] = fields;
+        }
+        __syncthreads();
+
+        // ---- store ------------------------------------------------------------------------------
+        {
+            uint8_t* dst = p.state + (size_t)row0 * row_bytes;
+            if (aligned16) {
+                const uint4* s4 = reinterpret_cast<const uint4*>(so_s);
+                uint4* d4 = reinterpret_cast<uint4*>(dst);
+                for (int i = tid; i < nrows * (row_bytes >> 4); i += kUpdThreads) d4[i] = s4[i];
+            } else {
+                uint32_t* d1 = reinterpret_cast<uint32_t*>(dst);
+                const int wpr = row_bytes >> 2;
+                for (int i = tid; i < nrows * wpr; i += kUpdThreads) {
+                    const int r = i / wpr, w = i - r * wpr;
+                    d1[i] = reinterpret_cast<const uint32_t*>(so_s + (size_t)r * L.sb)[w];
+                }
+            }
+            if (p.packed2 != nullptr) {
+                uint32_t* d = p.packed2 + (size_t)row0 * upr;
+                if (aligned16) {
+                    const uint4* s4 = reinterpret_cast<const uint4*>(p2_s);
+                    uint4* d4 = reinterpret_cast<uint4*>(d);
+                    for (int i = tid; i < (nrows * upr) >> 2; i += kUpdThreads) d4[i] = s4[i];
+                } else {
+                    for (int i = tid; i < nrows * upr; i += kUpdThreads) d[i] = p2_s[i];
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
 size_t upd_smem_bytes(int I, int R, bool with_q) {
     const int gpr = I / 4;
     const size_t sb = (size_t)((gpr * 3 + 15) & ~15) + 16;
     const size_t pb = (size_t)((gpr + 15) & ~15);
     return sizeof(DecodeLut) + sizeof(RowConst) * kMaxRowsPerBatch + sizeof(float) * 64 * kMaxRowsPerBatch +
+           sizeof(RowEntry) * 64 * kMaxRowsPerBatch + sizeof(unsigned short) * ((4 * kTailRow + 7) & ~7) +
            (size_t)R * I * sizeof(float) * (with_q ? 2 : 1) + (size_t)R * (2 * sb + pb);
 }
 
@@ -313,16 +682,16 @@ __global__ void pack2_kernel(const uint8_t* __restrict__ state, uint32_t* __rest
 
 // Opt a kernel in to the device's full dynamic shared memory, once per device and kernel slot.
 cudaError_t ensure_dynamic_smem(const void* kern, int slot, size_t max_smem) {
-    static bool done[64][4] = {};
+    static bool done[64][8] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && slot < 4 && done[dev][slot]) return cudaSuccess;
+    if (dev >= 0 && dev < 64 && slot < 8 && done[dev][slot]) return cudaSuccess;
     cudaFuncAttributes fa;
     cudaError_t e = cudaFuncGetAttributes(&fa, kern);
     if (e != cudaSuccess) return e;
     // the opt-in limit covers static + dynamic shared memory
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(max_smem - fa.sharedSizeBytes));
-    if (e == cudaSuccess && dev >= 0 && dev < 64 && slot < 4) done[dev][slot] = true;
+    if (e == cudaSuccess && dev >= 0 && dev < 64 && slot < 8) done[dev][slot] = true;
     return e;
 }
 
@@ -332,8 +701,38 @@ cudaError_t launch_counter_update_dense(uint8_t* state, float* scale, float* v, 
                                         float rms_eps, uint32_t seed, const uint32_t* seed_offset, int sm_count,
                                         size_t max_smem, cudaStream_t stream) {
     const bool with_q = (lr_scale != 0.0f);
+    const uintptr_t sp0 = reinterpret_cast<uintptr_t>(state), pp0 = reinterpret_cast<uintptr_t>(packed2);
+    if (in_features % 16 == 0 && sp0 % 4 == 0) {
+        // fast variant: rows per batch sized for four CTAs per SM when a row allows it
+        const size_t target = (max_smem - 4096) / 4;
+        int Ru = kMaxRowsU16;
+        while (Ru > 1 && u16_layout(in_features, Ru, with_q).total > target) --Ru;
+        const U16Layout L = u16_layout(in_features, Ru, with_q);
+        if (L.total <= max_smem - 1024) {
+            UpdParams p;
+            p.state = state; p.scale = scale; p.v = v; p.grad_w = grad_w; p.packed2 = packed2;
+            p.C = C; p.in_features = in_features; p.rows = rows; p.row_offset = row_offset;
+            p.rows_per_batch = Ru;
+            p.state_align = (in_features % 64 == 0 && sp0 % 16 == 0 && pp0 % 16 == 0) ? 16 : 4;
+            p.lr = lr; p.lr_scale = lr_scale; p.rms_beta = rms_beta; p.rms_eps = rms_eps;
+            p.seed = seed; p.seed_offset = seed_offset;
+            const int nb = (rows + Ru - 1) / Ru;
+            int per_sm = (int)((max_smem - 1024) / L.total);
+            if (per_sm > 4) per_sm = 4;
+            if (per_sm < 1) per_sm = 1;
+            int grid = sm_count * per_sm;
+            if (grid > nb) grid = nb;
+            const uint32_t upr = (uint32_t)(in_features / 16);
+            const uint32_t magic = upr == 1 ? 0u : (uint32_t)((0x100000000ull + upr - 1) / upr);   // u / upr = mulhi(u, magic), u * upr < 2^32
+            auto kern = with_q ? counter_update_u16_kernel<true> : counter_update_u16_kernel<false>;
+            cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), with_q ? 2 : 3, max_smem);
+            if (e != cudaSuccess) return e;
+            kern<<<grid, kUpdThreads, L.total, stream>>>(p, magic, 1u << 16, 1u << 17);
+            return cudaGetLastError();
+        }
+    }
     int R = kMaxRowsPerBatch;
-    while (R > 1 && upd_smem_bytes(in_features, R, with_q) > max_smem / 2) --R;
+    while (R > 1 && upd_smem_bytes(in_features, R, with_q) > (max_smem - 3072) / 3) --R;   // three CTAs per SM (the register limit)
     const size_t smem = upd_smem_bytes(in_features, R, with_q);
     if (smem > max_smem) return cudaErrorInvalidConfiguration;   // row too long for shared memory
     UpdParams p;

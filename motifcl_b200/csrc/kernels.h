@@ -30,6 +30,11 @@ cudaError_t launch_simt_counter_backward_input(const uint8_t* state, const float
                                                const float* grad_out, float* grad_x, int batch,
                                                int in_features, int out_features, int C,
                                                cudaStream_t stream);
+cudaError_t launch_simt_ternary_forward(const float* x, const uint32_t* packed2, const float* scale, float* y,
+                                        int batch, int in_features, int out_features, cudaStream_t stream);
+cudaError_t launch_simt_ternary_backward_input(const uint32_t* packed2, const float* scale, const float* grad_out,
+                                               float* grad_x, int batch, int in_features, int out_features,
+                                               cudaStream_t stream);
 // dW rows [row0, row0+rows) of dY^T X into grad_w[rows, in]
 cudaError_t launch_simt_grad_w(const float* grad_out, const float* x, float* grad_w, int batch,
                                int in_features, int out_features, int row0, int rows,
@@ -51,6 +56,9 @@ cudaError_t launch_split_planes(const float* src, int R, int Cc, const float* co
 // packed 6-bit state -> bf16 ternary digits T [O][ld_i] and/or T^T [I][ld_o]
 cudaError_t launch_expand_ternary(const uint8_t* state, int C, int O, int I, void* T, int ld_i, void* Tt, int ld_o,
                                   cudaStream_t stream);
+
+cudaError_t launch_expand_ternary_p2(const uint32_t* packed2, int O, int I, void* T, int ld_i, void* Tt, int ld_o,
+                                     cudaStream_t stream);
 
 // gemv.cu
 cudaError_t launch_ternary_gemv(const float* x, const uint32_t* packed2, const float* scale, float* y,

@@ -64,6 +64,21 @@ struct OpTernary {
     }
 };
 
+// The same operand read from 2-bit packed weights (field = t + 1).
+struct OpTernaryP2 {
+    const uint32_t* packed2;
+    const float* scale;   // null: unscaled
+    int in_features, out_features;
+    bool k_is_in;
+    __device__ __forceinline__ float operator()(int k, int n) const {
+        const int i = k_is_in ? k : n, o = k_is_in ? n : k;
+        if (i >= in_features || o >= out_features) return 0.0f;
+        const uint32_t w = __ldg(packed2 + (size_t)o * (in_features >> 4) + (i >> 4));
+        const float t = (float)((int)((w >> (2 * (i & 15))) & 3u) - 1);
+        return scale ? __fmul_rn(__ldg(scale + o), t) : t;
+    }
+};
+
 template <class OpA, class OpB, bool A_KFAST, bool B_KFAST>
 __global__ void __launch_bounds__(256) simt_gemm_kernel(OpA A, OpB B, float* __restrict__ C, int M,
                                                         int N, int K, int ldc) {
@@ -155,6 +170,22 @@ cudaError_t launch_simt_counter_backward_input(const uint8_t* state, const float
     OpTernary B{state, nullptr, in_features, out_features, 2 * C - 1, false};
     return run<OpGradScaled, OpTernary, true, false>(A, B, grad_x, batch, in_features, out_features,
                                                      in_features, stream);
+}
+
+cudaError_t launch_simt_ternary_forward(const float* x, const uint32_t* packed2, const float* scale, float* y,
+                                        int batch, int in_features, int out_features, cudaStream_t stream) {
+    OpF32 A{x, batch, in_features, in_features, false};
+    OpTernaryP2 B{packed2, scale, in_features, out_features, true};
+    return run<OpF32, OpTernaryP2, true, true>(A, B, y, batch, out_features, in_features, out_features, stream);
+}
+
+cudaError_t launch_simt_ternary_backward_input(const uint32_t* packed2, const float* scale, const float* grad_out,
+                                               float* grad_x, int batch, int in_features, int out_features,
+                                               cudaStream_t stream) {
+    OpGradScaled A{grad_out, scale, batch, out_features};
+    OpTernaryP2 B{packed2, nullptr, in_features, out_features, false};
+    return run<OpGradScaled, OpTernaryP2, true, false>(A, B, grad_x, batch, in_features, out_features, in_features,
+                                                       stream);
 }
 
 cudaError_t launch_simt_grad_w(const float* grad_out, const float* x, float* grad_w, int batch,

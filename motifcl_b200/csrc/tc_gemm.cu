@@ -407,6 +407,37 @@ __global__ void __launch_bounds__(256) expand_ternary_kernel(const uint8_t* __re
     }
 }
 
+// Same expansion from the 2-bit packed weights (field = t + 1, 16 per word): what ranks that do
+// not own a layer's counter state use after the all-gather of packed weights.
+__global__ void __launch_bounds__(256) expand_ternary_p2_kernel(const uint32_t* __restrict__ packed2, int O, int I,
+                                                                __nv_bfloat16* __restrict__ T, int ld_i,
+                                                                __nv_bfloat16* __restrict__ Tt, int ld_o) {
+    __shared__ __nv_bfloat16 tile[64][66];
+    const int o0 = blockIdx.y * 64, i0 = blockIdx.x * 64;
+    const int wpr = I >> 4;
+    // 64 rows x 4 words per tile; thread handles one word (16 weights)
+    {
+        const int oo = threadIdx.x >> 2, wq = threadIdx.x & 3;
+        const int o = o0 + oo, wi = (i0 >> 4) + wq;
+        if (o < O && wi < wpr) {
+            const uint32_t word = __ldg(packed2 + (size_t)o * wpr + wi);
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                const __nv_bfloat16 t = __float2bfloat16_rn((float)((int)((word >> (2 * k)) & 3u) - 1));
+                tile[oo][wq * 16 + k] = t;
+                if (T != nullptr) T[(size_t)o * ld_i + wi * 16 + k] = t;
+            }
+        }
+    }
+    if (Tt == nullptr) return;
+    __syncthreads();
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+    for (int ii = ty; ii < 64; ii += 4) {
+        const int i = i0 + ii, o = o0 + tx;
+        if (i < I && o < O) Tt[(size_t)i * ld_o + o] = tile[tx][ii];
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -507,7 +538,7 @@ cudaError_t launch_tc_gemm(const void* a_planes, int a_nplanes, int lda, size_t 
     p.C = splits > 1 ? splitk_ws : c;
     p.ldc = splits > 1 ? N : ldc;
     const size_t smem = (size_t)stages * stage_bytes + 1024;
-    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(tc_gemm_kernel), 2, max_smem);
+    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(tc_gemm_kernel), 4, max_smem);
     if (e != cudaSuccess) return e;
     dim3 grid((N + bn - 1) / bn, (M + BM - 1) / BM, splits);
     tc_gemm_kernel<<<grid, 128, smem, stream>>>(ma, mb, p);
@@ -546,6 +577,14 @@ cudaError_t launch_expand_ternary(const uint8_t* state, int C, int O, int I, voi
     dim3 grid((I + 63) / 64, (O + 63) / 64);
     expand_ternary_kernel<<<grid, 256, 0, stream>>>(state, C, O, I, static_cast<__nv_bfloat16*>(T), ld_i,
                                                     static_cast<__nv_bfloat16*>(Tt), ld_o);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_expand_ternary_p2(const uint32_t* packed2, int O, int I, void* T, int ld_i, void* Tt, int ld_o,
+                                     cudaStream_t stream) {
+    dim3 grid((I + 63) / 64, (O + 63) / 64);
+    expand_ternary_p2_kernel<<<grid, 256, 0, stream>>>(packed2, O, I, static_cast<__nv_bfloat16*>(T), ld_i,
+                                                       static_cast<__nv_bfloat16*>(Tt), ld_o);
     return cudaGetLastError();
 }
 

@@ -147,6 +147,12 @@ class Context:
             _ptr(grad_w), _ptr(packed2_out), C_, in_features, out_features, batch, update_rows, row_offset,
             lr, lr_scale, rms_beta, rms_eps, seed & 0xFFFFFFFF))
 
+    def ternary_linear_products(self, x, grad_out, packed2, scale, y, grad_x, grad_w, in_features,
+                                out_features, batch):
+        self._check(self._lib.mcl_cuda_ternary_linear_products(
+            self._ctx, _ptr(x), _ptr(grad_out), _ptr(packed2), _ptr(scale), _ptr(y), _ptr(grad_x), _ptr(grad_w),
+            in_features, out_features, batch))
+
     def matmul_f32(self, a, b, c, M, K, N, trans_a=False, trans_b=False):
         self._check(self._lib.mcl_cuda_matmul_f32(self._ctx, _ptr(a), _ptr(b), _ptr(c), M, K, N,
                                                   int(trans_a), int(trans_b)))

@@ -333,6 +333,7 @@ counter_update_dense_kernel(const UpdParams p) {
 //   * the right shifts of the integer hash are issued as mul.hi (FMA pipe) because the ALU
 //     pipe is the busiest one in this kernel.
 constexpr int kMaxRowsU16 = 64;
+constexpr int kTail16 = 256;          // tail-table row of the fast variant: rounded counter in [-128, 127]
 constexpr int kPairs = kUpdThreads / 64;
 
 __device__ __forceinline__ int swz4(int f) {          // float4 index -> swizzled float4 index
@@ -353,8 +354,8 @@ __host__ __device__ inline U16Layout u16_layout(int I, int R, bool with_q) {
     const int row_bytes = (I >> 2) * 3;
     L.sb = (row_bytes + 15) & ~15;
     size_t o = sizeof(DecodeLut);
-    L.off_tailc = (int)o; o += (4 * kTailRow + 15) & ~15;
-    L.off_tailf = (int)o; o += (4 * kTailRow + 15) & ~15;
+    L.off_tailc = (int)o; o += 4 * kTail16;
+    L.off_tailf = (int)o; o += 4 * kTail16;
     L.off_rowc = (int)o; o += sizeof(RowConst) * R;
     L.off_part = (int)o; o += sizeof(float) * 64 * kPairs;
     L.off_rowtab = (int)o; o += sizeof(RowEntry) * 64 * (size_t)R;
@@ -397,14 +398,13 @@ counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const ui
     const int lv = 2 * p.C - 1;
     const float Cf = (float)p.C;
     const float neg_lr = -p.lr;
-    const bool check_t = 4 * lv < 64;
     const uint32_t seed = p.seed + (p.seed_offset ? __ldg(p.seed_offset) : 0u);
     const bool aligned16 = p.state_align >= 16;
 
     build_decode_lut(lut, p.C, tid, kUpdThreads);
-    for (int e = tid; e < 4 * kTailRow; e += kUpdThreads) {     // kernels/compact_counter.cl:129-136
-        const int t = e / kTailRow - 1;
-        const float ccv = (float)(e % kTailRow - kTailK);
+    for (int e = tid; e < 4 * kTail16; e += kUpdThreads) {     // kernels/compact_counter.cl:129-136
+        const int t = e / kTail16 - 1;
+        const float ccv = (float)(e % kTail16 - 128);
         const float carry = truncf(__fdiv_rn(ccv, Cf));
         float rem = __fsub_rn(ccv, __fmul_rn(carry, Cf));
         const int nt = t + (int)carry;
@@ -518,9 +518,11 @@ counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const ui
             {   // per-row table of rebased counters, one entry per old code value
                 const float2 tc = lut->e[vlane];
                 RowEntry re;
-                re.creb = __fmul_rn(tc.y, rowc[r].k_reb);
                 const int ti = (int)tc.x + 1;
-                re.tail_base = (ti >= 0 && ti < 4) ? ti * kTailRow + kTailK : -(1 << 20);
+                // a code whose ternary digit the tail table lacks gets an infinite counter, which
+                // sends its unit down the formula path
+                re.creb = (ti >= 0 && ti < 4) ? __fmul_rn(tc.y, rowc[r].k_reb) : __int_as_float(0x7f800000);
+                re.tail_base = (ti >= 0 && ti < 4) ? ti * kTail16 + 128 : 128;
                 rowtab[r * 64 + vlane] = re;
             }
         }
@@ -541,6 +543,7 @@ counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const ui
             const int jsw = (j >> 1) & 3;
             const uint32_t e_unit = (uint32_t)(p.row_offset + row0 + r) * (uint32_t)I + (uint32_t)(16 * j);
             uint32_t nwd[4], fields = 0;
+            float vmax = 0.0f;          // largest |counter + tick| of the unit
 #pragma unroll
             for (int gg = 0; gg < 4; ++gg) {
                 const float4 gw = g4[gg ^ jsw];
@@ -551,10 +554,10 @@ counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const ui
                 uint32_t nw = 0;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const uint32_t code_old = (w >> (6 * k)) & 63u;
-                    const RowEntry re = rt[code_old];
+                    const RowEntry re = rt[(w >> (6 * k)) & 63u];
                     const float tick = __fmul_rn(__fmul_rn(neg_lr, __fdiv_rn(gwv[k], rc.dn)), rc.k_tick);
                     const float val = __fadd_rn(re.creb, tick);
+                    vmax = fmaxf(vmax, fabsf(val));
                     uint32_t x = (e0x ^ (uint32_t)k) * 0x7feb352du;
                     x ^= shr_mulhi(x, pow17);            // x >> 15
                     x *= 0x846ca68bu;
@@ -564,24 +567,35 @@ counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const ui
                     x ^= shr_mulhi(x, pow17);
                     x *= 0x846ca68bu;
                     const uint32_t h = (x ^ shr_mulhi(x, pow16)) & 0x00ffffffu;
-                    uint32_t code, fld;
-                    if (fabsf(val) < (float)(kTailK - 1) && (!check_t || re.tail_base >= 0)) {
-                        const float f = floorf(val);
-                        const float rnd = __fmul_rn((float)h, 1.0f / 16777216.0f);
-                        const float up = (rnd < __fsub_rn(val, f)) ? 1.0f : 0.0f;
-                        const int idx = re.tail_base + __float2int_rn(__fadd_rn(f, up));
-                        code = tail_code[idx];
-                        fld = tail_field[idx];
-                    } else {
-                        const float2 tc = lut->e[code_old];
-                        code = counter_tick(gwv[k], tc.x, tc.y, e0 + (uint32_t)k, seed, neg_lr, rc.dn, rc.k_tick,
-                                            rc.k_reb, Cf, p.C, lv, &fld) & 0x3Fu;
-                        fld &= 3u;
-                    }
-                    nw += code << (6 * k);
-                    fields += fld << (2 * (4 * gg + k));
+                    const float f = floorf(val);
+                    const float rnd = __fmul_rn((float)h, 1.0f / 16777216.0f);
+                    const float up = (rnd < __fsub_rn(val, f)) ? 1.0f : 0.0f;
+                    int iccv;           // saturating conversion keeps the table index in range whatever val is
+                    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(iccv) : "f"(__fadd_rn(f, up)));
+                    const int idx = re.tail_base + iccv;
+                    nw += (uint32_t)tail_code[idx] << (6 * k);
+                    fields += (uint32_t)tail_field[idx] << (2 * (4 * gg + k));
                 }
                 nwd[gg] = nw;
+            }
+            if (!(vmax < 126.0f)) {
+                // rare: a rounded counter beyond the table (or a code outside it): redo the unit
+                // with the reference formulas
+                fields = 0;
+                for (int gg = 0; gg < 4; ++gg) {
+                    const float4 gw = g4[gg ^ jsw];
+                    const float gwv[4] = {gw.x, gw.y, gw.z, gw.w};
+                    uint32_t nw = 0;
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 tc = lut->e[(gwd[gg] >> (6 * k)) & 63u];
+                        uint32_t fld;
+                        const uint32_t code = counter_tick(gwv[k], tc.x, tc.y, e_unit + (uint32_t)(4 * gg + k), seed,
+                                                           neg_lr, rc.dn, rc.k_tick, rc.k_reb, Cf, p.C, lv, &fld);
+                        nw += (code & 0x3Fu) << (6 * k);
+                        fields += (fld & 3u) << (2 * (4 * gg + k));
+                    }
+                    nwd[gg] = nw;
+                }
             }
             uint32_t* so = reinterpret_cast<uint32_t*>(so_s + (size_t)r * L.sb) + 3 * j;
             so[0] = nwd[0] | (nwd[1] << 24);

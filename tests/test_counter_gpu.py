@@ -84,10 +84,12 @@ def test_dense_update_row_shard_matches_full(ctx, orc):
     (9, 14336, 11, 3e-3, 0.0),     # the longest row of the 8B-scale configuration
     (6, 5632, 11, 1.0, 0.01),
     (70, 260, 5, 2.0, 0.1),        # in % 16 != 0: byte path, no 2-bit output
+    (40, 64, 3, 1.0, 0.05),        # C = 3 with arbitrary bytes: codes whose digit is far outside {-1,0,1}
+    (300, 288, 11, 50.0, 0.0),     # huge learning rate: rounded counters far beyond the tick table
 ])
 def test_dense_update_shapes_bit_exact(ctx, orc, O, I, C, lr, lr_scale):
     rng = np.random.default_rng(O * 100003 + I)
-    ncodes = 64 if C == 11 else 3 * (2 * C - 1)
+    ncodes = 64 if (C == 11 or (O, I) == (40, 64)) else 3 * (2 * C - 1)
     state = codec.pack_codes(rng.integers(0, ncodes, size=(O, I)).astype(np.uint8)).reshape(-1)
     c = dict(I=I, O=O, C=C, state=state, scale=rng.uniform(0.02, 0.2, O).astype(np.float32),
              v=rng.uniform(1e-4, 1e-2, O).astype(np.float32), lr=lr, lr_scale=lr_scale, beta=0.9,

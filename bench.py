@@ -346,22 +346,10 @@ def main():
     alg = algorithmic(wl)
     hbm_peak, tf_peak, peak_kind = measured_peaks()
 
-    def upd_only():
-        for l in stack.linears:
-            O, I = l.shape.out_features, l.shape.in_features
-            ctx.counter_update_dense(l.state, l.scale, l.v, l.grad_w, l.packed2, 11, I, O, 0,
-                                     3e-3, 0.0, 0.9, 1e-3, 777)
-    ms_upd, n_upd = timed(upd_only, args.steps, 3)
-
-    def gemm_only():
-        for l, x, dy in zip(stack.linears, xs, dys):
-            O, I = l.shape.out_features, l.shape.in_features
-            ctx.counter_forward(x, l.state, l.scale, l.y, T, I, O, 11)
-            ctx.counter_backward_input(l.state, l.scale, dy, l.dx, T, I, O, 11)
-            ctx.matmul_f32(dy, x, l.grad_w, O, T, I, trans_a=True)
-    ms_gemm, n_gemm = timed(gemm_only, args.steps, 3)
+    ms_upd, n_upd = timed(stack.update_only, args.steps, 3)
+    ms_gemm, n_gemm = timed(lambda: stack.products_only(xs, dys), args.steps, 3)
     gemm_tf = alg["gemm_flop"] / (ms_gemm * 1e-3) / 1e12
-    upd_gbs = alg["update_bytes"] / (ms_upd * 1e-3) / 1e9
+    upd_gbs = alg["update_bytes"] / world / (ms_upd * 1e-3) / 1e9      # each rank updates its row shard
     roofline = {"kernel": "counter-linear contractions (Y, dX, dW) of all linears", "bound": "tensor",
                 "achieved": gemm_tf, "peak": tf_peak, "unit": "TFLOP/s", "frac": gemm_tf / tf_peak,
                 "peak_kind": f"{peak_kind} bf16 sustained", "traffic": None,

@@ -7,11 +7,10 @@ time; at backward time dX from the PRE-update state, then the update.  Here the 
 the dense form (dW = dY^T X materialised once, then one fused kernel) because that is the
 form whose gradient can be summed across data-parallel ranks.
 
-Data parallelism (not present in the reference; defined here): every rank holds the packed
-state, scale and v of its contiguous block of weight rows plus replicated 2-bit weights and
-scales.  Per linear: local dW = dY^T X -> reduce-scatter (sum) along rows -> fused update of
-the local row shard with row_offset (so the random stream matches the unsharded layer) ->
-all-gather of the shard's 2-bit words and scales.
+Single GPU: one mcl_cuda_counter_linear_step per linear, spread over parallel lanes and
+recorded into one batch.  Data parallel (see dp.py): the three products come from the
+replicated 2-bit weights, the update runs on the local row shard after a reduce-scatter, and
+the new 2-bit words and scales are all-gathered.
 """
 from __future__ import annotations
 
@@ -20,6 +19,8 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
+from . import dp
+from .dp import shard_rows  # noqa: F401  (re-exported)
 from .runtime import Context
 from .synth import LinearShape
 
@@ -33,17 +34,8 @@ class Hyper:
     rms_eps: float = 1e-3
 
 
-def shard_rows(out_features: int, rank: int, world: int) -> tuple[int, int]:
-    """(row_offset, rows) of `rank`'s contiguous block; the first (out % world) ranks get one
-    extra row so any out_features shards."""
-    base, extra = divmod(out_features, world)
-    rows = base + (1 if rank < extra else 0)
-    off = rank * base + min(rank, extra)
-    return off, rows
-
-
 class CounterLinearState:
-    """Device tensors of one counter linear on one rank."""
+    """Device tensors of one counter linear on one rank (whole layer when world == 1)."""
 
     def __init__(self, shape: LinearShape, state: np.ndarray, scale: np.ndarray, v: np.ndarray,
                  device, rank: int = 0, world: int = 1):
@@ -51,7 +43,7 @@ class CounterLinearState:
         O, I = shape.out_features, shape.in_features
         self.row_bytes = I // 4 * 3
         self.off, self.rows = shard_rows(O, rank, world)
-        # replicated: full packed state (forward/backward read it), full scale
+        self.world = world
         self.state = torch.from_numpy(np.ascontiguousarray(state).reshape(-1)).to(device)
         self.scale = torch.from_numpy(np.ascontiguousarray(scale)).to(device)
         self.v = torch.from_numpy(np.ascontiguousarray(v)).to(device)
@@ -59,6 +51,7 @@ class CounterLinearState:
         self.grad_w = torch.empty(O, I, dtype=torch.float32, device=device)
         self.y = None
         self.dx = None
+        self.sharded = None     # dp.ShardedLinear once the stack knows its process group
 
 
 class CounterStack:
@@ -74,10 +67,18 @@ class CounterStack:
         self.rank = 0 if group is None else torch.distributed.get_rank(group)
         dev = linears[0].state.device
         for l in linears:
-            l.y = torch.empty(tokens, l.shape.out_features, dtype=torch.float32, device=dev)
-            l.dx = torch.empty(tokens, l.shape.in_features, dtype=torch.float32, device=dev)
+            O, I = l.shape.out_features, l.shape.in_features
+            l.y = torch.empty(tokens, O, dtype=torch.float32, device=dev)
+            l.dx = torch.empty(tokens, I, dtype=torch.float32, device=dev)
             if self.world > 1:
-                l.gw_shard = torch.empty(max(l.rows, 1), l.shape.in_features, dtype=torch.float32, device=dev)
+                # the 2-bit weights of the initial state are replicated; state and v keep only the shard
+                ctx.counter_pack2(l.state, l.packed2, I, O, hyper.C)
+                ctx.finish()
+                l.sharded = dp.ShardedLinear(O, I, l.state.cpu(), l.scale.cpu(), l.v.cpu(), l.packed2.cpu(),
+                                             self.rank, self.world, dev)
+                l.sharded.grad_w = l.grad_w
+                l.state, l.v, l.scale, l.packed2 = (l.sharded.state, l.sharded.v, l.sharded.scale,
+                                                    l.sharded.packed2)
         self.step_index = 0
         self._batch = None
         self._batch_key = None
@@ -86,15 +87,20 @@ class CounterStack:
     def step(self, xs, dys, base_seed: int = 12345, recorded: bool = False):
         """xs[i]: [tokens, in_i], dys[i]: [tokens, out_i] device tensors.  One full step.
 
-        recorded=True (single GPU): the first call runs eagerly (sizing the workspace), the
-        second records the same calls into one batch, later ones replay it -- one graph launch
-        per step, as the reference submits one command buffer per step.  The per-step seed then
+        recorded=True (single GPU): the first call runs eagerly (sizing the workspace) and
+        records the same calls into one batch; later calls replay it -- one graph launch per
+        step, as the reference submits one command buffer per step.  The per-step seed then
         comes from a device word that is bumped after every replay."""
-        if recorded and self.world == 1:
+        if self.world > 1:
+            self._step_dp(xs, dys, (base_seed + self.step_index) & 0xFFFFFFFF)
+            self.step_index += 1
+            return
+        if recorded:
             return self._step_recorded(xs, dys, base_seed)
         self._step_eager(xs, dys, (base_seed + self.step_index) & 0xFFFFFFFF)
         self.step_index += 1
 
+    # -- single GPU --------------------------------------------------------------------------
     def _step_recorded(self, xs, dys, base_seed):
         key = (tuple(t.data_ptr() for t in xs), tuple(t.data_ptr() for t in dys), base_seed)
         if self._batch is None or self._batch_key != key:
@@ -123,40 +129,69 @@ class CounterStack:
         self._step_word.add_(1)
         self.step_index += 1
 
+    def _fork(self):
+        for lane in self.lanes[1:]:
+            self.ctx.lane_fork(lane)
+
+    def _join(self):
+        for lane in self.lanes[1:]:
+            self.ctx.lane_join(lane)
+
     def _step_eager(self, xs, dys, seed):
-        ctx, h = self.ctx, self.h
-        nl = len(self.lanes) if self.world == 1 else 1      # collectives stay on the main stream
-        for lane in self.lanes[1:nl]:
-            ctx.lane_fork(lane)
+        h, nl = self.h, len(self.lanes)
+        self._fork()
         for i, (l, x, dy) in enumerate(zip(self.linears, xs, dys)):
             O, I = l.shape.out_features, l.shape.in_features
-            upd = O if self.world == 1 else 0     # data parallel: reduce grad_w first, then update the shard
             self.lanes[i % nl].counter_linear_step(x, dy, l.state, l.scale, l.v, l.y, l.dx, l.grad_w, l.packed2,
-                                                   h.C, I, O, self.tokens, upd, 0, h.lr, h.lr_scale, h.rms_beta,
+                                                   h.C, I, O, self.tokens, O, 0, h.lr, h.lr_scale, h.rms_beta,
                                                    h.rms_eps, seed)
-            if self.world > 1:
-                self._dp_update(l, seed)
-        for lane in self.lanes[1:nl]:
-            ctx.lane_join(lane)
+        self._join()
 
-    def _dp_update(self, l: CounterLinearState, seed: int):
-        import torch.distributed as dist
-        ctx, h = self.ctx, self.h
-        O, I = l.shape.out_features, l.shape.in_features
-        if O % self.world == 0:
-            dist.reduce_scatter_tensor(l.gw_shard, l.grad_w, op=dist.ReduceOp.SUM, group=self.group)
-        else:   # ragged shards: all-reduce then slice (rare; none of the benchmark shapes)
-            dist.all_reduce(l.grad_w, op=dist.ReduceOp.SUM, group=self.group)
-            l.gw_shard.copy_(l.grad_w[l.off:l.off + l.rows])
-        st = l.state[l.off * l.row_bytes:(l.off + l.rows) * l.row_bytes]
-        p2 = l.packed2[l.off:l.off + l.rows]
-        ctx.counter_update_dense(st, l.scale[l.off:l.off + l.rows], l.v[l.off:l.off + l.rows],
-                                 l.gw_shard, p2, h.C, I, l.rows, l.off, h.lr, h.lr_scale, h.rms_beta,
-                                 h.rms_eps, seed)
-        if O % self.world == 0:
-            dist.all_gather_into_tensor(l.packed2, p2.contiguous(), group=self.group)
-            dist.all_gather_into_tensor(l.scale, l.scale[l.off:l.off + l.rows].contiguous(), group=self.group)
-            dist.all_gather_into_tensor(l.state.view(O, l.row_bytes), st.view(l.rows, l.row_bytes).contiguous(),
-                                        group=self.group)
-        else:
-            raise NotImplementedError("all-gather of ragged shards")
+    # -- data parallel -------------------------------------------------------------------------
+    def _step_dp(self, xs, dys, seed):
+        h, nl = self.h, len(self.lanes)
+        # products of all linears from the replicated 2-bit weights, lanes side by side
+        self._fork()
+        for i, (l, x, dy) in enumerate(zip(self.linears, xs, dys)):
+            O, I = l.shape.out_features, l.shape.in_features
+            self.lanes[i % nl].ternary_linear_products(x, dy, l.packed2, l.scale, l.y, l.dx, l.grad_w, I, O,
+                                                       self.tokens)
+        self._join()
+        ctx = self.ctx
+
+        def update_fn(st, sc, vv, gw, p2, rows, off, sd, I=None):
+            ctx.counter_update_dense(st, sc, vv, gw, p2, h.C, gw.shape[1], rows, off, h.lr, h.lr_scale,
+                                     h.rms_beta, h.rms_eps, sd)
+
+        for l in self.linears:
+            dp.exchange_and_update(l.sharded, update_fn, seed, self.group)
+
+    # -- parts of a step, for per-kernel timing ---------------------------------------------------
+    def products_only(self, xs, dys):
+        """Y, dX and dW of every linear, no update (and no collectives)."""
+        h, nl = self.h, len(self.lanes)
+        self._fork()
+        for i, (l, x, dy) in enumerate(zip(self.linears, xs, dys)):
+            O, I = l.shape.out_features, l.shape.in_features
+            if self.world > 1:
+                self.lanes[i % nl].ternary_linear_products(x, dy, l.packed2, l.scale, l.y, l.dx, l.grad_w, I, O,
+                                                           self.tokens)
+            else:
+                self.lanes[i % nl].counter_linear_step(x, dy, l.state, l.scale, l.v, l.y, l.dx, l.grad_w, None,
+                                                       h.C, I, O, self.tokens, 0, 0, h.lr, h.lr_scale, h.rms_beta,
+                                                       h.rms_eps, 0)
+        self._join()
+
+    def update_only(self, seed: int = 777):
+        """The fused update of every linear's local rows from the gradient already in place."""
+        h = self.h
+        for l in self.linears:
+            I = l.shape.in_features
+            if self.world > 1:
+                sh = l.sharded
+                sl = slice(sh.off, sh.off + sh.rows)
+                self.ctx.counter_update_dense(sh.state, sh.scale[sl], sh.v, sh.gw_shard[:sh.rows], sh.packed2[sl], h.C,
+                                              I, sh.rows, sh.off, h.lr, h.lr_scale, h.rms_beta, h.rms_eps, seed)
+            else:
+                self.ctx.counter_update_dense(l.state, l.scale, l.v, l.grad_w, l.packed2, h.C, I,
+                                              l.shape.out_features, 0, h.lr, h.lr_scale, h.rms_beta, h.rms_eps, seed)

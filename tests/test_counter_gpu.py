@@ -426,3 +426,34 @@ def test_recorded_batch_replays_the_step_with_a_per_step_seed(ctx, orc):
     ctx.finish()
     o = orc.update_dense(c["state"], c["scale"], c["v"], lin.grad_w.cpu().numpy(), 11, I, O, 0, 0.05, 0.0, 0.9, 1e-3, 100)
     assert np.array_equal(lin.state.cpu().numpy(), o[0])
+
+
+@pytest.mark.parametrize("mode", ["tensor", "exact"])
+def test_products_from_packed2_equal_products_from_state(ctx, orc, mode):
+    """What a data-parallel rank runs for layers whose state it does not own: Y, dX, dW from the
+    2-bit words must equal the same products computed from the 6-bit state (bit for bit: the
+    ternary digits are identical and so is every kernel that consumes them)."""
+    c = CASES["cfg1"]
+    N, I, O, C = c["N"], c["I"], c["O"], c["C"]
+    st, sc, x, dy = _t(c["state"]), _t(c["scale"]), _t(c["x"]), _t(c["dy"])
+    p2 = torch.empty(O, I // 16, dtype=torch.int32, device=DEV)
+    ctx.counter_pack2(st, p2, I, O, C)
+    outs = []
+    ctx.set_gemm_mode(mode)
+    try:
+        for src in ("state", "packed2"):
+            y = torch.empty(N, O, dtype=torch.float32, device=DEV)
+            gx = torch.empty(N, I, dtype=torch.float32, device=DEV)
+            gw = torch.empty(O, I, dtype=torch.float32, device=DEV)
+            if src == "state":
+                ctx.counter_linear_step(x, dy, st.clone(), sc.clone(), _t(c["v"]), y, gx, gw, None, C, I, O, N, 0, 0,
+                                        *_hy(c))
+            else:
+                ctx.ternary_linear_products(x, dy, p2, sc, y, gx, gw, I, O, N)
+            ctx.finish()
+            outs.append((y.cpu().numpy(), gx.cpu().numpy(), gw.cpu().numpy()))
+    finally:
+        ctx.set_gemm_mode("auto")
+    for a, b in zip(*outs):
+        assert np.array_equal(a, b)
+    assert rel_l2(outs[1][0], orc.forward(c["x"], c["state"], c["scale"], C, O)) <= 1e-5

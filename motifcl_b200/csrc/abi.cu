@@ -217,7 +217,7 @@ int tc_product(mcl_cuda_ctx* ctx, const void* a, int a_planes, int lda, size_t a
     int launches = 0;
     cudaError_t e = mcl::launch_tc_gemm(a, a_planes, lda, a_stride, b, b_planes, ldb, b_stride, c, ldc, M, N, K,
                                         pa, pb, nterms, col_scale, splitk_ws, splits, ctx->err_word,
-                                        ctx->max_smem, ctx->stream, &launches);
+                                        ctx->max_smem, ctx->sm_count, ctx->stream, &launches);
     ctx->launches += launches;
     if (e != cudaSuccess) return fail_cuda(ctx, "tensor-core contraction", e);
     return MCL_CUDA_OK;

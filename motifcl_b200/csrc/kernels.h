@@ -48,7 +48,7 @@ cudaError_t launch_tc_gemm(const void* a_planes, int a_nplanes, int lda, size_t 
                            const void* b_planes, int b_nplanes, int ldb, size_t b_plane_stride, float* c,
                            int ldc, int M, int N, int K, const int* pa, const int* pb, int nterms,
                            const float* col_scale, float* splitk_ws, int splits, int* err_word,
-                           size_t max_smem, cudaStream_t stream, int* launches);
+                           size_t max_smem, int sm_count, cudaStream_t stream, int* launches);
 // fp32 [R,Cc] -> bf16 term planes [t][R][ld_n] of (src * col_scale) and/or transposed planes
 // [t][Cc][ld_t] of src
 cudaError_t launch_split_planes(const float* src, int R, int Cc, const float* col_scale, void* planes, int ld_n,

@@ -129,11 +129,23 @@ __device__ __forceinline__ uint32_t idesc_bf16(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-__global__ void __launch_bounds__(128) tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
-                                                      const __grid_constant__ CUtensorMap tmB,
-                                                      const TcParams p) {
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Persistent CTA of 192 threads; work items (output tile x split-K slice) are dealt round-robin.
+//   warp 0        TMA producer (one elected lane)
+//   warp 1        MMA issuer (one elected lane); also allocates / frees TMEM
+//   warps 2..5    epilogue: TMEM lanes 32*(warp%4) .. +31
+// Two accumulators live in TMEM (columns [0,BN) and [ACC,ACC+BN)), so the epilogue of one item
+// overlaps the main loop of the next.
+constexpr int kTcThreads = 192;
+
+__global__ void __launch_bounds__(kTcThreads) tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                             const __grid_constant__ CUtensorMap tmB,
+                                                             const TcParams p) {
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 1];
+    __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 4];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -144,23 +156,24 @@ __global__ void __launch_bounds__(128) tc_gemm_kernel(const __grid_constant__ CU
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
-    const uint32_t accum_bar = bar0 + 8u * (2 * kMaxStages);
-    uint32_t tmem_cols = 32;
-    while ((int)tmem_cols < BN) tmem_cols <<= 1;
+    auto acc_full = [&](int a) { return bar0 + 8u * (2 * kMaxStages + a); };
+    auto acc_empty = [&](int a) { return bar0 + 8u * (2 * kMaxStages + 2 + a); };
+    uint32_t acc_cols = 32;                       // columns of one accumulator (power of two >= BN)
+    while ((int)acc_cols < BN) acc_cols <<= 1;
+    const uint32_t tmem_cols = 2 * acc_cols;      // <= 512
 
-    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, split = blockIdx.z;
+    const int tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + BM - 1) / BM;
     const int ktiles = (p.K + BK - 1) / BK;
-    const int kt0 = split * p.ktiles_per_split;
-    const int my_kt = min(p.ktiles_per_split, ktiles - kt0);
-    const int total = p.nterms * my_kt;
+    const int n_items = tiles_m * tiles_n * p.splits;
+    // item -> (m tile fastest, then n tile, then split): CTAs running together share a B tile
 
     if (threadIdx.x == 0) {
         abort_flag = (*reinterpret_cast<volatile int*>(p.err) != 0);   // an earlier CTA gave up: do not wait at all
         for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        mbar_init(accum_bar, 1);
+        for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 128); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 2) {
+    if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(&tmem_slot)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -170,73 +183,102 @@ __global__ void __launch_bounds__(128) tc_gemm_kernel(const __grid_constant__ CU
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
 
-    if (warp == 0 && lane == 0) {
-        // ---- TMA producer ------------------------------------------------------------------
-        for (int it = 0; it < total; ++it) {
-            const int s = it % S;
-            const uint32_t ph = (uint32_t)(it / S) & 1u;
-            if (!mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 1); break; }
-            const int term = it / my_kt, kt = kt0 + it % my_kt;
-            const uint32_t a_dst = tiles + (uint32_t)s * stage_bytes;
-            mbar_expect_tx(full_bar(s), stage_bytes);
-            tma_load_3d(a_dst, &tmA, full_bar(s), kt * BK, m0, p.pa[term]);
-            tma_load_3d(a_dst + kATileBytes, &tmB, full_bar(s), kt * BK, n0, p.pb[term]);
-        }
-    } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer --------------------------------------------------------------------
-        const uint32_t idesc = idesc_bf16(BM, BN);
-        bool ok = true;
-        for (int it = 0; it < total; ++it) {
-            const int s = it % S;
-            const uint32_t ph = (uint32_t)(it / S) & 1u;
-            if (!mbar_wait(full_bar(s), ph, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 2); ok = false; break; }
-            tc_fence_after();
-            const uint32_t a_addr = tiles + (uint32_t)s * stage_bytes;
-            const uint64_t da = smem_desc_k_sw128(a_addr), db = smem_desc_k_sw128(a_addr + kATileBytes);
-#pragma unroll
-            for (int kk = 0; kk < BK / 16; ++kk)   // 16 bf16 = 32 bytes = +2 in the address field
-                umma_bf16(tmem_base, da + 2u * kk, db + 2u * kk, idesc, (it | kk) != 0 ? 1u : 0u);
-            umma_commit(empty_bar(s));
-        }
-        if (ok) umma_commit(accum_bar);
-    }
-    __syncwarp();
-
-    // ---- epilogue: TMEM -> registers -> global ---------------------------------------------
-    bool have_acc = total > 0;
-    if (have_acc) {
-        if (!mbar_wait(accum_bar, 0, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 3); have_acc = false; }
-    }
-    have_acc = __all_sync(0xffffffffu, have_acc);
-    tc_fence_after();
-    const int row = m0 + warp * 32 + lane;
-    float* crow = p.C + ((size_t)split * p.M + row) * p.ldc;
-    const bool scale = (p.col_scale != nullptr) && p.splits == 1;
-    for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (n0 + c0 >= p.N) break;
-        uint32_t r[32];
-        if (have_acc) {
-            tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
-            tmem_ld_wait();
-        } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = 0u;
-        }
-        if (row < p.M) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-                const int col = n0 + c0 + j;
-                if (col >= p.N) break;
-                float4 o = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                       __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                if (scale) {
-                    const float4 sc = __ldg(reinterpret_cast<const float4*>(p.col_scale + col));
-                    o.x *= sc.x; o.y *= sc.y; o.z *= sc.z; o.w *= sc.w;
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer --------------------------------------------------------------
+            uint32_t it = 0;       // slot counter across all items of this CTA
+            for (int item = blockIdx.x; item < n_items && !abort_flag; item += gridDim.x) {
+                const int mt = item % tiles_m, rest = item / tiles_m;
+                const int nt = rest % tiles_n, split = rest / tiles_n;
+                const int kt0 = split * p.ktiles_per_split;
+                const int my_kt = min(p.ktiles_per_split, ktiles - kt0);
+                for (int term = 0; term < p.nterms; ++term) {
+                    const int pa = p.pa[term], pb = p.pb[term];
+                    for (int kk = 0; kk < my_kt; ++kk, ++it) {
+                        const int s = (int)(it % (uint32_t)S);
+                        const uint32_t ph = (it / (uint32_t)S) & 1u;
+                        if (!mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 1); break; }
+                        const uint32_t a_dst = tiles + (uint32_t)s * stage_bytes;
+                        mbar_expect_tx(full_bar(s), stage_bytes);
+                        tma_load_3d(a_dst, &tmA, full_bar(s), (kt0 + kk) * BK, mt * BM, pa);
+                        tma_load_3d(a_dst + kATileBytes, &tmB, full_bar(s), (kt0 + kk) * BK, nt * BN, pb);
+                    }
+                    if (abort_flag) break;
                 }
-                *reinterpret_cast<float4*>(crow + col) = o;    // N % 4 == 0, ldc % 4 == 0
             }
         }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer ----------------------------------------------------------------
+            const uint32_t idesc = idesc_bf16(BM, BN);
+            uint32_t it = 0, n_local = 0;
+            for (int item = blockIdx.x; item < n_items && !abort_flag; item += gridDim.x, ++n_local) {
+                const int split = item / (tiles_m * tiles_n);
+                const int kt0 = split * p.ktiles_per_split;
+                const int my_kt = min(p.ktiles_per_split, ktiles - kt0);
+                const int total = p.nterms * my_kt;
+                const uint32_t acc = n_local & 1u, aph = (n_local >> 1) & 1u;
+                if (!mbar_wait(acc_empty(acc), aph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 4); break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * acc_cols;
+                for (int j = 0; j < total; ++j, ++it) {
+                    const int s = (int)(it % (uint32_t)S);
+                    const uint32_t ph = (it / (uint32_t)S) & 1u;
+                    if (!mbar_wait(full_bar(s), ph, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 2); break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = tiles + (uint32_t)s * stage_bytes;
+                    const uint64_t da = smem_desc_k_sw128(a_addr), db = smem_desc_k_sw128(a_addr + kATileBytes);
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk)   // 16 bf16 = 32 bytes = +2 in the address field
+                        umma_bf16(d_tmem, da + 2u * kk, db + 2u * kk, idesc, (j | kk) != 0 ? 1u : 0u);
+                    umma_commit(empty_bar(s));
+                }
+                if (abort_flag) break;
+                umma_commit(acc_full(acc));
+            }
+        }
+    } else {
+        // ---- epilogue warps: TMEM -> registers -> global ---------------------------------------
+        const int q = warp & 3;                        // TMEM lane quarter this warp may read
+        const bool scale = (p.col_scale != nullptr) && p.splits == 1;
+        uint32_t n_local = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_local) {
+            const int mt = item % tiles_m, rest = item / tiles_m;
+            const int nt = rest % tiles_n, split = rest / tiles_n;
+            const uint32_t acc = n_local & 1u, aph = (n_local >> 1) & 1u;
+            bool ok = !abort_flag;
+            if (ok && !mbar_wait(acc_full(acc), aph, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 3); ok = false; }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int n0 = nt * BN;
+            const int row = mt * BM + q * 32 + lane;
+            float* crow = p.C + ((size_t)split * p.M + row) * p.ldc;
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= p.N) break;
+                uint32_t r[32];
+                tmem_ld32(tmem_base + acc * acc_cols + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                tmem_ld_wait();
+                if (row < p.M) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const int col = n0 + c0 + j;
+                        if (col >= p.N) break;
+                        float4 o = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                               __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                        if (scale) {
+                            const float4 sc = __ldg(reinterpret_cast<const float4*>(p.col_scale + col));
+                            o.x *= sc.x; o.y *= sc.y; o.z *= sc.z; o.w *= sc.w;
+                        }
+                        *reinterpret_cast<float4*>(crow + col) = o;    // N % 4 == 0, ldc % 4 == 0
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(acc_empty(acc));               // 128 arrivals free the accumulator
+        }
     }
+    __syncwarp();
     if (abort_flag) {
         // gave up: let copies that are still in flight land before the shared memory is released
         const unsigned long long t0 = clock64();
@@ -244,7 +286,7 @@ __global__ void __launch_bounds__(128) tc_gemm_kernel(const __grid_constant__ CU
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 2) {
+    if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
 }
@@ -502,7 +544,7 @@ cudaError_t launch_tc_gemm(const void* a_planes, int a_nplanes, int lda, size_t 
                            const void* b_planes, int b_nplanes, int ldb, size_t b_plane_stride, float* c,
                            int ldc, int M, int N, int K, const int* pa, const int* pb,
                            int nterms, const float* col_scale, float* splitk_ws, int splits, int* err_word,
-                           size_t max_smem, cudaStream_t stream, int* launches) {
+                           size_t max_smem, int sm_count, cudaStream_t stream, int* launches) {
     if (nterms < 1 || nterms > 6 || (N & 3) || (ldc & 3) || (lda & 7) || (ldb & 7)) return cudaErrorInvalidValue;
     const int bn = tc_pick_bn(N);
     CUtensorMap ma, mb;
@@ -516,12 +558,14 @@ cudaError_t launch_tc_gemm(const void* a_planes, int a_nplanes, int lda, size_t 
     const int ktiles = (K + BK - 1) / BK;
     int stages = (int)((max_smem - 2048) / stage_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
-    const int want = nterms * ((ktiles + splits - 1) / splits);   // slots one CTA ever fills
-    if (want <= 32) {
-        // short main loops: leave room for two resident CTAs, so that the epilogue of one
-        // overlaps the main loop of the other
+    const int want = nterms * ((ktiles + splits - 1) / splits);   // slots one work item fills
+    // Two accumulators of one CTA take 2 * pow2(BN) TMEM columns of the SM's 512.  Narrow tiles
+    // (BN <= 128) with short main loops leave room for a second resident CTA, which doubles the
+    // loads in flight where the loop is latency-bound; then each CTA gets half the shared memory.
+    bool two_ctas = false;
+    if (bn <= 128 && want <= 32) {
         const int half = (int)((((max_smem - 4096) / 2) - 1024) / stage_bytes);
-        if (half >= 3 && half < stages) stages = half;
+        if (half >= 3) { two_ctas = true; if (half < stages) stages = half; }
     }
     if (stages > want) stages = want;
     if (stages < 2) stages = 2;
@@ -540,8 +584,10 @@ cudaError_t launch_tc_gemm(const void* a_planes, int a_nplanes, int lda, size_t 
     const size_t smem = (size_t)stages * stage_bytes + 1024;
     cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(tc_gemm_kernel), 4, max_smem);
     if (e != cudaSuccess) return e;
-    dim3 grid((N + bn - 1) / bn, (M + BM - 1) / BM, splits);
-    tc_gemm_kernel<<<grid, 128, smem, stream>>>(ma, mb, p);
+    const int n_items = ((N + bn - 1) / bn) * ((M + BM - 1) / BM) * splits;
+    int ctas = sm_count * (two_ctas ? 2 : 1);
+    if (ctas > n_items) ctas = n_items;
+    tc_gemm_kernel<<<ctas, kTcThreads, smem, stream>>>(ma, mb, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     ++*launches;

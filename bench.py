@@ -366,11 +366,31 @@ def main():
               torch.empty_like(l.v, device="cpu").pin_memory()) for l in stack.linears]
     out_bytes = sum(sum(t.numel() * t.element_size() for t in o) for o in out_h)
 
+    copy_stream = torch.cuda.Stream(device=local)
+    main_stream = torch.cuda.current_stream(local)
+    ready = [torch.cuda.Event() for _ in xs]
+    consumed = torch.cuda.Event()
+    consumed.record(main_stream)
+    e2e_seed = [0]
+
     def e2e_step():
-        for i in range(len(xs)):
-            xs[i].copy_(xs_h[i], non_blocking=True)
-            dys[i].copy_(dys_h[i], non_blocking=True)
-        stack.step(xs, dys, recorded=not args.eager)
+        # host->device copies run on their own stream, linear by linear; the step of linear i
+        # starts as soon as its X and dY have landed, so transfer and compute overlap
+        copy_stream.wait_event(consumed)          # the previous step has finished reading xs / dys
+        with torch.cuda.stream(copy_stream):
+            for i in range(len(xs)):
+                xs[i].copy_(xs_h[i], non_blocking=True)
+                dys[i].copy_(dys_h[i], non_blocking=True)
+                ready[i].record(copy_stream)
+        if world == 1:
+            for i in range(len(xs)):
+                main_stream.wait_event(ready[i])
+                stack.step_linear(i, xs[i], dys[i], 12345 + e2e_seed[0])
+        else:
+            main_stream.wait_event(ready[-1])
+            stack.step(xs, dys)
+        e2e_seed[0] += 1
+        consumed.record(main_stream)
         for l, o in zip(stack.linears, out_h):
             o[0].copy_(l.state, non_blocking=True)
             o[1].copy_(l.packed2, non_blocking=True)

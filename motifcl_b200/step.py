@@ -166,6 +166,14 @@ class CounterStack:
         for l in self.linears:
             dp.exchange_and_update(l.sharded, update_fn, seed, self.group)
 
+    def step_linear(self, i: int, x, dy, seed: int):
+        """The step of linear `i` alone on the main context (single GPU), for callers that
+        pipeline host-to-device copies against compute linear by linear."""
+        h, l = self.h, self.linears[i]
+        O, I = l.shape.out_features, l.shape.in_features
+        self.ctx.counter_linear_step(x, dy, l.state, l.scale, l.v, l.y, l.dx, l.grad_w, l.packed2, h.C, I, O,
+                                     self.tokens, O, 0, h.lr, h.lr_scale, h.rms_beta, h.rms_eps, seed)
+
     # -- parts of a step, for per-kernel timing ---------------------------------------------------
     def products_only(self, xs, dys):
         """Y, dX and dW of every linear, no update (and no collectives)."""

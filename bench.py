@@ -239,6 +239,33 @@ def run_micro(args):
             nbytes = O * I / 4 + 4 * O + 4 * M * (I + O)
             out = {"kernel": "ternary_gemv_kernel", "bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": hbm_peak,
                    "unit": "GB/s", "bytes_per_launch": nbytes, "tokens_per_s": M / (ms * 1e-3)}
+        elif kind == "gemvsweep":
+            # the decode-GEMV configuration: 32 layers of w1, w3 (14336x4096), w2 (4096x14336), q, o
+            # (4096x4096) as 2-bit weights, every matrix distinct (1.68 GB), one recorded batch per sweep
+            M = dims[0]
+            layers = int(rest[0]) if rest else 32
+            shapes = [(14336, 4096), (14336, 4096), (4096, 14336), (4096, 4096), (4096, 4096)]
+            mats = []
+            for _ in range(layers):
+                for (O, I) in shapes:
+                    mats.append((torch.randint(-2 ** 31, 2 ** 31 - 1, (O, I // 16), dtype=torch.int32, device=dev,
+                                               generator=g), torch.full((O,), 0.05, device=dev), O, I))
+            xs_ = {I: torch.randn(M, I, device=dev, generator=g) for I in (4096, 14336)}
+            ys_ = {O: torch.empty(M, O, device=dev) for O in (4096, 14336)}
+
+            def sweep():
+                for p2, sc, O, I in mats:
+                    ctx.ternary_gemv(xs_[I], p2, sc, ys_[O], M, I, O)
+            sweep()
+            ctx.finish()
+            ctx.batch_begin()
+            sweep()
+            batch = ctx.batch_end()
+            ms = timed(lambda i: batch.launch(), args.steps, max(args.warmup, 3))
+            nbytes = sum(O * I / 4 + 4 * O + 4 * M * (I + O) for _, _, O, I in mats)
+            out = {"kernel": "ternary GEMV sweep (%d layers x 5 matrices)" % layers, "bound": "hbm",
+                   "achieved": nbytes / ms / 1e6, "peak": hbm_peak, "unit": "GB/s", "bytes_per_launch": nbytes,
+                   "tokens_per_s": M / (ms * 1e-3), "us_per_matrix": ms * 1e3 / len(mats)}
         elif kind == "step":
             T, I, O = dims
             x = torch.randn(T, I, device=dev, generator=g)

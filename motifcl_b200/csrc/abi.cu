@@ -779,6 +779,19 @@ int mcl_cuda_ternary_gemv(mcl_cuda_ctx* ctx, const float* x, const uint32_t* pac
     MCL_TRY(check_ptr(ctx, op, "scale", scale, 4));
     MCL_TRY(check_ptr(ctx, op, "y", y, 4));
     DeviceGuard guard(ctx->device);
+    if (ctx->gemm_mode != MCL_CUDA_GEMM_EXACT && out_features >= 128 &&
+        mcl::gemv_tc_supported((int)M, (int)in_features, (int)out_features) &&
+        reinterpret_cast<uintptr_t>(packed2) % 16 == 0) {
+        void* wsp = nullptr;
+        MCL_TRY(ws_reserve(ctx, mcl::gemv_tc_workspace_bytes((int)M, (int)in_features, (int)out_features), &wsp));
+        int launches = 0;
+        cudaError_t e = mcl::launch_ternary_gemv_tc(x, packed2, scale, y, (int)M, (int)in_features, (int)out_features,
+                                                    wsp, ctx->err_word, ctx->sm_count, ctx->max_smem, ctx->stream,
+                                                    &launches);
+        ctx->launches += launches;
+        if (e != cudaSuccess) return fail_cuda(ctx, op, e);
+        return MCL_CUDA_OK;
+    }
     MCL_LAUNCH(ctx, op, mcl::launch_ternary_gemv(x, packed2, scale, y, (int)M, (int)in_features,
                                                  (int)out_features, ctx->sm_count, ctx->stream));
     return MCL_CUDA_OK;

@@ -65,4 +65,12 @@ cudaError_t launch_ternary_gemv(const float* x, const uint32_t* packed2, const f
                                 int M, int in_features, int out_features, int sm_count,
                                 cudaStream_t stream);
 
+
+// gemv_tc.cu -- the same GEMV as integer tensor-core MMA on digit-split activations
+bool gemv_tc_supported(int M, int in_features, int out_features);
+size_t gemv_tc_workspace_bytes(int M, int in_features, int out_features);
+cudaError_t launch_ternary_gemv_tc(const float* x, const uint32_t* packed2, const float* scale, float* y, int M,
+                                   int in_features, int out_features, void* workspace, int* err_word, int sm_count,
+                                   size_t max_smem, cudaStream_t stream, int* launches);
+
 }  // namespace mcl

@@ -163,8 +163,7 @@ class CounterStack:
             ctx.counter_update_dense(st, sc, vv, gw, p2, h.C, gw.shape[1], rows, off, h.lr, h.lr_scale,
                                      h.rms_beta, h.rms_eps, sd)
 
-        for l in self.linears:
-            dp.exchange_and_update(l.sharded, update_fn, seed, self.group)
+        dp.exchange_and_update_many([l.sharded for l in self.linears], update_fn, seed, self.group)
 
     def step_linear(self, i: int, x, dy, seed: int):
         """The step of linear `i` alone on the main context (single GPU), for callers that

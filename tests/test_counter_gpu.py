@@ -219,8 +219,11 @@ def test_pack2_matches_oracle(ctx, orc):
 
 
 @pytest.mark.parametrize("M", [1, 3, 4, 16])
-@pytest.mark.parametrize("O,I", [(288, 288), (96, 2048), (40, 5632)])
+@pytest.mark.parametrize("O,I", [(288, 288), (96, 2048), (40, 5632),         # CUDA-core kernel
+                                 (256, 2048), (300, 4160), (1000, 512), (4096, 1024)])   # tensor-core kernel
 def test_ternary_gemv_vs_oracle(ctx, orc, M, O, I):
+    if M == 3 and O == 4096:
+        M = 13      # an activation-row count that is not a multiple of four
     rng = np.random.default_rng(M * 7 + O)
     st = synth.counters(5, O % 97, O, I).reshape(-1)
     p2 = orc.pack2(st, 11, I, O)

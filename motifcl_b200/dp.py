@@ -98,26 +98,41 @@ def exchange_and_update(lin: ShardedLinear, update_fn, seed: int, group=None):
     all_gather_rows(lin.scale, lin.rank, lin.world, group)
 
 
-def exchange_and_update_many(lins, update_fn, seed: int, group=None):
-    """exchange_and_update for a whole stack.  With NCCL and evenly divisible layers the
-    reduce-scatters of all layers are issued as ONE coalesced collective, then all shard
-    updates run, then the all-gathers of 2-bit words and scales go out as one coalesced
-    collective: three launches' worth of latency per step instead of three per layer."""
-    backend = dist.get_backend(group)
-    even = all(l.O % l.world == 0 for l in lins)
-    if backend != "nccl" or not even:
+def _coalescable(lins, group) -> bool:
+    return dist.get_backend(group) == "nccl" and all(l.O % l.world == 0 for l in lins)
+
+
+def reduce_scatter_many(lins, group=None):
+    """gw_shard[:rows] of every linear = its rows of the rank-summed grad_w; one coalesced NCCL
+    collective when all layers divide evenly."""
+    if not _coalescable(lins, group):
         for l in lins:
-            exchange_and_update(l, update_fn, seed, group)
+            reduce_scatter_rows(l.grad_w, l.gw_shard, l.rank, l.world, group)
         return
-    dev = lins[0].grad_w.device
-    with dist._coalescing_manager(group=group, device=dev, async_ops=False):
+    with dist._coalescing_manager(group=group, device=lins[0].grad_w.device, async_ops=False):
         for l in lins:
             dist.reduce_scatter_tensor(l.gw_shard[:l.rows], l.grad_w, op=dist.ReduceOp.SUM, group=group)
-    for l in lins:
-        sl = slice(l.off, l.off + l.rows)
-        update_fn(l.state, l.scale[sl], l.v, l.gw_shard[:l.rows], l.packed2[sl], l.rows, l.off, seed)
+
+
+def all_gather_many(lins, group=None):
+    """Replicate every linear's freshly updated 2-bit words and scales."""
+    if not _coalescable(lins, group):
+        for l in lins:
+            all_gather_rows(l.packed2, l.rank, l.world, group)
+            all_gather_rows(l.scale, l.rank, l.world, group)
+        return
     shards = [(l.packed2[l.off:l.off + l.rows].clone(), l.scale[l.off:l.off + l.rows].clone()) for l in lins]
-    with dist._coalescing_manager(group=group, device=dev, async_ops=False):
+    with dist._coalescing_manager(group=group, device=lins[0].grad_w.device, async_ops=False):
         for l, (p2s, scs) in zip(lins, shards):
             dist.all_gather_into_tensor(l.packed2, p2s, group=group)
             dist.all_gather_into_tensor(l.scale, scs, group=group)
+
+
+def exchange_and_update_many(lins, update_fn, seed: int, group=None):
+    """exchange_and_update for a whole stack: reduce-scatter all, update all shards, gather all."""
+    reduce_scatter_many(lins, group)
+    for l in lins:
+        if l.rows > 0:
+            sl = slice(l.off, l.off + l.rows)
+            update_fn(l.state, l.scale[sl], l.v, l.gw_shard[:l.rows], l.packed2[sl], l.rows, l.off, seed)
+    all_gather_many(lins, group)

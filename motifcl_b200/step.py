@@ -148,22 +148,46 @@ class CounterStack:
         self._join()
 
     # -- data parallel -------------------------------------------------------------------------
+    def _record(self, fn):
+        """Run fn once eagerly (sizes workspaces), then record the same calls into a batch."""
+        fn()
+        self.ctx.finish()
+        self.ctx.batch_begin()
+        try:
+            fn()
+        finally:
+            batch = self.ctx.batch_end()
+        return batch
+
     def _step_dp(self, xs, dys, seed):
-        h, nl = self.h, len(self.lanes)
-        # products of all linears from the replicated 2-bit weights, lanes side by side
-        self._fork()
-        for i, (l, x, dy) in enumerate(zip(self.linears, xs, dys)):
-            O, I = l.shape.out_features, l.shape.in_features
-            self.lanes[i % nl].ternary_linear_products(x, dy, l.packed2, l.scale, l.y, l.dx, l.grad_w, I, O,
-                                                       self.tokens)
-        self._join()
-        ctx = self.ctx
-
-        def update_fn(st, sc, vv, gw, p2, rows, off, sd, I=None):
-            ctx.counter_update_dense(st, sc, vv, gw, p2, h.C, gw.shape[1], rows, off, h.lr, h.lr_scale,
-                                     h.rms_beta, h.rms_eps, sd)
-
-        dp.exchange_and_update_many([l.sharded for l in self.linears], update_fn, seed, self.group)
+        """Products of all linears (one recorded batch), coalesced reduce-scatter, shard updates
+        (a second recorded batch, seeded through the device word), coalesced all-gather."""
+        key = (tuple(t.data_ptr() for t in xs), tuple(t.data_ptr() for t in dys))
+        first = self._batch is None or self._batch_key != key
+        if first:
+            self._batch = self._record(lambda: self.products_only(xs, dys))     # also this step's products
+            self._batch_key = key
+        else:
+            self._batch.launch()
+        lins = [l.sharded for l in self.linears]
+        dp.reduce_scatter_many(lins, self.group)
+        self._step_word.fill_(seed - (1 << 32) if seed >= (1 << 31) else seed)     # uint32 bits in an int32 word
+        if getattr(self, "_upd_batch", None) is None:
+            self.ctx.set_seed_offset(self._step_word)
+            try:
+                self.ctx.finish()
+                self.update_only(seed=0)                    # this step's update (seed = 0 + word)
+                self.ctx.finish()
+                self.ctx.batch_begin()
+                try:
+                    self.update_only(seed=0)
+                finally:
+                    self._upd_batch = self.ctx.batch_end()
+            finally:
+                self.ctx.set_seed_offset(None)
+        else:
+            self._upd_batch.launch()
+        dp.all_gather_many(lins, self.group)
 
     def step_linear(self, i: int, x, dy, seed: int):
         """The step of linear `i` alone on the main context (single GPU), for callers that

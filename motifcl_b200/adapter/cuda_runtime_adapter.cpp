@@ -1,0 +1,349 @@
+// MotifCL runtime seam on CUDA: defines the symbols of MotifCL's `motifcl_vulkan_runtime`
+// link target (include/motifcl/runtime/vulkan_backend.hpp: VulkanRuntime, VulkanBuffer,
+// probe_vulkan_runtime and the run_vulkan_* free functions) on top of the C ABI of
+// libmotifcl_cuda.so.  Linked in place of MotifCL's src/runtime/vulkan_backend.cpp it turns
+// Backend::create_vulkan() into a CUDA backend, so MotifCL's own sources -- nn::CounterStateLinear,
+// its autograd node, its tests -- run unchanged against the B200 kernels.
+//
+// This file implements the counter-synapse path and the f32 matmuls; every other run_vulkan_*
+// entry is a generated stub that reports "not implemented in CUDA runtime" (gen_stubs.py).
+// It is compiled against the MotifCL headers where they lie; nothing of MotifCL is copied here.
+#include <motifcl/runtime/vulkan_backend.hpp>
+
+#include <cstring>
+#include <stdexcept>
+#include <utility>
+
+#include "motifcl_cuda.h"
+
+namespace motifcl {
+
+namespace {
+// Free functions cannot see the private parts of VulkanBuffer; like MotifCL's own runtime they
+// funnel through the public VulkanRuntime::dispatch_cached, which here recognises this tag in
+// place of a SPIR-V pointer and reads the operation and its scalar arguments from the
+// "word count" and "push constants".
+const std::uint32_t kNativeTag[1] = {0x4D434C55u};
+enum NativeOp : std::size_t { kOpDecode = 1, kOpForward, kOpBackwardInput, kOpUpdateFused, kOpMatmul };
+struct NativeArgs {
+    std::size_t a = 0, b = 0, c = 0, d = 0;          // dimensions (meaning depends on the op)
+    float lr = 0, lr_scale = 0, rms_beta = 0, rms_eps = 0;
+    std::uint32_t seed = 0;
+    int trans_a = 0, trans_b = 0;
+};
+
+// Owns the C-ABI context; shared by the runtime and every buffer so that buffers may outlive
+// the VulkanRuntime object that made them, as MotifCL's Storage assumes.
+struct CtxHolder {
+    mcl_cuda_ctx* ctx = nullptr;
+    ~CtxHolder() { if (ctx) mcl_cuda_destroy(ctx); }
+};
+}  // namespace
+
+struct VulkanBuffer::Impl {
+    std::shared_ptr<CtxHolder> holder;
+    void* dptr = nullptr;
+    std::size_t nbytes = 0;
+    ~Impl() { if (dptr && holder && holder->ctx) mcl_cuda_free(holder->ctx, dptr); }
+};
+
+struct VulkanDispatchRecording::Impl {};
+
+struct VulkanRuntime::Impl {
+    std::shared_ptr<CtxHolder> holder;
+    std::string device_name;
+    std::string error;
+    VulkanDeviceCaps caps;
+    bool batch = false;
+    bool capture = false;
+};
+
+// ---- VulkanBuffer -------------------------------------------------------------------------
+VulkanBuffer::VulkanBuffer() = default;
+VulkanBuffer::~VulkanBuffer() = default;
+VulkanBuffer::VulkanBuffer(VulkanBuffer&&) noexcept = default;
+VulkanBuffer& VulkanBuffer::operator=(VulkanBuffer&&) noexcept = default;
+VulkanBuffer::VulkanBuffer(std::shared_ptr<Impl> impl) : impl_(std::move(impl)) {}
+bool VulkanBuffer::valid() const { return impl_ && impl_->dptr != nullptr; }
+std::size_t VulkanBuffer::nbytes() const { return impl_ ? impl_->nbytes : 0; }
+
+void VulkanBuffer::upload(const void* data, std::size_t bytes, std::size_t offset) {
+    if (!valid()) throw std::runtime_error("VulkanBuffer::upload on an invalid buffer");
+    if (offset > impl_->nbytes || bytes > impl_->nbytes - offset)
+        throw std::runtime_error("VulkanBuffer::upload out of bounds");
+    mcl_cuda_ctx* ctx = impl_->holder->ctx;
+    if (mcl_cuda_upload(ctx, static_cast<char*>(impl_->dptr) + offset, data, bytes) != MCL_CUDA_OK)
+        throw std::runtime_error(std::string("VulkanBuffer::upload failed: ") + mcl_cuda_last_error(ctx));
+}
+void VulkanBuffer::download(void* data, std::size_t bytes, std::size_t offset) const {
+    if (!valid()) throw std::runtime_error("VulkanBuffer::download on an invalid buffer");
+    if (offset > impl_->nbytes || bytes > impl_->nbytes - offset)
+        throw std::runtime_error("VulkanBuffer::download out of bounds");
+    mcl_cuda_ctx* ctx = impl_->holder->ctx;
+    if (mcl_cuda_download(ctx, data, static_cast<const char*>(impl_->dptr) + offset, bytes) != MCL_CUDA_OK)
+        throw std::runtime_error(std::string("VulkanBuffer::download failed: ") + mcl_cuda_last_error(ctx));
+}
+
+// ---- VulkanDispatchRecording (capture / replay is not offered by this runtime) --------------
+VulkanDispatchRecording::VulkanDispatchRecording() = default;
+VulkanDispatchRecording::~VulkanDispatchRecording() = default;
+VulkanDispatchRecording::VulkanDispatchRecording(VulkanDispatchRecording&&) noexcept = default;
+VulkanDispatchRecording& VulkanDispatchRecording::operator=(VulkanDispatchRecording&&) noexcept = default;
+bool VulkanDispatchRecording::empty() const { return true; }
+std::size_t VulkanDispatchRecording::size() const { return 0; }
+
+// ---- VulkanRuntime --------------------------------------------------------------------------
+VulkanRuntime::VulkanRuntime() = default;
+VulkanRuntime::~VulkanRuntime() = default;
+VulkanRuntime::VulkanRuntime(VulkanRuntime&&) noexcept = default;
+VulkanRuntime& VulkanRuntime::operator=(VulkanRuntime&&) noexcept = default;
+VulkanRuntime::VulkanRuntime(std::shared_ptr<Impl> impl) : impl_(std::move(impl)) {}
+
+VulkanRuntime VulkanRuntime::create() {
+    auto impl = std::make_shared<Impl>();
+    impl->holder = std::make_shared<CtxHolder>();
+    const int rc = mcl_cuda_create(0, &impl->holder->ctx);
+    if (rc != MCL_CUDA_OK) {
+        impl->error = mcl_cuda_last_error(nullptr);
+        impl->holder->ctx = nullptr;
+    } else {
+        impl->device_name = mcl_cuda_device_name(impl->holder->ctx);
+        impl->caps.timestamps = false;
+        impl->caps.max_shared_memory_bytes = 232448;
+        impl->caps.max_workgroup_invocations = 1024;
+        impl->caps.subgroup_arithmetic_compute = true;
+        impl->caps.subgroup_size = 32;
+        impl->caps.supports_atomic_float = true;
+        impl->caps.prefer_rb4_matmul = true;
+    }
+    return VulkanRuntime(std::move(impl));
+}
+
+static const std::string kEmpty;
+bool VulkanRuntime::available() const { return impl_ && impl_->holder && impl_->holder->ctx != nullptr; }
+const std::string& VulkanRuntime::device_name() const { return impl_ ? impl_->device_name : kEmpty; }
+const std::string& VulkanRuntime::error() const { return impl_ ? impl_->error : kEmpty; }
+bool VulkanRuntime::supports_storage_buffer_i8() const { return available(); }
+const VulkanDeviceCaps& VulkanRuntime::caps() const {
+    static const VulkanDeviceCaps none;
+    return impl_ ? impl_->caps : none;
+}
+
+// The reference defers a step's dispatches into one submit; here calls run eagerly on the
+// context's in-order stream, so a batch is only a bracket whose end waits for the stream.
+bool VulkanRuntime::batch_begin() {
+    if (!available() || impl_->batch) return false;
+    impl_->batch = true;
+    return true;
+}
+VulkanOpResult VulkanRuntime::batch_end() {
+    VulkanOpResult r;
+    r.device_name = device_name();
+    if (!available() || !impl_->batch) { r.error = "batch_end without batch_begin"; return r; }
+    impl_->batch = false;
+    if (mcl_cuda_finish(impl_->holder->ctx) != MCL_CUDA_OK) { r.error = mcl_cuda_last_error(impl_->holder->ctx); return r; }
+    r.success = true;
+    return r;
+}
+bool VulkanRuntime::batch_active() const { return impl_ && impl_->batch; }
+void VulkanRuntime::set_gpu_timing_enabled(bool) {}
+double VulkanRuntime::last_gpu_time_us() const { return -1.0; }
+void VulkanRuntime::finish() const {
+    if (available()) mcl_cuda_finish(impl_->holder->ctx);
+}
+bool VulkanRuntime::capture_begin() { return false; }
+VulkanDispatchRecording VulkanRuntime::capture_end() { return VulkanDispatchRecording(); }
+bool VulkanRuntime::capture_active() const { return false; }
+VulkanOpResult VulkanRuntime::replay(const VulkanDispatchRecording&) {
+    VulkanOpResult r;
+    r.device_name = device_name();
+    r.error = "dispatch capture/replay is not implemented in CUDA runtime";
+    return r;
+}
+
+VulkanBuffer VulkanRuntime::create_buffer(std::size_t nbytes, const void* initial_data) {
+    if (!available()) throw std::runtime_error("VulkanRuntime::create_buffer: runtime is not available");
+    auto impl = std::make_shared<VulkanBuffer::Impl>();
+    impl->holder = impl_->holder;
+    impl->nbytes = nbytes;
+    if (mcl_cuda_alloc(impl_->holder->ctx, nbytes ? nbytes : 16, &impl->dptr) != MCL_CUDA_OK)
+        throw std::runtime_error(std::string("VulkanRuntime::create_buffer failed: ") +
+                                 mcl_cuda_last_error(impl_->holder->ctx));
+    VulkanBuffer buf(std::move(impl));
+    if (initial_data && nbytes) buf.upload(initial_data, nbytes, 0);
+    return buf;
+}
+
+VulkanOpResult VulkanRuntime::dispatch_cached(const std::uint32_t* spirv, std::size_t op,
+                                              const std::vector<const VulkanBuffer*>& bufs, const void* push,
+                                              std::uint32_t push_bytes, std::uint32_t, std::uint32_t, std::uint32_t) {
+    VulkanOpResult r;
+    r.device_name = device_name();
+    if (!available()) { r.error = "CUDA runtime is not available"; return r; }
+    if (spirv != kNativeTag || push_bytes != sizeof(NativeArgs)) {
+        r.error = "SPIR-V dispatch is not implemented in CUDA runtime";
+        return r;
+    }
+    for (const VulkanBuffer* b : bufs)
+        if (b == nullptr || !b->valid()) { r.error = "invalid buffer"; return r; }
+    mcl_cuda_ctx* ctx = impl_->holder->ctx;
+    NativeArgs a;
+    std::memcpy(&a, push, sizeof(a));
+    auto p = [&](std::size_t i) { return bufs[i]->impl_->dptr; };
+    int rc = MCL_CUDA_EINVAL;
+    switch (op) {
+        case kOpDecode:          // state, scale, weight | in, out, C
+            rc = mcl_cuda_counter_decode_weight(ctx, (const uint8_t*)p(0), (const float*)p(1), (float*)p(2), a.a, a.b, a.c);
+            break;
+        case kOpForward:         // x, state, scale, out | batch, in, out, C
+            rc = mcl_cuda_counter_forward(ctx, (const float*)p(0), (const uint8_t*)p(1), (const float*)p(2), (float*)p(3),
+                                          a.a, a.b, a.c, a.d);
+            break;
+        case kOpBackwardInput:   // state, scale, grad_out, grad_x | batch, in, out, C
+            rc = mcl_cuda_counter_backward_input(ctx, (const uint8_t*)p(0), (const float*)p(1), (const float*)p(2),
+                                                 (float*)p(3), a.a, a.b, a.c, a.d);
+            break;
+        case kOpUpdateFused:     // state, scale, v, grad_out, x, scratch, scratch | C, in, out, batch
+            rc = mcl_cuda_counter_update_fused(ctx, (uint8_t*)p(0), (float*)p(1), (float*)p(2), (const float*)p(3),
+                                               (const float*)p(4), (float*)p(5), (float*)p(6), nullptr, a.a, a.b, a.c,
+                                               a.d, a.lr, a.lr_scale, a.rms_beta, a.rms_eps, a.seed);
+            break;
+        case kOpMatmul:          // a, b, c | m, k, n
+            rc = mcl_cuda_matmul_f32(ctx, (const float*)p(0), (const float*)p(1), (float*)p(2), a.a, a.b, a.c, a.trans_a,
+                                     a.trans_b);
+            break;
+        default:
+            r.error = "unknown native operation";
+            return r;
+    }
+    if (rc != MCL_CUDA_OK) { r.error = mcl_cuda_last_error(ctx); return r; }
+    r.success = true;
+    return r;
+}
+VulkanStorageBufferDispatchResult VulkanRuntime::dispatch_storage_buffers(
+    const std::uint32_t*, std::size_t, const std::vector<VulkanStorageBufferSpec>&, const std::vector<std::size_t>&,
+    std::uint32_t, std::uint32_t, std::uint32_t) {
+    VulkanStorageBufferDispatchResult r;
+    r.error = "SPIR-V dispatch is not implemented in CUDA runtime";
+    return r;
+}
+VulkanStorageBufferDispatchResult VulkanRuntime::dispatch_storage_buffers(
+    const std::uint32_t*, std::size_t, const std::vector<const VulkanBuffer*>&, const std::vector<std::size_t>&,
+    std::uint32_t, std::uint32_t, std::uint32_t) {
+    VulkanStorageBufferDispatchResult r;
+    r.error = "SPIR-V dispatch is not implemented in CUDA runtime";
+    return r;
+}
+
+// ---- probe ------------------------------------------------------------------------------------
+VulkanProbeResult probe_vulkan_runtime() {
+    VulkanProbeResult r;
+    if (mcl_cuda_device_count() <= 0) {
+        r.error = "no CUDA device available";
+        return r;           // loader_found stays false: device tests skip, as without a Vulkan loader
+    }
+    mcl_cuda_ctx* ctx = nullptr;
+    if (mcl_cuda_create(0, &ctx) != MCL_CUDA_OK) {
+        r.error = mcl_cuda_last_error(nullptr);
+        return r;
+    }
+    r.loader_found = true;
+    r.instance_created = true;
+    r.loader_path = "libmotifcl_cuda.so";
+    r.physical_device_count = 1;
+    VulkanPhysicalDeviceInfo d;
+    d.name = mcl_cuda_device_name(ctx);
+    d.vendor_id = 0x10DE;
+    d.device_type = 2;      // discrete GPU
+    r.devices.push_back(d);
+    mcl_cuda_destroy(ctx);
+    return r;
+}
+
+// ---- counter-synapse path and f32 matmuls ---------------------------------------------------------
+namespace {
+VulkanOpResult refuse(VulkanRuntime& rt, const std::string& msg) {
+    VulkanOpResult r;
+    r.device_name = rt.device_name();
+    r.error = msg;
+    return r;
+}
+VulkanOpResult native(VulkanRuntime& rt, NativeOp op, const std::vector<const VulkanBuffer*>& bufs, const NativeArgs& a) {
+    return rt.dispatch_cached(kNativeTag, op, bufs, &a, sizeof(a), 1, 1, 1);
+}
+}  // namespace
+
+// Buffer-size checks live here because the C ABI sees raw pointers; dimension and hyper-parameter
+// checks are repeated inside the C ABI with the reference's wording.
+VulkanOpResult run_vulkan_compact_counter_decode_weight(VulkanRuntime& rt, const VulkanBuffer& state,
+                                                        const VulkanBuffer& scale, VulkanBuffer& weight,
+                                                        std::size_t in_features, std::size_t out_features,
+                                                        std::size_t C) {
+    const std::size_t groups = out_features * (in_features / 4);
+    if (state.nbytes() < groups * 3 || scale.nbytes() < out_features * 4 ||
+        weight.nbytes() < out_features * in_features * 4)
+        return refuse(rt, "Vulkan counter decode buffer is too small");
+    NativeArgs a; a.a = in_features; a.b = out_features; a.c = C;
+    return native(rt, kOpDecode, {&state, &scale, &weight}, a);
+}
+VulkanOpResult run_vulkan_compact_counter_forward_u8(VulkanRuntime& rt, const VulkanBuffer& x, const VulkanBuffer& state,
+                                                     const VulkanBuffer& scale, VulkanBuffer& out, std::size_t batch,
+                                                     std::size_t in_features, std::size_t out_features, std::size_t C) {
+    if (x.nbytes() < batch * in_features * 4 || out.nbytes() < batch * out_features * 4 ||
+        state.nbytes() < out_features * (in_features / 4) * 3 || scale.nbytes() < out_features * 4)
+        return refuse(rt, "Vulkan counter forward buffer is too small");
+    NativeArgs a; a.a = batch; a.b = in_features; a.c = out_features; a.d = C;
+    return native(rt, kOpForward, {&x, &state, &scale, &out}, a);
+}
+VulkanOpResult run_vulkan_compact_counter_backward_input_u8(VulkanRuntime& rt, const VulkanBuffer& state,
+                                                            const VulkanBuffer& scale, const VulkanBuffer& grad_out,
+                                                            VulkanBuffer& grad_x, std::size_t batch,
+                                                            std::size_t in_features, std::size_t out_features,
+                                                            std::size_t C) {
+    if (grad_out.nbytes() < batch * out_features * 4 || grad_x.nbytes() < batch * in_features * 4 ||
+        state.nbytes() < out_features * (in_features / 4) * 3 || scale.nbytes() < out_features * 4)
+        return refuse(rt, "Vulkan counter backward_input buffer is too small");
+    NativeArgs a; a.a = batch; a.b = in_features; a.c = out_features; a.d = C;
+    return native(rt, kOpBackwardInput, {&state, &scale, &grad_out, &grad_x}, a);
+}
+VulkanOpResult run_vulkan_compact_counter_apply_update_fused(VulkanRuntime& rt, VulkanBuffer& state, VulkanBuffer& scale,
+                                                             VulkanBuffer& v, const VulkanBuffer& grad_out,
+                                                             const VulkanBuffer& x, VulkanBuffer& scale_new_scratch,
+                                                             VulkanBuffer& denom_scratch, std::size_t C,
+                                                             std::size_t in_features, std::size_t out_features,
+                                                             std::size_t batch, float lr, float lr_scale, float rms_beta,
+                                                             float rms_eps, std::uint32_t seed) {
+    if (in_features % 4 == 0 && state.nbytes() < out_features * (in_features / 4) * 3)
+        return refuse(rt, "Vulkan counter update state buffer is too small");
+    if (scale.nbytes() < out_features * 4 || v.nbytes() < out_features * 4 ||
+        scale_new_scratch.nbytes() < out_features * 4 || denom_scratch.nbytes() < out_features * 4)
+        return refuse(rt, "Vulkan counter update per-row buffer is too small");
+    if (grad_out.nbytes() < batch * out_features * 4 || x.nbytes() < batch * in_features * 4)
+        return refuse(rt, "Vulkan counter update activation buffer is too small");
+    NativeArgs a; a.a = C; a.b = in_features; a.c = out_features; a.d = batch;
+    a.lr = lr; a.lr_scale = lr_scale; a.rms_beta = rms_beta; a.rms_eps = rms_eps; a.seed = seed;
+    return native(rt, kOpUpdateFused, {&state, &scale, &v, &grad_out, &x, &scale_new_scratch, &denom_scratch}, a);
+}
+
+namespace {
+VulkanOpResult matmul(VulkanRuntime& rt, const VulkanBuffer& a, const VulkanBuffer& b, VulkanBuffer& c, std::size_t m,
+                      std::size_t k, std::size_t n, int ta, int tb) {
+    if (a.nbytes() < m * k * 4 || b.nbytes() < k * n * 4 || c.nbytes() < m * n * 4)
+        return refuse(rt, "Vulkan f32 matmul buffer is too small");
+    NativeArgs g; g.a = m; g.b = k; g.c = n; g.trans_a = ta; g.trans_b = tb;
+    return native(rt, kOpMatmul, {&a, &b, &c}, g);
+}
+}  // namespace
+VulkanOpResult run_vulkan_f32_matmul(VulkanRuntime& rt, const VulkanBuffer& a, const VulkanBuffer& b, VulkanBuffer& c,
+                                     std::size_t m, std::size_t k, std::size_t n) { return matmul(rt, a, b, c, m, k, n, 0, 0); }
+VulkanOpResult run_vulkan_f32_matmul_transpose_b(VulkanRuntime& rt, const VulkanBuffer& a, const VulkanBuffer& b,
+                                                 VulkanBuffer& c, std::size_t m, std::size_t k, std::size_t n) {
+    return matmul(rt, a, b, c, m, k, n, 0, 1);
+}
+VulkanOpResult run_vulkan_f32_matmul_transpose_a(VulkanRuntime& rt, const VulkanBuffer& a, const VulkanBuffer& b,
+                                                 VulkanBuffer& c, std::size_t m, std::size_t k, std::size_t n) {
+    return matmul(rt, a, b, c, m, k, n, 1, 0);
+}
+VulkanOpResult run_vulkan_f32_m1_matmul(VulkanRuntime& rt, const VulkanBuffer& a, const VulkanBuffer& b, VulkanBuffer& c,
+                                        std::size_t k, std::size_t n) { return matmul(rt, a, b, c, 1, k, n, 0, 0); }
+}  // namespace motifcl

@@ -178,6 +178,19 @@ int mcl_cuda_ternary_linear_products(mcl_cuda_ctx* ctx, const float* x, const fl
 int mcl_cuda_matmul_f32(mcl_cuda_ctx* ctx, const float* a, const float* b, float* c, size_t M,
                         size_t K, size_t N, int trans_a, int trans_b);
 
+/* ---- elementwise fp32 helpers: replace run_vulkan_add / _sub / _mul / _mul_scalar / _add_scalar /
+ * _zero_f32 (include/motifcl/runtime/vulkan_backend.hpp; src/ops/basic_ops.cpp:67-92,208-211,409,462;
+ * kernels/basic.cl), which MotifCL's autograd and its counter tests call between counter layers.
+ * out[i] = a[i] (+,-,*) b[i], a[i]*alpha, a[i]+alpha, or 0.  b may be NULL for the scalar ops. ---- */
+#define MCL_CUDA_ELT_ADD 0
+#define MCL_CUDA_ELT_SUB 1
+#define MCL_CUDA_ELT_MUL 2
+#define MCL_CUDA_ELT_MUL_SCALAR 3
+#define MCL_CUDA_ELT_ADD_SCALAR 4
+#define MCL_CUDA_ELT_ZERO 5
+int mcl_cuda_eltwise_f32(mcl_cuda_ctx* ctx, int op, const float* a, const float* b, float* out, size_t elements,
+                         float alpha);
+
 /* ---- ternary decode GEMV, M <= 16 (no reference kernel; semantics of the forward above
  * applied to 2-bit weights).  y[M,out] = x[M,in] * (scale . t)^T.  Requires in % 16 == 0. ---- */
 int mcl_cuda_ternary_gemv(mcl_cuda_ctx* ctx, const float* x, const uint32_t* packed2,

@@ -24,12 +24,14 @@ namespace {
 // place of a SPIR-V pointer and reads the operation and its scalar arguments from the
 // "word count" and "push constants".
 const std::uint32_t kNativeTag[1] = {0x4D434C55u};
-enum NativeOp : std::size_t { kOpDecode = 1, kOpForward, kOpBackwardInput, kOpUpdateFused, kOpMatmul };
+enum NativeOp : std::size_t { kOpDecode = 1, kOpForward, kOpBackwardInput, kOpUpdateFused, kOpMatmul, kOpEltwise };
 struct NativeArgs {
     std::size_t a = 0, b = 0, c = 0, d = 0;          // dimensions (meaning depends on the op)
     float lr = 0, lr_scale = 0, rms_beta = 0, rms_eps = 0;
     std::uint32_t seed = 0;
     int trans_a = 0, trans_b = 0;
+    int elt_op = 0;
+    float alpha = 0;
 };
 
 // Owns the C-ABI context; shared by the runtime and every buffer so that buffers may outlive
@@ -212,6 +214,11 @@ VulkanOpResult VulkanRuntime::dispatch_cached(const std::uint32_t* spirv, std::s
             rc = mcl_cuda_matmul_f32(ctx, (const float*)p(0), (const float*)p(1), (float*)p(2), a.a, a.b, a.c, a.trans_a,
                                      a.trans_b);
             break;
+        case kOpEltwise:         // [a, [b,]] out | elements; the last buffer is the output
+            rc = mcl_cuda_eltwise_f32(ctx, a.elt_op, bufs.size() > 1 ? (const float*)p(0) : nullptr,
+                                      bufs.size() > 2 ? (const float*)p(1) : nullptr, (float*)p(bufs.size() - 1), a.a,
+                                      a.alpha);
+            break;
         default:
             r.error = "unknown native operation";
             return r;
@@ -346,4 +353,31 @@ VulkanOpResult run_vulkan_f32_matmul_transpose_a(VulkanRuntime& rt, const Vulkan
 }
 VulkanOpResult run_vulkan_f32_m1_matmul(VulkanRuntime& rt, const VulkanBuffer& a, const VulkanBuffer& b, VulkanBuffer& c,
                                         std::size_t k, std::size_t n) { return matmul(rt, a, b, c, 1, k, n, 0, 0); }
+
+namespace {
+VulkanOpResult eltwise(VulkanRuntime& rt, int op, const VulkanBuffer* a, const VulkanBuffer* b, VulkanBuffer& out,
+                       std::size_t elements, float alpha) {
+    if (out.nbytes() < elements * 4 || (a && a->nbytes() < elements * 4) || (b && b->nbytes() < elements * 4))
+        return refuse(rt, "Vulkan elementwise buffer is too small");
+    NativeArgs g; g.a = elements; g.elt_op = op; g.alpha = alpha;
+    std::vector<const VulkanBuffer*> bufs;
+    if (a) bufs.push_back(a);
+    if (b) bufs.push_back(b);
+    bufs.push_back(&out);
+    return native(rt, kOpEltwise, bufs, g);
+}
+}  // namespace
+VulkanOpResult run_vulkan_add(VulkanRuntime& rt, const VulkanBuffer& a, const VulkanBuffer& b, VulkanBuffer& out,
+                              std::size_t n) { return eltwise(rt, MCL_CUDA_ELT_ADD, &a, &b, out, n, 0.0f); }
+VulkanOpResult run_vulkan_sub(VulkanRuntime& rt, const VulkanBuffer& a, const VulkanBuffer& b, VulkanBuffer& out,
+                              std::size_t n) { return eltwise(rt, MCL_CUDA_ELT_SUB, &a, &b, out, n, 0.0f); }
+VulkanOpResult run_vulkan_mul(VulkanRuntime& rt, const VulkanBuffer& a, const VulkanBuffer& b, VulkanBuffer& out,
+                              std::size_t n) { return eltwise(rt, MCL_CUDA_ELT_MUL, &a, &b, out, n, 0.0f); }
+VulkanOpResult run_vulkan_mul_scalar(VulkanRuntime& rt, const VulkanBuffer& x, VulkanBuffer& out, std::size_t n,
+                                     float alpha) { return eltwise(rt, MCL_CUDA_ELT_MUL_SCALAR, &x, nullptr, out, n, alpha); }
+VulkanOpResult run_vulkan_add_scalar(VulkanRuntime& rt, const VulkanBuffer& x, VulkanBuffer& out, std::size_t n,
+                                     float value) { return eltwise(rt, MCL_CUDA_ELT_ADD_SCALAR, &x, nullptr, out, n, value); }
+VulkanOpResult run_vulkan_zero_f32(VulkanRuntime& rt, VulkanBuffer& out, std::size_t n) {
+    return eltwise(rt, MCL_CUDA_ELT_ZERO, nullptr, nullptr, out, n, 0.0f);
+}
 }  // namespace motifcl

@@ -765,6 +765,20 @@ int mcl_cuda_matmul_f32(mcl_cuda_ctx* ctx, const float* a, const float* b, float
     return MCL_CUDA_OK;
 }
 
+int mcl_cuda_eltwise_f32(mcl_cuda_ctx* ctx, int op, const float* a, const float* b, float* out, size_t elements,
+                         float alpha) {
+    MCL_NEED_CTX(ctx);
+    const char* name = "eltwise_f32";
+    if (op < 0 || op > MCL_CUDA_ELT_ZERO) return fail(ctx, MCL_CUDA_EINVAL, "eltwise_f32: unknown op");
+    if (elements == 0) return fail(ctx, MCL_CUDA_EINVAL, "eltwise_f32 requires non-zero elements");
+    MCL_TRY(check_ptr(ctx, name, "out", out, 4));
+    if (op != MCL_CUDA_ELT_ZERO) MCL_TRY(check_ptr(ctx, name, "a", a, 4));
+    if (op <= MCL_CUDA_ELT_MUL) MCL_TRY(check_ptr(ctx, name, "b", b, 4));
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, name, mcl::launch_eltwise_f32(op, a, b, out, elements, alpha, ctx->sm_count, ctx->stream));
+    return MCL_CUDA_OK;
+}
+
 int mcl_cuda_ternary_gemv(mcl_cuda_ctx* ctx, const float* x, const uint32_t* packed2,
                           const float* scale, float* y, size_t M, size_t in_features,
                           size_t out_features) {

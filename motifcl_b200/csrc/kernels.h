@@ -73,4 +73,8 @@ cudaError_t launch_ternary_gemv_tc(const float* x, const uint32_t* packed2, cons
                                    int in_features, int out_features, void* workspace, int* err_word, int sm_count,
                                    size_t max_smem, cudaStream_t stream, int* launches);
 
+// eltwise.cu: op 0 add, 1 sub, 2 mul, 3 mul_scalar, 4 add_scalar, 5 zero
+cudaError_t launch_eltwise_f32(int op, const float* a, const float* b, float* out, size_t n, float alpha,
+                               int sm_count, cudaStream_t stream);
+
 }  // namespace mcl

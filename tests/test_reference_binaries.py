@@ -9,7 +9,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 BUILD = os.path.join(ROOT, "motifcl_b200", "adapter", "_build")
-BINARIES = ["test_vulkan_counter_fused"]
+BINARIES = ["test_vulkan_counter_fused", "test_vulkan_memory_native", "test_matmul_transpose_b_autograd"]
 
 
 def _run(name):
@@ -33,7 +33,11 @@ def test_reference_binary_skips_without_a_device(name):
 def test_reference_binary_passes_on_the_cuda_backend(name):
     """tests/test_vulkan_counter_fused.cpp: same-seed layers start identical; forward and grad_x
     within 2e-5 of decode_weight + matmul_transpose_b / a host loop; the autograd-driven update
-    equals a direct apply_update_backward exactly (state, scale, v); state and scale change."""
+    equals a direct apply_update_backward exactly (state, scale, v); state and scale change.
+    tests/test_vulkan_memory_native.cpp: teacher recovery (loss halves, ternary accuracy >= 0.8) and
+    a 4-block reversible + counter stack whose loss falls.
+    tests/test_matmul_transpose_b_autograd.cpp: NT matmul gradients vs the NN path (<= 1e-4) and
+    gradient accumulation on a shared tensor."""
     r = _run(name)
     assert r.returncode == 0, r.stdout + r.stderr
-    assert "PASS" in r.stdout
+    assert "PASS" in r.stdout and "FAIL" not in r.stdout

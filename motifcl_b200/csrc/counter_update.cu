@@ -345,6 +345,24 @@ __device__ __forceinline__ uint32_t shr_mulhi(uint32_t x, uint32_t pow2) {   // 
     return r;
 }
 
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
+    uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v;
+}
+__device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
+    uint32_t v; asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a)); return v;
+}
+__device__ __forceinline__ float2 lds_f2(uint32_t a) {
+    float2 v; asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a)); return v;
+}
+__device__ __forceinline__ float4 lds_f4(uint32_t a) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void sts_u32(uint32_t a, uint32_t v) {
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
+}
+
 struct U16Layout {
     int sb, off_tailc, off_tailf, off_rowc, off_part, off_rowtab, off_gw, off_q, off_st, off_so, off_p2;
     size_t total;
@@ -390,6 +408,9 @@ counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const ui
     unsigned char* st_s = smem + L.off_st;
     unsigned char* so_s = smem + L.off_so;
     uint32_t* p2_s = reinterpret_cast<uint32_t*>(smem + L.off_p2);
+    const uint32_t sa0 = (uint32_t)__cvta_generic_to_shared(smem);
+    const uint32_t sa_tail = sa0 + L.off_tailc, sa_rowc = sa0 + L.off_rowc, sa_rowtab = sa0 + L.off_rowtab;
+    const uint32_t sa_gw = sa0 + L.off_gw, sa_st = sa0 + L.off_st, sa_so = sa0 + L.off_so, sa_p2 = sa0 + L.off_p2;
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -529,24 +550,26 @@ counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const ui
         __syncthreads();
 
         // ---- tick: 16 weights per thread-iteration, units of the whole batch flattened --------
+        // Shared memory is addressed with 32-bit shared-space addresses (ld.shared / st.shared), which
+        // keeps the address arithmetic of the data-dependent table look-ups to one add each.
         const int nunits = nrows * upr;
         for (int u = tid; u < nunits; u += kUpdThreads) {
             const int r = unit_magic ? (int)__umulhi((uint32_t)u, unit_magic) : u;       // u / upr (magic 0: upr == 1)
             const int j = u - r * upr;
-            const RowConst rc = rowc[r];
-            const RowEntry* rt = rowtab + r * 64;
-            const uint32_t* sw = reinterpret_cast<const uint32_t*>(st_s + (size_t)r * L.sb) + 3 * j;
-            const uint32_t s0 = sw[0], s1 = sw[1], s2 = sw[2];
+            const float4 rcv = lds_f4(sa_rowc + (uint32_t)r * 16u);       // dn, k_tick, k_reb
+            const uint32_t rt = sa_rowtab + (uint32_t)r * 512u;
+            const uint32_t sw = sa_st + (uint32_t)r * (uint32_t)L.sb + 12u * (uint32_t)j;
+            const uint32_t s0 = lds_u32(sw), s1 = lds_u32(sw + 4), s2 = lds_u32(sw + 8);
             const uint32_t gwd[4] = {s0 & 0xFFFFFFu, (s0 >> 24) | ((s1 & 0xFFFFu) << 8),
                                      (s1 >> 16) | ((s2 & 0xFFu) << 16), s2 >> 8};
-            const float4* g4 = gw_s + r * gpr + 4 * j;
-            const int jsw = (j >> 1) & 3;
+            const uint32_t g4 = sa_gw + ((uint32_t)(r * gpr + 4 * j) << 4);
+            const uint32_t jsw = (uint32_t)((j >> 1) & 3);
             const uint32_t e_unit = (uint32_t)(p.row_offset + row0 + r) * (uint32_t)I + (uint32_t)(16 * j);
             uint32_t nwd[4], fields = 0;
             float vmax = 0.0f;          // largest |counter + tick| of the unit
 #pragma unroll
             for (int gg = 0; gg < 4; ++gg) {
-                const float4 gw = g4[gg ^ jsw];
+                const float4 gw = lds_f4(g4 + (((uint32_t)gg ^ jsw) << 4));
                 const float gwv[4] = {gw.x, gw.y, gw.z, gw.w};
                 const uint32_t w = gwd[gg];
                 const uint32_t e0 = e_unit + 4u * gg;
@@ -554,9 +577,11 @@ counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const ui
                 uint32_t nw = 0;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const RowEntry re = rt[(w >> (6 * k)) & 63u];
-                    const float tick = __fmul_rn(__fmul_rn(neg_lr, __fdiv_rn(gwv[k], rc.dn)), rc.k_tick);
-                    const float val = __fadd_rn(re.creb, tick);
+                    // byte offset of the row-table entry of the old code: code * 8
+                    const uint32_t c8 = (k == 0 ? (w << 3) : (w >> (6 * k - 3))) & 0x1F8u;
+                    const float2 re = lds_f2(rt + c8);            // x = rebased counter, y = tail-table base (int bits)
+                    const float tick = __fmul_rn(__fmul_rn(neg_lr, __fdiv_rn(gwv[k], rcv.x)), rcv.y);
+                    const float val = __fadd_rn(re.x, tick);
                     vmax = fmaxf(vmax, fabsf(val));
                     uint32_t x = (e0x ^ (uint32_t)k) * 0x7feb352du;
                     x ^= shr_mulhi(x, pow17);            // x >> 15
@@ -572,9 +597,9 @@ counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const ui
                     const float up = (rnd < __fsub_rn(val, f)) ? 1.0f : 0.0f;
                     int iccv;           // saturating conversion keeps the table index in range whatever val is
                     asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(iccv) : "f"(__fadd_rn(f, up)));
-                    const int idx = re.tail_base + iccv;
-                    nw += (uint32_t)tail_code[idx] << (6 * k);
-                    fields += (uint32_t)tail_field[idx] << (2 * (4 * gg + k));
+                    const uint32_t ta = sa_tail + (uint32_t)(__float_as_int(re.y) + iccv);
+                    nw += lds_u8(ta) << (6 * k);
+                    fields += lds_u8(ta + 4 * kTail16) << (2 * (4 * gg + k));
                 }
                 nwd[gg] = nw;
             }
@@ -583,25 +608,25 @@ counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const ui
                 // with the reference formulas
                 fields = 0;
                 for (int gg = 0; gg < 4; ++gg) {
-                    const float4 gw = g4[gg ^ jsw];
+                    const float4 gw = lds_f4(g4 + (((uint32_t)gg ^ jsw) << 4));
                     const float gwv[4] = {gw.x, gw.y, gw.z, gw.w};
                     uint32_t nw = 0;
                     for (int k = 0; k < 4; ++k) {
                         const float2 tc = lut->e[(gwd[gg] >> (6 * k)) & 63u];
                         uint32_t fld;
                         const uint32_t code = counter_tick(gwv[k], tc.x, tc.y, e_unit + (uint32_t)(4 * gg + k), seed,
-                                                           neg_lr, rc.dn, rc.k_tick, rc.k_reb, Cf, p.C, lv, &fld);
+                                                           neg_lr, rcv.x, rcv.y, rcv.z, Cf, p.C, lv, &fld);
                         nw += (code & 0x3Fu) << (6 * k);
                         fields += (fld & 3u) << (2 * (4 * gg + k));
                     }
                     nwd[gg] = nw;
                 }
             }
-            uint32_t* so = reinterpret_cast<uint32_t*>(so_s + (size_t)r * L.sb) + 3 * j;
-            so[0] = nwd[0] | (nwd[1] << 24);
-            so[1] = (nwd[1] >> 8) | (nwd[2] << 16);
-            so[2] = (nwd[2] >> 16) | (nwd[3] << 8);
-            p2_s[r * upr + j] = fields;
+            const uint32_t so = sa_so + (uint32_t)r * (uint32_t)L.sb + 12u * (uint32_t)j;
+            sts_u32(so, nwd[0] | (nwd[1] << 24));
+            sts_u32(so + 4, (nwd[1] >> 8) | (nwd[2] << 16));
+            sts_u32(so + 8, (nwd[2] >> 16) | (nwd[3] << 8));
+            sts_u32(sa_p2 + 4u * (uint32_t)(r * upr + j), fields);
         }
         __syncthreads();
 

@@ -2,6 +2,7 @@
 // The declarations and the reference interfaces they replace are in include/motifcl_cuda.h.
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -156,6 +157,7 @@ int create_impl(int device, cudaStream_t stream, bool own, mcl_cuda_ctx** out_ct
         delete ctx;
         return fail_cuda(nullptr, "context setup", e);
     }
+    if (const char* e = std::getenv("MCL_CUDA_TC_MAX_KTILES")) mcl::tc_set_max_ktiles(std::atoi(e));
     *out_ctx = ctx;
     return MCL_CUDA_OK;
 }
@@ -451,7 +453,7 @@ int mcl_cuda_counter_forward(mcl_cuda_ctx* ctx, const float* x, const uint8_t* s
         const int ta = ctx->act_terms, ldi = up8(in_features);
         int splits = 1;
         const size_t sk = mcl::tc_splitk_workspace_bytes((int)batch, (int)out_features, (int)in_features,
-                                                         ctx->sm_count, &splits);
+                                                         ctx->sm_count, 0, &splits);
         Carver cv;
         const size_t o_x = cv.reserve((size_t)ta * batch * ldi * 2), o_t = cv.reserve(out_features * (size_t)ldi * 2),
                      o_k = cv.reserve(sk);
@@ -489,7 +491,7 @@ int mcl_cuda_counter_backward_input(mcl_cuda_ctx* ctx, const uint8_t* state, con
         const int ta = ctx->act_terms, ldo = up8(out_features);
         int splits = 1;
         const size_t sk = mcl::tc_splitk_workspace_bytes((int)batch, (int)in_features, (int)out_features,
-                                                         ctx->sm_count, &splits);
+                                                         ctx->sm_count, 0, &splits);
         Carver cv;
         const size_t o_g = cv.reserve((size_t)ta * batch * ldo * 2), o_t = cv.reserve(in_features * (size_t)ldo * 2),
                      o_k = cv.reserve(sk);
@@ -578,7 +580,7 @@ int mcl_cuda_counter_update_fused(mcl_cuda_ctx* ctx, uint8_t* state, float* scal
     if (tc) {
         grad_term_list(ctx->grad_terms, pa, pb, &nt, &planes);
         const size_t sk = mcl::tc_splitk_workspace_bytes((int)tile_rows, (int)in_features, (int)batch,
-                                                         ctx->sm_count, &splits);
+                                                         ctx->sm_count, mcl::kGradDepthLimit, &splits);
         o_a = cv.reserve((size_t)planes * out_features * ldn * 2);   // dY^T term planes (activation-sized)
         o_b = cv.reserve((size_t)planes * in_features * ldn * 2);    // X^T term planes
         o_k = cv.reserve(sk);
@@ -637,9 +639,9 @@ static int linear_products(mcl_cuda_ctx* ctx, const char* op, const float* x, co
     grad_term_list(ctx->grad_terms, pa, pb, &nt, &gp);
     const int ldi = up8(I), ldo = up8(O), ldn = up8(Nt);
     int s_y = 1, s_x = 1, s_w = 1;
-    const size_t k_y = mcl::tc_splitk_workspace_bytes((int)Nt, (int)O, (int)I, ctx->sm_count, &s_y);
-    const size_t k_x = mcl::tc_splitk_workspace_bytes((int)Nt, (int)I, (int)O, ctx->sm_count, &s_x);
-    const size_t k_w = mcl::tc_splitk_workspace_bytes((int)O, (int)I, (int)Nt, ctx->sm_count, &s_w);
+    const size_t k_y = mcl::tc_splitk_workspace_bytes((int)Nt, (int)O, (int)I, ctx->sm_count, 0, &s_y);
+    const size_t k_x = mcl::tc_splitk_workspace_bytes((int)Nt, (int)I, (int)O, ctx->sm_count, 0, &s_x);
+    const size_t k_w = mcl::tc_splitk_workspace_bytes((int)O, (int)I, (int)Nt, ctx->sm_count, mcl::kGradDepthLimit, &s_w);
     size_t k_max = k_y > k_x ? k_y : k_x;
     if (k_w > k_max) k_max = k_w;
     Carver cv;
@@ -745,7 +747,7 @@ int mcl_cuda_matmul_f32(mcl_cuda_ctx* ctx, const float* a, const float* b, float
         grad_term_list(ctx->grad_terms, pa, pb, &nt, &planes);
         const int ldk = up8(K);
         int splits = 1;
-        const size_t sk = mcl::tc_splitk_workspace_bytes((int)M, (int)N, (int)K, ctx->sm_count, &splits);
+        const size_t sk = mcl::tc_splitk_workspace_bytes((int)M, (int)N, (int)K, ctx->sm_count, mcl::kGradDepthLimit, &splits);
         Carver cv;
         const size_t o_a = cv.reserve((size_t)planes * M * ldk * 2), o_b = cv.reserve((size_t)planes * N * ldk * 2),
                      o_k = cv.reserve(sk);

@@ -425,6 +425,12 @@ def main():
             o[3].copy_(l.v, non_blocking=True)
     ms_e2e, _ = timed(e2e_step, max(2, args.steps // 4), 2)
 
+    # the same step with two bf16 terms per activation and three term products for dW (both settings
+    # keep every product within 1e-5 relative L2 of the fp32 reference; the headline uses 3 / 6)
+    stack.set_gemm_mode("auto", 2, 3)
+    ms_step_23, _ = timed(lambda: stack.step(xs, dys, recorded=not args.eager), args.steps, 3)
+    stack.set_gemm_mode("auto", 3, 6)
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu, _ = cpu_reference_rate(wl)
@@ -437,7 +443,12 @@ def main():
                 "config": {"workload": f"{args.workload}: {wl['desc']}", "tokens_per_gpu": T,
                            "linears": len(wl["linears"]), "weights": alg["weights"],
                            "parallelism": f"dp{world}" if world > 1 else "single",
-                           "l2": "inputs larger than L2 (X and dY of all linears: %.2f GB)" % (in_bytes / 1e9)},
+                           "l2": "inputs larger than L2 (X and dY of all linears: %.2f GB)" % (in_bytes / 1e9),
+                           "precision": "fp32 in/out; tcgen05 bf16 with 3 bf16 terms per fp32 activation (Y, dX) and 6 "
+                                        "term products (dW), fp32 accumulate; relative L2 <= 1e-5 vs the fp32 "
+                                        "reference (measured <= 2.1e-6); counter update bit-exact",
+                           "lanes": args.lanes, "recorded_batch": not args.eager},
+                "value_terms_2_3": T * world / (ms_step_23 * 1e-3),
                 "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
                 "e2e": {"value": T * world / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
                         "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes},

@@ -84,6 +84,17 @@ class CounterStack:
         self._batch_key = None
         self._step_word = torch.zeros(1, dtype=torch.int32, device=dev)
 
+    def set_gemm_mode(self, mode: str = "auto", act_terms: int = 3, grad_terms: int = 6):
+        """Applies to every lane; recorded batches are dropped because they bake the old setting in."""
+        for lane in self.lanes:
+            lane.set_gemm_mode(mode, act_terms, grad_terms)
+        for name in ("_batch", "_upd_batch"):
+            b = getattr(self, name, None)
+            if b is not None:
+                b.close()
+            setattr(self, name, None)
+        self._batch_key = None
+
     def step(self, xs, dys, base_seed: int = 12345, recorded: bool = False):
         """xs[i]: [tokens, in_i], dys[i]: [tokens, out_i] device tensors.  One full step.
 

@@ -34,6 +34,8 @@ struct mcl_cuda_ctx {
     uint64_t recorded_launches = 0;
 };
 
+static bool g_fused_enabled = true;   // environment MCL_CUDA_FUSED=0 turns the grouped fused-split kernel off (A/B timing)
+
 struct mcl_cuda_batch {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
@@ -158,6 +160,7 @@ int create_impl(int device, cudaStream_t stream, bool own, mcl_cuda_ctx** out_ct
         return fail_cuda(nullptr, "context setup", e);
     }
     if (const char* e = std::getenv("MCL_CUDA_TC_MAX_KTILES")) mcl::tc_set_max_ktiles(std::atoi(e));
+    if (const char* e = std::getenv("MCL_CUDA_FUSED")) g_fused_enabled = std::atoi(e) != 0;
     *out_ctx = ctx;
     return MCL_CUDA_OK;
 }
@@ -618,6 +621,86 @@ int mcl_cuda_counter_update_fused(mcl_cuda_ctx* ctx, uint8_t* state, float* scal
 
 // Y, dX and dW of one linear; the ternary digits come from the packed 6-bit state or, when
 // state == NULL, from the 2-bit packed weights.
+// Narrow layers take the grouped kernel that splits fp32 operands in shared memory (tc_fused.cu):
+// every column tile of a product converts its A slab again, so the form pays while a layer has few
+// column tiles; wide layers amortise the pre-split planes of tc_gemm.cu better.
+static bool fused_wanted(const mcl_cuda_ctx* ctx, const float* x, const float* grad_out, const float* scale,
+                         const float* y, const float* grad_x, const float* grad_w, size_t I, size_t O, size_t Nt) {
+    if (!g_fused_enabled || I % 16 != 0 || O % 16 != 0 || Nt % 4 != 0 || I > 1024 || O > 1024) return false;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(grad_out) |
+                           reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(y) |
+                           reinterpret_cast<uintptr_t>(grad_x) | reinterpret_cast<uintptr_t>(grad_w);
+    if (bits & 15) return false;
+    return 2 * (size_t)(6 * 128 * 128) + 8192 <= ctx->max_smem;
+}
+
+static uint32_t pack_products(const int* pa, const int* pb, int n) {
+    uint32_t v = 0;
+    for (int t = 0; t < n; ++t) v |= (uint32_t)(pa[t] | (pb[t] << 2)) << (4 * t);
+    return v;
+}
+
+static int fused_products(mcl_cuda_ctx* ctx, const char* op, const float* x, const float* grad_out,
+                          const uint8_t* state, const uint32_t* packed2, const float* scale, float* y,
+                          float* grad_x, float* grad_w, size_t C, size_t I, size_t O, size_t Nt) {
+    const int ta = ctx->act_terms;
+    int pa[6], pb[6], nt, gp, qa[6], qb[6], qn;
+    grad_term_list(ctx->grad_terms, pa, pb, &nt, &gp);
+    act_term_list(ta, qa, qb, &qn);
+    mcl::FusedProblem pr[3];
+    int n = 0, i_dw = -1;
+    auto base = [&](int mode, int M, int N, int K) {
+        mcl::FusedProblem& p = pr[n];
+        p = mcl::FusedProblem();
+        p.mode = mode; p.M = M; p.N = N; p.K = K;
+        p.packed2 = nullptr; p.p2_stride = (int)(I / 16);
+        return &p;
+    };
+    if (y) {
+        mcl::FusedProblem* p = base(mcl::kFusedY, (int)Nt, (int)O, (int)I);
+        p->a_src = x; p->lda = (int)I; p->col_scale = scale; p->C = y; p->ldc = (int)O;
+        p->na = ta; p->nprod = qn; p->prod = pack_products(qa, qb, qn);
+        mcl::fused_plan(p, 0, 0);
+        ++n;
+    }
+    if (grad_x) {
+        mcl::FusedProblem* p = base(mcl::kFusedDX, (int)Nt, (int)I, (int)O);
+        p->a_src = grad_out; p->lda = (int)O; p->a_kscale = scale; p->C = grad_x; p->ldc = (int)I;
+        p->na = ta; p->nprod = qn; p->prod = pack_products(qa, qb, qn);
+        mcl::fused_plan(p, 0, 0);
+        ++n;
+    }
+    size_t k_floats = 0;
+    if (grad_w) {
+        mcl::FusedProblem* p = base(mcl::kFusedDW, (int)O, (int)I, (int)Nt);
+        p->a_src = grad_out; p->lda = (int)O; p->b_src = x; p->ldb = (int)I; p->C = grad_w; p->ldc = (int)I;
+        p->na = gp; p->nprod = nt; p->prod = pack_products(pa, pb, nt);
+        k_floats = mcl::fused_plan(p, ctx->sm_count, mcl::kGradDepthLimit);
+        i_dw = n++;
+    }
+    Carver cv;
+    const size_t o_p2 = cv.reserve(state ? O * (I / 16) * 4 : 0);
+    const size_t o_k = cv.reserve(k_floats * 4);
+    void* wsp = nullptr;
+    MCL_TRY(ws_reserve(ctx, cv.off, &wsp));
+    char* w = static_cast<char*>(wsp);
+    if (state) {   // the 2-bit form of the state is what the kernel expands
+        MCL_LAUNCH(ctx, op, mcl::launch_pack2(state, reinterpret_cast<uint32_t*>(w + o_p2), (int)C, (int)I, (int)O,
+                                              ctx->sm_count, ctx->stream));
+        packed2 = reinterpret_cast<const uint32_t*>(w + o_p2);
+    }
+    for (int i = 0; i < n; ++i) pr[i].packed2 = packed2;
+    if (i_dw >= 0 && pr[i_dw].splits > 1) { pr[i_dw].C = reinterpret_cast<float*>(w + o_k); pr[i_dw].ldc = (int)I; }
+    int launches = 0;
+    cudaError_t e = mcl::launch_tc_fused(pr, n, ctx->err_word, ctx->max_smem, ctx->sm_count, ctx->stream, &launches);
+    ctx->launches += launches;
+    if (e != cudaSuccess) return fail_cuda(ctx, op, e);
+    if (i_dw >= 0 && pr[i_dw].splits > 1)
+        MCL_LAUNCH(ctx, op, mcl::launch_splitk_reduce(reinterpret_cast<const float*>(w + o_k), grad_w, nullptr, (int)O,
+                                                      (int)I, (int)I, pr[i_dw].splits, ctx->stream));
+    return MCL_CUDA_OK;
+}
+
 static int linear_products(mcl_cuda_ctx* ctx, const char* op, const float* x, const float* grad_out,
                            const uint8_t* state, const uint32_t* packed2, const float* scale, float* y,
                            float* grad_x, float* grad_w, size_t C, size_t I, size_t O, size_t Nt) {
@@ -634,6 +717,8 @@ static int linear_products(mcl_cuda_ctx* ctx, const char* op, const float* x, co
         if (grad_w) MCL_TRY(mcl_cuda_matmul_f32(ctx, grad_out, x, grad_w, O, Nt, I, 1, 0));
         return MCL_CUDA_OK;
     }
+    if (fused_wanted(ctx, x, grad_out, scale, y, grad_x, grad_w, I, O, Nt))
+        return fused_products(ctx, op, x, grad_out, state, packed2, scale, y, grad_x, grad_w, C, I, O, Nt);
     const int ta = ctx->act_terms;
     int pa[6], pb[6], nt, gp;
     grad_term_list(ctx->grad_terms, pa, pb, &nt, &gp);

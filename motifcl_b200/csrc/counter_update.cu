@@ -721,16 +721,16 @@ __global__ void pack2_kernel(const uint8_t* __restrict__ state, uint32_t* __rest
 
 // Opt a kernel in to the device's full dynamic shared memory, once per device and kernel slot.
 cudaError_t ensure_dynamic_smem(const void* kern, int slot, size_t max_smem) {
-    static bool done[64][8] = {};
+    static bool done[64][16] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && slot < 8 && done[dev][slot]) return cudaSuccess;
+    if (dev >= 0 && dev < 64 && slot < 16 && done[dev][slot]) return cudaSuccess;
     cudaFuncAttributes fa;
     cudaError_t e = cudaFuncGetAttributes(&fa, kern);
     if (e != cudaSuccess) return e;
     // the opt-in limit covers static + dynamic shared memory
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(max_smem - fa.sharedSizeBytes));
-    if (e == cudaSuccess && dev >= 0 && dev < 64 && slot < 8) done[dev][slot] = true;
+    if (e == cudaSuccess && dev >= 0 && dev < 64 && slot < 16) done[dev][slot] = true;
     return e;
 }
 

@@ -62,6 +62,31 @@ cudaError_t launch_expand_ternary(const uint8_t* state, int C, int O, int I, voi
 cudaError_t launch_expand_ternary_p2(const uint32_t* packed2, int O, int I, void* T, int ld_i, void* Tt, int ld_o,
                                      cudaStream_t stream);
 
+// tc_fused.cu -- grouped tcgen05 contractions that split fp32 operands to bf16 terms in the kernel
+enum { kFusedY = 0, kFusedDX = 1, kFusedDW = 2 };
+constexpr int kFusedMaxProblems = 128;
+struct FusedProblem {
+    const float* a_src;        // Y, DX: A[m][k] = a_src[m*lda + k];  DW: A[m][k] = a_src[k*lda + m]
+    const float* b_src;        // DW: B[n][k] = b_src[k*ldb + n]
+    const uint32_t* packed2;   // Y: B[n][k] = field(n, k) - 1;  DX: B[n][k] = field(k, n) - 1
+    const float* a_kscale;     // DX: A is multiplied by a_kscale[k] (rounded to fp32) before the split
+    const float* col_scale;    // optional scale of output column n (ignored for split-K partials)
+    float* C;                  // [M, ldc], or split-K partials [splits][M][ldc]
+    int M, N, K, lda, ldb, ldc;
+    int p2_stride;             // 32-bit words per packed2 row
+    int mode;
+    int na;                    // bf16 terms per fp32 operand (2 or 3)
+    int nprod;                 // products per k-tile
+    uint32_t prod;             // 4 bits each: A term | B term << 2
+    int BN, tiles_m, tiles_n, splits, ktiles_per_split, item_begin;   // filled by fused_plan / launch
+};
+// chooses the column tile and the K split of a problem; returns the floats of split-K workspace it needs
+size_t fused_plan(FusedProblem* p, int target_items, int depth_limit);
+cudaError_t launch_tc_fused(FusedProblem* probs, int n, int* err_word, size_t max_smem, int sm_count,
+                            cudaStream_t stream, int* launches);
+cudaError_t launch_splitk_reduce(const float* partial, float* c, const float* col_scale, int M, int N, int ldc,
+                                 int splits, cudaStream_t stream);
+
 // gemv.cu
 cudaError_t launch_ternary_gemv(const float* x, const uint32_t* packed2, const float* scale, float* y,
                                 int M, int in_features, int out_features, int sm_count,

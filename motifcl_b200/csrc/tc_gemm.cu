@@ -538,6 +538,15 @@ cudaError_t launch_tc_gemm(const void* a_planes, int a_nplanes, int lda, size_t 
     return cudaSuccess;
 }
 
+cudaError_t launch_splitk_reduce(const float* partial, float* c, const float* col_scale, int M, int N, int ldc,
+                                 int splits, cudaStream_t stream) {
+    const size_t n4 = (size_t)M * (N / 4);
+    int blocks = (int)((n4 + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(partial, c, col_scale, M, N, ldc, splits);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_split_planes(const float* src, int R, int Cc, const float* col_scale, void* planes, int ld_n,
                                 int nterms, void* planes_t, int ld_t, int nterms_t, cudaStream_t stream) {
     dim3 grid((Cc + 63) / 64, (R + 63) / 64);

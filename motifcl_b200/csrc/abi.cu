@@ -626,73 +626,66 @@ int mcl_cuda_counter_update_fused(mcl_cuda_ctx* ctx, uint8_t* state, float* scal
 // column tiles; wide layers amortise the pre-split planes of tc_gemm.cu better.
 static bool fused_wanted(const mcl_cuda_ctx* ctx, const float* x, const float* grad_out, const float* scale,
                          const float* y, const float* grad_x, const float* grad_w, size_t I, size_t O, size_t Nt) {
-    if (!g_fused_enabled || I % 16 != 0 || O % 16 != 0 || Nt % 4 != 0 || I > 1024 || O > 1024) return false;
+    if (!g_fused_enabled || I % 32 != 0 || O % 32 != 0 || Nt % 4 != 0 || I > 1024 || O > 1024) return false;
     const uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(grad_out) |
                            reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(y) |
                            reinterpret_cast<uintptr_t>(grad_x) | reinterpret_cast<uintptr_t>(grad_w);
     if (bits & 15) return false;
-    return 2 * (size_t)(6 * 128 * 128) + 8192 <= ctx->max_smem;
-}
-
-static uint32_t pack_products(const int* pa, const int* pb, int n) {
-    uint32_t v = 0;
-    for (int t = 0; t < n; ++t) v |= (uint32_t)(pa[t] | (pb[t] << 2)) << (4 * t);
-    return v;
+    return 3 * (size_t)65536 + 8192 <= ctx->max_smem;
 }
 
 static int fused_products(mcl_cuda_ctx* ctx, const char* op, const float* x, const float* grad_out,
                           const uint8_t* state, const uint32_t* packed2, const float* scale, float* y,
                           float* grad_x, float* grad_w, size_t C, size_t I, size_t O, size_t Nt) {
-    const int ta = ctx->act_terms;
-    int pa[6], pb[6], nt, gp, qa[6], qb[6], qn;
-    grad_term_list(ctx->grad_terms, pa, pb, &nt, &gp);
-    act_term_list(ta, qa, qb, &qn);
     mcl::FusedProblem pr[3];
+    mcl::FusedOperand oa[3], ob[3];
     int n = 0, i_dw = -1;
-    auto base = [&](int mode, int M, int N, int K) {
+    size_t k_floats = 0;
+    // the kernel's split-K slices are 32 deep; the depth limit is stated in k-tiles of 64
+    const int depth = 2 * mcl::kGradDepthLimit;
+    auto add = [&](int mode, int M, int N, int K) {
         mcl::FusedProblem& p = pr[n];
         p = mcl::FusedProblem();
         p.mode = mode; p.M = M; p.N = N; p.K = K;
-        p.packed2 = nullptr; p.p2_stride = (int)(I / 16);
         return &p;
     };
+    auto operand = [](const float* p, size_t rows, size_t cols, int mn, int box_outer) {
+        mcl::FusedOperand o = {p, (int)rows, (int)cols, (int)cols, mn, box_outer};
+        return o;
+    };
     if (y) {
-        mcl::FusedProblem* p = base(mcl::kFusedY, (int)Nt, (int)O, (int)I);
-        p->a_src = x; p->lda = (int)I; p->col_scale = scale; p->C = y; p->ldc = (int)O;
-        p->na = ta; p->nprod = qn; p->prod = pack_products(qa, qb, qn);
+        mcl::FusedProblem* p = add(mcl::kFusedY, (int)Nt, (int)O, (int)I);
+        p->col_scale = scale; p->C = y; p->ldc = (int)O;
         mcl::fused_plan(p, 0, 0);
-        ++n;
+        oa[n] = operand(x, Nt, I, 0, 128); ob[n] = operand(nullptr, O, I, 0, p->BN); ++n;
     }
     if (grad_x) {
-        mcl::FusedProblem* p = base(mcl::kFusedDX, (int)Nt, (int)I, (int)O);
-        p->a_src = grad_out; p->lda = (int)O; p->a_kscale = scale; p->C = grad_x; p->ldc = (int)I;
-        p->na = ta; p->nprod = qn; p->prod = pack_products(qa, qb, qn);
+        mcl::FusedProblem* p = add(mcl::kFusedDX, (int)Nt, (int)I, (int)O);
+        p->a_kscale = scale; p->C = grad_x; p->ldc = (int)I;
         mcl::fused_plan(p, 0, 0);
-        ++n;
+        oa[n] = operand(grad_out, Nt, O, 0, 128); ob[n] = operand(nullptr, O, I, 1, p->BN / 32); ++n;
     }
-    size_t k_floats = 0;
     if (grad_w) {
-        mcl::FusedProblem* p = base(mcl::kFusedDW, (int)O, (int)I, (int)Nt);
-        p->a_src = grad_out; p->lda = (int)O; p->b_src = x; p->ldb = (int)I; p->C = grad_w; p->ldc = (int)I;
-        p->na = gp; p->nprod = nt; p->prod = pack_products(pa, pb, nt);
-        k_floats = mcl::fused_plan(p, ctx->sm_count, mcl::kGradDepthLimit);
-        i_dw = n++;
+        mcl::FusedProblem* p = add(mcl::kFusedDW, (int)O, (int)I, (int)Nt);
+        p->C = grad_w; p->ldc = (int)I;
+        k_floats = mcl::fused_plan(p, ctx->sm_count, depth);
+        oa[n] = operand(grad_out, Nt, O, 1, 4); ob[n] = operand(x, Nt, I, 1, p->BN / 32); i_dw = n++;
     }
     Carver cv;
-    const size_t o_p2 = cv.reserve(state ? O * (I / 16) * 4 : 0);
+    const size_t o_t = cv.reserve((y || grad_x) ? O * I * 4 : 0);
     const size_t o_k = cv.reserve(k_floats * 4);
     void* wsp = nullptr;
     MCL_TRY(ws_reserve(ctx, cv.off, &wsp));
     char* w = static_cast<char*>(wsp);
-    if (state) {   // the 2-bit form of the state is what the kernel expands
-        MCL_LAUNCH(ctx, op, mcl::launch_pack2(state, reinterpret_cast<uint32_t*>(w + o_p2), (int)C, (int)I, (int)O,
-                                              ctx->sm_count, ctx->stream));
-        packed2 = reinterpret_cast<const uint32_t*>(w + o_p2);
+    if (y || grad_x) {   // the ternary digits as fp32: the exact operand of Y and dX
+        float* T = reinterpret_cast<float*>(w + o_t);
+        MCL_LAUNCH(ctx, op, mcl::launch_ternary_f32(state, packed2, (int)C, (int)O, (int)I, T, ctx->sm_count, ctx->stream));
+        for (int i = 0; i < n; ++i)
+            if (pr[i].mode != mcl::kFusedDW) ob[i].ptr = T;
     }
-    for (int i = 0; i < n; ++i) pr[i].packed2 = packed2;
-    if (i_dw >= 0 && pr[i_dw].splits > 1) { pr[i_dw].C = reinterpret_cast<float*>(w + o_k); pr[i_dw].ldc = (int)I; }
+    if (i_dw >= 0 && pr[i_dw].splits > 1) pr[i_dw].C = reinterpret_cast<float*>(w + o_k);
     int launches = 0;
-    cudaError_t e = mcl::launch_tc_fused(pr, n, ctx->err_word, ctx->max_smem, ctx->sm_count, ctx->stream, &launches);
+    cudaError_t e = mcl::launch_tc_fused(pr, oa, ob, n, ctx->err_word, ctx->max_smem, ctx->sm_count, ctx->stream, &launches);
     ctx->launches += launches;
     if (e != cudaSuccess) return fail_cuda(ctx, op, e);
     if (i_dw >= 0 && pr[i_dw].splits > 1)

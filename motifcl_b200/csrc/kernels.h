@@ -62,28 +62,35 @@ cudaError_t launch_expand_ternary(const uint8_t* state, int C, int O, int I, voi
 cudaError_t launch_expand_ternary_p2(const uint32_t* packed2, int O, int I, void* T, int ld_i, void* Tt, int ld_o,
                                      cudaStream_t stream);
 
-// tc_fused.cu -- grouped tcgen05 contractions that split fp32 operands to bf16 terms in the kernel
+// tc_fused.cu -- grouped tcgen05 (tf32, two terms) contractions straight from fp32 tensors
 enum { kFusedY = 0, kFusedDX = 1, kFusedDW = 2 };
-constexpr int kFusedMaxProblems = 128;
-struct FusedProblem {
-    const float* a_src;        // Y, DX: A[m][k] = a_src[m*lda + k];  DW: A[m][k] = a_src[k*lda + m]
-    const float* b_src;        // DW: B[n][k] = b_src[k*ldb + n]
-    const uint32_t* packed2;   // Y: B[n][k] = field(n, k) - 1;  DX: B[n][k] = field(k, n) - 1
+constexpr int kFusedMaxProblems = 63;
+struct FusedOperand {          // a row-major fp32 tensor read through TMA (host side only)
+    const float* ptr;
+    int rows, cols, ld;
+    int mn_major;              // read as a transposed operand (cols % 32 == 0): 32-byte-atom swizzle, 3-D box
+    int box_outer;             // rows of the box (K-major) or 32-column chunks per box (MN-major)
+};
+struct FusedProblem {          // C[M,N] = A[M,K] . B[N,K]^T, see the kinds in tc_fused.cu
     const float* a_kscale;     // DX: A is multiplied by a_kscale[k] (rounded to fp32) before the split
     const float* col_scale;    // optional scale of output column n (ignored for split-K partials)
     float* C;                  // [M, ldc], or split-K partials [splits][M][ldc]
-    int M, N, K, lda, ldb, ldc;
-    int p2_stride;             // 32-bit words per packed2 row
+    int M, N, K, ldc;
     int mode;
-    int na;                    // bf16 terms per fp32 operand (2 or 3)
+    int BN, tiles_m, tiles_n, splits, ktiles_per_split;   // filled by fused_plan (k-tiles of 32)
     int nprod;                 // products per k-tile
-    uint32_t prod;             // 4 bits each: A term | B term << 2
-    int BN, tiles_m, tiles_n, splits, ktiles_per_split, item_begin;   // filled by fused_plan / launch
+    uint32_t prod;             // 4 bits each: A term | B term << 2 (0 = hi, 1 = lo), smallest first
+    int a_map, b_map, item_begin;                         // filled by the launcher
 };
 // chooses the column tile and the K split of a problem; returns the floats of split-K workspace it needs
 size_t fused_plan(FusedProblem* p, int target_items, int depth_limit);
-cudaError_t launch_tc_fused(FusedProblem* probs, int n, int* err_word, size_t max_smem, int sm_count,
-                            cudaStream_t stream, int* launches);
+cudaError_t launch_tc_fused(const FusedProblem* probs, const FusedOperand* a_ops, const FusedOperand* b_ops, int n,
+                            int* err_word, size_t max_smem, int sm_count, cudaStream_t stream, int* launches);
+// ternary digits of a layer as fp32 [O][I], from the 6-bit state (state != null) or the 2-bit words
+cudaError_t launch_ternary_f32(const uint8_t* state, const uint32_t* packed2, int C, int O, int I, float* T,
+                               int sm_count, cudaStream_t stream);
+// tc_gemm.cu: TMA map of a row-major fp32 matrix, 128-byte swizzle, zero fill outside
+bool tc_encode_map_f32(void* map, const float* base, int cols, int rows, int ld, int mn_major, int box_outer);
 cudaError_t launch_splitk_reduce(const float* partial, float* c, const float* col_scale, int M, int N, int ldc,
                                  int splits, cudaStream_t stream);
 

@@ -538,6 +538,33 @@ cudaError_t launch_tc_gemm(const void* a_planes, int a_nplanes, int lda, size_t 
     return cudaSuccess;
 }
 
+// K-major use: 2-D {cols, rows}, box {32, box_outer rows}, 128-byte swizzle.  MN-major use (cols % 32 == 0):
+// 3-D {32, rows, cols / 32} with the 32-column chunk as the outermost index, box {32, 32, box_outer chunks},
+// 128-byte swizzle with 32-byte atoms.  Elements outside the tensor read as zero.
+bool tc_encode_map_f32(void* map, const float* base, int cols, int rows, int ld, int mn_major, int box_outer) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return false;
+    CUtensorMap* m = static_cast<CUtensorMap*>(map);
+    void* ptr = const_cast<float*>(base);
+    if (!mn_major) {
+        cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+        cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+        cuuint32_t box[2] = {32, (cuuint32_t)box_outer};
+        cuuint32_t estr[2] = {1, 1};
+        return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
+    if (cols % 32 != 0) return false;
+    cuuint64_t dims[3] = {32, (cuuint64_t)rows, (cuuint64_t)(cols / 32)};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 4, 128};
+    cuuint32_t box[3] = {32, 32, (cuuint32_t)box_outer};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 cudaError_t launch_splitk_reduce(const float* partial, float* c, const float* col_scale, int M, int N, int ldc,
                                  int splits, cudaStream_t stream) {
     const size_t n4 = (size_t)M * (N / 4);

@@ -42,6 +42,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
     return true;
 }
+// The same wait for a whole (converged) warp: one lane polls, so that 32 lanes do not flood the
+// shared-memory pipe with try_wait while the lanes that issue TMA and MMA need it; then every
+// lane confirms the phase itself (one try_wait that succeeds at once), which gives each lane its
+// own acquire of the data the barrier guards.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) {
+        if (!mbar_try_wait(bar, parity)) {
+            const unsigned long long t0 = clock64();
+            unsigned spins = 0;
+            while (!mbar_try_wait(bar, parity)) {
+                __nanosleep(20);
+                if ((++spins & 0xFFu) == 0) {
+                    if (*abort_flag || clock64() - t0 > kWaitCycles) { ok = false; break; }
+                }
+            }
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (ok) ok = mbar_try_wait(bar, parity);      // completed phase: returns true without waiting
+    return __all_sync(0xffffffffu, ok);
+}
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
                                             int c1, int c2) {
     asm volatile(

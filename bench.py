@@ -298,6 +298,7 @@ def main():
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--lanes", type=int, default=8, help="contexts (streams) that independent linears are spread over")
+    ap.add_argument("--no-group", action="store_true", help="one call per linear (spread over --lanes) instead of the grouped step call")
     ap.add_argument("--eager", action="store_true", help="do not record the step into one batch (for per-kernel profiling)")
     ap.add_argument("--micro", default=None, help="single-kernel timing, see run_micro()")
     args = ap.parse_args()
@@ -335,7 +336,7 @@ def main():
         # every rank draws its own tokens (data parallel): offset the linear index by rank
         xs_h.append(torch.from_numpy(synth.activations(cfg, idx + 100 * rank, T, I)).pin_memory())
         dys_h.append(torch.from_numpy(synth.upstream_grad(cfg, idx + 100 * rank, T, O, sigma)).pin_memory())
-    stack = CounterStack(ctx, lin_states, Hyper(), T, group, lanes=args.lanes)
+    stack = CounterStack(ctx, lin_states, Hyper(), T, group, lanes=args.lanes, grouped=not args.no_group)
     xs = [t.to(dev, non_blocking=True) for t in xs_h]
     dys = [t.to(dev, non_blocking=True) for t in dys_h]
     torch.cuda.synchronize()

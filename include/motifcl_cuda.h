@@ -149,6 +149,30 @@ int mcl_cuda_counter_update_fused(mcl_cuda_ctx* ctx, uint8_t* state, float* scal
 #define MCL_CUDA_GEMM_TENSOR 2
 int mcl_cuda_set_gemm_mode(mcl_cuda_ctx* ctx, int mode, int act_terms, int grad_terms);
 
+/* ---- the steps of SEVERAL counter linears in one call (the reference records the dispatches of
+ * a step into one command buffer, include/motifcl/runtime/vulkan_backend.hpp:138 VulkanDispatchRecording; this is
+ * that recording stated as data).  Layer i does exactly what mcl_cuda_counter_linear_step does with
+ * the same arguments; layers whose shapes allow it (in and out features multiples of 32 up to 1024,
+ * 16-byte aligned tensors) share grouped launches: one expansion of the ternary digits, the
+ * products of all layers as one table of tensor-core work items, one split-K reduction, one
+ * update.  Layers are independent: no tensor of one may alias a tensor of another. ---- */
+typedef struct mcl_cuda_linear_desc {
+    const float* x;          /* [batch, in] */
+    const float* grad_out;   /* [batch, out] */
+    uint8_t* state;          /* [out, in/4*3], updated */
+    float* scale;            /* [out], updated */
+    float* v;                /* [out], updated */
+    float* y;                /* [batch, out] or NULL */
+    float* grad_x;           /* [batch, in] or NULL */
+    float* grad_w;           /* [out, in] */
+    uint32_t* packed2_out;   /* [out, in/16] or NULL */
+    size_t in_features, out_features, batch;
+    size_t update_rows, row_offset;   /* as in mcl_cuda_counter_linear_step */
+} mcl_cuda_linear_desc;
+int mcl_cuda_counter_linear_step_many(mcl_cuda_ctx* ctx, const mcl_cuda_linear_desc* layers, size_t n_layers,
+                                      size_t C, float lr, float lr_scale, float rms_beta, float rms_eps,
+                                      uint32_t seed);
+
 /* ---- one whole training step of one counter linear (what MotifCL's autograd does around
  * CounterStateLinear, src/nn/compact_counter.cpp:40-50,266-300, with the dense update of
  * :113-156): y = x W^T; grad_x = (grad_out . scale) T from the PRE-update state; grad_w =

@@ -6,6 +6,7 @@
 #include <cstring>
 #include <new>
 #include <string>
+#include <vector>
 
 #include "kernels.h"
 #include "motifcl_cuda.h"
@@ -150,8 +151,8 @@ int create_impl(int device, cudaStream_t stream, bool own, mcl_cuda_ctx** out_ct
     } else {
         ctx->stream = stream;
     }
-    e = cudaMalloc(reinterpret_cast<void**>(&ctx->err_word), sizeof(int));
-    if (e == cudaSuccess) e = cudaMemset(ctx->err_word, 0, sizeof(int));
+    e = cudaMalloc(reinterpret_cast<void**>(&ctx->err_word), 16 * sizeof(int));    // [0] error word, [1] work-item counter
+    if (e == cudaSuccess) e = cudaMemset(ctx->err_word, 0, 16 * sizeof(int));
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_join, cudaEventDisableTiming);
     if (e != cudaSuccess) {
@@ -624,14 +625,16 @@ int mcl_cuda_counter_update_fused(mcl_cuda_ctx* ctx, uint8_t* state, float* scal
 // Narrow layers take the grouped kernel that splits fp32 operands in shared memory (tc_fused.cu):
 // every column tile of a product converts its A slab again, so the form pays while a layer has few
 // column tiles; wide layers amortise the pre-split planes of tc_gemm.cu better.
-static bool fused_wanted(const mcl_cuda_ctx* ctx, const float* x, const float* grad_out, const float* scale,
-                         const float* y, const float* grad_x, const float* grad_w, size_t I, size_t O, size_t Nt) {
+static bool fused_wanted(const mcl_cuda_ctx* ctx, const float* x, const float* grad_out, const void* ternary,
+                         const float* scale, const float* y, const float* grad_x, const float* grad_w, size_t I,
+                         size_t O, size_t Nt) {
+    (void)ternary;
     if (!g_fused_enabled || I % 32 != 0 || O % 32 != 0 || Nt % 4 != 0 || I > 1024 || O > 1024) return false;
     const uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(grad_out) |
                            reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(y) |
                            reinterpret_cast<uintptr_t>(grad_x) | reinterpret_cast<uintptr_t>(grad_w);
     if (bits & 15) return false;
-    return 3 * (size_t)65536 + 8192 <= ctx->max_smem;
+    return 200 * (size_t)1024 <= ctx->max_smem;
 }
 
 static int fused_products(mcl_cuda_ctx* ctx, const char* op, const float* x, const float* grad_out,
@@ -653,6 +656,12 @@ static int fused_products(mcl_cuda_ctx* ctx, const char* op, const float* x, con
         mcl::FusedOperand o = {p, (int)rows, (int)cols, (int)cols, mn, box_outer};
         return o;
     };
+    if (grad_w) {      // the long work items (K = tokens) first
+        mcl::FusedProblem* p = add(mcl::kFusedDW, (int)O, (int)I, (int)Nt);
+        p->C = grad_w; p->ldc = (int)I;
+        k_floats = mcl::fused_plan(p, ctx->sm_count, depth);
+        oa[n] = operand(grad_out, Nt, O, 1, 4); ob[n] = operand(x, Nt, I, 1, p->BN / 32); i_dw = n++;
+    }
     if (y) {
         mcl::FusedProblem* p = add(mcl::kFusedY, (int)Nt, (int)O, (int)I);
         p->col_scale = scale; p->C = y; p->ldc = (int)O;
@@ -664,12 +673,6 @@ static int fused_products(mcl_cuda_ctx* ctx, const char* op, const float* x, con
         p->a_kscale = scale; p->C = grad_x; p->ldc = (int)I;
         mcl::fused_plan(p, 0, 0);
         oa[n] = operand(grad_out, Nt, O, 0, 128); ob[n] = operand(nullptr, O, I, 1, p->BN / 32); ++n;
-    }
-    if (grad_w) {
-        mcl::FusedProblem* p = add(mcl::kFusedDW, (int)O, (int)I, (int)Nt);
-        p->C = grad_w; p->ldc = (int)I;
-        k_floats = mcl::fused_plan(p, ctx->sm_count, depth);
-        oa[n] = operand(grad_out, Nt, O, 1, 4); ob[n] = operand(x, Nt, I, 1, p->BN / 32); i_dw = n++;
     }
     Carver cv;
     const size_t o_t = cv.reserve((y || grad_x) ? O * I * 4 : 0);
@@ -685,12 +688,13 @@ static int fused_products(mcl_cuda_ctx* ctx, const char* op, const float* x, con
     }
     if (i_dw >= 0 && pr[i_dw].splits > 1) pr[i_dw].C = reinterpret_cast<float*>(w + o_k);
     int launches = 0;
-    cudaError_t e = mcl::launch_tc_fused(pr, oa, ob, n, ctx->err_word, ctx->max_smem, ctx->sm_count, ctx->stream, &launches);
+    cudaError_t e = mcl::launch_tc_fused(pr, oa, ob, n, ctx->err_word, ctx->max_smem, ctx->sm_count, ctx->stream,
+                                         &launches);
     ctx->launches += launches;
     if (e != cudaSuccess) return fail_cuda(ctx, op, e);
     if (i_dw >= 0 && pr[i_dw].splits > 1)
-        MCL_LAUNCH(ctx, op, mcl::launch_splitk_reduce(reinterpret_cast<const float*>(w + o_k), grad_w, nullptr, (int)O,
-                                                      (int)I, (int)I, pr[i_dw].splits, ctx->stream));
+        MCL_LAUNCH(ctx, op, mcl::launch_splitk_reduce(reinterpret_cast<const float*>(w + o_k), grad_w, nullptr, (int)O, (int)I,
+                                                      (int)I, pr[i_dw].splits, ctx->stream));
     return MCL_CUDA_OK;
 }
 
@@ -710,7 +714,7 @@ static int linear_products(mcl_cuda_ctx* ctx, const char* op, const float* x, co
         if (grad_w) MCL_TRY(mcl_cuda_matmul_f32(ctx, grad_out, x, grad_w, O, Nt, I, 1, 0));
         return MCL_CUDA_OK;
     }
-    if (fused_wanted(ctx, x, grad_out, scale, y, grad_x, grad_w, I, O, Nt))
+    if (fused_wanted(ctx, x, grad_out, state ? static_cast<const void*>(state) : packed2, scale, y, grad_x, grad_w, I, O, Nt))
         return fused_products(ctx, op, x, grad_out, state, packed2, scale, y, grad_x, grad_w, C, I, O, Nt);
     const int ta = ctx->act_terms;
     int pa[6], pb[6], nt, gp;
@@ -785,6 +789,178 @@ int mcl_cuda_counter_linear_step(mcl_cuda_ctx* ctx, const float* x, const float*
                                              grad_w + row_offset * I,
                                              packed2_out ? packed2_out + row_offset * (I / 16) : nullptr, C, I,
                                              update_rows, row_offset, lr, lr_scale, rms_beta, rms_eps, seed);
+    return MCL_CUDA_OK;
+}
+
+int mcl_cuda_counter_linear_step_many(mcl_cuda_ctx* ctx, const mcl_cuda_linear_desc* layers, size_t n_layers,
+                                      size_t C, float lr, float lr_scale, float rms_beta, float rms_eps,
+                                      uint32_t seed) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "counter linear step (many)";
+    if (!layers || n_layers == 0) return fail(ctx, MCL_CUDA_EINVAL, "counter linear step (many): no layers");
+    MCL_TRY(check_hypers(ctx, op, lr, lr_scale, rms_beta, rms_eps));
+    std::vector<size_t> grouped, single;
+    for (size_t i = 0; i < n_layers; ++i) {
+        const mcl_cuda_linear_desc& L = layers[i];
+        MCL_TRY(check_counter_dims(ctx, op, C, L.in_features, L.out_features));
+        if (L.batch == 0 || L.batch > 0x7fffffffull) return fail(ctx, MCL_CUDA_EINVAL, "counter linear step (many) requires 0 < batch < 2^31");
+        MCL_TRY(check_ptr(ctx, op, "x", L.x, 4));
+        MCL_TRY(check_ptr(ctx, op, "grad_out", L.grad_out, 4));
+        MCL_TRY(check_ptr(ctx, op, "state", L.state, 1));
+        MCL_TRY(check_ptr(ctx, op, "scale", L.scale, 4));
+        MCL_TRY(check_ptr(ctx, op, "v", L.v, 4));
+        MCL_TRY(check_ptr(ctx, op, "grad_w", L.grad_w, 16));
+        if (L.row_offset + L.update_rows > L.out_features)
+            return fail(ctx, MCL_CUDA_EINVAL, "counter linear step (many): update rows exceed out_features");
+        const bool tc = tc_wanted(ctx, L.batch, L.out_features, L.in_features);
+        if (tc && fused_wanted(ctx, L.x, L.grad_out, L.state, L.scale, L.y, L.grad_x, L.grad_w, L.in_features, L.out_features,
+                               L.batch))
+            grouped.push_back(i);
+        else
+            single.push_back(i);
+    }
+    DeviceGuard guard(ctx->device);
+    for (size_t i : single) {
+        const mcl_cuda_linear_desc& L = layers[i];
+        MCL_TRY(mcl_cuda_counter_linear_step(ctx, L.x, L.grad_out, L.state, L.scale, L.v, L.y, L.grad_x, L.grad_w, L.packed2_out,
+                                             C, L.in_features, L.out_features, L.batch, L.update_rows, L.row_offset, lr,
+                                             lr_scale, rms_beta, rms_eps, seed));
+    }
+    if (grouped.empty()) return MCL_CUDA_OK;
+    const int depth = 2 * mcl::kGradDepthLimit;
+    const size_t ng = grouped.size();
+    // with many layers in flight the K splits of dW only have to respect the accumulation depth
+    const int target_items = (int)((2 * (size_t)ctx->sm_count + ng - 1) / ng);
+    std::vector<mcl::FusedProblem> pr;
+    std::vector<mcl::FusedOperand> oa, ob;
+    std::vector<size_t> t_off(ng), k_off(ng);
+    std::vector<int> dw_splits(ng, 1);
+    Carver cv;
+    auto operand = [](const float* p, size_t rows, size_t cols, int mn, int box_outer) {
+        mcl::FusedOperand o = {p, (int)rows, (int)cols, (int)cols, mn, box_outer};
+        return o;
+    };
+    for (size_t gi = 0; gi < ng; ++gi) {
+        const mcl_cuda_linear_desc& L = layers[grouped[gi]];
+        t_off[gi] = cv.reserve(L.out_features * L.in_features * 4);
+        mcl::FusedProblem p = mcl::FusedProblem();
+        p.mode = mcl::kFusedDW; p.M = (int)L.out_features; p.N = (int)L.in_features; p.K = (int)L.batch;
+        k_off[gi] = cv.reserve(mcl::fused_plan(&p, target_items, depth) * 4);
+        dw_splits[gi] = p.splits;
+    }
+    void* wsp = nullptr;
+    MCL_TRY(ws_reserve(ctx, cv.off, &wsp));
+    char* w = static_cast<char*>(wsp);
+    // 1. ternary digits of every layer as fp32
+    {
+        std::vector<const uint8_t*> st(ng);
+        std::vector<float*> T(ng);
+        std::vector<int> Os(ng), Is(ng);
+        for (size_t gi = 0; gi < ng; ++gi) {
+            const mcl_cuda_linear_desc& L = layers[grouped[gi]];
+            st[gi] = L.state; T[gi] = reinterpret_cast<float*>(w + t_off[gi]);
+            Os[gi] = (int)L.out_features; Is[gi] = (int)L.in_features;
+        }
+        int launches = 0;
+        cudaError_t e = mcl::launch_ternary_f32_group(st.data(), T.data(), Os.data(), Is.data(), (int)ng, (int)C, ctx->sm_count,
+                                                      ctx->stream, &launches);
+        ctx->launches += launches;
+        if (e != cudaSuccess) return fail_cuda(ctx, op, e);
+    }
+    // 2. all products.  A launch takes kFusedMaxProblems problems, i.e. the three products of a third as many
+    // layers; within a launch the long work items (dW: K = tokens) come first so that the short ones fill the tail.
+    {
+        const size_t per_launch = mcl::kFusedMaxProblems / 3;
+        for (size_t g0 = 0; g0 < ng; g0 += per_launch) {
+            const size_t g1 = g0 + per_launch < ng ? g0 + per_launch : ng;
+            for (size_t gi = g0; gi < g1; ++gi) {
+                const mcl_cuda_linear_desc& L = layers[grouped[gi]];
+                const size_t I = L.in_features, O = L.out_features, Nt = L.batch;
+                mcl::FusedProblem p = mcl::FusedProblem();
+                p.mode = mcl::kFusedDW; p.M = (int)O; p.N = (int)I; p.K = (int)Nt;
+                mcl::fused_plan(&p, target_items, depth);
+                p.C = p.splits > 1 ? reinterpret_cast<float*>(w + k_off[gi]) : L.grad_w; p.ldc = (int)I;
+                pr.push_back(p); oa.push_back(operand(L.grad_out, Nt, O, 1, 4)); ob.push_back(operand(L.x, Nt, I, 1, p.BN / 32));
+            }
+            for (size_t gi = g0; gi < g1; ++gi) {
+                const mcl_cuda_linear_desc& L = layers[grouped[gi]];
+                const size_t I = L.in_features, O = L.out_features, Nt = L.batch;
+                const float* T = reinterpret_cast<const float*>(w + t_off[gi]);
+                mcl::FusedProblem p;
+                if (L.y) {
+                    p = mcl::FusedProblem();
+                    p.mode = mcl::kFusedY; p.M = (int)Nt; p.N = (int)O; p.K = (int)I;
+                    p.col_scale = L.scale; p.C = L.y; p.ldc = (int)O;
+                    mcl::fused_plan(&p, 0, 0);
+                    pr.push_back(p); oa.push_back(operand(L.x, Nt, I, 0, 128)); ob.push_back(operand(T, O, I, 0, p.BN));
+                }
+                if (L.grad_x) {
+                    p = mcl::FusedProblem();
+                    p.mode = mcl::kFusedDX; p.M = (int)Nt; p.N = (int)I; p.K = (int)O;
+                    p.a_kscale = L.scale; p.C = L.grad_x; p.ldc = (int)I;
+                    mcl::fused_plan(&p, 0, 0);
+                    pr.push_back(p); oa.push_back(operand(L.grad_out, Nt, O, 0, 128)); ob.push_back(operand(T, O, I, 1, p.BN / 32));
+                }
+            }
+            int launches = 0;
+            cudaError_t e = mcl::launch_tc_fused(pr.data(), oa.data(), ob.data(), (int)pr.size(), ctx->err_word, ctx->max_smem,
+                                                 ctx->sm_count, ctx->stream, &launches);
+            ctx->launches += launches;
+            if (e != cudaSuccess) return fail_cuda(ctx, op, e);
+            pr.clear(); oa.clear(); ob.clear();
+        }
+    }
+    // 3. split-K reductions of dW
+    {
+        std::vector<const float*> part;
+        std::vector<float*> out;
+        std::vector<int> elems, splits;
+        for (size_t gi = 0; gi < ng; ++gi) {
+            if (dw_splits[gi] <= 1) continue;
+            const mcl_cuda_linear_desc& L = layers[grouped[gi]];
+            part.push_back(reinterpret_cast<const float*>(w + k_off[gi]));
+            out.push_back(L.grad_w);
+            elems.push_back((int)(L.out_features * L.in_features));
+            splits.push_back(dw_splits[gi]);
+        }
+        if (!part.empty()) {
+            int launches = 0;
+            cudaError_t e = mcl::launch_splitk_reduce_group(part.data(), out.data(), elems.data(), splits.data(), (int)part.size(),
+                                                            ctx->sm_count, ctx->stream, &launches);
+            ctx->launches += launches;
+            if (e != cudaSuccess) return fail_cuda(ctx, op, e);
+        }
+    }
+    // 4. updates
+    {
+        std::vector<mcl::UpdateDesc> ud;
+        for (size_t gi = 0; gi < ng; ++gi) {
+            const mcl_cuda_linear_desc& L = layers[grouped[gi]];
+            if (L.update_rows == 0) continue;
+            if ((L.row_offset + L.update_rows) * L.in_features > 0xffffffffull)
+                return fail(ctx, MCL_CUDA_EINVAL, "counter update: (row_offset + rows) * in_features exceeds 32-bit element indexing");
+            const size_t I = L.in_features, rb = I / 4 * 3;
+            mcl::UpdateDesc u;
+            u.state = L.state + L.row_offset * rb; u.scale = L.scale + L.row_offset; u.v = L.v + L.row_offset;
+            u.grad_w = L.grad_w + L.row_offset * I;
+            u.packed2 = L.packed2_out ? L.packed2_out + L.row_offset * (I / 16) : nullptr;
+            u.in_features = (int)I; u.rows = (int)L.update_rows; u.row_offset = (int)L.row_offset;
+            ud.push_back(u);
+        }
+        if (!ud.empty()) {
+            int launches = 0;
+            cudaError_t e = mcl::launch_counter_update_group(ud.data(), (int)ud.size(), (int)C, lr, lr_scale, rms_beta, rms_eps, seed,
+                                                             ctx->seed_offset, ctx->sm_count, ctx->max_smem, ctx->stream, &launches);
+            ctx->launches += launches;
+            if (e == cudaErrorNotSupported) {
+                for (const mcl::UpdateDesc& u : ud)
+                    MCL_TRY(mcl_cuda_counter_update_dense(ctx, u.state, u.scale, u.v, u.grad_w, u.packed2, C, (size_t)u.in_features,
+                                                          (size_t)u.rows, (size_t)u.row_offset, lr, lr_scale, rms_beta, rms_eps, seed));
+            } else if (e != cudaSuccess) {
+                return fail_cuda(ctx, op, e);
+            }
+        }
+    }
     return MCL_CUDA_OK;
 }
 

@@ -386,9 +386,13 @@ __host__ __device__ inline U16Layout u16_layout(int I, int R, bool with_q) {
     return L;
 }
 
+// Body shared by the single-layer and the grouped kernel: batches batch0, batch0 + batch_step, ... of the
+// layer `p`.  The decode and tail tables depend on C alone; `build_tables` is false when an earlier call
+// of the same CTA already built them for this C.
 template <bool WITH_Q>
-__global__ void __launch_bounds__(kUpdThreads, 4)
-counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const uint32_t pow16, const uint32_t pow17) {
+__device__ __forceinline__ void update_u16_body(const UpdParams& p, const uint32_t unit_magic, const uint32_t pow16,
+                                                const uint32_t pow17, const int batch0, const int batch_step,
+                                                const bool build_tables) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int I = p.in_features;
     const int gpr = I >> 2;               // packed groups (float4s) per row
@@ -422,8 +426,8 @@ counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const ui
     const uint32_t seed = p.seed + (p.seed_offset ? __ldg(p.seed_offset) : 0u);
     const bool aligned16 = p.state_align >= 16;
 
-    build_decode_lut(lut, p.C, tid, kUpdThreads);
-    for (int e = tid; e < 4 * kTail16; e += kUpdThreads) {     // kernels/compact_counter.cl:129-136
+    if (build_tables) build_decode_lut(lut, p.C, tid, kUpdThreads);
+    for (int e = tid; build_tables && e < 4 * kTail16; e += kUpdThreads) {     // kernels/compact_counter.cl:129-136
         const int t = e / kTail16 - 1;
         const float ccv = (float)(e % kTail16 - 128);
         const float carry = truncf(__fdiv_rn(ccv, Cf));
@@ -439,7 +443,7 @@ counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const ui
     __syncthreads();
 
     const int nbatches = (p.rows + R - 1) / R;
-    for (int batch = blockIdx.x; batch < nbatches; batch += gridDim.x) {
+    for (int batch = batch0; batch < nbatches; batch += batch_step) {
         const int row0 = batch * R;
         const int nrows = min(R, p.rows - row0);
 
@@ -660,6 +664,35 @@ counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const ui
     }
 }
 
+template <bool WITH_Q>
+__global__ void __launch_bounds__(kUpdThreads, 4)
+counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const uint32_t pow16, const uint32_t pow17) {
+    update_u16_body<WITH_Q>(p, unit_magic, pow16, pow17, blockIdx.x, gridDim.x, true);
+}
+
+// Several layers in one launch: their batches form one sequence that is dealt round-robin to the CTAs.
+constexpr int kUpdGroupCap = 64;
+struct UpdGroup {
+    int n;
+    int batch_begin[kUpdGroupCap + 1];
+    uint32_t magic[kUpdGroupCap];
+    UpdParams p[kUpdGroupCap];
+};
+template <bool WITH_Q>
+__global__ void __launch_bounds__(kUpdThreads, 4)
+counter_update_u16_group_kernel(const __grid_constant__ UpdGroup g, const uint32_t pow16, const uint32_t pow17) {
+    const int grid = (int)gridDim.x, b = (int)blockIdx.x;
+    int built_c = -1;
+    for (int j = 0; j < g.n; ++j) {
+        // first batch of layer j whose global index is congruent to this CTA
+        int first = (b - g.batch_begin[j]) % grid;
+        if (first < 0) first += grid;
+        if (first >= g.batch_begin[j + 1] - g.batch_begin[j]) continue;
+        update_u16_body<WITH_Q>(g.p[j], g.magic[j], pow16, pow17, first, grid, g.p[j].C != built_c);
+        built_c = g.p[j].C;
+    }
+}
+
 size_t upd_smem_bytes(int I, int R, bool with_q) {
     const int gpr = I / 4;
     const size_t sb = (size_t)((gpr * 3 + 15) & ~15) + 16;
@@ -793,6 +826,63 @@ cudaError_t launch_counter_update_dense(uint8_t* state, float* scale, float* v, 
     if (e != cudaSuccess) return e;
     kern<<<grid, kUpdThreads, smem, stream>>>(p);
     return cudaGetLastError();
+}
+
+// The fused update of several layers in one launch (same C and hyper-parameters).  Returns
+// cudaErrorNotSupported, having launched nothing, when a layer does not qualify for the 16-weight
+// kernel; the caller then updates layer by layer.
+cudaError_t launch_counter_update_group(const UpdateDesc* d, int n, int C, float lr, float lr_scale, float rms_beta,
+                                        float rms_eps, uint32_t seed, const uint32_t* seed_offset, int sm_count,
+                                        size_t max_smem, cudaStream_t stream, int* launches) {
+    const bool with_q = (lr_scale != 0.0f);
+    const size_t target = (max_smem - 4096) / 4;
+    for (int i = 0; i < n; ++i) {
+        if (d[i].in_features % 16 != 0 || reinterpret_cast<uintptr_t>(d[i].state) % 4 != 0) return cudaErrorNotSupported;
+        if (u16_layout(d[i].in_features, 1, with_q).total > max_smem - 1024) return cudaErrorNotSupported;
+    }
+    for (int done = 0; done < n;) {
+        UpdGroup g;
+        const int take = n - done < kUpdGroupCap ? n - done : kUpdGroupCap;
+        size_t smem = 0;
+        int batches = 0;
+        for (int j = 0; j < take; ++j) {
+            const UpdateDesc& u = d[done + j];
+            int Ru = kMaxRowsU16;
+            while (Ru > 1 && u16_layout(u.in_features, Ru, with_q).total > target) --Ru;
+            const U16Layout L = u16_layout(u.in_features, Ru, with_q);
+            if (L.total > smem) smem = L.total;
+            UpdParams& p = g.p[j];
+            p.state = u.state; p.scale = u.scale; p.v = u.v; p.grad_w = u.grad_w; p.packed2 = u.packed2;
+            p.C = C; p.in_features = u.in_features; p.rows = u.rows; p.row_offset = u.row_offset;
+            p.rows_per_batch = Ru;
+            const uintptr_t sp = reinterpret_cast<uintptr_t>(u.state), pp = reinterpret_cast<uintptr_t>(u.packed2);
+            p.state_align = (u.in_features % 64 == 0 && sp % 16 == 0 && pp % 16 == 0) ? 16 : 4;
+            p.lr = lr; p.lr_scale = lr_scale; p.rms_beta = rms_beta; p.rms_eps = rms_eps;
+            p.seed = seed; p.seed_offset = seed_offset;
+            const uint32_t upr = (uint32_t)(u.in_features / 16);
+            g.magic[j] = upr == 1 ? 0u : (uint32_t)((0x100000000ull + upr - 1) / upr);
+            g.batch_begin[j] = batches;
+            batches += (u.rows + Ru - 1) / Ru;
+        }
+        g.batch_begin[take] = batches;
+        g.n = take;
+        int per_sm = (int)((max_smem - 1024) / smem);
+        if (per_sm > 4) per_sm = 4;
+        if (per_sm < 1) per_sm = 1;
+        int grid = sm_count * per_sm;
+        if (grid > batches) grid = batches;
+        if (grid > 0) {
+            auto kern = with_q ? counter_update_u16_group_kernel<true> : counter_update_u16_group_kernel<false>;
+            cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), with_q ? 8 : 9, max_smem);
+            if (e != cudaSuccess) return e;
+            kern<<<grid, kUpdThreads, smem, stream>>>(g, 1u << 16, 1u << 17);
+            e = cudaGetLastError();
+            if (e != cudaSuccess) return e;
+            ++*launches;
+        }
+        done += take;
+    }
+    return cudaSuccess;
 }
 
 cudaError_t launch_decode_weight(const uint8_t* state, const float* scale, float* w, int C,

@@ -15,6 +15,17 @@ cudaError_t launch_counter_update_dense(uint8_t* state, float* scale, float* v, 
                                         int row_offset, float lr, float lr_scale, float rms_beta,
                                         float rms_eps, uint32_t seed, const uint32_t* seed_offset, int sm_count,
                                         size_t max_smem, cudaStream_t stream);
+struct UpdateDesc {            // rows [row_offset, row_offset + rows) of one layer; pointers at the first row
+    uint8_t* state;
+    float* scale;
+    float* v;
+    const float* grad_w;
+    uint32_t* packed2;         // may be null
+    int in_features, rows, row_offset;
+};
+cudaError_t launch_counter_update_group(const UpdateDesc* d, int n, int C, float lr, float lr_scale, float rms_beta,
+                                        float rms_eps, uint32_t seed, const uint32_t* seed_offset, int sm_count,
+                                        size_t max_smem, cudaStream_t stream, int* launches);
 cudaError_t launch_decode_weight(const uint8_t* state, const float* scale, float* w, int C,
                                  int in_features, int out_features, int sm_count, cudaStream_t stream);
 cudaError_t launch_pack2(const uint8_t* state, uint32_t* packed2, int C, int in_features,
@@ -84,11 +95,17 @@ struct FusedProblem {          // C[M,N] = A[M,K] . B[N,K]^T, see the kinds in t
 };
 // chooses the column tile and the K split of a problem; returns the floats of split-K workspace it needs
 size_t fused_plan(FusedProblem* p, int target_items, int depth_limit);
+// err_word points at two ints: the error word and the work-item counter (zeroed by the launcher)
 cudaError_t launch_tc_fused(const FusedProblem* probs, const FusedOperand* a_ops, const FusedOperand* b_ops, int n,
                             int* err_word, size_t max_smem, int sm_count, cudaStream_t stream, int* launches);
 // ternary digits of a layer as fp32 [O][I], from the 6-bit state (state != null) or the 2-bit words
 cudaError_t launch_ternary_f32(const uint8_t* state, const uint32_t* packed2, int C, int O, int I, float* T,
                                int sm_count, cudaStream_t stream);
+// grouped forms: one launch for the layers of a step
+cudaError_t launch_ternary_f32_group(const uint8_t* const* state, float* const* T, const int* O, const int* I, int n, int C,
+                                     int sm_count, cudaStream_t stream, int* launches);
+cudaError_t launch_splitk_reduce_group(const float* const* partial, float* const* out, const int* elements, const int* splits,
+                                       int n, int sm_count, cudaStream_t stream, int* launches);
 // tc_gemm.cu: TMA map of a row-major fp32 matrix, 128-byte swizzle, zero fill outside
 bool tc_encode_map_f32(void* map, const float* base, int cols, int rows, int ld, int mn_major, int box_outer);
 cudaError_t launch_splitk_reduce(const float* partial, float* c, const float* col_scale, int M, int N, int ldc,

@@ -26,8 +26,10 @@
 // operand has; the tensor core reads it in place (instruction-descriptor transpose bits), so no
 // transposed copy of an activation is ever made.
 //
-// CTA = 16 warps, 3 shared-memory stages of one 32-deep k-tile each:
-//   warp 0        TMA producer (one lane): 32 x 32 boxes of A and B, mbarrier complete_tx
+// CTA = 16 warps.  Shared memory holds two rings of 32-deep k-tiles: the RAW ring (4 to 6 slots: A and B
+// as TMA delivers them; deep, because it has to cover the latency of HBM) and the LO ring (2 slots:
+// the lo tiles, which only bridge converter and MMA).
+//   warp 0        one lane draws work items from a global counter and issues the TMA copies
 //   warp 1        allocates TMEM; one lane issues tcgen05.mma and commits
 //   warps 4..7    epilogue: tcgen05.ld of TMEM lane quarter (warp & 3), scale, 128-bit stores
 //   warps 8..15   converters: wait for the boxes, write the `lo` tiles (and the scaled `hi` tile
@@ -49,18 +51,20 @@ constexpr int kFThreads = 16 * 32;
 constexpr int kEpiWarp0 = 4;
 constexpr int kConvWarp0 = 8;
 constexpr int kConvThreads = 8 * 32;
-constexpr int kStages = 3;
 constexpr int kBox = 32 * 32 * 4;            // bytes of one 32 x 32 fp32 box
-constexpr int kALo = 4 * kBox;               // stage layout: A hi (4 boxes), A lo, B hi (<= 8 boxes) ...
-constexpr int kBHi = 8 * kBox;               // ... and, for two fp32 operands, B lo at kBHi + 4 boxes
-constexpr int kBLo = 12 * kBox;
-constexpr int kStage = 16 * kBox;            // 64 KiB
+constexpr int kABytes = 4 * kBox;            // an A tile: 128 rows (or 128 m) x 32 k
+constexpr int kMaxRaw = 6;                   // slots of the raw ring (A hi + B hi as TMA delivers them)
+constexpr int kLoSlots = 2;                  // slots of the lo ring (A lo, and B lo for two fp32 operands)
+constexpr int kQueue = 4;                    // work items in flight between the scheduler lane and the other roles
+constexpr int kQueueReaders = 1 + 4 + 8;     // MMA lane, epilogue warps, converter warps
+constexpr int kScratch = 4 * 4096;           // epilogue staging, 4 KiB per warp
 constexpr int kAccStride = 256;              // TMEM columns between the two accumulators
 
 template <int CAP>
 struct FusedTable {
     CUtensorMap maps[2 * CAP];
-    int n_problems, n_items, pad0, pad1;
+    int n_problems, n_items;
+    int n_raw, raw_slot, lo_slot, pad0;      // ring geometry (bytes), chosen by the launcher for the table's tiles
     FusedProblem p[CAP];
 };
 
@@ -87,11 +91,12 @@ struct Item {
     int pi, mt, nt, kt0, nkt, split;
 };
 
-// item -> problem (items of a problem are contiguous; `pi` only moves forward)
-template <int CAP>
-__device__ __forceinline__ Item decode_item(const FusedTable<CAP>& tab, int item, int& pi) {
-    while (pi + 1 < tab.n_problems && item >= tab.p[pi + 1].item_begin) ++pi;
-    const FusedProblem& P = tab.p[pi];
+// item -> problem (items of a problem are contiguous; `pi` only moves forward).  `sp` is the CTA's copy of
+// the problem table in shared memory: the roles walk it at every item, and the constant bank that holds
+// the kernel argument is far too small a cache for it.
+__device__ __forceinline__ Item decode_item(const FusedProblem* sp, int n_problems, int item, int& pi) {
+    while (pi + 1 < n_problems && item >= sp[pi + 1].item_begin) ++pi;
+    const FusedProblem& P = sp[pi];
     const int local = item - P.item_begin;
     Item it;
     it.pi = pi;
@@ -125,8 +130,9 @@ __device__ __forceinline__ float4 lo_term4(float4 v) {
     return make_float4(lo_term(v.x), lo_term(v.y), lo_term(v.z), lo_term(v.w));
 }
 
+
 #ifdef MCL_FUSED_PROF
-__device__ long long g_fused_prof[148 * 16];
+__device__ long long g_fused_prof[148 * 16 + 148 * 8];
 #define PROF_T(var) const long long var = clock64()
 #define PROF_ADD(acc, a, b) acc += (b) - (a)
 #else
@@ -135,30 +141,49 @@ __device__ long long g_fused_prof[148 * 16];
 #endif
 
 template <int CAP>
-__global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_constant__ FusedTable<CAP> tab, int* err) {
+__global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_constant__ FusedTable<CAP> tab, int* err,
+                                                                int* next_item) {
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bars[3 * kStages + 4];
+    __shared__ __align__(8) uint64_t bars[2 * kMaxRaw + 4 + 4 + 2 * kQueue];
+    __shared__ int queue_item[kQueue];
+    __shared__ FusedProblem sp[CAP];
+#ifdef MCL_FUSED_PROF
+    __shared__ long long t_issue[kMaxRaw], t_conv[kMaxRaw], t_arr[kMaxRaw], t_mma[kMaxRaw], t_commit[kMaxRaw];
+#endif
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int n_raw = tab.n_raw;
+    const uint32_t raw_slot = (uint32_t)tab.raw_slot, lo_slot = (uint32_t)tab.lo_slot;
+    const uint32_t raw0 = (smem_u32(smem_raw) + 1023u) & ~1023u;        // raw ring: A hi at +0, B hi at +kABytes
+    const uint32_t lo0 = raw0 + (uint32_t)n_raw * raw_slot;             // lo ring:  A lo at +0, B lo at +kABytes
+    const uint32_t scratch0 = lo0 + (uint32_t)kLoSlots * lo_slot;       // 4 KiB per epilogue warp
     const uint32_t bar0 = smem_u32(bars);
-    auto tma_full = [&](int s) { return bar0 + 8u * s; };
-    auto conv_full = [&](int s) { return bar0 + 8u * (kStages + s); };
-    auto empty_bar = [&](int s) { return bar0 + 8u * (2 * kStages + s); };
-    auto acc_full = [&](int a) { return bar0 + 8u * (3 * kStages + a); };
-    auto acc_empty = [&](int a) { return bar0 + 8u * (3 * kStages + 2 + a); };
+    auto raw_full = [&](int s) { return bar0 + 8u * s; };
+    auto raw_empty = [&](int s) { return bar0 + 8u * (kMaxRaw + s); };
+    auto lo_full = [&](int s) { return bar0 + 8u * (2 * kMaxRaw + s); };
+    auto lo_empty = [&](int s) { return bar0 + 8u * (2 * kMaxRaw + 2 + s); };
+    auto acc_full = [&](int a) { return bar0 + 8u * (2 * kMaxRaw + 4 + a); };
+    auto acc_empty = [&](int a) { return bar0 + 8u * (2 * kMaxRaw + 6 + a); };
+    auto q_full = [&](int s) { return bar0 + 8u * (2 * kMaxRaw + 8 + s); };
+    auto q_empty = [&](int s) { return bar0 + 8u * (2 * kMaxRaw + 8 + kQueue + s); };
 
     if (threadIdx.x == 0) {
         abort_flag = (*reinterpret_cast<volatile int*>(err) != 0);
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(tma_full(s), 1);
-            mbar_init(conv_full(s), kConvThreads);
-            mbar_init(empty_bar(s), 1);
-        }
+        for (int s = 0; s < kMaxRaw; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), 1); }
+        for (int s = 0; s < kLoSlots; ++s) { mbar_init(lo_full(s), kConvThreads); mbar_init(lo_empty(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 128); }
+        for (int s = 0; s < kQueue; ++s) { mbar_init(q_full(s), 1); mbar_init(q_empty(s), kQueueReaders); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    const int n_problems = tab.n_problems;
+    {
+        static_assert(sizeof(FusedProblem) % 4 == 0, "FusedProblem is copied word by word");
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(tab.p);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(sp);
+        const int words = n_problems * (int)(sizeof(FusedProblem) / 4);
+        for (int i = threadIdx.x; i < words; i += kFThreads) dst[i] = src[i];
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -171,50 +196,111 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
     const uint32_t tmem_base = tmem_slot;
     const int n_items = tab.n_items;
 
+    // Work items come from a global counter (long items first), so CTAs stay busy until the table is
+    // empty.  The TMA lane draws them and passes every item number, the end marker included, to the
+    // other roles through a small queue in shared memory.
+    uint32_t q_seq = 0;
+    auto next_from_queue = [&]() -> int {       // called by converged warps (or by the single MMA lane)
+        const int s = (int)(q_seq % kQueue);
+        int item = n_items;
+        if (mbar_wait_warp(q_full(s), (q_seq / kQueue) & 1u, &abort_flag)) {
+            item = *reinterpret_cast<volatile int*>(&queue_item[s]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(q_empty(s));
+        } else {
+            abort_flag = 1;
+            atomicExch(err, 16);
+        }
+        ++q_seq;
+        return item;
+    };
+
     if (warp == 0) {
         if (lane == 0) {
-            // ---- TMA producer ----------------------------------------------------------------------
-            uint32_t it = 0;
+            // ---- scheduler + TMA producer --------------------------------------------------------------
+            uint32_t it = 0, rs = 0, rph = 0;          // tiles issued, raw slot, its phase parity
             int pi = 0;
             long long pf_wait = 0, pf_issue = 0; (void)pf_wait; (void)pf_issue;
+            long long h0 = 0, h1 = 0, h2 = 0, h3 = 0, h4 = 0; (void)h0; (void)h1; (void)h2; (void)h3; (void)h4;
             PROF_T(tstart);
-            for (int item = blockIdx.x; item < n_items && !abort_flag; item += gridDim.x) {
-                const Item I = decode_item(tab, item, pi);
-                const FusedProblem& P = tab.p[I.pi];
+            int drawn = atomicAdd(next_item, 1);
+            for (;;) {
+                const int item = abort_flag ? n_items : drawn;
+                if (item < n_items) drawn = atomicAdd(next_item, 1);      // in flight while this item is issued
+                {
+                    const int s = (int)(q_seq % kQueue);
+                    if (!mbar_wait(q_empty(s), ((q_seq / kQueue) & 1u) ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 17); break; }
+                    *reinterpret_cast<volatile int*>(&queue_item[s]) = item < n_items ? item : n_items;
+                    mbar_arrive(q_full(s));
+                    ++q_seq;
+                }
+                if (item >= n_items) break;
+                const Item I = decode_item(sp, n_problems, item, pi);
+                const FusedProblem& P = sp[I.pi];
                 const CUtensorMap* ma = &tab.maps[P.a_map];
                 const CUtensorMap* mb = &tab.maps[P.b_map];
-                const int m0 = I.mt * 128, n0 = I.nt * P.BN;
+                const int m0 = I.mt * 128, n0 = I.nt * P.BN, mode = P.mode;
+                const uint32_t bytes = (uint32_t)kABytes + (uint32_t)P.BN * 128u;
                 for (int j = 0; j < I.nkt; ++j, ++it) {
-                    const int s = (int)(it % kStages);
-                    const uint32_t ph = (it / kStages) & 1u;
+                    const int s = (int)rs;
+                    const uint32_t ph = rph;
+                    if (++rs == (uint32_t)n_raw) { rs = 0; rph ^= 1u; }
                     PROF_T(t0);
-                    if (!mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 11); break; }
+                    if (!mbar_wait(raw_empty(s), ph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 11); break; }
                     PROF_T(t1); PROF_ADD(pf_wait, t0, t1);
-                    const uint32_t st = tiles + (uint32_t)s * kStage;
+#ifdef MCL_FUSED_PROF
+                    if (it >= (uint32_t)n_raw) {
+                        h0 += t_conv[s] - t_issue[s]; h1 += t_arr[s] - t_conv[s]; h2 += t_mma[s] - t_arr[s];
+                        h3 += t_commit[s] - t_mma[s]; h4 += t1 - t_commit[s];
+                    }
+#endif
+                    const uint32_t st = raw0 + (uint32_t)s * raw_slot;
                     const int k0 = (I.kt0 + j) * 32;
-                    mbar_expect_tx(tma_full(s), 4u * kBox + (uint32_t)P.BN * 128u);
+#ifdef MCL_FUSED_PROF
+                    t_issue[s] = clock64();
+#endif
+                    mbar_expect_tx(raw_full(s), bytes);
                     // K-major: one box of 32 k x rows; MN-major: one box of 32 m x 32 k x chunks (3-D map)
-                    if (P.mode == kFusedDW) tma_load_3d(st, ma, tma_full(s), 0, k0, m0 >> 5);
-                    else tma_load_2d(st, ma, tma_full(s), k0, m0);
-                    if (P.mode == kFusedY) tma_load_2d(st + kBHi, mb, tma_full(s), k0, n0);
-                    else tma_load_3d(st + kBHi, mb, tma_full(s), 0, k0, n0 >> 5);
+                    // K-major: one box of 32 k x rows; MN-major: one box of 32 m x 32 k x chunks (3-D map)
+                    if (mode == kFusedDW) tma_load_3d(st, ma, raw_full(s), 0, k0, m0 >> 5);
+                    else tma_load_2d(st, ma, raw_full(s), k0, m0);
+                    if (mode == kFusedY) tma_load_2d(st + kABytes, mb, raw_full(s), k0, n0);
+                    else tma_load_3d(st + kABytes, mb, raw_full(s), 0, k0, n0 >> 5);
                     PROF_T(t2); PROF_ADD(pf_issue, t1, t2);
+                }
+                if (abort_flag) {      // tell the other roles to stop
+                    const int s = (int)(q_seq % kQueue);
+                    if (mbar_wait(q_empty(s), ((q_seq / kQueue) & 1u) ^ 1u, &abort_flag)) {
+                        *reinterpret_cast<volatile int*>(&queue_item[s]) = n_items;
+                        mbar_arrive(q_full(s));
+                    }
+                    break;
                 }
             }
 #ifdef MCL_FUSED_PROF
-            { PROF_T(tend); long long* o = g_fused_prof + blockIdx.x * 16; o[0] = pf_wait; o[1] = pf_issue; o[2] = tend - tstart; o[3] = it; }
+            { PROF_T(tend); long long* o = g_fused_prof + blockIdx.x * 16; o[0] = pf_wait; o[1] = pf_issue; o[2] = tend - tstart; o[3] = it; long long* o2 = g_fused_prof + 148 * 16 + blockIdx.x * 8; o2[0] = h0; o2[1] = h1; o2[2] = h2; o2[3] = h3; o2[4] = h4; }
 #endif
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- MMA issuer ------------------------------------------------------------------------
-            uint32_t it = 0, n_local = 0;
+            uint32_t it = 0, n_local = 0, rs = 0, rph = 0;
             int pi = 0;
             long long pf_acc = 0, pf_full = 0, pf_issue = 0; (void)pf_acc; (void)pf_full; (void)pf_issue;
             PROF_T(tstart);
-            for (int item = blockIdx.x; item < n_items && !abort_flag; item += gridDim.x, ++n_local) {
-                const Item I = decode_item(tab, item, pi);
-                const FusedProblem& P = tab.p[I.pi];
+            for (;; ++n_local) {
+                int item = n_items;
+                {   // single-lane form of next_from_queue
+                    const int s = (int)(q_seq % kQueue);
+                    if (mbar_wait(q_full(s), (q_seq / kQueue) & 1u, &abort_flag)) {
+                        item = *reinterpret_cast<volatile int*>(&queue_item[s]);
+                        mbar_arrive(q_empty(s));
+                    } else { abort_flag = 1; atomicExch(err, 16); }
+                    ++q_seq;
+                }
+                if (item >= n_items || abort_flag) break;
+                const Item I = decode_item(sp, n_problems, item, pi);
+                const FusedProblem& P = sp[I.pi];
                 const bool a_mn = P.mode == kFusedDW, b_mn = P.mode != kFusedY;
                 const uint32_t idesc = idesc_tf32(128, P.BN, a_mn, b_mn);
                 // descriptor words: low = address / 16 | leading byte offset / 16 << 16, high = stride byte offset / 16 |
@@ -225,6 +311,11 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 const uint32_t a_hi = a_mn ? ((512u >> 4) | (1u << 14) | (1u << 29)) : ((1024u >> 4) | (1u << 14) | (2u << 29));
                 const uint32_t b_hi = b_mn ? ((512u >> 4) | (1u << 14) | (1u << 29)) : ((1024u >> 4) | (1u << 14) | (2u << 29));
                 const uint32_t nprod = (uint32_t)P.nprod, prod0 = P.prod;
+                #ifdef MCL_FUSED_PROF
+                const bool early = (tab.pad0 & 16) && P.mode != kFusedDX;
+#else
+                const bool early = false;                   // hi.hi before the converters finish: measured slower overall
+#endif
                 const uint32_t acc = n_local & 1u, aph = (n_local >> 1) & 1u;
                 PROF_T(ta0);
                 if (!mbar_wait(acc_empty(acc), aph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 14); break; }
@@ -233,16 +324,14 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 const uint32_t d_tmem = tmem_base + acc * kAccStride;
                 uint32_t accum = 0;
                 for (int j = 0; j < I.nkt; ++j, ++it) {
-                    const int s = (int)(it % kStages);
-                    PROF_T(t0);
-                    if (!mbar_wait(conv_full(s), (it / kStages) & 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 12); break; }
-                    PROF_T(t1); PROF_ADD(pf_full, t0, t1);
-                    tc_fence_after();
-                    const uint32_t st16 = (tiles + (uint32_t)s * kStage) >> 4;
+                    const int s = (int)rs, sl = (int)(it % kLoSlots);
+                    const uint32_t ph = rph;
+                    if (++rs == (uint32_t)n_raw) { rs = 0; rph ^= 1u; }
+                    const uint32_t hi16 = (raw0 + (uint32_t)s * raw_slot) >> 4, lo16 = (lo0 + (uint32_t)sl * lo_slot) >> 4;
                     uint32_t prod = prod0;
-                    for (uint32_t q = 0; q < nprod; ++q, prod >>= 4) {
-                        const uint32_t a16 = a_lo | (st16 + ((prod & 3u) ? (kALo >> 4) : 0u));
-                        const uint32_t b16 = b_lo | (st16 + (((prod >> 2) & 3u) ? (kBLo >> 4) : (kBHi >> 4)));
+                    auto issue = [&](uint32_t pr) {
+                        const uint32_t a16 = a_lo | ((pr & 3u) ? lo16 : hi16);
+                        const uint32_t b16 = b_lo | ((((pr >> 2) & 3u) ? lo16 : hi16) + (kABytes >> 4));
 #pragma unroll
                         for (uint32_t kk = 0; kk < 4; ++kk) {
                             const uint64_t da = ((uint64_t)a_hi << 32) | (uint64_t)(a16 + kk * a_step);
@@ -250,9 +339,37 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                             umma_tf32(d_tmem, da, db, idesc, accum);
                             accum = 1u;
                         }
+                    };
+                    PROF_T(t0);
+                    uint32_t q = 0;
+                    if (early) {
+                        // the hi.hi product reads only what TMA delivered: it runs while the converters work
+                        if (!mbar_wait(raw_full(s), ph, &abort_flag)) { abort_flag = 1; atomicExch(err, 18); break; }
+                        tc_fence_after();
+#ifdef MCL_FUSED_PROF
+                        if (!(tab.pad0 & 2))
+#endif
+                        issue(prod);
+                        prod >>= 4;
+                        q = 1;
                     }
-                    umma_commit(empty_bar(s));
+                    // the converters arrive after they have seen the raw tile, so this wait covers both rings
+                    if (!mbar_wait(lo_full(sl), (it / kLoSlots) & 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 12); break; }
+                    PROF_T(t1); PROF_ADD(pf_full, t0, t1);
+#ifdef MCL_FUSED_PROF
+                    t_mma[s] = t1;
+#endif
+                    tc_fence_after();
+#ifdef MCL_FUSED_PROF
+                    if (!(tab.pad0 & 2))
+#endif
+                    for (; q < nprod; ++q, prod >>= 4) issue(prod);
+                    umma_commit(raw_empty(s));
+                    umma_commit(lo_empty(sl));
                     PROF_T(t2); PROF_ADD(pf_issue, t1, t2);
+#ifdef MCL_FUSED_PROF
+                    t_commit[s] = t2;
+#endif
                 }
                 if (abort_flag) break;
                 umma_commit(acc_full(acc));
@@ -268,10 +385,12 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
         int pi = 0;
         long long pf_wait = 0, pf_store = 0; (void)pf_wait; (void)pf_store;
         PROF_T(tstart);
-        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_local) {
+        for (;; ++n_local) {
             PROF_T(t0);
-            const Item I = decode_item(tab, item, pi);
-            const FusedProblem& P = tab.p[I.pi];
+            const int item = next_from_queue();
+            if (item >= n_items) break;
+            const Item I = decode_item(sp, n_problems, item, pi);
+            const FusedProblem& P = sp[I.pi];
             const uint32_t acc = n_local & 1u, aph = (n_local >> 1) & 1u;
             bool ok = !abort_flag;
             if (ok && !mbar_wait_warp(acc_full(acc), aph, &abort_flag)) { abort_flag = 1; atomicExch(err, 13); ok = false; }
@@ -285,8 +404,11 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
             float* cbase = P.C + ((size_t)I.split * P.M + row0) * P.ldc;
             // The TMEM fragment (lane = row, 32 columns) goes through a swizzled 4 KiB tile of shared memory so
             // that a store instruction writes 4 rows x 128 contiguous bytes instead of 32 rows x 16 bytes.
-            const uint32_t scratch = tiles + (uint32_t)kStages * kStage + (uint32_t)q * 4096u;
+            const uint32_t scratch = scratch0 + (uint32_t)q * 4096u;
             const int rsub = lane >> 3, j4 = lane & 7;
+#ifdef MCL_FUSED_PROF
+            if (!(tab.pad0 & 4))
+#endif
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 if (n0 + c0 >= P.N) break;
                 uint32_t r[32];
@@ -323,52 +445,70 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
     } else if (warp >= kConvWarp0) {
         // ---- converters --------------------------------------------------------------------------------
         const int tg = threadIdx.x - kConvWarp0 * 32;
-        uint32_t it = 0;
+        uint32_t it = 0, rs = 0, rph = 0;
         int pi = 0;
-        long long pf_wait = 0, pf_work = 0; (void)pf_wait; (void)pf_work;
+        long long pf_wait = 0, pf_work = 0, pf_lat = 0; (void)pf_wait; (void)pf_work; (void)pf_lat;
         PROF_T(tstart);
-        for (int item = blockIdx.x; item < n_items && !abort_flag; item += gridDim.x) {
-            const Item I = decode_item(tab, item, pi);
-            const FusedProblem& P = tab.p[I.pi];
-            const int nb_lo = P.mode == kFusedDW ? (P.BN >> 5) : 0;     // boxes of B that need a lo tile
+        for (;;) {
+            const int item = next_from_queue();
+            if (item >= n_items || abort_flag) break;
+            const Item I = decode_item(sp, n_problems, item, pi);
+            const FusedProblem& P = sp[I.pi];
+            const int nb_lo = P.mode == kFusedDW ? P.BN * 8 : 0;        // 16-byte chunks of B that need a lo part
             const float* ksc = P.a_kscale;
+            const int K = P.K;
             bool ok = true;
             for (int j = 0; j < I.nkt; ++j, ++it) {
-                const int s = (int)(it % kStages);
+                const int s = (int)rs, sl = (int)(it % kLoSlots);
+                const uint32_t ph = rph;
+                if (++rs == (uint32_t)n_raw) { rs = 0; rph ^= 1u; }
                 PROF_T(t0);
-                ok = mbar_wait_warp(tma_full(s), (it / kStages) & 1u, &abort_flag);
+                ok = mbar_wait_warp(raw_full(s), ph, &abort_flag) &&
+                     mbar_wait_warp(lo_empty(sl), ((it / kLoSlots) & 1u) ^ 1u, &abort_flag);
                 if (!ok) break;
-                PROF_T(t1); PROF_ADD(pf_wait, t0, t1);
-                const uint32_t st = tiles + (uint32_t)s * kStage;
                 const int k0 = (I.kt0 + j) * 32;
+                PROF_T(t1); PROF_ADD(pf_wait, t0, t1);
+#ifdef MCL_FUSED_PROF
+                pf_lat += t1 - t_issue[s];
+                if (tg == 0) t_conv[s] = t1;
+#endif
+                const uint32_t st = raw0 + (uint32_t)s * raw_slot, sto = lo0 + (uint32_t)sl * lo_slot;
+#ifdef MCL_FUSED_PROF
+                if (!(tab.pad0 & 1))
+#endif
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
+                for (int r = 0; r < kABytes / 16 / kConvThreads; ++r) {
                     const int idx = tg + kConvThreads * r;            // 16-byte chunk of the A tile
-                    const uint32_t addr = st + (uint32_t)idx * 16u;
-                    float4 v = lds128(addr);
+                    float4 v = lds128(st + (uint32_t)idx * 16u);
                     if (ksc != nullptr) {
                         const int k = k0 + 4 * ((idx & 7) ^ ((idx >> 3) & 7));     // undo the swizzle: logical k of this chunk
-                        if (k < P.K) {
+                        if (k < K) {
                             const float4 sc = __ldg(reinterpret_cast<const float4*>(ksc + k));
                             v.x = __fmul_rn(v.x, sc.x); v.y = __fmul_rn(v.y, sc.y);
                             v.z = __fmul_rn(v.z, sc.z); v.w = __fmul_rn(v.w, sc.w);
-                            sts128(addr, v);
+                            sts128(st + (uint32_t)idx * 16u, v);
                         }
                     }
-                    sts128(addr + kALo, lo_term4(v));
+                    sts128(sto + (uint32_t)idx * 16u, lo_term4(v));
                 }
-                for (int r = 0; r < nb_lo; ++r) {
-                    const uint32_t addr = st + kBHi + (uint32_t)(tg + kConvThreads * r) * 16u;
-                    sts128(addr + (kBLo - kBHi), lo_term4(lds128(addr)));
+#ifdef MCL_FUSED_PROF
+                if (!(tab.pad0 & 1))
+#endif
+                for (int c = tg; c < nb_lo; c += kConvThreads) {
+                    const uint32_t off = (uint32_t)kABytes + (uint32_t)c * 16u;
+                    sts128(sto + off, lo_term4(lds128(st + off)));
                 }
                 fence_proxy_async();
-                mbar_arrive(conv_full(s));
+                mbar_arrive(lo_full(sl));
                 PROF_T(t2); PROF_ADD(pf_work, t1, t2);
+#ifdef MCL_FUSED_PROF
+                if (tg == kConvThreads - 1) t_arr[s] = t2;
+#endif
             }
             if (!ok) { abort_flag = 1; atomicExch(err, 15); break; }
         }
 #ifdef MCL_FUSED_PROF
-        if (tg == 0) { PROF_T(tend); long long* o = g_fused_prof + blockIdx.x * 16 + 12; o[0] = pf_wait; o[1] = pf_work; o[2] = tend - tstart; o[3] = it; }
+        if (tg == 0) { PROF_T(tend); long long* o = g_fused_prof + blockIdx.x * 16 + 12; o[0] = pf_wait; o[1] = pf_work; o[2] = pf_lat; o[3] = it; }
 #endif
     }
     __syncwarp();
@@ -407,6 +547,66 @@ __global__ void __launch_bounds__(256) ternary_f32_from_p2_kernel(const uint32_t
             reinterpret_cast<float4*>(T)[i * 4 + q] = make_float4((float)((int)(b & 3u) - 1), (float)((int)((b >> 2) & 3u) - 1),
                                                                   (float)((int)((b >> 4) & 3u) - 1), (float)((int)((b >> 6) & 3u) - 1));
         }
+    }
+}
+
+// fewest column tiles of at most `hi` columns, then the narrowest tile (a multiple of `step`) that covers N
+constexpr int kTernCap = 64;
+struct TernaryGroup {
+    int n, C;
+    long long unit_begin[kTernCap + 1];        // units of 4 weights (one float4 of T)
+    const uint8_t* state[kTernCap];
+    float* T[kTernCap];
+};
+__global__ void __launch_bounds__(256) ternary_f32_group_kernel(const __grid_constant__ TernaryGroup g) {
+    __shared__ DecodeLut lut;
+    build_decode_lut(&lut, g.C, threadIdx.x, blockDim.x);
+    __syncthreads();
+    const long long total = g.unit_begin[g.n];
+    for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (long long)gridDim.x * blockDim.x) {
+        int lo = 0, hi = g.n - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (g.unit_begin[mid] <= u) lo = mid; else hi = mid - 1;
+        }
+        const long long q = u - g.unit_begin[lo];
+        const uint8_t* s = g.state[lo] + q * 3;
+        const uint32_t w = (uint32_t)__ldg(s) | ((uint32_t)__ldg(s + 1) << 8) | ((uint32_t)__ldg(s + 2) << 16);
+        reinterpret_cast<float4*>(g.T[lo])[q] = make_float4(lut.e[w & 63u].x, lut.e[(w >> 6) & 63u].x,
+                                                            lut.e[(w >> 12) & 63u].x, lut.e[(w >> 18) & 63u].x);
+    }
+}
+
+// ---- the split-K reduction of several layers in one launch ----------------------------------------------------
+constexpr int kGroupCap = 64;
+struct ReduceGroup {
+    int n;
+    long long unit_begin[kGroupCap + 1];       // units of one float4 of the result
+    const float* partial[kGroupCap];
+    float* out[kGroupCap];
+    int splits[kGroupCap];
+};
+__device__ __forceinline__ int find_group(const long long* begin, int n, long long u) {
+    int lo = 0, hi = n - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (begin[mid] <= u) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+// out = sum over z (ascending: deterministic) of partial[z]; all tensors dense [rows * cols]
+__global__ void __launch_bounds__(256) splitk_reduce_group_kernel(const __grid_constant__ ReduceGroup g) {
+    const long long total = g.unit_begin[g.n];
+    for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (long long)gridDim.x * blockDim.x) {
+        const int j = find_group(g.unit_begin, g.n, u);
+        const long long q = u - g.unit_begin[j], n4 = g.unit_begin[j + 1] - g.unit_begin[j];
+        const float4* src = reinterpret_cast<const float4*>(g.partial[j]) + q;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int z = 0; z < g.splits[j]; ++z) {
+            const float4 v = __ldg(src + (long long)z * n4);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        reinterpret_cast<float4*>(g.out[j])[q] = acc;
     }
 }
 
@@ -461,13 +661,33 @@ cudaError_t launch_fused_cap(const FusedProblem* probs, const FusedOperand* a_op
     if (taken == 0) return cudaErrorInvalidValue;
     tab.n_problems = taken;
     tab.n_items = items;
-    tab.pad0 = tab.pad1 = 0;
-    if (const char* dbg = getenv("MCL_FUSED_DBG")) sscanf(dbg, "%d,%d", &tab.pad0, &tab.pad1);
-    const size_t smem = (size_t)kStages * kStage + 4 * 4096 + 1024;
-    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(tc_fused_kernel<CAP>), slot, max_smem);
+    // ring geometry: a raw slot holds the A tile and the widest B tile of the table, a lo slot the A lo
+    // tile and the widest B tile that needs a lo part
+    int bhi = 0, blo = 0;
+    for (int i = 0; i < taken; ++i) {
+        const int bytes = tab.p[i].BN * 128;
+        if (bytes > bhi) bhi = bytes;
+        if (tab.p[i].mode == kFusedDW && bytes > blo) blo = bytes;      // only two fp32 operands need a B lo tile
+    }
+    cudaFuncAttributes fa;
+    cudaError_t e = cudaFuncGetAttributes(&fa, reinterpret_cast<const void*>(tc_fused_kernel<CAP>));
+    if (e != cudaSuccess) return e;
+    tab.raw_slot = kABytes + ((bhi + 1023) & ~1023);
+    tab.lo_slot = kABytes + ((blo + 1023) & ~1023);
+    tab.pad0 = 0;
+    if (const char* dbg = getenv("MCL_FUSED_DBG")) tab.pad0 = atoi(dbg);
+    const long long budget = (long long)max_smem - (long long)fa.sharedSizeBytes - 1024 - kScratch - kLoSlots * (long long)tab.lo_slot;
+    int n_raw = (int)(budget / tab.raw_slot);
+    if (n_raw > kMaxRaw) n_raw = kMaxRaw;
+    if (n_raw < 2) return cudaErrorInvalidConfiguration;
+    tab.n_raw = n_raw;
+    const size_t smem = (size_t)n_raw * tab.raw_slot + (size_t)kLoSlots * tab.lo_slot + kScratch + 1024;
+    e = ensure_dynamic_smem(reinterpret_cast<const void*>(tc_fused_kernel<CAP>), slot, max_smem);
+    if (e != cudaSuccess) return e;
+    e = cudaMemsetAsync(err_word + 1, 0, sizeof(int), stream);          // the work-item counter
     if (e != cudaSuccess) return e;
     const int ctas = items < sm_count ? items : sm_count;
-    tc_fused_kernel<CAP><<<ctas, kFThreads, smem, stream>>>(tab, err_word);
+    tc_fused_kernel<CAP><<<ctas, kFThreads, smem, stream>>>(tab, err_word, err_word + 1);
     *used = taken;
     return cudaGetLastError();
 }
@@ -478,18 +698,19 @@ size_t fused_plan(FusedProblem* p, int target_items, int depth_limit) {
     const int ktiles = (p->K + 31) / 32;
     p->tiles_m = (p->M + 127) / 128;
     if (p->mode != kFusedDW) {
-        p->BN = pick_bn(p->N, p->mode == kFusedY ? 16 : 32, 256);
+        // B tiles of at most 20 KiB keep the raw ring four slots deep; wider tiles (three slots) measured 1.4x slower
+        p->BN = pick_bn(p->N, p->mode == kFusedY ? 16 : 32, 160);
         p->tiles_n = (p->N + p->BN - 1) / p->BN;
         p->splits = 1;
         p->ktiles_per_split = ktiles;
         p->nprod = 2;
-        p->prod = 0x01u;              // lo.b, then hi.b
+        p->prod = 0x10u;              // hi.b, then lo.b
         return 0;
     }
     p->BN = pick_bn(p->N, 32, 128);
     p->tiles_n = (p->N + p->BN - 1) / p->BN;
     p->nprod = 3;
-    p->prod = 0x041u;                 // lo_a.hi_b, hi_a.lo_b, hi_a.hi_b
+    p->prod = 0x410u;                 // hi_a.hi_b, then lo_a.hi_b, hi_a.lo_b
     const int tiles = p->tiles_m * p->tiles_n;
     int splits = (target_items + tiles - 1) / tiles;
     if (splits > ktiles / 8) splits = ktiles / 8;
@@ -503,10 +724,9 @@ size_t fused_plan(FusedProblem* p, int target_items, int depth_limit) {
 
 cudaError_t launch_tc_fused(const FusedProblem* probs, const FusedOperand* a_ops, const FusedOperand* b_ops, int n,
                             int* err_word, size_t max_smem, int sm_count, cudaStream_t stream, int* launches) {
-    if ((size_t)kStages * kStage + 4 * 4096 + 1024 + 2048 > max_smem) return cudaErrorInvalidConfiguration;
     for (int i = 0; i < n; ++i) {
         const FusedProblem& p = probs[i];
-        if (p.mode == kFusedDW ? (p.BN > 128 || (p.BN & 31)) : (p.BN > 256 || (p.BN & (p.mode == kFusedY ? 15 : 31))))
+        if (p.mode == kFusedDW ? (p.BN > 128 || (p.BN & 31)) : (p.BN > 160 || (p.BN & (p.mode == kFusedY ? 15 : 31))))
             return cudaErrorInvalidValue;
         if ((p.N & 3) || (p.ldc & 3) || (a_ops[i].ld & 3) || (b_ops[i].ld & 3)) return cudaErrorInvalidValue;
     }
@@ -541,9 +761,61 @@ cudaError_t launch_ternary_f32(const uint8_t* state, const uint32_t* packed2, in
     return cudaGetLastError();
 }
 
+
+cudaError_t launch_ternary_f32_group(const uint8_t* const* state, float* const* T, const int* O, const int* I, int n, int C,
+                                     int sm_count, cudaStream_t stream, int* launches) {
+    for (int done = 0; done < n;) {
+        TernaryGroup g;
+        const int take = n - done < kTernCap ? n - done : kTernCap;
+        long long units = 0;
+        for (int j = 0; j < take; ++j) {
+            g.unit_begin[j] = units;
+            g.state[j] = state[done + j];
+            g.T[j] = T[done + j];
+            units += (long long)O[done + j] * (I[done + j] / 4);
+        }
+        g.unit_begin[take] = units;
+        g.n = take; g.C = C;
+        long long blocks = (units + 255) / 256;
+        if (blocks > (long long)sm_count * 8) blocks = (long long)sm_count * 8;
+        ternary_f32_group_kernel<<<(int)blocks, 256, 0, stream>>>(g);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        ++*launches;
+        done += take;
+    }
+    return cudaSuccess;
+}
+
+cudaError_t launch_splitk_reduce_group(const float* const* partial, float* const* out, const int* elements, const int* splits,
+                                       int n, int sm_count, cudaStream_t stream, int* launches) {
+    for (int done = 0; done < n;) {
+        ReduceGroup g;
+        const int take = n - done < kGroupCap ? n - done : kGroupCap;
+        long long units = 0;
+        for (int j = 0; j < take; ++j) {
+            g.unit_begin[j] = units;
+            g.partial[j] = partial[done + j];
+            g.out[j] = out[done + j];
+            g.splits[j] = splits[done + j];
+            units += elements[done + j] / 4;
+        }
+        g.unit_begin[take] = units;
+        g.n = take;
+        long long blocks = (units + 255) / 256;
+        if (blocks > (long long)sm_count * 8) blocks = (long long)sm_count * 8;
+        splitk_reduce_group_kernel<<<(int)blocks, 256, 0, stream>>>(g);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        ++*launches;
+        done += take;
+    }
+    return cudaSuccess;
+}
+
 #ifdef MCL_FUSED_PROF
 extern "C" int mcl_debug_fused_prof(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_fused_prof, sizeof(long long) * 148 * 16);
+    return (int)cudaMemcpyFromSymbol(out, g_fused_prof, sizeof(long long) * (148 * 16 + 148 * 8));
 }
 #endif
 

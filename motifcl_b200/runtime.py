@@ -6,6 +6,7 @@ MotifclCudaError when the C call refuses or fails.
 """
 from __future__ import annotations
 
+import ctypes
 import ctypes as C
 
 from ._lib import MotifclCudaError, lib
@@ -17,6 +18,25 @@ def _ptr(t):
     if isinstance(t, int):
         return t
     return t.data_ptr()
+
+
+class LinearDesc(ctypes.Structure):
+    """mcl_cuda_linear_desc: one layer of mcl_cuda_counter_linear_step_many."""
+    _fields_ = [("x", ctypes.c_void_p), ("grad_out", ctypes.c_void_p), ("state", ctypes.c_void_p),
+                ("scale", ctypes.c_void_p), ("v", ctypes.c_void_p), ("y", ctypes.c_void_p),
+                ("grad_x", ctypes.c_void_p), ("grad_w", ctypes.c_void_p), ("packed2_out", ctypes.c_void_p),
+                ("in_features", ctypes.c_size_t), ("out_features", ctypes.c_size_t), ("batch", ctypes.c_size_t),
+                ("update_rows", ctypes.c_size_t), ("row_offset", ctypes.c_size_t)]
+
+
+def linear_descs(entries):
+    """entries: dicts with the fields of LinearDesc (tensors or None for pointers) -> ctypes array."""
+    arr = (LinearDesc * len(entries))()
+    for d, e in zip(arr, entries):
+        for name, ctype in LinearDesc._fields_:
+            val = e.get(name)
+            setattr(d, name, _ptr(val) if ctype is ctypes.c_void_p else int(val))
+    return arr
 
 
 class Context:
@@ -146,6 +166,12 @@ class Context:
             self._ctx, _ptr(x), _ptr(grad_out), _ptr(state), _ptr(scale), _ptr(v), _ptr(y), _ptr(grad_x),
             _ptr(grad_w), _ptr(packed2_out), C_, in_features, out_features, batch, update_rows, row_offset,
             lr, lr_scale, rms_beta, rms_eps, seed & 0xFFFFFFFF))
+
+    def counter_linear_step_many(self, descs, C_, lr, lr_scale, rms_beta, rms_eps, seed):
+        """descs: array from linear_descs(); the steps of all its layers with grouped launches."""
+        self._check(self._lib.mcl_cuda_counter_linear_step_many(
+            self._ctx, ctypes.cast(descs, ctypes.c_void_p), len(descs), C_, lr, lr_scale, rms_beta, rms_eps,
+            seed & 0xFFFFFFFF))
 
     def ternary_linear_products(self, x, grad_out, packed2, scale, y, grad_x, grad_w, in_features,
                                 out_features, batch):

@@ -56,11 +56,12 @@ class CounterLinearState:
 
 class CounterStack:
     def __init__(self, ctx: Context, linears: list[CounterLinearState], hyper: Hyper, tokens: int,
-                 group=None, lanes: int = 1):
+                 group=None, lanes: int = 1, grouped: bool = False):
         """lanes > 1: the linears of a step are independent, so they are spread round-robin over
         `lanes` contexts (own stream, own workspace) that run side by side between a fork and a
         join on `ctx`."""
         self.ctx, self.linears, self.h, self.tokens = ctx, linears, hyper, tokens
+        self.grouped = grouped      # single GPU: all linears through mcl_cuda_counter_linear_step_many
         self.lanes = [ctx] + [Context(ctx.device) for _ in range(max(0, lanes - 1))]
         self.group = group
         self.world = 1 if group is None else torch.distributed.get_world_size(group)
@@ -148,8 +149,25 @@ class CounterStack:
         for lane in self.lanes[1:]:
             self.ctx.lane_join(lane)
 
+    def _descs(self, xs, dys, update: bool):
+        key = (tuple(t.data_ptr() for t in xs), tuple(t.data_ptr() for t in dys), update)
+        if getattr(self, "_desc_key", None) != key:
+            from .runtime import linear_descs
+            self._desc_arr = linear_descs([
+                dict(x=x, grad_out=dy, state=l.state, scale=l.scale, v=l.v, y=l.y, grad_x=l.dx, grad_w=l.grad_w,
+                     packed2_out=l.packed2 if update else None, in_features=l.shape.in_features,
+                     out_features=l.shape.out_features, batch=self.tokens,
+                     update_rows=l.shape.out_features if update else 0, row_offset=0)
+                for l, x, dy in zip(self.linears, xs, dys)])
+            self._desc_key = key
+        return self._desc_arr
+
     def _step_eager(self, xs, dys, seed):
         h, nl = self.h, len(self.lanes)
+        if self.grouped:
+            self.ctx.counter_linear_step_many(self._descs(xs, dys, True), h.C, h.lr, h.lr_scale, h.rms_beta, h.rms_eps,
+                                              seed)
+            return
         self._fork()
         for i, (l, x, dy) in enumerate(zip(self.linears, xs, dys)):
             O, I = l.shape.out_features, l.shape.in_features
@@ -212,6 +230,9 @@ class CounterStack:
     def products_only(self, xs, dys):
         """Y, dX and dW of every linear, no update (and no collectives)."""
         h, nl = self.h, len(self.lanes)
+        if self.grouped and self.world == 1:
+            self.ctx.counter_linear_step_many(self._descs(xs, dys, False), h.C, h.lr, h.lr_scale, h.rms_beta, h.rms_eps, 0)
+            return
         self._fork()
         for i, (l, x, dy) in enumerate(zip(self.linears, xs, dys)):
             O, I = l.shape.out_features, l.shape.in_features

@@ -460,3 +460,76 @@ def test_products_from_packed2_equal_products_from_state(ctx, orc, mode):
     for a, b in zip(*outs):
         assert np.array_equal(a, b)
     assert rel_l2(outs[1][0], orc.forward(c["x"], c["state"], c["scale"], C, O)) <= 1e-5
+
+
+FUSED_SHAPES = [(256, 64, 64), (1000, 96, 32), (2048, 288, 288), (1024, 288, 768), (1024, 768, 288),
+                (516, 1024, 1024), (512, 32, 1024)]
+
+
+@pytest.mark.parametrize("N,I,O", FUSED_SHAPES)
+def test_fused_tf32_products_vs_oracle(ctx, orc, N, I, O):
+    """Layers up to 1024 features whose dimensions are multiples of 32 take the kernel that reads the
+    fp32 tensors through TMA and multiplies tf32 hi/lo terms (transposed operands in place):
+    every product within 1e-5 relative L2 of the fp32 reference sums, ragged token counts included."""
+    rng = np.random.default_rng(N + 3 * I + 7 * O)
+    C = 11
+    state = codec.pack_codes(rng.integers(0, 64, size=(O, I)).astype(np.uint8)).reshape(-1)
+    x = rng.standard_normal((N, I)).astype(np.float32)
+    dy = (0.02 * rng.standard_normal((N, O))).astype(np.float32)
+    sc = rng.uniform(0.02, 0.2, O).astype(np.float32)
+    y = torch.full((N, O), 7.0, dtype=torch.float32, device=DEV)
+    gx = torch.full((N, I), 7.0, dtype=torch.float32, device=DEV)
+    gw = torch.full((O, I), 7.0, dtype=torch.float32, device=DEV)
+    v = torch.zeros(O, dtype=torch.float32, device=DEV)
+    ctx.set_gemm_mode("tensor")
+    try:
+        ctx.counter_linear_step(_t(x), _t(dy), _t(state), _t(sc), v, y, gx, gw, None, C, I, O, N, 0, 0,
+                                3e-3, 0.0, 0.9, 1e-3, 1)
+        ctx.finish()
+    finally:
+        ctx.set_gemm_mode("auto")
+    assert rel_l2(y.cpu().numpy(), orc.forward(x, state, sc, C, O)) <= 1e-5
+    assert rel_l2(gx.cpu().numpy(), orc.backward_input(dy, state, sc, C, I)) <= 1e-5
+    assert rel_l2(gw.cpu().numpy(), orc.grad_w(dy, x)) <= 1e-5
+
+
+def test_linear_step_many_equals_layer_by_layer(ctx, orc):
+    """mcl_cuda_counter_linear_step_many: grouped launches for the layers that qualify, single calls for
+    the rest; each layer's products within tolerance and its update bit-exact given its own grad_w."""
+    from motifcl_b200.runtime import linear_descs
+    rng = np.random.default_rng(5)
+    C, N = 11, 1024
+    shapes = [(288, 288), (288, 768), (768, 288), (64, 96), (36, 40)]     # the last one does not qualify
+    hy = (0.3, 0.05, 0.9, 1e-3)
+    layers, entries = [], []
+    for (I, O) in shapes:
+        state = codec.pack_codes(rng.integers(0, 64, size=(O, I)).astype(np.uint8)).reshape(-1)
+        L = dict(I=I, O=O, state=state, x=rng.standard_normal((N, I)).astype(np.float32),
+                 dy=(0.02 * rng.standard_normal((N, O))).astype(np.float32),
+                 sc=rng.uniform(0.02, 0.2, O).astype(np.float32), v=rng.uniform(1e-4, 1e-2, O).astype(np.float32))
+        L["d"] = dict(x=_t(L["x"]), grad_out=_t(L["dy"]), state=_t(state), scale=_t(L["sc"]), v=_t(L["v"]),
+                      y=torch.empty(N, O, dtype=torch.float32, device=DEV),
+                      grad_x=torch.empty(N, I, dtype=torch.float32, device=DEV),
+                      grad_w=torch.empty(O, I, dtype=torch.float32, device=DEV),
+                      packed2_out=torch.zeros(O, (I + 15) // 16, dtype=torch.int32, device=DEV) if I % 16 == 0 else None,
+                      in_features=I, out_features=O, batch=N, update_rows=O, row_offset=0)
+        layers.append(L)
+        entries.append(L["d"])
+    ctx.set_gemm_mode("tensor")
+    try:
+        ctx.counter_linear_step_many(linear_descs(entries), C, *hy, 4242)
+        ctx.finish()
+    finally:
+        ctx.set_gemm_mode("auto")
+    for L in layers:
+        I, O, d = L["I"], L["O"], L["d"]
+        assert rel_l2(d["y"].cpu().numpy(), orc.forward(L["x"], L["state"], L["sc"], C, O)) <= 1e-5
+        assert rel_l2(d["grad_x"].cpu().numpy(), orc.backward_input(L["dy"], L["state"], L["sc"], C, I)) <= 1e-5
+        gw = d["grad_w"].cpu().numpy()
+        assert rel_l2(gw, orc.grad_w(L["dy"], L["x"])) <= 1e-5
+        o = orc.update_dense(L["state"], L["sc"], L["v"], gw, C, I, O, 0, *hy, 4242)
+        assert np.array_equal(d["state"].cpu().numpy(), o[0])
+        assert np.array_equal(_bits(d["scale"].cpu().numpy()), _bits(o[1]))
+        assert np.array_equal(_bits(d["v"].cpu().numpy()), _bits(o[2]))
+        if d["packed2_out"] is not None:
+            assert np.array_equal(d["packed2_out"].cpu().numpy().view(np.uint32), o[3])

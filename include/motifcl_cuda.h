@@ -168,10 +168,28 @@ typedef struct mcl_cuda_linear_desc {
     uint32_t* packed2_out;   /* [out, in/16] or NULL */
     size_t in_features, out_features, batch;
     size_t update_rows, row_offset;   /* as in mcl_cuda_counter_linear_step */
+    const uint32_t* packed2_in;  /* used when state is NULL: the layer's 2-bit words; the products come from them as
+                                    in mcl_cuda_ternary_linear_products and nothing is updated (update_rows must be 0,
+                                    scale is read only, v is ignored) */
 } mcl_cuda_linear_desc;
 int mcl_cuda_counter_linear_step_many(mcl_cuda_ctx* ctx, const mcl_cuda_linear_desc* layers, size_t n_layers,
                                       size_t C, float lr, float lr_scale, float rms_beta, float rms_eps,
                                       uint32_t seed);
+
+/* ---- the fused updates of several layers (or row shards of layers) in one launch: layer i is exactly
+ * mcl_cuda_counter_update_dense with the same arguments.  A data-parallel rank calls this on its
+ * shards after the reduce-scatter of the gradients. ---- */
+typedef struct mcl_cuda_update_desc {
+    uint8_t* state;          /* first updated row */
+    float* scale;
+    float* v;
+    const float* grad_w;     /* [rows, in] */
+    uint32_t* packed2_out;   /* [rows, in/16] or NULL */
+    size_t in_features, rows, row_offset;
+} mcl_cuda_update_desc;
+int mcl_cuda_counter_update_dense_many(mcl_cuda_ctx* ctx, const mcl_cuda_update_desc* layers, size_t n_layers,
+                                       size_t C, float lr, float lr_scale, float rms_beta, float rms_eps,
+                                       uint32_t seed);
 
 /* ---- one whole training step of one counter linear (what MotifCL's autograd does around
  * CounterStateLinear, src/nn/compact_counter.cpp:40-50,266-300, with the dense update of

@@ -87,6 +87,7 @@ def lib() -> C.CDLL:
         L.mcl_cuda_counter_linear_step.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, sz, sz,
                                                    f, f, f, f, u32]
         L.mcl_cuda_counter_linear_step_many.argtypes = [vp, vp, sz, sz, f, f, f, f, u32]
+        L.mcl_cuda_counter_update_dense_many.argtypes = [vp, vp, sz, sz, f, f, f, f, u32]
         L.mcl_cuda_ternary_linear_products.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, sz, sz]
         L.mcl_cuda_eltwise_f32.argtypes = [vp, i, vp, vp, vp, sz, f]
         L.mcl_cuda_matmul_f32.argtypes = [vp, vp, vp, vp, sz, sz, sz, i, i]

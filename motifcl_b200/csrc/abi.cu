@@ -806,14 +806,22 @@ int mcl_cuda_counter_linear_step_many(mcl_cuda_ctx* ctx, const mcl_cuda_linear_d
         if (L.batch == 0 || L.batch > 0x7fffffffull) return fail(ctx, MCL_CUDA_EINVAL, "counter linear step (many) requires 0 < batch < 2^31");
         MCL_TRY(check_ptr(ctx, op, "x", L.x, 4));
         MCL_TRY(check_ptr(ctx, op, "grad_out", L.grad_out, 4));
-        MCL_TRY(check_ptr(ctx, op, "state", L.state, 1));
         MCL_TRY(check_ptr(ctx, op, "scale", L.scale, 4));
-        MCL_TRY(check_ptr(ctx, op, "v", L.v, 4));
         MCL_TRY(check_ptr(ctx, op, "grad_w", L.grad_w, 16));
+        if (L.state != nullptr) {
+            MCL_TRY(check_ptr(ctx, op, "v", L.v, 4));
+        } else {
+            MCL_TRY(check_ptr(ctx, op, "packed2_in", L.packed2_in, 4));
+            if (L.update_rows != 0)
+                return fail(ctx, MCL_CUDA_EINVAL, "counter linear step (many): a layer given by its 2-bit words cannot be updated");
+            if (L.in_features % 16 != 0)
+                return fail(ctx, MCL_CUDA_EINVAL, "counter linear step (many): 2-bit words require in_features % 16 == 0");
+        }
         if (L.row_offset + L.update_rows > L.out_features)
             return fail(ctx, MCL_CUDA_EINVAL, "counter linear step (many): update rows exceed out_features");
         const bool tc = tc_wanted(ctx, L.batch, L.out_features, L.in_features);
-        if (tc && fused_wanted(ctx, L.x, L.grad_out, L.state, L.scale, L.y, L.grad_x, L.grad_w, L.in_features, L.out_features,
+        const void* tern = L.state ? static_cast<const void*>(L.state) : L.packed2_in;
+        if (tc && fused_wanted(ctx, L.x, L.grad_out, tern, L.scale, L.y, L.grad_x, L.grad_w, L.in_features, L.out_features,
                                L.batch))
             grouped.push_back(i);
         else
@@ -822,6 +830,11 @@ int mcl_cuda_counter_linear_step_many(mcl_cuda_ctx* ctx, const mcl_cuda_linear_d
     DeviceGuard guard(ctx->device);
     for (size_t i : single) {
         const mcl_cuda_linear_desc& L = layers[i];
+        if (L.state == nullptr) {
+            MCL_TRY(mcl_cuda_ternary_linear_products(ctx, L.x, L.grad_out, L.packed2_in, L.scale, L.y, L.grad_x, L.grad_w,
+                                                     L.in_features, L.out_features, L.batch));
+            continue;
+        }
         MCL_TRY(mcl_cuda_counter_linear_step(ctx, L.x, L.grad_out, L.state, L.scale, L.v, L.y, L.grad_x, L.grad_w, L.packed2_out,
                                              C, L.in_features, L.out_features, L.batch, L.update_rows, L.row_offset, lr,
                                              lr_scale, rms_beta, rms_eps, seed));
@@ -854,15 +867,16 @@ int mcl_cuda_counter_linear_step_many(mcl_cuda_ctx* ctx, const mcl_cuda_linear_d
     // 1. ternary digits of every layer as fp32
     {
         std::vector<const uint8_t*> st(ng);
+        std::vector<const uint32_t*> p2(ng);
         std::vector<float*> T(ng);
         std::vector<int> Os(ng), Is(ng);
         for (size_t gi = 0; gi < ng; ++gi) {
             const mcl_cuda_linear_desc& L = layers[grouped[gi]];
-            st[gi] = L.state; T[gi] = reinterpret_cast<float*>(w + t_off[gi]);
+            st[gi] = L.state; p2[gi] = L.packed2_in; T[gi] = reinterpret_cast<float*>(w + t_off[gi]);
             Os[gi] = (int)L.out_features; Is[gi] = (int)L.in_features;
         }
         int launches = 0;
-        cudaError_t e = mcl::launch_ternary_f32_group(st.data(), T.data(), Os.data(), Is.data(), (int)ng, (int)C, ctx->sm_count,
+        cudaError_t e = mcl::launch_ternary_f32_group(st.data(), p2.data(), T.data(), Os.data(), Is.data(), (int)ng, (int)C, ctx->sm_count,
                                                       ctx->stream, &launches);
         ctx->launches += launches;
         if (e != cudaSuccess) return fail_cuda(ctx, op, e);
@@ -961,6 +975,45 @@ int mcl_cuda_counter_linear_step_many(mcl_cuda_ctx* ctx, const mcl_cuda_linear_d
             }
         }
     }
+    return MCL_CUDA_OK;
+}
+
+int mcl_cuda_counter_update_dense_many(mcl_cuda_ctx* ctx, const mcl_cuda_update_desc* layers, size_t n_layers,
+                                       size_t C, float lr, float lr_scale, float rms_beta, float rms_eps,
+                                       uint32_t seed) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "counter update (many)";
+    if (!layers || n_layers == 0) return fail(ctx, MCL_CUDA_EINVAL, "counter update (many): no layers");
+    MCL_TRY(check_hypers(ctx, op, lr, lr_scale, rms_beta, rms_eps));
+    std::vector<mcl::UpdateDesc> ud;
+    for (size_t i = 0; i < n_layers; ++i) {
+        const mcl_cuda_update_desc& L = layers[i];
+        if (L.rows == 0) continue;
+        MCL_TRY(check_counter_dims(ctx, op, C, L.in_features, L.rows));
+        if ((L.row_offset + L.rows) * L.in_features > 0xffffffffull)
+            return fail(ctx, MCL_CUDA_EINVAL, "counter update: (row_offset + rows) * in_features exceeds 32-bit element indexing");
+        MCL_TRY(check_ptr(ctx, op, "state", L.state, 1));
+        MCL_TRY(check_ptr(ctx, op, "scale", L.scale, 4));
+        MCL_TRY(check_ptr(ctx, op, "v", L.v, 4));
+        MCL_TRY(check_ptr(ctx, op, "grad_w", L.grad_w, 16));
+        mcl::UpdateDesc u;
+        u.state = L.state; u.scale = L.scale; u.v = L.v; u.grad_w = L.grad_w; u.packed2 = L.packed2_out;
+        u.in_features = (int)L.in_features; u.rows = (int)L.rows; u.row_offset = (int)L.row_offset;
+        ud.push_back(u);
+    }
+    if (ud.empty()) return MCL_CUDA_OK;
+    DeviceGuard guard(ctx->device);
+    int launches = 0;
+    cudaError_t e = mcl::launch_counter_update_group(ud.data(), (int)ud.size(), (int)C, lr, lr_scale, rms_beta, rms_eps, seed,
+                                                     ctx->seed_offset, ctx->sm_count, ctx->max_smem, ctx->stream, &launches);
+    ctx->launches += launches;
+    if (e == cudaErrorNotSupported) {
+        for (const mcl::UpdateDesc& u : ud)
+            MCL_TRY(mcl_cuda_counter_update_dense(ctx, u.state, u.scale, u.v, u.grad_w, u.packed2, C, (size_t)u.in_features,
+                                                  (size_t)u.rows, (size_t)u.row_offset, lr, lr_scale, rms_beta, rms_eps, seed));
+        return MCL_CUDA_OK;
+    }
+    if (e != cudaSuccess) return fail_cuda(ctx, op, e);
     return MCL_CUDA_OK;
 }
 

@@ -102,7 +102,7 @@ cudaError_t launch_tc_fused(const FusedProblem* probs, const FusedOperand* a_ops
 cudaError_t launch_ternary_f32(const uint8_t* state, const uint32_t* packed2, int C, int O, int I, float* T,
                                int sm_count, cudaStream_t stream);
 // grouped forms: one launch for the layers of a step
-cudaError_t launch_ternary_f32_group(const uint8_t* const* state, float* const* T, const int* O, const int* I, int n, int C,
+cudaError_t launch_ternary_f32_group(const uint8_t* const* state, const uint32_t* const* packed2, float* const* T, const int* O, const int* I, int n, int C,
                                      int sm_count, cudaStream_t stream, int* launches);
 cudaError_t launch_splitk_reduce_group(const float* const* partial, float* const* out, const int* elements, const int* splits,
                                        int n, int sm_count, cudaStream_t stream, int* launches);

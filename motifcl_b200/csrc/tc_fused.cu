@@ -555,7 +555,8 @@ constexpr int kTernCap = 64;
 struct TernaryGroup {
     int n, C;
     long long unit_begin[kTernCap + 1];        // units of 4 weights (one float4 of T)
-    const uint8_t* state[kTernCap];
+    const uint8_t* state[kTernCap];            // 6-bit state of layer j, or null: then
+    const uint32_t* packed2[kTernCap];         // its 2-bit words
     float* T[kTernCap];
 };
 __global__ void __launch_bounds__(256) ternary_f32_group_kernel(const __grid_constant__ TernaryGroup g) {
@@ -570,10 +571,17 @@ __global__ void __launch_bounds__(256) ternary_f32_group_kernel(const __grid_con
             if (g.unit_begin[mid] <= u) lo = mid; else hi = mid - 1;
         }
         const long long q = u - g.unit_begin[lo];
-        const uint8_t* s = g.state[lo] + q * 3;
-        const uint32_t w = (uint32_t)__ldg(s) | ((uint32_t)__ldg(s + 1) << 8) | ((uint32_t)__ldg(s + 2) << 16);
-        reinterpret_cast<float4*>(g.T[lo])[q] = make_float4(lut.e[w & 63u].x, lut.e[(w >> 6) & 63u].x,
-                                                            lut.e[(w >> 12) & 63u].x, lut.e[(w >> 18) & 63u].x);
+        float4 t;
+        if (g.state[lo] != nullptr) {
+            const uint8_t* s = g.state[lo] + q * 3;
+            const uint32_t w = (uint32_t)__ldg(s) | ((uint32_t)__ldg(s + 1) << 8) | ((uint32_t)__ldg(s + 2) << 16);
+            t = make_float4(lut.e[w & 63u].x, lut.e[(w >> 6) & 63u].x, lut.e[(w >> 12) & 63u].x, lut.e[(w >> 18) & 63u].x);
+        } else {
+            const uint32_t b = __ldg(g.packed2[lo] + (q >> 2)) >> (8 * (int)(q & 3));
+            t = make_float4((float)((int)(b & 3u) - 1), (float)((int)((b >> 2) & 3u) - 1), (float)((int)((b >> 4) & 3u) - 1),
+                            (float)((int)((b >> 6) & 3u) - 1));
+        }
+        reinterpret_cast<float4*>(g.T[lo])[q] = t;
     }
 }
 
@@ -762,7 +770,7 @@ cudaError_t launch_ternary_f32(const uint8_t* state, const uint32_t* packed2, in
 }
 
 
-cudaError_t launch_ternary_f32_group(const uint8_t* const* state, float* const* T, const int* O, const int* I, int n, int C,
+cudaError_t launch_ternary_f32_group(const uint8_t* const* state, const uint32_t* const* packed2, float* const* T, const int* O, const int* I, int n, int C,
                                      int sm_count, cudaStream_t stream, int* launches) {
     for (int done = 0; done < n;) {
         TernaryGroup g;
@@ -771,6 +779,7 @@ cudaError_t launch_ternary_f32_group(const uint8_t* const* state, float* const* 
         for (int j = 0; j < take; ++j) {
             g.unit_begin[j] = units;
             g.state[j] = state[done + j];
+            g.packed2[j] = packed2[done + j];
             g.T[j] = T[done + j];
             units += (long long)O[done + j] * (I[done + j] / 4);
         }

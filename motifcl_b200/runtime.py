@@ -26,17 +26,33 @@ class LinearDesc(ctypes.Structure):
                 ("scale", ctypes.c_void_p), ("v", ctypes.c_void_p), ("y", ctypes.c_void_p),
                 ("grad_x", ctypes.c_void_p), ("grad_w", ctypes.c_void_p), ("packed2_out", ctypes.c_void_p),
                 ("in_features", ctypes.c_size_t), ("out_features", ctypes.c_size_t), ("batch", ctypes.c_size_t),
-                ("update_rows", ctypes.c_size_t), ("row_offset", ctypes.c_size_t)]
+                ("update_rows", ctypes.c_size_t), ("row_offset", ctypes.c_size_t), ("packed2_in", ctypes.c_void_p)]
+
+
+class UpdateDesc(ctypes.Structure):
+    """mcl_cuda_update_desc: one layer (or row shard) of mcl_cuda_counter_update_dense_many."""
+    _fields_ = [("state", ctypes.c_void_p), ("scale", ctypes.c_void_p), ("v", ctypes.c_void_p),
+                ("grad_w", ctypes.c_void_p), ("packed2_out", ctypes.c_void_p),
+                ("in_features", ctypes.c_size_t), ("rows", ctypes.c_size_t), ("row_offset", ctypes.c_size_t)]
+
+
+def _fill(struct_type, entries):
+    arr = (struct_type * len(entries))()
+    for d, e in zip(arr, entries):
+        for name, ctype in struct_type._fields_:
+            val = e.get(name)
+            setattr(d, name, _ptr(val) if ctype is ctypes.c_void_p else int(val or 0))
+    return arr
 
 
 def linear_descs(entries):
     """entries: dicts with the fields of LinearDesc (tensors or None for pointers) -> ctypes array."""
-    arr = (LinearDesc * len(entries))()
-    for d, e in zip(arr, entries):
-        for name, ctype in LinearDesc._fields_:
-            val = e.get(name)
-            setattr(d, name, _ptr(val) if ctype is ctypes.c_void_p else int(val))
-    return arr
+    return _fill(LinearDesc, entries)
+
+
+def update_descs(entries):
+    """entries: dicts with the fields of UpdateDesc -> ctypes array."""
+    return _fill(UpdateDesc, entries)
 
 
 class Context:
@@ -170,6 +186,12 @@ class Context:
     def counter_linear_step_many(self, descs, C_, lr, lr_scale, rms_beta, rms_eps, seed):
         """descs: array from linear_descs(); the steps of all its layers with grouped launches."""
         self._check(self._lib.mcl_cuda_counter_linear_step_many(
+            self._ctx, ctypes.cast(descs, ctypes.c_void_p), len(descs), C_, lr, lr_scale, rms_beta, rms_eps,
+            seed & 0xFFFFFFFF))
+
+    def counter_update_dense_many(self, descs, C_, lr, lr_scale, rms_beta, rms_eps, seed):
+        """descs: array from update_descs(); the fused updates of all its layers in one launch."""
+        self._check(self._lib.mcl_cuda_counter_update_dense_many(
             self._ctx, ctypes.cast(descs, ctypes.c_void_p), len(descs), C_, lr, lr_scale, rms_beta, rms_eps,
             seed & 0xFFFFFFFF))
 

@@ -154,9 +154,10 @@ class CounterStack:
         if getattr(self, "_desc_key", None) != key:
             from .runtime import linear_descs
             self._desc_arr = linear_descs([
-                dict(x=x, grad_out=dy, state=l.state, scale=l.scale, v=l.v, y=l.y, grad_x=l.dx, grad_w=l.grad_w,
-                     packed2_out=l.packed2 if update else None, in_features=l.shape.in_features,
-                     out_features=l.shape.out_features, batch=self.tokens,
+                dict(x=x, grad_out=dy, state=None if self.world > 1 else l.state, scale=l.scale, v=l.v, y=l.y,
+                     grad_x=l.dx, grad_w=l.grad_w, packed2_out=l.packed2 if update else None,
+                     packed2_in=l.packed2 if self.world > 1 else None,      # ranks compute from the replicated 2-bit words
+                     in_features=l.shape.in_features, out_features=l.shape.out_features, batch=self.tokens,
                      update_rows=l.shape.out_features if update else 0, row_offset=0)
                 for l, x, dy in zip(self.linears, xs, dys)])
             self._desc_key = key
@@ -230,7 +231,7 @@ class CounterStack:
     def products_only(self, xs, dys):
         """Y, dX and dW of every linear, no update (and no collectives)."""
         h, nl = self.h, len(self.lanes)
-        if self.grouped and self.world == 1:
+        if self.grouped:
             self.ctx.counter_linear_step_many(self._descs(xs, dys, False), h.C, h.lr, h.lr_scale, h.rms_beta, h.rms_eps, 0)
             return
         self._fork()
@@ -248,6 +249,27 @@ class CounterStack:
     def update_only(self, seed: int = 777):
         """The fused update of every linear's local rows from the gradient already in place."""
         h = self.h
+        if self.grouped:
+            if getattr(self, "_upd_descs", None) is None:
+                from .runtime import update_descs
+                ents = []
+                for l in self.linears:
+                    if self.world > 1:
+                        sh = l.sharded
+                        if sh.rows == 0:
+                            continue
+                        sl = slice(sh.off, sh.off + sh.rows)
+                        ents.append(dict(state=sh.state, scale=sh.scale[sl], v=sh.v, grad_w=sh.gw_shard[:sh.rows],
+                                         packed2_out=sh.packed2[sl], in_features=l.shape.in_features, rows=sh.rows,
+                                         row_offset=sh.off))
+                    else:
+                        ents.append(dict(state=l.state, scale=l.scale, v=l.v, grad_w=l.grad_w, packed2_out=l.packed2,
+                                         in_features=l.shape.in_features, rows=l.shape.out_features, row_offset=0))
+                self._upd_descs = update_descs(ents)
+                self._upd_keep = ents        # the sliced views must outlive the descriptor array
+            if len(self._upd_descs):
+                self.ctx.counter_update_dense_many(self._upd_descs, h.C, h.lr, h.lr_scale, h.rms_beta, h.rms_eps, seed)
+            return
         for l in self.linears:
             I = l.shape.in_features
             if self.world > 1:

@@ -13,12 +13,12 @@
 // two fp32 operands; the dropped lo.lo and the rounding of lo are ~2^-22 relative.
 //
 // One launch runs a TABLE of problems (the three products of a step for many linears): work items
-// (problem, 128-row tile, column tile, K slice) are dealt round-robin to persistent CTAs.
+// (problem, 128-row tile, column tile, K slice) are drawn from a global counter by persistent CTAs.
 //   MotifCL computes the same products with scalar fp32 FMAs: kernels/compact_counter.cl:37-65
 //   (forward), :207-233 (backward to input), kernels/matmul.cl:413-563 (dW = dY^T X).
 //
 // Problem kinds (C[M,N] = A[M,K] . B[N,K]^T); every tensor is row-major fp32 behind a TMA map with
-// a 32 x 32 box and the 128-byte swizzle:
+// 32-float-wide boxes (K-major use: 128-byte swizzle; MN-major use: 3-D map, 32-byte-atom swizzle):
 //   kFusedY   A = X  [tokens,in]  K-major              B = T [out,in]  K-major   (exact)
 //   kFusedDX  A = dY [tokens,out] K-major, x scale[k]  B = T [out,in]  MN-major  (exact)
 //   kFusedDW  A = dY [tokens,out] MN-major             B = X [tokens,in] MN-major
@@ -26,7 +26,7 @@
 // operand has; the tensor core reads it in place (instruction-descriptor transpose bits), so no
 // transposed copy of an activation is ever made.
 //
-// CTA = 16 warps.  Shared memory holds two rings of 32-deep k-tiles: the RAW ring (4 to 6 slots: A and B
+// CTA = 16 warps.  Shared memory holds two rings of 32-deep k-tiles: the RAW ring (2 to 6 slots: A and B
 // as TMA delivers them; deep, because it has to cover the latency of HBM) and the LO ring (2 slots:
 // the lo tiles, which only bridge converter and MMA).
 //   warp 0        one lane draws work items from a global counter and issues the TMA copies
@@ -683,7 +683,9 @@ cudaError_t launch_fused_cap(const FusedProblem* probs, const FusedOperand* a_op
     tab.raw_slot = kABytes + ((bhi + 1023) & ~1023);
     tab.lo_slot = kABytes + ((blo + 1023) & ~1023);
     tab.pad0 = 0;
-    if (const char* dbg = getenv("MCL_FUSED_DBG")) tab.pad0 = atoi(dbg);
+#ifdef MCL_FUSED_PROF
+    if (const char* dbg = getenv("MCL_FUSED_DBG")) tab.pad0 = atoi(dbg);      // ablation switches of the profiling build
+#endif
     const long long budget = (long long)max_smem - (long long)fa.sharedSizeBytes - 1024 - kScratch - kLoSlots * (long long)tab.lo_slot;
     int n_raw = (int)(budget / tab.raw_slot);
     if (n_raw > kMaxRaw) n_raw = kMaxRaw;

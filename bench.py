@@ -322,6 +322,105 @@ def run_micro(args):
     print(json.dumps(out))
 
 
+def run_gemv_tp(args):
+    """--micro gemvtp:M[:LAYERS]  the decode-GEMV sweep with the weights sharded over the ranks of the job
+    (q, w1, w3 split by output features; o, w2 split by input features + one all-reduce each): what a
+    tensor-parallel decoder does per token.  Run under torchrun; with one rank it is the plain sweep."""
+    import torch
+    import torch.distributed as dist
+    from motifcl_b200 import Context, gemv_tp
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+    torch.cuda.set_stream(torch.cuda.Stream(device=local))
+    ctx = Context.on_torch_stream(local)
+    _, shape, *rest = args.micro.split(":")
+    M = int(shape)
+    layers = int(rest[0]) if rest else 32
+    dim, ffn = 4096, 14336
+    g = torch.Generator(device=dev).manual_seed(1234)          # every rank draws the same full matrices
+    rnd = lambda O, I: torch.randint(-2 ** 31, 2 ** 31 - 1, (O, I // 16), dtype=torch.int32, device=dev, generator=g)
+    sc = lambda O: torch.full((O,), 0.05, device=dev)
+    blocks = []
+    for _ in range(layers):
+        q = gemv_tp.ColumnParallelGemv(rnd(dim, dim), sc(dim), dim, rank, world)
+        o = gemv_tp.RowParallelGemv(rnd(dim, dim), sc(dim), dim, rank, world)
+        mlp = gemv_tp.TensorParallelMlp(rnd(ffn, dim), sc(ffn), rnd(ffn, dim), sc(ffn), rnd(dim, ffn), sc(dim), dim, ffn,
+                                        rank, world)
+        blocks.append((q, o, mlp))
+        torch.cuda.empty_cache()
+    x = torch.randn(M, dim, device=dev, generator=g)
+    fn = lambda a, p2, s_, y_, m, i, o_: ctx.ternary_gemv(a, p2, s_, y_, m, i, o_)
+    yq = torch.empty(M, blocks[0][0].rows, device=dev)
+    xo = torch.randn(M, blocks[0][1].cols, device=dev, generator=g)
+    yo, ym = torch.empty(M, dim, device=dev), torch.empty(M, dim, device=dev)
+    h1, h3 = torch.empty(M, blocks[0][2].cols, device=dev), torch.empty(M, blocks[0][2].cols, device=dev)
+
+    def sweep():
+        for q, o, mlp in blocks:
+            q(fn, x, yq)
+            o(fn, xo, yo)
+            mlp(fn, x, h1, h3, ym)
+
+    def timed(steps, warm):
+        for _ in range(warm):
+            sweep()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            sweep()
+        e1.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+    # one recorded batch per sweep on a single rank; with several ranks the sweep is launched eagerly (recording a
+    # sweep that contains NCCL all-reduces into this library's batch did not return on the 2-GPU box)
+    recorded = False
+    try:
+        if world > 1:
+            raise RuntimeError("several ranks")
+        sweep()
+        ctx.finish()
+        ctx.batch_begin()
+        try:
+            sweep()
+        finally:
+            batch = ctx.batch_end()
+        eager_sweep, sweep = sweep, batch.launch
+        sweep()
+        ctx.finish()
+        recorded = True
+    except Exception as exc:      # noqa: BLE001
+        if world == 1:
+            print(f"[rank {rank}] recording refused ({exc}); timing eager launches", file=sys.stderr)
+    with ClockSampler(local) as clk:
+        ms = timed(args.steps, max(args.warmup, 3))
+    hbm_peak, _, peak_kind = measured_peaks()
+    nbytes = layers * (2 * (dim * dim / 4) + 3 * (dim * ffn / 4))          # 2-bit weights of the whole model
+    if rank == 0:
+        print(json.dumps({"micro": args.micro, "kernel": "tensor-parallel ternary GEMV sweep", "n_gpus": world, "M": M,
+                          "layers": layers, "ms_per_sweep": ms, "tokens_per_s": M / (ms * 1e-3),
+                          "weight_bytes": nbytes, "achieved": nbytes / ms / 1e6, "unit": "GB/s (all ranks)",
+                          "peak": hbm_peak * world, "frac": nbytes / ms / 1e6 / (hbm_peak * world),
+                          "peak_kind": peak_kind, "all_reduces_per_sweep": 2 * layers if world > 1 else 0,
+                          "recorded_batch": recorded, "clocks": clk.summary(), "gpu_launches": ctx.launch_count}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -335,6 +434,8 @@ def main():
     ap.add_argument("--eager", action="store_true", help="do not record the step into one batch (for per-kernel profiling)")
     ap.add_argument("--micro", default=None, help="single-kernel timing, see run_micro()")
     args = ap.parse_args()
+    if args.micro and args.micro.startswith("gemvtp"):
+        return run_gemv_tp(args)
     if args.micro:
         return run_micro(args)
     wl = workload(args.workload)

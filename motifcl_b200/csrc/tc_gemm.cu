@@ -17,13 +17,14 @@
 // A_p[M,K] . B_q[N,K]^T, optionally scaled per column, or writes split-K partial sums that a
 // fixed-order reduction kernel adds up (deterministic).
 //
-// Structure of a CTA (128 threads, one 128 x BN output tile, BN a multiple of 32 up to 256):
+// Structure of the persistent CTA (192 threads; work items = 128 x BN output tile x split-K slice, dealt
+// round-robin; BN a multiple of 32 up to 256):
 //   warp 0 lane 0   TMA producer: cp.async.bulk.tensor (3-D tile {64 k, rows, plane}, 128-byte
 //                   swizzle) into a ring of `stages` shared-memory slots, mbarrier complete_tx
 //   warp 1 lane 0   MMA issuer: four tcgen05.mma (K = 16 each) per slot, tcgen05.commit to
-//                   release the slot, final commit to signal the accumulator
-//   warp 2          allocates / frees the TMEM columns
-//   all warps       epilogue: tcgen05.ld 32 lanes x 32 columns, scale, 128-bit stores
+//                   release the slot, final commit to signal the accumulator; warp 1 owns TMEM
+//   warps 2..5      epilogue: tcgen05.ld 32 lanes x 32 columns, scale, 128-bit stores
+// Two accumulators in TMEM let the epilogue of one item overlap the main loop of the next.
 // Every mbarrier wait is bounded: on time-out the kernel records an error word, skips the
 // rest of its work, frees its TMEM and returns.
 #include <cuda.h>

@@ -28,8 +28,6 @@ struct mcl_cuda_ctx {
     int act_terms = 3;
     int grad_terms = 6;
     int* err_word = nullptr;     // device word the tensor-core kernels set when a bounded wait gives up
-    void* gv_state = nullptr;    // accumulators and arrival counters of the tensor-core GEMV: zero between calls
-    size_t gv_state_bytes = 0;
     const uint32_t* seed_offset = nullptr;   // device word added to every update seed (mcl_cuda_set_seed_offset)
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     uint64_t lane_mark = 0;      // launches at the last lane_fork (when this context is a lane)
@@ -175,11 +173,10 @@ int check_device_error(mcl_cuda_ctx* ctx) {
     if (e != cudaSuccess) return fail_cuda(ctx, "error-word read", e);
     if (w != 0) {
         cudaMemset(ctx->err_word, 0, sizeof(int));
-        if (ctx->gv_state) cudaMemset(ctx->gv_state, 0, ctx->gv_state_bytes);      // a call that gave up may have left sums behind
-        const char* who = (w % 10) == 1 ? "copy producer (slot never released)" : (w % 10) == 2 ? "MMA issuer (tile never arrived)"
-                          : (w % 10) == 3 ? "epilogue (accumulator never completed)" : "a role of the kernel";
-        return fail(ctx, MCL_CUDA_ECUDA, std::string("tensor-core kernel gave up a bounded wait (code ") + std::to_string(w) +
-                                             "): " + who + "; results of that call are invalid");
+        const char* who = w == 1 ? "TMA producer (slot never released)" : w == 2 ? "MMA issuer (tile never arrived)"
+                                                                                 : "epilogue (accumulator never completed)";
+        return fail(ctx, MCL_CUDA_ECUDA, std::string("tensor-core kernel gave up a bounded wait: ") + who +
+                                             "; results of that call are invalid");
     }
     return MCL_CUDA_OK;
 }
@@ -251,7 +248,6 @@ void mcl_cuda_destroy(mcl_cuda_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->err_word) cudaFree(ctx->err_word);
-    if (ctx->gv_state) cudaFree(ctx->gv_state);
     if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
     if (ctx->ev_join) cudaEventDestroy(ctx->ev_join);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
@@ -1111,20 +1107,10 @@ int mcl_cuda_ternary_gemv(mcl_cuda_ctx* ctx, const float* x, const uint32_t* pac
         reinterpret_cast<uintptr_t>(packed2) % 16 == 0) {
         void* wsp = nullptr;
         MCL_TRY(ws_reserve(ctx, mcl::gemv_tc_workspace_bytes((int)M, (int)in_features, (int)out_features), &wsp));
-        const size_t need = mcl::gemv_tc_state_bytes((int)M, (int)in_features, (int)out_features);
-        if (need > ctx->gv_state_bytes) {      // grow-only, zeroed once; every call leaves it zero
-            if (ctx->recording) return fail(ctx, MCL_CUDA_EINVAL, "ternary gemv: the first call of a shape must run outside a recorded batch");
-            MCL_CU(ctx, op, cudaStreamSynchronize(ctx->stream));
-            if (ctx->gv_state) cudaFree(ctx->gv_state);
-            ctx->gv_state = nullptr; ctx->gv_state_bytes = 0;
-            MCL_CU(ctx, op, cudaMalloc(&ctx->gv_state, need));
-            MCL_CU(ctx, op, cudaMemset(ctx->gv_state, 0, need));
-            ctx->gv_state_bytes = need;
-        }
         int launches = 0;
         cudaError_t e = mcl::launch_ternary_gemv_tc(x, packed2, scale, y, (int)M, (int)in_features, (int)out_features,
-                                                    wsp, ctx->gv_state, ctx->err_word, ctx->sm_count, ctx->max_smem,
-                                                    ctx->stream, &launches);
+                                                    wsp, ctx->err_word, ctx->sm_count, ctx->max_smem, ctx->stream,
+                                                    &launches);
         ctx->launches += launches;
         if (e != cudaSuccess) return fail_cuda(ctx, op, e);
         return MCL_CUDA_OK;

@@ -12,11 +12,8 @@
 //     int32 accumulators in TMEM;
 //   * sum_k x t = sum_k x f - sum_k x, so a per-row digit sum is subtracted at the end.
 // Integer accumulation is exact and order-independent, which makes split-K over atomics
-// deterministic.  The digits are recombined in double precision by the epilogue warp that brings the
-// last K slice of a row (from its registers when K is not split), which also zeroes the accumulator,
-// so a call is two launches: quantize, contraction.
+// deterministic.  A finalize kernel recombines the digits in double precision.
 #include <cuda.h>
-#include <cstdlib>
 
 #include "kernels.h"
 #include "tc_ptx.cuh"
@@ -34,15 +31,8 @@ constexpr int GV_MAX_STAGES = 6;
 struct GvParams {
     int O, I, Nq;
     int kblocks, kb_per_split, splits, stages;
-    int* acc;          // int32 [Nq][O]: column n of all rows contiguous, so a warp's 32 rows coalesce; zero between calls
-    int* done;         // arrivals per (row tile, lane quarter) when k is split; zero between calls
+    int* acc;          // int32 [Nq][O]: column n of all rows contiguous, so a warp's 32 rows coalesce
     int* err;
-    // finalize, done by the last CTA that adds into a row: y[m,o] = scale[o] * xscale[m] * sum_d 128^-d (acc - corr)
-    const int* corr;
-    const float* xscale;
-    const float* scale;
-    float* y;
-    int M;
 };
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
@@ -110,35 +100,12 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
     if (warp == 0) {
         if (lane == 0) {
             // ---- TMA producer: packed weight tile + the two activation-digit tiles of a k-block ----
-            // The weights do not depend on the quantize kernel that precedes this one in the stream: when the
-            // launch allows it (programmatic dependent launch) the first ring of weight tiles is already in
-            // flight while that kernel still runs; the digit tiles follow once it has completed.
-            uint32_t pre = 0;
-            int pre_kb[GV_MAX_STAGES];
-            for (int item = blockIdx.x; item < n_items && pre < (uint32_t)S; item += gridDim.x) {
-                const int rt = item % row_tiles, split = item / row_tiles;
-                const int kb0 = split * p.kb_per_split;
-                const int nkb = min(p.kb_per_split, p.kblocks - kb0);
-                for (int j = 0; j < nkb && pre < (uint32_t)S; ++j, ++pre) {
-                    const uint32_t st = base + pre * stage_bytes;
-                    mbar_expect_tx(raw_full((int)pre), GV_RAW + 2 * b_tile);
-                    tma_load_2d(st, &tmP, raw_full((int)pre), (kb0 + j) * (GV_KB / 4), rt * GV_ROWS);
-                    pre_kb[pre] = kb0 + j;
-                }
-            }
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            for (uint32_t t = 0; t < pre; ++t) {
-                const uint32_t st = base + t * stage_bytes;
-                tma_load_2d(st + GV_RAW + 2 * GV_ATILE, &tmX, raw_full((int)t), pre_kb[t] * GV_KB, 0);
-                tma_load_2d(st + GV_RAW + 2 * GV_ATILE + b_tile, &tmX, raw_full((int)t), pre_kb[t] * GV_KB + 128, 0);
-            }
             uint32_t it = 0;
             for (int item = blockIdx.x; item < n_items && !abort_flag; item += gridDim.x) {
                 const int rt = item % row_tiles, split = item / row_tiles;
                 const int kb0 = split * p.kb_per_split;
                 const int nkb = min(p.kb_per_split, p.kblocks - kb0);
                 for (int j = 0; j < nkb; ++j, ++it) {
-                    if (it < pre) continue;              // issued above
                     const int s = (int)(it % (uint32_t)S);
                     const uint32_t ph = (it / (uint32_t)S) & 1u;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 11); break; }
@@ -224,7 +191,6 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
         }
     } else {
         // ---- epilogue warps: int32 accumulator -> global (atomic when k is split) ---------------
-        asm volatile("griddepcontrol.wait;" ::: "memory");      // corr and xscale come from the preceding kernel
         const int q = warp & 3;
         uint32_t n_local = 0;
         for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_local) {
@@ -237,52 +203,18 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
             tc_fence_after();
             const int row = rt * GV_ROWS + q * 32 + lane;
             int* dst = p.acc + row;
-            const bool row_ok = row < p.O;
-            const float row_scale = row_ok ? __ldg(p.scale + row) : 0.0f;
-            auto finish = [&](int m, int a0, int a1, int a2, int a3) {      // four digit sums of activation row m -> y
-                const double sum = (double)(a0 - __ldg(p.corr + 4 * m)) + (double)(a1 - __ldg(p.corr + 4 * m + 1)) * (1.0 / 128.0) +
-                                   (double)(a2 - __ldg(p.corr + 4 * m + 2)) * (1.0 / 16384.0) +
-                                   (double)(a3 - __ldg(p.corr + 4 * m + 3)) * (1.0 / 2097152.0);
-                p.y[(size_t)m * p.O + row] = (float)((double)row_scale * (double)__ldg(p.xscale + m) * sum);
-            };
             for (int c0 = 0; c0 < Nq; c0 += 16) {
                 uint32_t v[16];
                 tmem_ld16(tmem_base + acc * (uint32_t)Nq + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
                 tmem_ld_wait();
-                if (row_ok) {
-                    if (p.splits == 1) {      // the whole sum is in the accumulator: finish from registers
+                if (row < p.O) {
+                    if (p.splits == 1) {
 #pragma unroll
-                        for (int j = 0; j < 16; j += 4)
-                            if ((c0 + j) / 4 < p.M) finish((c0 + j) / 4, (int)v[j], (int)v[j + 1], (int)v[j + 2], (int)v[j + 3]);
+                        for (int j = 0; j < 16; ++j) dst[(size_t)(c0 + j) * p.O] = (int)v[j];
                     } else {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) atomicAdd(dst + (size_t)(c0 + j) * p.O, (int)v[j]);
                     }
-                }
-            }
-            if (p.splits > 1) {
-                // The warp that brings the last K slice of its 32 rows finishes them and leaves the accumulator
-                // and the counter zero for the next call (integer sums do not depend on the order of arrival).
-                __threadfence();
-                __syncwarp();
-                int old = 0;
-                if (lane == 0) old = atomicAdd(p.done + rt * 4 + q, 1);
-                old = __shfl_sync(0xffffffffu, old, 0);
-                if (old == p.splits - 1) {
-                    __threadfence();
-                    if (row_ok) {
-                        for (int c0 = 0; c0 < Nq; c0 += 16) {      // 16 loads in flight per round trip to L2
-                            int a[16];
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) a[j] = __ldcg(dst + (size_t)(c0 + j) * p.O);
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) __stcg(dst + (size_t)(c0 + j) * p.O, 0);
-#pragma unroll
-                            for (int j = 0; j < 16; j += 4)
-                                if ((c0 + j) / 4 < p.M) finish((c0 + j) / 4, a[j], a[j + 1], a[j + 2], a[j + 3]);
-                        }
-                    }
-                    if (lane == 0) p.done[rt * 4 + q] = 0;
                 }
             }
             tc_fence_before();
@@ -302,28 +234,21 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
 }
 
 // ---- activation rows -> four int8 digit rows each, digit sums, power-of-two scale ---------------
-// grid = (Nq / 4 activation row slots, chunks).  Every block scans the whole row (it is at most 56 KiB
-// and sits in L2) for the row maximum, block 0 of a row also for the digit sums; each block writes the
-// digits of its own chunk of `chunk` columns.  Slots >= M are written as zeros.
-__global__ void __launch_bounds__(256) gemv_quantize_kernel(const float* __restrict__ x, int M, int I, int chunk,
+// grid = Nq / 4 blocks (one per activation row slot; slots >= M are written as zeros)
+__global__ void __launch_bounds__(256) gemv_quantize_kernel(const float* __restrict__ x, int M, int I,
                                                             signed char* __restrict__ xq, int* __restrict__ corr,
                                                             float* __restrict__ xscale) {
     __shared__ float red[256];
     __shared__ int isum[4];
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the contraction may start fetching weights
     const int m = blockIdx.x, tid = threadIdx.x;
-    const int k_begin = blockIdx.y * chunk, k_end = min(I, k_begin + chunk);
     signed char* q0 = xq + (size_t)(4 * m) * I;
     if (m >= M) {
-        for (int k = k_begin + tid; k < k_end; k += 256) { q0[k] = 0; q0[I + k] = 0; q0[2 * (size_t)I + k] = 0; q0[3 * (size_t)I + k] = 0; }
+        for (int k = tid; k < I; k += 256) { q0[k] = 0; q0[I + k] = 0; q0[2 * (size_t)I + k] = 0; q0[3 * (size_t)I + k] = 0; }
         return;
     }
-    const float4* xr4 = reinterpret_cast<const float4*>(x + (size_t)m * I);      // I % 64 == 0, x 16-byte aligned
+    const float* xr = x + (size_t)m * I;
     float amax = 0.0f;
-    for (int k4 = tid; k4 < (I >> 2); k4 += 256) {
-        const float4 v = __ldg(xr4 + k4);
-        amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
-    }
+    for (int k = tid; k < I; k += 256) amax = fmaxf(amax, fabsf(__ldg(xr + k)));
     red[tid] = amax;
     if (tid < 4) isum[tid] = 0;
     __syncthreads();
@@ -335,27 +260,35 @@ __global__ void __launch_bounds__(256) gemv_quantize_kernel(const float* __restr
     int e = 0;
     if (amax > 0.0f) frexpf(amax, &e);              // amax = f * 2^e, f in [0.5, 1): 2^e > amax
     const float inv = ldexpf(64.0f, -e);            // x * inv = x' * 64 with |x'| < 1, exact scaling
-    const float* xr = x + (size_t)m * I;
-    const bool sums = blockIdx.y == 0;
     int s0 = 0, s1 = 0, s2 = 0, s3 = 0;
-    for (int k = (sums ? 0 : k_begin) + tid; k < (sums ? I : k_end); k += 256) {
+    for (int k = tid; k < I; k += 256) {
         float v = __ldg(xr + k) * inv;
         const float d0 = rintf(v); v = (v - d0) * 128.0f;
         const float d1 = rintf(v); v = (v - d1) * 128.0f;
         const float d2 = rintf(v); v = (v - d2) * 128.0f;
         const float d3 = rintf(v);
-        if (k >= k_begin && k < k_end) {
-            const int kp = gv_kperm(k);          // the order in which the expanded weights lie
-            q0[kp] = (signed char)d0; q0[I + kp] = (signed char)d1;
-            q0[2 * (size_t)I + kp] = (signed char)d2; q0[3 * (size_t)I + kp] = (signed char)d3;
-        }
+        const int kp = gv_kperm(k);          // the order in which the expanded weights lie
+        q0[kp] = (signed char)d0; q0[I + kp] = (signed char)d1;
+        q0[2 * (size_t)I + kp] = (signed char)d2; q0[3 * (size_t)I + kp] = (signed char)d3;
         s0 += (int)d0; s1 += (int)d1; s2 += (int)d2; s3 += (int)d3;
     }
-    if (!sums) return;
     atomicAdd(&isum[0], s0); atomicAdd(&isum[1], s1); atomicAdd(&isum[2], s2); atomicAdd(&isum[3], s3);
     __syncthreads();
     if (tid < 4) corr[4 * m + tid] = isum[tid];
     if (tid == 0) xscale[m] = ldexpf(1.0f, e) / 64.0f;
+}
+
+// y[m,o] = scale[o] * xscale[m] * sum_d 128^-d * (acc[o][4m+d] - corr[4m+d])
+__global__ void gemv_finalize_kernel(const int* __restrict__ acc, const int* __restrict__ corr,
+                                     const float* __restrict__ xscale, const float* __restrict__ scale,
+                                     float* __restrict__ y, int M, int O, int Nq) {
+    const int o = blockIdx.x * blockDim.x + threadIdx.x, m = blockIdx.y;
+    if (o >= O) return;
+    const int a0 = __ldg(acc + (size_t)(4 * m + 0) * O + o), a1 = __ldg(acc + (size_t)(4 * m + 1) * O + o);
+    const int a2 = __ldg(acc + (size_t)(4 * m + 2) * O + o), a3 = __ldg(acc + (size_t)(4 * m + 3) * O + o);
+    const double sum = (double)(a0 - corr[4 * m]) + (double)(a1 - corr[4 * m + 1]) * (1.0 / 128.0) +
+                       (double)(a2 - corr[4 * m + 2]) * (1.0 / 16384.0) + (double)(a3 - corr[4 * m + 3]) * (1.0 / 2097152.0);
+    y[(size_t)m * O + o] = (float)((double)__ldg(scale + o) * (double)xscale[m] * sum);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -392,22 +325,18 @@ bool gemv_tc_supported(int M, int in_features, int out_features) {
     return M >= 1 && M <= 16 && in_features % 64 == 0 && in_features >= 256 && out_features >= 1;
 }
 
-// workspace (scratch of one call): Xq [64][in] int8 | corr [64] int | xscale [16] float
+// workspace: Xq [64][in] int8 | corr [64] int | xscale [16] float | acc [Nq][out] int32
 size_t gemv_tc_workspace_bytes(int M, int in_features, int out_features) {
-    (void)M; (void)out_features;
-    return (((size_t)64 * in_features + 1023) & ~size_t(1023)) + 1024;
-}
-// state (kept zero between calls by the kernel itself): acc [Nq][out] int32 | arrivals [row tiles * 4] int
-size_t gemv_tc_state_bytes(int M, int in_features, int out_features) {
-    (void)in_features;
     const int Nq = 16 * ((M + 3) / 4);
-    const size_t row_tiles = ((size_t)out_features + GV_ROWS - 1) / GV_ROWS;
-    return (((size_t)out_features * Nq * sizeof(int) + 1023) & ~size_t(1023)) + ((row_tiles * 4 * sizeof(int) + 1023) & ~size_t(1023));
+    size_t o = ((size_t)64 * in_features + 1023) & ~size_t(1023);
+    o += 1024;
+    o += ((size_t)out_features * Nq * sizeof(int) + 1023) & ~size_t(1023);
+    return o;
 }
 
 cudaError_t launch_ternary_gemv_tc(const float* x, const uint32_t* packed2, const float* scale, float* y, int M,
-                                   int in_features, int out_features, void* workspace, void* state, int* err_word,
-                                   int sm_count, size_t max_smem, cudaStream_t stream, int* launches) {
+                                   int in_features, int out_features, void* workspace, int* err_word, int sm_count,
+                                   size_t max_smem, cudaStream_t stream, int* launches) {
     const int I = in_features, O = out_features;
     const int Nq = 16 * ((M + 3) / 4);
     char* w = static_cast<char*>(workspace);
@@ -415,8 +344,7 @@ cudaError_t launch_ternary_gemv_tc(const float* x, const uint32_t* packed2, cons
     size_t o = ((size_t)64 * I + 1023) & ~size_t(1023);
     int* corr = reinterpret_cast<int*>(w + o);
     float* xscale = reinterpret_cast<float*>(w + o + 512);
-    int* acc = static_cast<int*>(state);
-    int* done = reinterpret_cast<int*>(static_cast<char*>(state) + (((size_t)O * Nq * sizeof(int) + 1023) & ~size_t(1023)));
+    int* acc = reinterpret_cast<int*>(w + o + 1024);
 
     GvParams p;
     p.O = O; p.I = I; p.Nq = Nq;
@@ -430,8 +358,7 @@ cudaError_t launch_ternary_gemv_tc(const float* x, const uint32_t* packed2, cons
     }
     p.kb_per_split = (p.kblocks + splits - 1) / splits;
     p.splits = splits = (p.kblocks + p.kb_per_split - 1) / p.kb_per_split;
-    p.acc = acc; p.done = done; p.err = err_word;
-    p.corr = corr; p.xscale = xscale; p.scale = scale; p.y = y; p.M = M;
+    p.acc = acc; p.err = err_word;
     const size_t stage_bytes = (size_t)GV_RAW + 2 * GV_ATILE + 2 * (size_t)Nq * 128;
     int stages = (int)((max_smem - 2048) / stage_bytes);
     if (stages > GV_MAX_STAGES) stages = GV_MAX_STAGES;
@@ -443,31 +370,24 @@ cudaError_t launch_ternary_gemv_tc(const float* x, const uint32_t* packed2, cons
         return cudaErrorInvalidValue;
     if (!gv_map_2d(&mx, xq, (size_t)I, 64, (size_t)I, 128, Nq, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
 
-    int chunks = (I + 511) / 512;
-    if (chunks > 32) chunks = 32;
-    const int chunk = (((I + chunks - 1) / chunks) + 15) & ~15;      // whole groups of 16 (the k permutation's unit)
-    gemv_quantize_kernel<<<dim3(Nq / 4, (I + chunk - 1) / chunk), 256, 0, stream>>>(x, M, I, chunk, xq, corr, xscale);
+    gemv_quantize_kernel<<<Nq / 4, 256, 0, stream>>>(x, M, I, xq, corr, xscale);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     ++*launches;
+    if (splits > 1) {
+        e = cudaMemsetAsync(acc, 0, (size_t)O * Nq * sizeof(int), stream);
+        if (e != cudaSuccess) return e;
+    }
     const size_t smem = (size_t)stages * stage_bytes + 1024;
     e = ensure_dynamic_smem(reinterpret_cast<const void*>(gemv_tc_kernel), 5, max_smem);
     if (e != cudaSuccess) return e;
     int ctas = row_tiles * splits;
     if (ctas > sm_count) ctas = sm_count;
-    static const bool pdl = getenv("MCL_CUDA_GEMV_PDL") ? atoi(getenv("MCL_CUDA_GEMV_PDL")) != 0 : false;
-    if (pdl) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(ctas); cfg.blockDim = dim3(GV_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
-        cudaLaunchAttribute at[1];
-        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        at[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = at; cfg.numAttrs = 1;
-        e = cudaLaunchKernelEx(&cfg, gemv_tc_kernel, mp, mx, p);
-        if (e != cudaSuccess) return e;
-    } else {
-        gemv_tc_kernel<<<ctas, GV_THREADS, smem, stream>>>(mp, mx, p);
-    }
+    gemv_tc_kernel<<<ctas, GV_THREADS, smem, stream>>>(mp, mx, p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    ++*launches;
+    gemv_finalize_kernel<<<dim3((O + 255) / 256, M), 256, 0, stream>>>(acc, corr, xscale, scale, y, M, O, Nq);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     ++*launches;

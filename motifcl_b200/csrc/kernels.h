@@ -120,11 +120,8 @@ cudaError_t launch_ternary_gemv(const float* x, const uint32_t* packed2, const f
 // gemv_tc.cu -- the same GEMV as integer tensor-core MMA on digit-split activations
 bool gemv_tc_supported(int M, int in_features, int out_features);
 size_t gemv_tc_workspace_bytes(int M, int in_features, int out_features);
-// persistent state of the contraction (int32 accumulators and arrival counters): must be zero before the first
-// call and is left zero by every call
-size_t gemv_tc_state_bytes(int M, int in_features, int out_features);
 cudaError_t launch_ternary_gemv_tc(const float* x, const uint32_t* packed2, const float* scale, float* y, int M,
-                                   int in_features, int out_features, void* workspace, void* state, int* err_word, int sm_count,
+                                   int in_features, int out_features, void* workspace, int* err_word, int sm_count,
                                    size_t max_smem, cudaStream_t stream, int* launches);
 
 // eltwise.cu: op 0 add, 1 sub, 2 mul, 3 mul_scalar, 4 add_scalar, 5 zero

@@ -236,6 +236,26 @@ def test_ternary_gemv_vs_oracle(ctx, orc, M, O, I):
     assert rel_l2(y.cpu().numpy(), orc.forward(x, st, scale, 11, O)) <= 1e-5
 
 
+def test_ternary_gemv_calls_in_a_row_leave_no_residue(ctx, orc):
+    """Split-K accumulators of the tensor-core GEMV live in the context's workspace: alternate shapes and
+    activation counts and repeat the first call at the end."""
+    calls = [(4, 4096, 1024), (1, 512, 2048), (16, 1000, 512), (4, 4096, 1024), (1, 256, 4096), (4, 4096, 1024)]
+    data = {}
+    for M, O, I in calls:
+        key = (M, O, I)
+        if key not in data:
+            rng = np.random.default_rng(M + O + I)
+            st = synth.counters(5, (O + I) % 97, O, I).reshape(-1)
+            p2 = orc.pack2(st, 11, I, O)
+            scale = rng.uniform(0.02, 0.2, O).astype(np.float32)
+            x = rng.standard_normal((M, I)).astype(np.float32)
+            data[key] = (_t(x), _t(p2.view(np.int32)), _t(scale), orc.ternary_gemv(x, p2, scale, f64=True))
+        xd, pd, sd, ref = data[key]
+        y = torch.full((M, O), 9.0, dtype=torch.float32, device=DEV)
+        ctx.ternary_gemv(xd, pd, sd, y, M, I, O)
+        assert rel_l2(y.cpu().numpy(), ref) <= 1e-5, key
+
+
 def test_argument_checks_mirror_the_reference(ctx):
     """Refusals of MotifCL src/runtime/vulkan_backend.cpp:8497-8521."""
     st = torch.zeros(48, dtype=torch.uint8, device=DEV)

@@ -322,6 +322,55 @@ def run_micro(args):
     print(json.dumps(out))
 
 
+# MotifCL's published records for the ops of this path (reports/vulkan-perf/*.json, Radeon RX 580, median
+# wall time of dispatch + wait): op -> {shape: (median_us, throughput, unit)}
+PUBLISHED_RX580 = {
+    "counter_update_f32": {"in1024_out256_N8": (608.6, None, None)},
+    "counter_decode_weight_f32": {"in1024_out256": (188.3, None, None)},
+    "counter_backward_input_f32": {"in1024_out256_N8": (501.2, 8.37, "GFLOP/s")},
+    "matmul_f32": {"512x512x512": (None, 609.5, "GFLOP/s")},
+    "matmul_f32_nt": {"512x512x512": (None, 451.2, "GFLOP/s")},
+    "matmul_f32_tn": {"512x512x512": (None, 538.2, "GFLOP/s")},
+    "matmul_f32_m1": {"1x2048x2048": (497.9, 16.8, "GFLOP/s")},
+}
+
+
+def run_refperf(args):
+    """--micro refperf  runs MotifCL's OWN micro-benchmark program (benchmarks/bench_vulkan_perf.cpp, compiled
+    unmodified against the CUDA adapter: motifcl_b200/adapter/Makefile) for the ops of the counter-linear path and
+    prints its records beside the numbers MotifCL publishes for them."""
+    import glob
+    import subprocess
+    exe = os.path.join(ROOT, "motifcl_b200", "adapter", "_build", "bench_vulkan_perf")
+    if not os.path.isfile(exe):
+        print(json.dumps({"micro": "refperf", "unavailable": "adapter binaries are not built (make -C motifcl_b200/adapter "
+                                                             "needs the MotifCL tree)"}))
+        return
+    out_dir = os.path.join(ROOT, "gpurun_out", "vulkan-perf")
+    rows = []
+    for flt in ("counter_", "matmul_f32"):
+        r = subprocess.run([exe, "--filter", flt, "--out", os.path.join(out_dir, flt.strip("_"))], capture_output=True,
+                           text=True, timeout=600)
+        if r.returncode != 0:
+            print(json.dumps({"micro": "refperf", "filter": flt, "returncode": r.returncode,
+                              "stderr": r.stderr[-400:]}))
+            continue
+        for f in sorted(glob.glob(os.path.join(out_dir, flt.strip("_"), "*.json"))):
+            rec = json.load(open(f))
+            for row in rec["rows"]:
+                pub = PUBLISHED_RX580.get(rec["op"], {}).get(row["shape"])
+                if row.get("result") == "ERROR" or pub is None:
+                    continue
+                rows.append({"op": rec["op"], "shape": row["shape"], "device": rec["vulkan_device"],
+                             "median_us": row["median_us"], "min_us": row["min_us"],
+                             "throughput": row.get("achieved_gflops", row.get("achieved_gbs")),
+                             "published_rx580_median_us": pub[0], "published_rx580_throughput": pub[1],
+                             "speedup_wall": (pub[0] / row["median_us"]) if pub[0] else
+                             (row.get("achieved_gflops", 0.0) / pub[1] if pub[1] else None)})
+    print(json.dumps({"micro": "refperf", "program": "MotifCL benchmarks/bench_vulkan_perf.cpp (unmodified)",
+                      "methodology": "median wall time of 50 runs after 5 warm-ups, dispatch + wait", "rows": rows}))
+
+
 def run_gemv_tp(args):
     """--micro gemvtp:M[:LAYERS]  the decode-GEMV sweep with the weights sharded over the ranks of the job
     (q, w1, w3 split by output features; o, w2 split by input features + one all-reduce each): what a
@@ -436,6 +485,8 @@ def main():
     args = ap.parse_args()
     if args.micro and args.micro.startswith("gemvtp"):
         return run_gemv_tp(args)
+    if args.micro == "refperf":
+        return run_refperf(args)
     if args.micro:
         return run_micro(args)
     wl = workload(args.workload)

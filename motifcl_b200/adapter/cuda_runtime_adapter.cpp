@@ -224,6 +224,9 @@ VulkanOpResult VulkanRuntime::dispatch_cached(const std::uint32_t* spirv, std::s
             return r;
     }
     if (rc != MCL_CUDA_OK) { r.error = mcl_cuda_last_error(ctx); return r; }
+    // Outside a batch the reference submits one command buffer and waits for its fence, so a caller that times
+    // a call (benchmarks/bench_vulkan_perf.cpp: "dispatch + wait wall time") times the work, not the enqueue.
+    if (!impl_->batch && mcl_cuda_finish(ctx) != MCL_CUDA_OK) { r.error = mcl_cuda_last_error(ctx); return r; }
     r.success = true;
     return r;
 }

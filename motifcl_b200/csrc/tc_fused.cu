@@ -31,6 +31,7 @@
 // the lo tiles, which only bridge converter and MMA).
 //   warp 0        one lane draws work items from a global counter and issues the TMA copies
 //   warp 1        allocates TMEM; one lane issues tcgen05.mma and commits
+//   warp 2        one lane asks the tiles of the next work item into L2 (TMA prefetch), a few tiles ahead
 //   warps 4..7    epilogue: tcgen05.ld of TMEM lane quarter (warp & 3), scale, 128-bit stores
 //   warps 8..15   converters: wait for the boxes, write the `lo` tiles (and the scaled `hi` tile
 //                 for dX), fence to the async proxy, arrive
@@ -56,7 +57,8 @@ constexpr int kABytes = 4 * kBox;            // an A tile: 128 rows (or 128 m) x
 constexpr int kMaxRaw = 6;                   // slots of the raw ring (A hi + B hi as TMA delivers them)
 constexpr int kLoSlots = 2;                  // slots of the lo ring (A lo, and B lo for two fp32 operands)
 constexpr int kQueue = 4;                    // work items in flight between the scheduler lane and the other roles
-constexpr int kQueueReaders = 1 + 4 + 8;     // MMA lane, epilogue warps, converter warps
+constexpr int kQueueReaders = 1 + 1 + 4 + 8; // MMA lane, prefetch lane, epilogue warps, converter warps
+constexpr int kPrefetchAhead = 12;           // k-tiles the prefetch lane may run ahead of the copies
 constexpr int kScratch = 4 * 4096;           // epilogue staging, 4 KiB per warp
 constexpr int kAccStride = 256;              // TMEM columns between the two accumulators
 
@@ -65,6 +67,7 @@ struct FusedTable {
     CUtensorMap maps[2 * CAP];
     int n_problems, n_items;
     int n_raw, raw_slot, lo_slot, pad0;      // ring geometry (bytes), chosen by the launcher for the table's tiles
+    int prefetch, pad1, pad2, pad3;          // prefetch: the prefetch lane asks tiles into L2 ahead of the copies
     FusedProblem p[CAP];
 };
 
@@ -145,7 +148,8 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                                                                 int* next_item) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bars[2 * kMaxRaw + 4 + 4 + 2 * kQueue];
-    __shared__ int queue_item[kQueue];
+    __shared__ int queue_item[kQueue], queue_next[kQueue];
+    __shared__ unsigned int tiles_issued;      // progress of the TMA lane, paces the prefetch lane
     __shared__ FusedProblem sp[CAP];
 #ifdef MCL_FUSED_PROF
     __shared__ long long t_issue[kMaxRaw], t_conv[kMaxRaw], t_arr[kMaxRaw], t_mma[kMaxRaw], t_commit[kMaxRaw];
@@ -171,6 +175,7 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
 
     if (threadIdx.x == 0) {
         abort_flag = (*reinterpret_cast<volatile int*>(err) != 0);
+        tiles_issued = 0;
         for (int s = 0; s < kMaxRaw; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), 1); }
         for (int s = 0; s < kLoSlots; ++s) { mbar_init(lo_full(s), kConvThreads); mbar_init(lo_empty(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 128); }
@@ -223,14 +228,19 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
             long long pf_wait = 0, pf_issue = 0; (void)pf_wait; (void)pf_issue;
             long long h0 = 0, h1 = 0, h2 = 0, h3 = 0, h4 = 0; (void)h0; (void)h1; (void)h2; (void)h3; (void)h4;
             PROF_T(tstart);
+            // two items are drawn ahead: the next one is published with the current one (the prefetch lane asks
+            // its tiles into L2), the one after is still in flight from the counter
             int drawn = atomicAdd(next_item, 1);
+            int drawn2 = atomicAdd(next_item, 1);
             for (;;) {
                 const int item = abort_flag ? n_items : drawn;
-                if (item < n_items) drawn = atomicAdd(next_item, 1);      // in flight while this item is issued
+                drawn = drawn2;
+                if (item < n_items) drawn2 = atomicAdd(next_item, 1);
                 {
                     const int s = (int)(q_seq % kQueue);
                     if (!mbar_wait(q_empty(s), ((q_seq / kQueue) & 1u) ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 17); break; }
                     *reinterpret_cast<volatile int*>(&queue_item[s]) = item < n_items ? item : n_items;
+                    *reinterpret_cast<volatile int*>(&queue_next[s]) = drawn < n_items ? drawn : n_items;
                     mbar_arrive(q_full(s));
                     ++q_seq;
                 }
@@ -266,12 +276,14 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                     else tma_load_2d(st, ma, raw_full(s), k0, m0);
                     if (mode == kFusedY) tma_load_2d(st + kABytes, mb, raw_full(s), k0, n0);
                     else tma_load_3d(st + kABytes, mb, raw_full(s), 0, k0, n0 >> 5);
+                    *reinterpret_cast<volatile unsigned int*>(&tiles_issued) = it + 1;
                     PROF_T(t2); PROF_ADD(pf_issue, t1, t2);
                 }
                 if (abort_flag) {      // tell the other roles to stop
                     const int s = (int)(q_seq % kQueue);
                     if (mbar_wait(q_empty(s), ((q_seq / kQueue) & 1u) ^ 1u, &abort_flag)) {
                         *reinterpret_cast<volatile int*>(&queue_item[s]) = n_items;
+                        *reinterpret_cast<volatile int*>(&queue_next[s]) = n_items;
                         mbar_arrive(q_full(s));
                     }
                     break;
@@ -377,6 +389,51 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
 #ifdef MCL_FUSED_PROF
             { PROF_T(tend); long long* o = g_fused_prof + blockIdx.x * 16 + 4; o[0] = pf_acc; o[1] = pf_full; o[2] = pf_issue; o[3] = tend - tstart; }
 #endif
+        }
+    } else if (warp == 2) {
+        if (lane == 0) {
+            // ---- prefetch lane: asks the tiles of the NEXT item into L2 ------------------------------------
+            // HBM is ~1.5 us away and the raw ring holds four tiles; a copy whose tile is already in L2 completes
+            // in a third of the time.  The lane stays at most kPrefetchAhead tiles ahead of the copies.
+            int pi = 0;
+            unsigned int pos = 0;      // tiles of the items published so far
+            for (;;) {
+                int item = n_items, nxt = n_items;
+                {
+                    const int s = (int)(q_seq % kQueue);
+                    if (mbar_wait(q_full(s), (q_seq / kQueue) & 1u, &abort_flag)) {
+                        item = *reinterpret_cast<volatile int*>(&queue_item[s]);
+                        nxt = *reinterpret_cast<volatile int*>(&queue_next[s]);
+                        mbar_arrive(q_empty(s));
+                    }
+                    ++q_seq;
+                }
+                if (item >= n_items || abort_flag) break;
+                int pc = pi;
+                const Item I = decode_item(sp, n_problems, item, pc);
+                pi = pc;
+                pos += (unsigned int)I.nkt;
+                if (nxt >= n_items || !tab.prefetch) continue;
+                int pn = pi;
+                const Item J = decode_item(sp, n_problems, nxt, pn);
+                const FusedProblem& Q = sp[J.pi];
+                const CUtensorMap* qa = &tab.maps[Q.a_map];
+                const CUtensorMap* qb = &tab.maps[Q.b_map];
+                const int qm = J.mt * 128, qn = J.nt * Q.BN, qmode = Q.mode;
+                for (int t = 0; t < J.nkt && !abort_flag; ++t) {
+                    // tile t of the next item is stream position pos + t
+                    while ((int)(pos + (unsigned int)t - *reinterpret_cast<volatile unsigned int*>(&tiles_issued)) > kPrefetchAhead &&
+                           !abort_flag)
+                        __nanosleep(100);
+                    const int k = (J.kt0 + t) * 32;
+                    if (qmode == kFusedDW) {
+                        tma_prefetch_3d(qa, 0, k, qm >> 5);
+                        tma_prefetch_3d(qb, 0, k, qn >> 5);
+                    } else {
+                        tma_prefetch_2d(qa, k, qm);      // the ternary operand is small and stays in L2 by itself
+                    }
+                }
+            }
         }
     } else if (warp >= kEpiWarp0 && warp < kConvWarp0) {
         // ---- epilogue warps ----------------------------------------------------------------------------
@@ -683,6 +740,8 @@ cudaError_t launch_fused_cap(const FusedProblem* probs, const FusedOperand* a_op
     tab.raw_slot = kABytes + ((bhi + 1023) & ~1023);
     tab.lo_slot = kABytes + ((blo + 1023) & ~1023);
     tab.pad0 = 0;
+    static const int prefetch_on = getenv("MCL_CUDA_FUSED_PREFETCH") ? atoi(getenv("MCL_CUDA_FUSED_PREFETCH")) : 0;
+    tab.prefetch = prefetch_on;
 #ifdef MCL_FUSED_PROF
     if (const char* dbg = getenv("MCL_FUSED_DBG")) tab.pad0 = atoi(dbg);      // ablation switches of the profiling build
 #endif

@@ -24,12 +24,15 @@ namespace {
 constexpr int GV_ROWS = 128;       // output rows per tile (UMMA M)
 constexpr int GV_KB = 256;         // weights per k-block = 64 packed bytes per row
 constexpr int GV_RAW = GV_ROWS * (GV_KB / 4);          // 8 KiB staging of packed bytes
-constexpr int GV_ATILE = GV_ROWS * 128;                // 16 KiB: 128 rows x 128 int8
+
 constexpr int GV_THREADS = 320;
-constexpr int GV_MAX_STAGES = 6;
+constexpr int GV_MAX_STAGES = 12;      // slots of the raw ring (packed weights + activation digits)
+constexpr int GV_EXP = 4;              // expanded tiles in flight in tensor memory, 64 columns each
+constexpr int GV_ACOLS = 64;           // a [128 rows x 256 int8] tile = 64 32-bit columns
 
 struct GvParams {
     int O, I, Nq;
+    int ncols;         // 4 * M: digit columns that carry data
     int kblocks, kb_per_split, splits, stages;
     int* acc;          // int32 [Nq][O]: column n of all rows contiguous, so a warp's 32 rows coalesce
     int* err;
@@ -56,34 +59,50 @@ __device__ __forceinline__ uint32_t idesc_i8(int m, int n) {
 // long as the activation digits are stored in the same order, which gemv_quantize_kernel does.
 __device__ __forceinline__ int gv_kperm(int k) { return (k & ~15) | ((k & 3) << 2) | ((k >> 2) & 3); }
 
+#ifdef MCL_GEMV_PROF
+__device__ long long g_gemv_prof[148 * 16];
+__device__ __forceinline__ long long gv_now() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define GVP(slot) do { if (blockIdx.x < 148) g_gemv_prof[blockIdx.x * 16 + (slot)] = gv_now(); } while (0)
+#else
+#define GVP(slot) do { } while (0)
+#endif
+
 __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_constant__ CUtensorMap tmP,
                                                              const __grid_constant__ CUtensorMap tmX,
                                                              const GvParams p) {
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bars[3 * GV_MAX_STAGES + 4];
+    __shared__ __align__(8) uint64_t bars[2 * GV_MAX_STAGES + 2 * GV_EXP + 4];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) GVP(0);
     const int S = p.stages, Nq = p.Nq;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t b_tile = (uint32_t)Nq * 128u;
-    const uint32_t stage_bytes = GV_RAW + 2 * GV_ATILE + 2 * b_tile;
+    // Shared memory holds only what TMA delivers (a raw slot = packed weights | the two digit tiles).  The
+    // expanded int8 weight tile is four times larger than its packed form; it is written to TENSOR MEMORY
+    // (tcgen05.st, thread = row = TMEM lane) and the MMA takes its A operand from there, so neither the
+    // expansion nor the operand fetch uses shared-memory bandwidth.
+    const uint32_t stage_bytes = GV_RAW + 2 * b_tile;
     const uint32_t bar0 = smem_u32(bars);
     auto raw_full = [&](int s) { return bar0 + 8u * s; };
-    auto a_full = [&](int s) { return bar0 + 8u * (GV_MAX_STAGES + s); };
-    auto empty_bar = [&](int s) { return bar0 + 8u * (2 * GV_MAX_STAGES + s); };
-    auto acc_full = [&](int a) { return bar0 + 8u * (3 * GV_MAX_STAGES + a); };
-    auto acc_empty = [&](int a) { return bar0 + 8u * (3 * GV_MAX_STAGES + 2 + a); };
-    uint32_t tmem_cols = 32;
-    while ((int)tmem_cols < 2 * Nq) tmem_cols <<= 1;
+    auto empty_bar = [&](int s) { return bar0 + 8u * (GV_MAX_STAGES + s); };
+    auto a_full = [&](int e) { return bar0 + 8u * (2 * GV_MAX_STAGES + e); };
+    auto a_empty = [&](int e) { return bar0 + 8u * (2 * GV_MAX_STAGES + GV_EXP + e); };
+    auto acc_full = [&](int a) { return bar0 + 8u * (2 * GV_MAX_STAGES + 2 * GV_EXP + a); };
+    auto acc_empty = [&](int a) { return bar0 + 8u * (2 * GV_MAX_STAGES + 2 * GV_EXP + 2 + a); };
+    // TMEM columns: [0, 2 Nq) two accumulators, [a_col0, a_col0 + GV_EXP * 64) expanded tiles
+    const uint32_t a_col0 = 128;
+    const uint32_t tmem_cols = 512;
 
     const int row_tiles = (p.O + GV_ROWS - 1) / GV_ROWS;
     const int n_items = row_tiles * p.splits;
 
     if (threadIdx.x == 0) {
         abort_flag = (*reinterpret_cast<volatile int*>(p.err) != 0);
-        for (int s = 0; s < S; ++s) { mbar_init(raw_full(s), 1); mbar_init(a_full(s), 128); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < S; ++s) { mbar_init(raw_full(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int e = 0; e < GV_EXP; ++e) { mbar_init(a_full(e), 128); mbar_init(a_empty(e), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 128); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -96,6 +115,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
+    if (threadIdx.x == 0) GVP(1);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -113,8 +133,8 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
                     const int kb = kb0 + j;
                     mbar_expect_tx(raw_full(s), GV_RAW + 2 * b_tile);
                     tma_load_2d(st, &tmP, raw_full(s), kb * (GV_KB / 4), rt * GV_ROWS);
-                    tma_load_2d(st + GV_RAW + 2 * GV_ATILE, &tmX, raw_full(s), kb * GV_KB, 0);
-                    tma_load_2d(st + GV_RAW + 2 * GV_ATILE + b_tile, &tmX, raw_full(s), kb * GV_KB + 128, 0);
+                    tma_load_2d(st + GV_RAW, &tmX, raw_full(s), kb * GV_KB, 0);
+                    tma_load_2d(st + GV_RAW + b_tile, &tmX, raw_full(s), kb * GV_KB + 128, 0);
                 }
             }
         }
@@ -123,6 +143,9 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
             // ---- MMA issuer: 8 x (128 x Nq x 32) int8 MMAs per k-block ------------------------------
             const uint32_t idesc = idesc_i8(GV_ROWS, Nq);
             uint32_t it = 0, n_local = 0;
+#ifdef MCL_GEMV_PROF
+            long long mm_wait = 0, mm_work = 0;
+#endif
             for (int item = blockIdx.x; item < n_items && !abort_flag; item += gridDim.x, ++n_local) {
                 const int split = item / row_tiles;
                 const int kb0 = split * p.kb_per_split;
@@ -133,32 +156,52 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
                 const uint32_t d_tmem = tmem_base + acc * (uint32_t)Nq;
                 for (int j = 0; j < nkb; ++j, ++it) {
                     const int s = (int)(it % (uint32_t)S);
-                    const uint32_t ph = (it / (uint32_t)S) & 1u;
-                    if (!mbar_wait(raw_full(s), ph, &abort_flag) || !mbar_wait(a_full(s), ph, &abort_flag)) {
-                        abort_flag = 1; atomicExch(p.err, 12); break;
-                    }
+#ifdef MCL_GEMV_PROF
+                    const long long tm0 = clock64();
+#endif
+                    const int e = (int)(it % GV_EXP);
+                    // the expanders arrive after they have seen the raw slot: this wait covers the digit tiles too
+                    if (!mbar_wait(a_full(e), (it / GV_EXP) & 1u, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 12); break; }
+                    if (it == 0) GVP(3);
+#ifdef MCL_GEMV_PROF
+                    const long long tm1 = clock64();
+                    mm_wait += tm1 - tm0;
+#endif
                     tc_fence_after();
                     const uint32_t st = base + (uint32_t)s * stage_bytes;
+                    const uint32_t a_tm = tmem_base + a_col0 + (uint32_t)e * GV_ACOLS;
 #pragma unroll
                     for (int t = 0; t < 2; ++t) {
-                        const uint64_t da = smem_desc_k_sw128(st + GV_RAW + t * GV_ATILE);
-                        const uint64_t db = smem_desc_k_sw128(st + GV_RAW + 2 * GV_ATILE + t * b_tile);
+                        const uint64_t db = smem_desc_k_sw128(st + GV_RAW + t * b_tile);
 #pragma unroll
-                        for (int kk = 0; kk < 4; ++kk)      // 32 int8 = 32 bytes = +2 in the address field
-                            umma_i8(d_tmem, da + 2u * kk, db + 2u * kk, idesc, (j | t | kk) != 0 ? 1u : 0u);
+                        for (int kk = 0; kk < 4; ++kk)      // 32 int8 of k = 8 TMEM columns of A, 32 bytes (+2) of B
+                            umma_i8_ts(d_tmem, a_tm + (uint32_t)(t * 32 + kk * 8), db + 2u * kk, idesc, (j | t | kk) != 0 ? 1u : 0u);
                     }
+                    umma_commit(a_empty(e));
                     umma_commit(empty_bar(s));
+#ifdef MCL_GEMV_PROF
+                    mm_work += clock64() - tm1;
+#endif
                 }
                 if (abort_flag) break;
                 umma_commit(acc_full(acc));
+                GVP(4);
+#ifdef MCL_GEMV_PROF
+                if (blockIdx.x < 148) { g_gemv_prof[blockIdx.x * 16 + 12] = mm_wait; g_gemv_prof[blockIdx.x * 16 + 13] = mm_work; }
+#endif
             }
         }
     } else if (warp < 6) {
-        // ---- expanders: 2-bit fields -> int8 in the swizzled K-major tiles; thread = tile row ----
-        const int r = threadIdx.x - 64;                 // 0..127
-        const uint32_t rsw64 = (uint32_t)((r >> 1) & 3), rsw128 = (uint32_t)(r & 7);
+        // ---- expanders: 2-bit fields -> int8, written to tensor memory; thread = tile row = TMEM lane ----
+        // a warp may touch the TMEM lanes of its quarter (warp % 4) only: that quarter is its 32 tile rows
+        const int r = ((warp & 3) << 5) | lane;         // 0..127
+        const uint32_t rsw64 = (uint32_t)((r >> 1) & 3);
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         uint32_t it = 0;
         bool ok = true;
+#ifdef MCL_GEMV_PROF
+        long long ex_wait = 0, ex_work = 0;
+#endif
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const int split = item / row_tiles;
             const int kb0 = split * p.kb_per_split;
@@ -166,29 +209,50 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
             for (int j = 0; j < nkb; ++j, ++it) {
                 const int s = (int)(it % (uint32_t)S);
                 const uint32_t ph = (it / (uint32_t)S) & 1u;
-                if (abort_flag || !mbar_wait(raw_full(s), ph, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 13); ok = false; break; }
+#ifdef MCL_GEMV_PROF
+                const long long tw0 = clock64();
+#endif
+                const int e = (int)(it % GV_EXP);
+                if (abort_flag || !mbar_wait(raw_full(s), ph, &abort_flag) ||
+                    !mbar_wait(a_empty(e), ((it / GV_EXP) & 1u) ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 13); ok = false; break; }
+                if (it == 0 && r == 0) GVP(2);
+#ifdef MCL_GEMV_PROF
+                const long long tw1 = clock64();
+                ex_wait += tw1 - tw0;
+#endif
+                tc_fence_after();      // the MMAs that read this TMEM slot have completed (a_empty)
                 unsigned char* st = smem_raw + (base - smem_u32(smem_raw)) + (size_t)s * stage_bytes;
                 const uint4* raw = reinterpret_cast<const uint4*>(st + r * 64);
+                const uint32_t a_tm = tmem_base + lane_base + a_col0 + (uint32_t)e * GV_ACOLS;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {           // 16 packed bytes = 64 weights
-                    const uint4 pk = raw[c ^ rsw64];    // staging was written with the 64-byte swizzle
-                    const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
+                for (int h = 0; h < 2; ++h) {           // half a row: 32 packed bytes = 128 weights = 32 TMEM columns
+                    uint32_t v[32];
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {       // one word = 16 weights = one 16-byte chunk of int8
-                        uint4 o;
-                        o.x = w[q] & 0x03030303u;
-                        o.y = (w[q] >> 2) & 0x03030303u;
-                        o.z = (w[q] >> 4) & 0x03030303u;
-                        o.w = (w[q] >> 6) & 0x03030303u;
-                        const int chunk = c * 4 + q;    // 0..15 along k; 8 chunks per A tile
-                        unsigned char* tile = st + GV_RAW + (chunk >> 3) * GV_ATILE;
-                        *reinterpret_cast<uint4*>(tile + r * 128 + (((uint32_t)(chunk & 7) ^ rsw128) << 4)) = o;
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const int c = 2 * h + cc;
+                        const uint4 pk = raw[c ^ rsw64];    // staging was written with the 64-byte swizzle
+                        const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {       // one word = 16 weights = four columns of int8
+                            v[cc * 16 + q * 4 + 0] = w[q] & 0x03030303u;
+                            v[cc * 16 + q * 4 + 1] = (w[q] >> 2) & 0x03030303u;
+                            v[cc * 16 + q * 4 + 2] = (w[q] >> 4) & 0x03030303u;
+                            v[cc * 16 + q * 4 + 3] = (w[q] >> 6) & 0x03030303u;
+                        }
                     }
+                    tmem_st32(a_tm + (uint32_t)(32 * h), v);
                 }
-                fence_proxy_async();
-                mbar_arrive(a_full(s));
+                tmem_st_wait();
+                tc_fence_before();
+                mbar_arrive(a_full(e));
+#ifdef MCL_GEMV_PROF
+                ex_work += clock64() - tw1;
+#endif
             }
         }
+#ifdef MCL_GEMV_PROF
+        if (r == 0 && blockIdx.x < 148) { g_gemv_prof[blockIdx.x * 16 + 10] = ex_wait; g_gemv_prof[blockIdx.x * 16 + 11] = ex_work; g_gemv_prof[blockIdx.x * 16 + 14] = it; }
+#endif
     } else {
         // ---- epilogue warps: int32 accumulator -> global (atomic when k is split) ---------------
         const int q = warp & 3;
@@ -200,6 +264,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
             if (ok && !mbar_wait(acc_full(acc), aph, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 15); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            if (n_local == 0 && warp == 6 && lane == 0) GVP(5);
             tc_fence_after();
             const int row = rt * GV_ROWS + q * 32 + lane;
             int* dst = p.acc + row;
@@ -208,17 +273,21 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
                 tmem_ld16(tmem_base + acc * (uint32_t)Nq + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
                 tmem_ld_wait();
                 if (row < p.O) {
+                    // columns at and beyond 4 M are padding of the digit matrix (all zero): nothing to add
                     if (p.splits == 1) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) dst[(size_t)(c0 + j) * p.O] = (int)v[j];
+                        for (int j = 0; j < 16; ++j)
+                            if (c0 + j < p.ncols) dst[(size_t)(c0 + j) * p.O] = (int)v[j];
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) atomicAdd(dst + (size_t)(c0 + j) * p.O, (int)v[j]);
+                        for (int j = 0; j < 16; ++j)
+                            if (c0 + j < p.ncols) atomicAdd(dst + (size_t)(c0 + j) * p.O, (int)v[j]);
                     }
                 }
             }
             tc_fence_before();
             mbar_arrive(acc_empty(acc));
+            if (warp == 6 && lane == 0) GVP(6);
         }
     }
     __syncwarp();
@@ -231,16 +300,28 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
+    if (threadIdx.x == 0) GVP(7);
 }
 
 // ---- activation rows -> four int8 digit rows each, digit sums, power-of-two scale ---------------
 // grid = Nq / 4 blocks (one per activation row slot; slots >= M are written as zeros)
 __global__ void __launch_bounds__(256) gemv_quantize_kernel(const float* __restrict__ x, int M, int I,
                                                             signed char* __restrict__ xq, int* __restrict__ corr,
-                                                            float* __restrict__ xscale) {
+                                                            float* __restrict__ xscale, int4* __restrict__ acc_clear,
+                                                            long long clear_int4) {
     __shared__ float red[256];
     __shared__ int isum[4];
     const int m = blockIdx.x, tid = threadIdx.x;
+    if (blockIdx.y > 0) {
+        // the blocks of the other grid rows only zero the split-K accumulators of the contraction that follows
+        const long long nthr = (long long)gridDim.x * (gridDim.y - 1) * 256;
+        for (long long i = ((long long)(blockIdx.y - 1) * gridDim.x + blockIdx.x) * 256 + tid; i < clear_int4; i += nthr)
+            acc_clear[i] = make_int4(0, 0, 0, 0);
+        return;
+    }
+#ifdef MCL_GEMV_PROF
+    if (tid == 0 && m == 0) g_gemv_prof[8] = gv_now();
+#endif
     signed char* q0 = xq + (size_t)(4 * m) * I;
     if (m >= M) {
         for (int k = tid; k < I; k += 256) { q0[k] = 0; q0[I + k] = 0; q0[2 * (size_t)I + k] = 0; q0[3 * (size_t)I + k] = 0; }
@@ -276,6 +357,9 @@ __global__ void __launch_bounds__(256) gemv_quantize_kernel(const float* __restr
     __syncthreads();
     if (tid < 4) corr[4 * m + tid] = isum[tid];
     if (tid == 0) xscale[m] = ldexpf(1.0f, e) / 64.0f;
+#ifdef MCL_GEMV_PROF
+    if (tid == 0 && m == 0) g_gemv_prof[9] = gv_now();
+#endif
 }
 
 // y[m,o] = scale[o] * xscale[m] * sum_d 128^-d * (acc[o][4m+d] - corr[4m+d])
@@ -347,7 +431,7 @@ cudaError_t launch_ternary_gemv_tc(const float* x, const uint32_t* packed2, cons
     int* acc = reinterpret_cast<int*>(w + o + 1024);
 
     GvParams p;
-    p.O = O; p.I = I; p.Nq = Nq;
+    p.O = O; p.I = I; p.Nq = Nq; p.ncols = 4 * M;
     p.kblocks = (I + GV_KB - 1) / GV_KB;
     const int row_tiles = (O + GV_ROWS - 1) / GV_ROWS;
     int splits = 1;
@@ -359,7 +443,7 @@ cudaError_t launch_ternary_gemv_tc(const float* x, const uint32_t* packed2, cons
     p.kb_per_split = (p.kblocks + splits - 1) / splits;
     p.splits = splits = (p.kblocks + p.kb_per_split - 1) / p.kb_per_split;
     p.acc = acc; p.err = err_word;
-    const size_t stage_bytes = (size_t)GV_RAW + 2 * GV_ATILE + 2 * (size_t)Nq * 128;
+    const size_t stage_bytes = (size_t)GV_RAW + 2 * (size_t)Nq * 128;
     int stages = (int)((max_smem - 2048) / stage_bytes);
     if (stages > GV_MAX_STAGES) stages = GV_MAX_STAGES;
     if (stages < 2) return cudaErrorInvalidConfiguration;
@@ -370,14 +454,20 @@ cudaError_t launch_ternary_gemv_tc(const float* x, const uint32_t* packed2, cons
         return cudaErrorInvalidValue;
     if (!gv_map_2d(&mx, xq, (size_t)I, 64, (size_t)I, 128, Nq, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
 
-    gemv_quantize_kernel<<<Nq / 4, 256, 0, stream>>>(x, M, I, xq, corr, xscale);
+    // one launch quantizes the activations and, when k is split, zeroes the digit columns of the accumulators
+    // that carry data (O * 4 M ints: O is padded to a multiple of 4 by the 1 KiB rounding of the workspace)
+    const long long clear_int4 = splits > 1 ? ((long long)O * 4 * M + 3) / 4 : 0;
+    int clear_rows = 0;
+    if (clear_int4 > 0) {
+        clear_rows = (int)((clear_int4 + (long long)(Nq / 4) * 256 * 8 - 1) / ((long long)(Nq / 4) * 256 * 8));
+        if (clear_rows < 1) clear_rows = 1;
+        if (clear_rows > 64) clear_rows = 64;
+    }
+    gemv_quantize_kernel<<<dim3(Nq / 4, 1 + clear_rows), 256, 0, stream>>>(x, M, I, xq, corr, xscale,
+                                                                           reinterpret_cast<int4*>(acc), clear_int4);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     ++*launches;
-    if (splits > 1) {
-        e = cudaMemsetAsync(acc, 0, (size_t)O * Nq * sizeof(int), stream);
-        if (e != cudaSuccess) return e;
-    }
     const size_t smem = (size_t)stages * stage_bytes + 1024;
     e = ensure_dynamic_smem(reinterpret_cast<const void*>(gemv_tc_kernel), 5, max_smem);
     if (e != cudaSuccess) return e;
@@ -393,5 +483,11 @@ cudaError_t launch_ternary_gemv_tc(const float* x, const uint32_t* packed2, cons
     ++*launches;
     return cudaSuccess;
 }
+
+#ifdef MCL_GEMV_PROF
+extern "C" int mcl_debug_gemv_prof(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_gemv_prof, sizeof(long long) * 148 * 16);
+}
+#endif
 
 }  // namespace mcl

@@ -230,8 +230,47 @@ int mcl_cuda_matmul_f32(mcl_cuda_ctx* ctx, const float* a, const float* b, float
 #define MCL_CUDA_ELT_MUL_SCALAR 3
 #define MCL_CUDA_ELT_ADD_SCALAR 4
 #define MCL_CUDA_ELT_ZERO 5
+#define MCL_CUDA_ELT_SGD 6   /* out = a - alpha*b: run_vulkan_sgd_update (src/ops/optim.cpp:16-29) */
 int mcl_cuda_eltwise_f32(mcl_cuda_ctx* ctx, int op, const float* a, const float* b, float* out, size_t elements,
                          float alpha);
+
+/* ---- fp32 row ops of the ternary15m block stack around its counter layers (tests/bench_ternary15m.cpp:145-190).
+ * Each replaces the run_vulkan_* free function of the same name in include/motifcl/runtime/vulkan_backend.hpp
+ * (:606 rmsnorm, :557 rmsnorm_backward_x, :567 rmsnorm_backward_weight, :613 swiglu, :575 swiglu_backward,
+ * :583 softmax_cross_entropy, :590 softmax_cross_entropy_backward, :294 grouped_query_attention_general,
+ * :345 grouped_query_attention_backward); callers: src/ops/norm.cpp:74-84,163-175,242-258,
+ * src/ops/activation.cpp:314,343, src/ops/loss.cpp:98-160, src/ops/attention.cpp:302-365,2248-2290.
+ * Same results as the reference's shaders up to fp32 summation order.
+ *   rmsnorm                 out = x * rsqrt(mean(x^2) + eps) * weight              x, out [rows, cols]
+ *   rmsnorm_backward_weight row_inv_scratch [rows] receives the inverse RMS; grad_weight [cols] is overwritten
+ *   swiglu                  packed [rows, 2*hidden] = gate | up; out = gate * sigmoid(gate) * up
+ *   softmax_cross_entropy   partial [rows] = per-row loss (0 for a target outside [0, cols)); out[0] = mean
+ *   ..._backward            grad_logits = grad_out[0] / rows * (softmax - onehot)
+ *   gqa_forward             q [B*Tq, n_head*hd], k [B*key_stride, n_kv*hd], v [B*key_stride, n_kv*vhd],
+ *                           out [B*Tq, n_head*vhd]; causal with query_offset, optional sliding window (0 = none);
+ *                           f32 keys/values, no mask
+ *   gqa_backward            probs_scratch, ds_scratch [B*n_head*Tq*Tk]; grad_q/k/v shaped like q/k/v ---- */
+int mcl_cuda_rmsnorm(mcl_cuda_ctx* ctx, const float* x, const float* weight, float* out, size_t rows, size_t cols,
+                     float eps);
+int mcl_cuda_rmsnorm_backward_x(mcl_cuda_ctx* ctx, const float* x, const float* weight, const float* grad_out,
+                                float* grad_x, size_t rows, size_t cols, float eps);
+int mcl_cuda_rmsnorm_backward_weight(mcl_cuda_ctx* ctx, const float* x, const float* grad_out, float* row_inv_scratch,
+                                     float* grad_weight, size_t rows, size_t cols, float eps);
+int mcl_cuda_swiglu(mcl_cuda_ctx* ctx, const float* packed, float* out, size_t rows, size_t hidden);
+int mcl_cuda_swiglu_backward(mcl_cuda_ctx* ctx, const float* packed, const float* grad_out, float* grad_packed,
+                             size_t rows, size_t hidden);
+int mcl_cuda_softmax_cross_entropy(mcl_cuda_ctx* ctx, const float* logits, const int32_t* targets, float* partial,
+                                   float* out, size_t rows, size_t cols);
+int mcl_cuda_softmax_cross_entropy_backward(mcl_cuda_ctx* ctx, const float* logits, const int32_t* targets,
+                                            const float* grad_out, float* grad_logits, size_t rows, size_t cols);
+int mcl_cuda_gqa_forward(mcl_cuda_ctx* ctx, const float* q, const float* k, const float* v, float* out, size_t batch,
+                         size_t query_tokens, size_t key_tokens, size_t key_stride, size_t n_head, size_t n_kv_head,
+                         size_t head_dim, size_t v_head_dim, int causal, size_t query_offset, size_t sliding_window,
+                         float scale);
+int mcl_cuda_gqa_backward(mcl_cuda_ctx* ctx, const float* q, const float* k, const float* v, const float* grad_out,
+                          float* probs_scratch, float* ds_scratch, float* grad_q, float* grad_k, float* grad_v,
+                          size_t batch, size_t query_tokens, size_t key_tokens, size_t n_head, size_t n_kv_head,
+                          size_t head_dim, int causal, size_t query_offset, float scale);
 
 /* ---- ternary decode GEMV, M <= 16 (no reference kernel; semantics of the forward above
  * applied to 2-bit weights).  y[M,out] = x[M,in] * (scale . t)^T.  Requires in % 16 == 0. ---- */

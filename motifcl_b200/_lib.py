@@ -91,6 +91,15 @@ def lib() -> C.CDLL:
         L.mcl_cuda_ternary_linear_products.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, sz, sz]
         L.mcl_cuda_eltwise_f32.argtypes = [vp, i, vp, vp, vp, sz, f]
         L.mcl_cuda_matmul_f32.argtypes = [vp, vp, vp, vp, sz, sz, sz, i, i]
+        L.mcl_cuda_rmsnorm.argtypes = [vp, vp, vp, vp, sz, sz, f]
+        L.mcl_cuda_rmsnorm_backward_x.argtypes = [vp, vp, vp, vp, vp, sz, sz, f]
+        L.mcl_cuda_rmsnorm_backward_weight.argtypes = [vp, vp, vp, vp, vp, sz, sz, f]
+        L.mcl_cuda_swiglu.argtypes = [vp, vp, vp, sz, sz]
+        L.mcl_cuda_swiglu_backward.argtypes = [vp, vp, vp, vp, sz, sz]
+        L.mcl_cuda_softmax_cross_entropy.argtypes = [vp, vp, vp, vp, vp, sz, sz]
+        L.mcl_cuda_softmax_cross_entropy_backward.argtypes = [vp, vp, vp, vp, vp, sz, sz]
+        L.mcl_cuda_gqa_forward.argtypes = [vp, vp, vp, vp, vp, sz, sz, sz, sz, sz, sz, sz, sz, i, sz, sz, f]
+        L.mcl_cuda_gqa_backward.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, sz, sz, i, sz, f]
         L.mcl_cuda_ternary_gemv.argtypes = [vp, vp, vp, vp, vp, sz, sz, sz]
         L.mcl_cuda_counter_update_fused_static.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, f, f, f, f, u32]
         L.mcl_cuda_static_scratch_floats.restype = C.c_size_t

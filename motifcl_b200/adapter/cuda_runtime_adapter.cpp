@@ -24,9 +24,14 @@ namespace {
 // place of a SPIR-V pointer and reads the operation and its scalar arguments from the
 // "word count" and "push constants".
 const std::uint32_t kNativeTag[1] = {0x4D434C55u};
-enum NativeOp : std::size_t { kOpDecode = 1, kOpForward, kOpBackwardInput, kOpUpdateFused, kOpMatmul, kOpEltwise };
+enum NativeOp : std::size_t {
+    kOpDecode = 1, kOpForward, kOpBackwardInput, kOpUpdateFused, kOpMatmul, kOpEltwise,
+    kOpRmsnorm, kOpRmsnormBwdX, kOpRmsnormBwdW, kOpSwiglu, kOpSwigluBwd, kOpCe, kOpCeBwd, kOpGqa, kOpGqaBwd
+};
 struct NativeArgs {
     std::size_t a = 0, b = 0, c = 0, d = 0;          // dimensions (meaning depends on the op)
+    std::size_t e = 0, f = 0, g = 0, h = 0, i = 0, j = 0;
+    int causal = 0;
     float lr = 0, lr_scale = 0, rms_beta = 0, rms_eps = 0;
     std::uint32_t seed = 0;
     int trans_a = 0, trans_b = 0;
@@ -219,6 +224,40 @@ VulkanOpResult VulkanRuntime::dispatch_cached(const std::uint32_t* spirv, std::s
                                       bufs.size() > 2 ? (const float*)p(1) : nullptr, (float*)p(bufs.size() - 1), a.a,
                                       a.alpha);
             break;
+        case kOpRmsnorm:         // x, weight, out | rows, cols, eps
+            rc = mcl_cuda_rmsnorm(ctx, (const float*)p(0), (const float*)p(1), (float*)p(2), a.a, a.b, a.alpha);
+            break;
+        case kOpRmsnormBwdX:     // x, weight, grad_out, grad_x | rows, cols, eps
+            rc = mcl_cuda_rmsnorm_backward_x(ctx, (const float*)p(0), (const float*)p(1), (const float*)p(2), (float*)p(3),
+                                             a.a, a.b, a.alpha);
+            break;
+        case kOpRmsnormBwdW:     // x, grad_out, row_inv, grad_weight | rows, cols, eps
+            rc = mcl_cuda_rmsnorm_backward_weight(ctx, (const float*)p(0), (const float*)p(1), (float*)p(2), (float*)p(3),
+                                                  a.a, a.b, a.alpha);
+            break;
+        case kOpSwiglu:          // packed, out | rows, hidden
+            rc = mcl_cuda_swiglu(ctx, (const float*)p(0), (float*)p(1), a.a, a.b);
+            break;
+        case kOpSwigluBwd:       // packed, grad_out, grad_packed | rows, hidden
+            rc = mcl_cuda_swiglu_backward(ctx, (const float*)p(0), (const float*)p(1), (float*)p(2), a.a, a.b);
+            break;
+        case kOpCe:              // logits, targets, partial, out | rows, cols
+            rc = mcl_cuda_softmax_cross_entropy(ctx, (const float*)p(0), (const int32_t*)p(1), (float*)p(2), (float*)p(3),
+                                                a.a, a.b);
+            break;
+        case kOpCeBwd:           // logits, targets, grad_out, grad_logits | rows, cols
+            rc = mcl_cuda_softmax_cross_entropy_backward(ctx, (const float*)p(0), (const int32_t*)p(1), (const float*)p(2),
+                                                         (float*)p(3), a.a, a.b);
+            break;
+        case kOpGqa:             // q, k, v, out | batch, tq, tk, key_stride, heads, kv heads, hd, vhd, offset, window
+            rc = mcl_cuda_gqa_forward(ctx, (const float*)p(0), (const float*)p(1), (const float*)p(2), (float*)p(3), a.a, a.b,
+                                      a.c, a.d, a.e, a.f, a.g, a.h, a.causal, a.i, a.j, a.alpha);
+            break;
+        case kOpGqaBwd:          // q, k, v, grad_out, probs, ds, dq, dk, dv | batch, tq, tk, heads, kv heads, hd, offset
+            rc = mcl_cuda_gqa_backward(ctx, (const float*)p(0), (const float*)p(1), (const float*)p(2), (const float*)p(3),
+                                       (float*)p(4), (float*)p(5), (float*)p(6), (float*)p(7), (float*)p(8), a.a, a.b, a.c,
+                                       a.e, a.f, a.g, a.causal, a.i, a.alpha);
+            break;
         default:
             r.error = "unknown native operation";
             return r;
@@ -382,5 +421,106 @@ VulkanOpResult run_vulkan_add_scalar(VulkanRuntime& rt, const VulkanBuffer& x, V
                                      float value) { return eltwise(rt, MCL_CUDA_ELT_ADD_SCALAR, &x, nullptr, out, n, value); }
 VulkanOpResult run_vulkan_zero_f32(VulkanRuntime& rt, VulkanBuffer& out, std::size_t n) {
     return eltwise(rt, MCL_CUDA_ELT_ZERO, nullptr, nullptr, out, n, 0.0f);
+}
+VulkanOpResult run_vulkan_sgd_update(VulkanRuntime& rt, const VulkanBuffer& param, const VulkanBuffer& grad,
+                                     VulkanBuffer& out, std::size_t n, float lr) {
+    return eltwise(rt, MCL_CUDA_ELT_SGD, &param, &grad, out, n, lr);
+}
+
+// ---- the fp32 row ops of the ternary15m block stack ------------------------------------------------
+VulkanOpResult run_vulkan_rmsnorm(VulkanRuntime& rt, const VulkanBuffer& x, const VulkanBuffer& weight, VulkanBuffer& out,
+                                  std::size_t rows, std::size_t cols, float eps) {
+    if (x.nbytes() < rows * cols * 4 || out.nbytes() < rows * cols * 4 || weight.nbytes() < cols * 4)
+        return refuse(rt, "Vulkan rmsnorm buffer is too small");
+    NativeArgs a; a.a = rows; a.b = cols; a.alpha = eps;
+    return native(rt, kOpRmsnorm, {&x, &weight, &out}, a);
+}
+VulkanOpResult run_vulkan_rmsnorm_backward_x(VulkanRuntime& rt, const VulkanBuffer& x, const VulkanBuffer& weight,
+                                             const VulkanBuffer& grad_out, VulkanBuffer& grad_x, std::size_t rows,
+                                             std::size_t cols, float eps) {
+    if (x.nbytes() < rows * cols * 4 || grad_out.nbytes() < rows * cols * 4 || grad_x.nbytes() < rows * cols * 4 ||
+        weight.nbytes() < cols * 4)
+        return refuse(rt, "Vulkan rmsnorm backward_x buffer is too small");
+    NativeArgs a; a.a = rows; a.b = cols; a.alpha = eps;
+    return native(rt, kOpRmsnormBwdX, {&x, &weight, &grad_out, &grad_x}, a);
+}
+VulkanOpResult run_vulkan_rmsnorm_backward_weight(VulkanRuntime& rt, const VulkanBuffer& x, const VulkanBuffer& grad_out,
+                                                  VulkanBuffer& row_inv_scratch, VulkanBuffer& grad_weight,
+                                                  std::size_t rows, std::size_t cols, float eps) {
+    if (x.nbytes() < rows * cols * 4 || grad_out.nbytes() < rows * cols * 4 || row_inv_scratch.nbytes() < rows * 4 ||
+        grad_weight.nbytes() < cols * 4)
+        return refuse(rt, "Vulkan rmsnorm backward_weight buffer is too small");
+    NativeArgs a; a.a = rows; a.b = cols; a.alpha = eps;
+    return native(rt, kOpRmsnormBwdW, {&x, &grad_out, &row_inv_scratch, &grad_weight}, a);
+}
+VulkanOpResult run_vulkan_swiglu(VulkanRuntime& rt, const VulkanBuffer& packed, VulkanBuffer& out, std::size_t rows,
+                                 std::size_t hidden) {
+    if (packed.nbytes() < rows * hidden * 8 || out.nbytes() < rows * hidden * 4)
+        return refuse(rt, "Vulkan swiglu buffer is too small");
+    NativeArgs a; a.a = rows; a.b = hidden;
+    return native(rt, kOpSwiglu, {&packed, &out}, a);
+}
+VulkanOpResult run_vulkan_swiglu_backward(VulkanRuntime& rt, const VulkanBuffer& packed, const VulkanBuffer& grad_out,
+                                          VulkanBuffer& grad_packed, std::size_t rows, std::size_t hidden) {
+    if (packed.nbytes() < rows * hidden * 8 || grad_packed.nbytes() < rows * hidden * 8 ||
+        grad_out.nbytes() < rows * hidden * 4)
+        return refuse(rt, "Vulkan swiglu backward buffer is too small");
+    NativeArgs a; a.a = rows; a.b = hidden;
+    return native(rt, kOpSwigluBwd, {&packed, &grad_out, &grad_packed}, a);
+}
+VulkanOpResult run_vulkan_softmax_cross_entropy(VulkanRuntime& rt, const VulkanBuffer& logits, const VulkanBuffer& targets,
+                                                VulkanBuffer& partial, VulkanBuffer& out, std::size_t rows,
+                                                std::size_t cols) {
+    if (logits.nbytes() < rows * cols * 4 || targets.nbytes() < rows * 4 || partial.nbytes() < rows * 4 || out.nbytes() < 4)
+        return refuse(rt, "Vulkan softmax_cross_entropy buffer is too small");
+    NativeArgs a; a.a = rows; a.b = cols;
+    return native(rt, kOpCe, {&logits, &targets, &partial, &out}, a);
+}
+VulkanOpResult run_vulkan_softmax_cross_entropy_backward(VulkanRuntime& rt, const VulkanBuffer& logits,
+                                                         const VulkanBuffer& targets, const VulkanBuffer& grad_out,
+                                                         VulkanBuffer& grad_logits, std::size_t rows, std::size_t cols) {
+    if (logits.nbytes() < rows * cols * 4 || grad_logits.nbytes() < rows * cols * 4 || targets.nbytes() < rows * 4 ||
+        grad_out.nbytes() < 4)
+        return refuse(rt, "Vulkan softmax_cross_entropy backward buffer is too small");
+    NativeArgs a; a.a = rows; a.b = cols;
+    return native(rt, kOpCeBwd, {&logits, &targets, &grad_out, &grad_logits}, a);
+}
+VulkanOpResult run_vulkan_grouped_query_attention_general(
+    VulkanRuntime& rt, const VulkanBuffer& q, const VulkanBuffer& k, const VulkanBuffer& v, const VulkanBuffer* k_scales,
+    const VulkanBuffer* v_scales, const VulkanBuffer* mask, VulkanBuffer& out, std::size_t batch, std::size_t query_tokens,
+    std::size_t key_tokens, std::size_t key_stride, std::size_t n_head, std::size_t n_kv_head, std::size_t head_dim,
+    std::size_t v_head_dim, bool causal, std::size_t query_offset, std::size_t sliding_window, std::uint32_t,
+    std::uint32_t, std::uint32_t mask_dtype, std::uint32_t kv_dtype, float scale) {
+    if (kv_dtype != 0 || k_scales != nullptr || v_scales != nullptr)
+        return refuse(rt, "quantized keys/values are not implemented in CUDA runtime");
+    if (mask != nullptr || mask_dtype != 0) return refuse(rt, "attention masks are not implemented in CUDA runtime");
+    if (q.nbytes() < batch * query_tokens * n_head * head_dim * 4 || k.nbytes() < batch * key_stride * n_kv_head * head_dim * 4 ||
+        v.nbytes() < batch * key_stride * n_kv_head * v_head_dim * 4 || out.nbytes() < batch * query_tokens * n_head * v_head_dim * 4)
+        return refuse(rt, "Vulkan grouped_query_attention buffer is too small");
+    NativeArgs a; a.a = batch; a.b = query_tokens; a.c = key_tokens; a.d = key_stride; a.e = n_head; a.f = n_kv_head;
+    a.g = head_dim; a.h = v_head_dim; a.causal = causal ? 1 : 0; a.i = query_offset; a.j = sliding_window; a.alpha = scale;
+    return native(rt, kOpGqa, {&q, &k, &v, &out}, a);
+}
+VulkanOpResult run_vulkan_grouped_query_attention(VulkanRuntime& rt, const VulkanBuffer& q, const VulkanBuffer& k,
+                                                  const VulkanBuffer& v, VulkanBuffer& out, std::size_t query_tokens,
+                                                  std::size_t key_tokens, std::size_t n_head, std::size_t n_kv_head,
+                                                  std::size_t head_dim, float scale) {
+    return run_vulkan_grouped_query_attention_general(rt, q, k, v, nullptr, nullptr, nullptr, out, 1, query_tokens, key_tokens,
+                                                      key_tokens, n_head, n_kv_head, head_dim, head_dim, false, 0, 0, 0, 0,
+                                                      0, 0, scale);
+}
+VulkanOpResult run_vulkan_grouped_query_attention_backward(
+    VulkanRuntime& rt, const VulkanBuffer& q, const VulkanBuffer& k, const VulkanBuffer& v, const VulkanBuffer& grad_out,
+    VulkanBuffer& probs_scratch, VulkanBuffer& ds_scratch, VulkanBuffer& grad_q, VulkanBuffer& grad_k, VulkanBuffer& grad_v,
+    std::size_t batch, std::size_t query_tokens, std::size_t key_tokens, std::size_t n_head, std::size_t n_kv_head,
+    std::size_t head_dim, bool causal, std::size_t query_offset, float scale) {
+    const std::size_t qn = batch * query_tokens * n_head * head_dim * 4, kn = batch * key_tokens * n_kv_head * head_dim * 4;
+    const std::size_t pn = batch * n_head * query_tokens * key_tokens * 4;
+    if (q.nbytes() < qn || grad_out.nbytes() < qn || grad_q.nbytes() < qn || k.nbytes() < kn || v.nbytes() < kn ||
+        grad_k.nbytes() < kn || grad_v.nbytes() < kn || probs_scratch.nbytes() < pn || ds_scratch.nbytes() < pn)
+        return refuse(rt, "Vulkan grouped_query_attention backward buffer is too small");
+    NativeArgs a; a.a = batch; a.b = query_tokens; a.c = key_tokens; a.e = n_head; a.f = n_kv_head; a.g = head_dim;
+    a.causal = causal ? 1 : 0; a.i = query_offset; a.alpha = scale;
+    return native(rt, kOpGqaBwd, {&q, &k, &v, &grad_out, &probs_scratch, &ds_scratch, &grad_q, &grad_k, &grad_v}, a);
 }
 }  // namespace motifcl

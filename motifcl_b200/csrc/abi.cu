@@ -151,6 +151,13 @@ int create_impl(int device, cudaStream_t stream, bool own, mcl_cuda_ctx** out_ct
     } else {
         ctx->stream = stream;
     }
+    {   // keep freed blocks in the default pool instead of returning them to the driver at every synchronisation
+        cudaMemPool_t pool = nullptr;
+        unsigned long long keep = ~0ull;
+        if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess)
+            cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+        cudaGetLastError();
+    }
     e = cudaMalloc(reinterpret_cast<void**>(&ctx->err_word), 16 * sizeof(int));    // [0] error word, [1] work-item counter
     if (e == cudaSuccess) e = cudaMemset(ctx->err_word, 0, 16 * sizeof(int));
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming);
@@ -366,7 +373,9 @@ int mcl_cuda_alloc(mcl_cuda_ctx* ctx, size_t bytes, void** out_dptr) {
     *out_dptr = nullptr;
     if (bytes == 0) return fail(ctx, MCL_CUDA_EINVAL, "alloc: zero-size buffer");
     DeviceGuard guard(ctx->device);
-    cudaError_t e = cudaMalloc(out_dptr, bytes);
+    // Stream-ordered allocation from the device's default pool: a training step allocates and drops
+    // hundreds of intermediate tensors, and the pool serves them without a device synchronisation.
+    cudaError_t e = cudaMallocAsync(out_dptr, bytes, ctx->stream);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return fail(ctx, MCL_CUDA_ENOMEM, "alloc of " + std::to_string(bytes) + " bytes failed: " + cudaGetErrorString(e));
@@ -378,11 +387,9 @@ int mcl_cuda_free(mcl_cuda_ctx* ctx, void* dptr) {
     MCL_NOT_RECORDING(ctx, "free");
     if (!dptr) return MCL_CUDA_OK;
     DeviceGuard guard(ctx->device);
-    // Work that still uses the buffer may be queued: wait for the stream first, which keeps
-    // the reference's "free while pending is safe" behaviour.
-    cudaError_t e = cudaStreamSynchronize(ctx->stream);
-    if (e != cudaSuccess) return fail_cuda(ctx, "free", e);
-    e = cudaFree(dptr);
+    // Work that still uses the buffer may be queued: the free is ordered after it on the context's
+    // stream, which keeps the reference's "free while pending is safe" behaviour without a wait.
+    cudaError_t e = cudaFreeAsync(dptr, ctx->stream);
     if (e != cudaSuccess) return fail_cuda(ctx, "free", e);
     return MCL_CUDA_OK;
 }
@@ -1080,13 +1087,188 @@ int mcl_cuda_eltwise_f32(mcl_cuda_ctx* ctx, int op, const float* a, const float*
                          float alpha) {
     MCL_NEED_CTX(ctx);
     const char* name = "eltwise_f32";
-    if (op < 0 || op > MCL_CUDA_ELT_ZERO) return fail(ctx, MCL_CUDA_EINVAL, "eltwise_f32: unknown op");
+    if (op < 0 || op > MCL_CUDA_ELT_SGD) return fail(ctx, MCL_CUDA_EINVAL, "eltwise_f32: unknown op");
     if (elements == 0) return fail(ctx, MCL_CUDA_EINVAL, "eltwise_f32 requires non-zero elements");
     MCL_TRY(check_ptr(ctx, name, "out", out, 4));
     if (op != MCL_CUDA_ELT_ZERO) MCL_TRY(check_ptr(ctx, name, "a", a, 4));
-    if (op <= MCL_CUDA_ELT_MUL) MCL_TRY(check_ptr(ctx, name, "b", b, 4));
+    if (op <= MCL_CUDA_ELT_MUL || op == MCL_CUDA_ELT_SGD) MCL_TRY(check_ptr(ctx, name, "b", b, 4));
     DeviceGuard guard(ctx->device);
     MCL_LAUNCH(ctx, name, mcl::launch_eltwise_f32(op, a, b, out, elements, alpha, ctx->sm_count, ctx->stream));
+    return MCL_CUDA_OK;
+}
+
+// ---- fp32 row ops of the block stack around the counter layers ----------------------------------------
+namespace {
+int check_rows(mcl_cuda_ctx* ctx, const char* op, size_t rows, size_t cols) {
+    if (rows == 0 || cols == 0) return fail(ctx, MCL_CUDA_EINVAL, std::string(op) + " requires non-zero dimensions");
+    if (cols > 0x7fffffffull || rows > 0xffffffffull) return fail(ctx, MCL_CUDA_EINVAL, std::string(op) + " dimension is too large");
+    return MCL_CUDA_OK;
+}
+}  // namespace
+
+int mcl_cuda_rmsnorm(mcl_cuda_ctx* ctx, const float* x, const float* weight, float* out, size_t rows, size_t cols,
+                     float eps) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "rmsnorm";
+    MCL_TRY(check_rows(ctx, op, rows, cols));
+    MCL_TRY(check_ptr(ctx, op, "x", x, 4));
+    MCL_TRY(check_ptr(ctx, op, "weight", weight, 4));
+    MCL_TRY(check_ptr(ctx, op, "out", out, 4));
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, op, mcl::launch_rmsnorm(x, weight, out, rows, (int)cols, eps, ctx->sm_count, ctx->stream));
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_rmsnorm_backward_x(mcl_cuda_ctx* ctx, const float* x, const float* weight, const float* grad_out,
+                                float* grad_x, size_t rows, size_t cols, float eps) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "rmsnorm backward_x";
+    MCL_TRY(check_rows(ctx, op, rows, cols));
+    MCL_TRY(check_ptr(ctx, op, "x", x, 4));
+    MCL_TRY(check_ptr(ctx, op, "weight", weight, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_out", grad_out, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_x", grad_x, 4));
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, op, mcl::launch_rmsnorm_backward_x(x, weight, grad_out, grad_x, rows, (int)cols, eps, ctx->sm_count, ctx->stream));
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_rmsnorm_backward_weight(mcl_cuda_ctx* ctx, const float* x, const float* grad_out, float* row_inv_scratch,
+                                     float* grad_weight, size_t rows, size_t cols, float eps) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "rmsnorm backward_weight";
+    MCL_TRY(check_rows(ctx, op, rows, cols));
+    MCL_TRY(check_ptr(ctx, op, "x", x, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_out", grad_out, 4));
+    MCL_TRY(check_ptr(ctx, op, "row_inv_scratch", row_inv_scratch, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_weight", grad_weight, 4));
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, op, mcl::launch_rmsnorm_backward_weight(x, grad_out, row_inv_scratch, grad_weight, rows, (int)cols, eps, ctx->sm_count, ctx->stream));
+    ctx->launches += 1;     // the row pass and the column pass
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_swiglu(mcl_cuda_ctx* ctx, const float* packed, float* out, size_t rows, size_t hidden) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "swiglu";
+    MCL_TRY(check_rows(ctx, op, rows, hidden));
+    MCL_TRY(check_ptr(ctx, op, "packed", packed, 4));
+    MCL_TRY(check_ptr(ctx, op, "out", out, 4));
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, op, mcl::launch_swiglu(packed, out, rows, (int)hidden, ctx->sm_count, ctx->stream));
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_swiglu_backward(mcl_cuda_ctx* ctx, const float* packed, const float* grad_out, float* grad_packed,
+                             size_t rows, size_t hidden) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "swiglu backward";
+    MCL_TRY(check_rows(ctx, op, rows, hidden));
+    MCL_TRY(check_ptr(ctx, op, "packed", packed, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_out", grad_out, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_packed", grad_packed, 4));
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, op, mcl::launch_swiglu_backward(packed, grad_out, grad_packed, rows, (int)hidden, ctx->sm_count, ctx->stream));
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_softmax_cross_entropy(mcl_cuda_ctx* ctx, const float* logits, const int32_t* targets, float* partial,
+                                   float* out, size_t rows, size_t cols) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "softmax_cross_entropy";
+    MCL_TRY(check_rows(ctx, op, rows, cols));
+    MCL_TRY(check_ptr(ctx, op, "logits", logits, 4));
+    MCL_TRY(check_ptr(ctx, op, "targets", targets, 4));
+    MCL_TRY(check_ptr(ctx, op, "partial", partial, 4));
+    MCL_TRY(check_ptr(ctx, op, "out", out, 4));
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, op, mcl::launch_softmax_cross_entropy(logits, targets, partial, out, rows, (int)cols, ctx->sm_count, ctx->stream));
+    ctx->launches += 1;     // row losses, then their mean
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_softmax_cross_entropy_backward(mcl_cuda_ctx* ctx, const float* logits, const int32_t* targets,
+                                            const float* grad_out, float* grad_logits, size_t rows, size_t cols) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "softmax_cross_entropy backward";
+    MCL_TRY(check_rows(ctx, op, rows, cols));
+    MCL_TRY(check_ptr(ctx, op, "logits", logits, 4));
+    MCL_TRY(check_ptr(ctx, op, "targets", targets, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_out", grad_out, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_logits", grad_logits, 4));
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, op, mcl::launch_softmax_cross_entropy_backward(logits, targets, grad_out, grad_logits, rows, (int)cols, ctx->sm_count, ctx->stream));
+    return MCL_CUDA_OK;
+}
+
+namespace {
+int check_gqa(mcl_cuda_ctx* ctx, const char* op, size_t batch, size_t tq, size_t tk, size_t key_stride, size_t n_head,
+              size_t n_kv, size_t hd, size_t vhd, size_t q_off, size_t window, bool backward) {
+    if (batch == 0 || tq == 0 || tk == 0 || n_head == 0 || n_kv == 0 || hd == 0 || vhd == 0)
+        return fail(ctx, MCL_CUDA_EINVAL, std::string(op) + " requires non-zero dimensions");
+    if (n_head % n_kv != 0) return fail(ctx, MCL_CUDA_EINVAL, std::string(op) + " requires n_head % n_kv_head == 0");
+    if (key_stride < tk) return fail(ctx, MCL_CUDA_EINVAL, std::string(op) + " requires key_stride >= key_tokens");
+    if (batch * n_head > 65535 || tq > 0x7fffffffull || tk > 0x7fffffffull || q_off > 0x3fffffffull ||
+        window > 0x3fffffffull || hd > 65536 || vhd > 65536)
+        return fail(ctx, MCL_CUDA_EINVAL, std::string(op) + " dimension is too large");
+    (void)backward;
+    return MCL_CUDA_OK;
+}
+}  // namespace
+
+int mcl_cuda_gqa_forward(mcl_cuda_ctx* ctx, const float* q, const float* k, const float* v, float* out, size_t batch,
+                         size_t query_tokens, size_t key_tokens, size_t key_stride, size_t n_head, size_t n_kv_head,
+                         size_t head_dim, size_t v_head_dim, int causal, size_t query_offset, size_t sliding_window,
+                         float scale) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "grouped_query_attention";
+    MCL_TRY(check_gqa(ctx, op, batch, query_tokens, key_tokens, key_stride, n_head, n_kv_head, head_dim, v_head_dim,
+                      query_offset, sliding_window, false));
+    MCL_TRY(check_ptr(ctx, op, "q", q, 4));
+    MCL_TRY(check_ptr(ctx, op, "k", k, 4));
+    MCL_TRY(check_ptr(ctx, op, "v", v, 4));
+    MCL_TRY(check_ptr(ctx, op, "out", out, 4));
+    DeviceGuard guard(ctx->device);
+    // scores of every (batch, head, query) row live in the workspace between the two products; the batch is
+    // served in slices that keep it under 4 GiB (one batch element at least)
+    const size_t per_batch = n_head * query_tokens * key_tokens * sizeof(float);
+    size_t slice = ((size_t)4 << 30) / per_batch;
+    if (slice < 1) slice = 1;
+    if (slice > batch) slice = batch;
+    void* ws = nullptr;
+    MCL_TRY(ws_reserve(ctx, slice * per_batch, &ws));
+    int launches = 0;
+    cudaError_t e = cudaSuccess;
+    for (size_t b0 = 0; b0 < batch && e == cudaSuccess; b0 += slice) {
+        const size_t nb = batch - b0 < slice ? batch - b0 : slice;
+        e = mcl::launch_gqa_forward(q + b0 * query_tokens * n_head * head_dim, k + b0 * key_stride * n_kv_head * head_dim,
+                                    v + b0 * key_stride * n_kv_head * v_head_dim, out + b0 * query_tokens * n_head * v_head_dim,
+                                    (int)nb, (int)query_tokens, (int)key_tokens, (int)key_stride, (int)n_head, (int)n_kv_head,
+                                    (int)head_dim, (int)v_head_dim, causal ? 1 : 0, (int)query_offset, (int)sliding_window,
+                                    scale, static_cast<float*>(ws), ctx->stream, &launches);
+    }
+    if (e != cudaSuccess) return fail_cuda(ctx, op, e);
+    ctx->launches += launches;
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_gqa_backward(mcl_cuda_ctx* ctx, const float* q, const float* k, const float* v, const float* grad_out,
+                          float* probs_scratch, float* ds_scratch, float* grad_q, float* grad_k, float* grad_v,
+                          size_t batch, size_t query_tokens, size_t key_tokens, size_t n_head, size_t n_kv_head,
+                          size_t head_dim, int causal, size_t query_offset, float scale) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "grouped_query_attention backward";
+    MCL_TRY(check_gqa(ctx, op, batch, query_tokens, key_tokens, key_tokens, n_head, n_kv_head, head_dim, head_dim,
+                      query_offset, 0, true));
+    MCL_TRY(check_ptr(ctx, op, "q", q, 4));
+    MCL_TRY(check_ptr(ctx, op, "k", k, 4));
+    MCL_TRY(check_ptr(ctx, op, "v", v, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_out", grad_out, 4));
+    MCL_TRY(check_ptr(ctx, op, "probs_scratch", probs_scratch, 4));
+    MCL_TRY(check_ptr(ctx, op, "ds_scratch", ds_scratch, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_q", grad_q, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_k", grad_k, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_v", grad_v, 4));
+    DeviceGuard guard(ctx->device);
+    int launches = 0;
+    cudaError_t e = mcl::launch_gqa_backward(q, k, v, grad_out, probs_scratch, ds_scratch, grad_q, grad_k, grad_v,
+                                             (int)batch, (int)query_tokens, (int)key_tokens, (int)n_head, (int)n_kv_head,
+                                             (int)head_dim, causal ? 1 : 0, (int)query_offset, scale, ctx->stream, &launches);
+    if (e != cudaSuccess) return fail_cuda(ctx, op, e);
+    ctx->launches += launches;
     return MCL_CUDA_OK;
 }
 

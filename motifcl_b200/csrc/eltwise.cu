@@ -17,6 +17,7 @@ __global__ void __launch_bounds__(256) eltwise_kernel(const float* __restrict__ 
         else if (OP == 2) r = __fmul_rn(a[i], b[i]);
         else if (OP == 3) r = __fmul_rn(a[i], alpha);
         else if (OP == 4) r = __fadd_rn(a[i], alpha);
+        else if (OP == 6) r = a[i] - alpha * b[i];      // sgd step (kernels/vulkan/sgd_update_f32.comp)
         else r = 0.0f;
         out[i] = r;
     }
@@ -36,6 +37,7 @@ cudaError_t launch_eltwise_f32(int op, const float* a, const float* b, float* ou
         case 3: eltwise_kernel<3><<<(int)blocks, 256, 0, stream>>>(a, b, out, n, alpha); break;
         case 4: eltwise_kernel<4><<<(int)blocks, 256, 0, stream>>>(a, b, out, n, alpha); break;
         case 5: eltwise_kernel<5><<<(int)blocks, 256, 0, stream>>>(a, b, out, n, alpha); break;
+        case 6: eltwise_kernel<6><<<(int)blocks, 256, 0, stream>>>(a, b, out, n, alpha); break;
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();

@@ -124,8 +124,30 @@ cudaError_t launch_ternary_gemv_tc(const float* x, const uint32_t* packed2, cons
                                    int in_features, int out_features, void* workspace, int* err_word, int sm_count,
                                    size_t max_smem, cudaStream_t stream, int* launches);
 
-// eltwise.cu: op 0 add, 1 sub, 2 mul, 3 mul_scalar, 4 add_scalar, 5 zero
+// eltwise.cu: op 0 add, 1 sub, 2 mul, 3 mul_scalar, 4 add_scalar, 5 zero, 6 a - alpha*b
 cudaError_t launch_eltwise_f32(int op, const float* a, const float* b, float* out, size_t n, float alpha,
                                int sm_count, cudaStream_t stream);
+
+// trainer_ops.cu -- the fp32 row ops of the ternary15m block stack around its counter layers
+cudaError_t launch_rmsnorm(const float* x, const float* w, float* out, size_t rows, int cols, float eps, int sm_count,
+                           cudaStream_t stream);
+cudaError_t launch_rmsnorm_backward_x(const float* x, const float* w, const float* dy, float* dx, size_t rows, int cols,
+                                      float eps, int sm_count, cudaStream_t stream);
+cudaError_t launch_rmsnorm_backward_weight(const float* x, const float* dy, float* row_inv, float* dw, size_t rows,
+                                           int cols, float eps, int sm_count, cudaStream_t stream);
+cudaError_t launch_swiglu(const float* packed, float* out, size_t rows, int hidden, int sm_count, cudaStream_t stream);
+cudaError_t launch_swiglu_backward(const float* packed, const float* dy, float* dpacked, size_t rows, int hidden,
+                                   int sm_count, cudaStream_t stream);
+cudaError_t launch_softmax_cross_entropy(const float* logits, const int* targets, float* partial, float* out, size_t rows,
+                                         int cols, int sm_count, cudaStream_t stream);
+cudaError_t launch_softmax_cross_entropy_backward(const float* logits, const int* targets, const float* grad_out,
+                                                  float* grad_logits, size_t rows, int cols, int sm_count,
+                                                  cudaStream_t stream);
+cudaError_t launch_gqa_forward(const float* q, const float* k, const float* v, float* out, int batch, int tq, int tk,
+                               int key_stride, int n_head, int n_kv, int hd, int vhd, int causal, int q_off, int window,
+                               float scale, float* scores_ws, cudaStream_t stream, int* launches);
+cudaError_t launch_gqa_backward(const float* q, const float* k, const float* v, const float* dout, float* probs, float* ds,
+                                float* dq, float* dk, float* dv, int batch, int tq, int tk, int n_head, int n_kv, int hd,
+                                int causal, int q_off, float scale, cudaStream_t stream, int* launches);
 
 }  // namespace mcl

@@ -205,6 +205,50 @@ class Context:
         self._check(self._lib.mcl_cuda_matmul_f32(self._ctx, _ptr(a), _ptr(b), _ptr(c), M, K, N,
                                                   int(trans_a), int(trans_b)))
 
+    # ---- fp32 row ops of the ternary15m block stack (MotifCL src/ops/norm.cpp, activation.cpp, loss.cpp,
+    # attention.cpp on its Vulkan seam) -------------------------------------------------------------
+    def eltwise(self, op: int, a, b, out, elements, alpha=0.0):
+        self._check(self._lib.mcl_cuda_eltwise_f32(self._ctx, op, _ptr(a) if a is not None else None,
+                                                   _ptr(b) if b is not None else None, _ptr(out), elements, alpha))
+
+    def rmsnorm(self, x, weight, out, rows, cols, eps):
+        self._check(self._lib.mcl_cuda_rmsnorm(self._ctx, _ptr(x), _ptr(weight), _ptr(out), rows, cols, eps))
+
+    def rmsnorm_backward_x(self, x, weight, grad_out, grad_x, rows, cols, eps):
+        self._check(self._lib.mcl_cuda_rmsnorm_backward_x(self._ctx, _ptr(x), _ptr(weight), _ptr(grad_out),
+                                                          _ptr(grad_x), rows, cols, eps))
+
+    def rmsnorm_backward_weight(self, x, grad_out, row_inv, grad_weight, rows, cols, eps):
+        self._check(self._lib.mcl_cuda_rmsnorm_backward_weight(self._ctx, _ptr(x), _ptr(grad_out), _ptr(row_inv),
+                                                               _ptr(grad_weight), rows, cols, eps))
+
+    def swiglu(self, packed, out, rows, hidden):
+        self._check(self._lib.mcl_cuda_swiglu(self._ctx, _ptr(packed), _ptr(out), rows, hidden))
+
+    def swiglu_backward(self, packed, grad_out, grad_packed, rows, hidden):
+        self._check(self._lib.mcl_cuda_swiglu_backward(self._ctx, _ptr(packed), _ptr(grad_out), _ptr(grad_packed),
+                                                       rows, hidden))
+
+    def softmax_cross_entropy(self, logits, targets, partial, out, rows, cols):
+        self._check(self._lib.mcl_cuda_softmax_cross_entropy(self._ctx, _ptr(logits), _ptr(targets), _ptr(partial),
+                                                             _ptr(out), rows, cols))
+
+    def softmax_cross_entropy_backward(self, logits, targets, grad_out, grad_logits, rows, cols):
+        self._check(self._lib.mcl_cuda_softmax_cross_entropy_backward(self._ctx, _ptr(logits), _ptr(targets),
+                                                                      _ptr(grad_out), _ptr(grad_logits), rows, cols))
+
+    def gqa_forward(self, q, k, v, out, batch, tq, tk, key_stride, n_head, n_kv_head, head_dim, v_head_dim,
+                    causal, query_offset, sliding_window, scale):
+        self._check(self._lib.mcl_cuda_gqa_forward(self._ctx, _ptr(q), _ptr(k), _ptr(v), _ptr(out), batch, tq, tk,
+                                                   key_stride, n_head, n_kv_head, head_dim, v_head_dim, int(causal),
+                                                   query_offset, sliding_window, scale))
+
+    def gqa_backward(self, q, k, v, grad_out, probs, ds, grad_q, grad_k, grad_v, batch, tq, tk, n_head, n_kv_head,
+                     head_dim, causal, query_offset, scale):
+        self._check(self._lib.mcl_cuda_gqa_backward(self._ctx, _ptr(q), _ptr(k), _ptr(v), _ptr(grad_out), _ptr(probs),
+                                                    _ptr(ds), _ptr(grad_q), _ptr(grad_k), _ptr(grad_v), batch, tq, tk,
+                                                    n_head, n_kv_head, head_dim, int(causal), query_offset, scale))
+
     def ternary_gemv(self, x, packed2, scale, y, M, in_features, out_features):
         self._check(self._lib.mcl_cuda_ternary_gemv(self._ctx, _ptr(x), _ptr(packed2), _ptr(scale),
                                                     _ptr(y), M, in_features, out_features))

@@ -1,0 +1,191 @@
+"""The fp32 row ops of the ternary15m block stack (rmsnorm, swiglu, softmax cross-entropy, batched
+grouped-query attention, their backward kernels, the sgd step) through the C ABI, against float64
+restatements of MotifCL's shader arithmetic (kernels/vulkan/rmsnorm_f32.comp, rmsnorm_bwd_x_f32.comp,
+rmsnorm_bwd_w_f32.comp, swiglu_f32.comp, swiglu_bwd_f32.comp, ce_fwd_rows_f32.comp, ce_bwd_f32.comp,
+gqa_fwd_general_f32.comp, gqa_bwd_probs_f32.comp, gqa_bwd_dkv_f32.comp).  These are floating-point
+kernels whose reduction order differs from the shaders', so the bar is a tolerance, stated per test:
+relative L2 error <= 2e-6 against the float64 result (fp32 rounding of sums of a few hundred terms).
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-6
+
+
+def rel_l2(a, ref):
+    a = a.detach().double().cpu()
+    ref = ref.detach().double().cpu()
+    return float((a - ref).norm() / max(float(ref.norm()), 1e-30))
+
+
+def dev(a):
+    return a.to("cuda", torch.float32).contiguous()
+
+
+@pytest.mark.parametrize("rows,cols", [(7, 288), (256, 288), (33, 100), (4, 4096)])
+def test_rmsnorm_forward_and_backward(ctx, rows, cols):
+    g = torch.Generator().manual_seed(rows * 1000 + cols)
+    x = torch.randn(rows, cols, generator=g, dtype=torch.float64)
+    w = torch.rand(cols, generator=g, dtype=torch.float64) + 0.5
+    dy = torch.randn(rows, cols, generator=g, dtype=torch.float64)
+    eps = 1e-5
+    inv = 1.0 / torch.sqrt((x * x).mean(dim=1, keepdim=True) + eps)
+    ref_y = x * inv * w
+    dot = (dy * w * x).sum(dim=1, keepdim=True)
+    ref_dx = dy * w * inv - x * inv ** 3 * dot / cols
+    ref_dw = (dy * x * inv).sum(dim=0)
+
+    xd, wd, dyd = dev(x), dev(w), dev(dy)
+    y = torch.empty_like(xd)
+    ctx.rmsnorm(xd, wd, y, rows, cols, eps)
+    dx = torch.empty_like(xd)
+    ctx.rmsnorm_backward_x(xd, wd, dyd, dx, rows, cols, eps)
+    row_inv = torch.empty(rows, device="cuda")
+    dw = torch.full((cols,), 123.0, device="cuda")          # must be overwritten, not accumulated into
+    ctx.rmsnorm_backward_weight(xd, dyd, row_inv, dw, rows, cols, eps)
+    torch.cuda.synchronize()
+    assert rel_l2(y, ref_y) <= TOL
+    assert rel_l2(dx, ref_dx) <= TOL
+    assert rel_l2(row_inv, inv.squeeze(1)) <= TOL
+    assert rel_l2(dw, ref_dw) <= TOL
+
+
+@pytest.mark.parametrize("rows,hidden", [(5, 768), (300, 64), (1, 1)])
+def test_swiglu_forward_and_backward(ctx, rows, hidden):
+    g = torch.Generator().manual_seed(rows + hidden)
+    packed = torch.randn(rows, 2 * hidden, generator=g, dtype=torch.float64) * 2
+    dy = torch.randn(rows, hidden, generator=g, dtype=torch.float64)
+    gate, up = packed[:, :hidden], packed[:, hidden:]
+    sig = torch.sigmoid(gate)
+    ref = gate * sig * up
+    ref_d = torch.cat([dy * up * (sig + gate * sig * (1 - sig)), dy * gate * sig], dim=1)
+    pd, dyd = dev(packed), dev(dy)
+    out = torch.empty(rows, hidden, device="cuda")
+    ctx.swiglu(pd, out, rows, hidden)
+    dp = torch.empty_like(pd)
+    ctx.swiglu_backward(pd, dyd, dp, rows, hidden)
+    torch.cuda.synchronize()
+    assert rel_l2(out, ref) <= TOL
+    assert rel_l2(dp, ref_d) <= TOL
+
+
+@pytest.mark.parametrize("rows,cols", [(9, 32000), (64, 257), (1, 2)])
+def test_softmax_cross_entropy_forward_and_backward(ctx, rows, cols):
+    g = torch.Generator().manual_seed(rows * 7 + cols)
+    logits = torch.randn(rows, cols, generator=g, dtype=torch.float64) * 3
+    targets = torch.randint(0, cols, (rows,), generator=g, dtype=torch.int32)
+    if rows > 2:
+        targets[1] = -1            # outside [0, cols): contributes a zero loss, like the reference's shader
+    valid = (targets >= 0) & (targets < cols)
+    lse = torch.logsumexp(logits, dim=1)
+    picked = logits[torch.arange(rows), targets.clamp(0, cols - 1).long()]
+    ref_rows = torch.where(valid, lse - picked, torch.zeros_like(lse))
+    ref_loss = ref_rows.sum() / rows
+    go = 0.75
+    onehot = torch.zeros_like(logits)
+    onehot[torch.arange(rows)[valid], targets[valid].long()] = 1.0
+    ref_grad = go / rows * (torch.softmax(logits, dim=1) - onehot)
+
+    ld, td = dev(logits), targets.to("cuda")
+    partial = torch.empty(rows, device="cuda")
+    out = torch.empty(1, device="cuda")
+    ctx.softmax_cross_entropy(ld, td, partial, out, rows, cols)
+    grad = torch.empty_like(ld)
+    ctx.softmax_cross_entropy_backward(ld, td, torch.tensor([go], device="cuda"), grad, rows, cols)
+    torch.cuda.synchronize()
+    assert rel_l2(partial, ref_rows) <= TOL
+    assert abs(float(out[0]) - float(ref_loss)) <= TOL * max(1.0, abs(float(ref_loss)))
+    assert rel_l2(grad, ref_grad) <= TOL
+
+
+def _attention_reference(q, k, v, B, Tq, Tk, H, G, hd, vhd, causal, q_off, window, scale):
+    """float64 attention with the reference's masking rules; returns out and the probabilities."""
+    qh = q.view(B, Tq, H, hd).permute(0, 2, 1, 3)
+    kh = k.view(B, Tk, G, hd).permute(0, 2, 1, 3).repeat_interleave(H // G, dim=1)
+    vh = v.view(B, Tk, G, vhd).permute(0, 2, 1, 3).repeat_interleave(H // G, dim=1)
+    s = qh @ kh.transpose(-1, -2) * scale
+    tq = torch.arange(Tq).view(Tq, 1) + q_off
+    tk = torch.arange(Tk).view(1, Tk)
+    allowed = torch.ones(Tq, Tk, dtype=torch.bool)
+    if causal:
+        allowed &= tk <= tq
+    if window:
+        allowed &= tk >= (tq + 1 - window).clamp(min=0)
+    s = s.masked_fill(~allowed, float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    out = (p @ vh).permute(0, 2, 1, 3).reshape(B * Tq, H * vhd)
+    return out, p
+
+
+@pytest.mark.parametrize("B,Tq,Tk,H,G,hd,causal,q_off,window", [
+    (2, 64, 64, 6, 6, 48, False, 0, 0),        # the block stack's call: batched, unmasked
+    (2, 64, 64, 6, 6, 48, True, 0, 0),         # the trainer's call: causal
+    (1, 5, 37, 4, 2, 16, True, 32, 0),         # grouped heads, decode-style offset
+    (1, 40, 40, 2, 1, 8, True, 0, 7),          # sliding window
+    (1, 3, 300, 2, 2, 130, False, 0, 0),       # head_dim above one block's thread count
+])
+def test_gqa_forward_and_backward(ctx, B, Tq, Tk, H, G, hd, causal, q_off, window):
+    g = torch.Generator().manual_seed(B * 100 + Tq + Tk + hd)
+    q = torch.randn(B * Tq, H * hd, generator=g, dtype=torch.float64, requires_grad=True)
+    k = torch.randn(B * Tk, G * hd, generator=g, dtype=torch.float64, requires_grad=True)
+    v = torch.randn(B * Tk, G * hd, generator=g, dtype=torch.float64, requires_grad=True)
+    dout = torch.randn(B * Tq, H * hd, generator=g, dtype=torch.float64)
+    scale = 1.0 / math.sqrt(hd)
+    ref, p = _attention_reference(q, k, v, B, Tq, Tk, H, G, hd, hd, causal, q_off, window, scale)
+
+    qd, kd, vd = dev(q), dev(k), dev(v)
+    out = torch.empty(B * Tq, H * hd, device="cuda")
+    ctx.gqa_forward(qd, kd, vd, out, B, Tq, Tk, Tk, H, G, hd, hd, causal, q_off, window, scale)
+    torch.cuda.synchronize()
+    assert rel_l2(out, ref) <= TOL
+
+    if window:
+        return                                  # the reference's backward has no sliding window either
+    ref.backward(dout)
+    probs = torch.empty(B * H * Tq * Tk, device="cuda")
+    ds = torch.empty_like(probs)
+    dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
+    ctx.gqa_backward(qd, kd, vd, dev(dout), probs, ds, dq, dk, dv, B, Tq, Tk, H, G, hd, causal, q_off, scale)
+    torch.cuda.synchronize()
+    assert rel_l2(probs.view(B, H, Tq, Tk), p) <= TOL
+    assert rel_l2(dq, q.grad) <= 2 * TOL
+    assert rel_l2(dk, k.grad) <= 2 * TOL
+    assert rel_l2(dv, v.grad) <= 2 * TOL
+
+
+def test_gqa_padded_key_stride(ctx):
+    """Keys stored with a stride larger than key_tokens (a KV cache with room to grow)."""
+    B, Tq, Tk, stride, H, G, hd = 2, 3, 10, 16, 4, 2, 32
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(B * Tq, H * hd, generator=g, dtype=torch.float64)
+    kfull = torch.randn(B, stride, G * hd, generator=g, dtype=torch.float64)
+    vfull = torch.randn(B, stride, G * hd, generator=g, dtype=torch.float64)
+    scale = 0.2
+    ref, _ = _attention_reference(q, kfull[:, :Tk].reshape(B * Tk, -1), vfull[:, :Tk].reshape(B * Tk, -1),
+                                  B, Tq, Tk, H, G, hd, hd, True, Tk - Tq, 0, scale)
+    out = torch.empty(B * Tq, H * hd, device="cuda")
+    ctx.gqa_forward(dev(q), dev(kfull.reshape(B * stride, -1)), dev(vfull.reshape(B * stride, -1)), out,
+                    B, Tq, Tk, stride, H, G, hd, hd, True, Tk - Tq, 0, scale)
+    torch.cuda.synchronize()
+    assert rel_l2(out, ref) <= TOL
+
+
+def test_sgd_step_and_argument_checks(ctx):
+    n = 1000
+    p = torch.randn(n, device="cuda")
+    gr = torch.randn(n, device="cuda")
+    out = torch.empty_like(p)
+    ctx.eltwise(6, p, gr, out, n, 0.01)
+    torch.cuda.synchronize()
+    assert rel_l2(out, p.double() - 0.01 * gr.double()) <= TOL
+    x = torch.zeros(4, 4, device="cuda")
+    with pytest.raises(RuntimeError, match="non-zero"):
+        ctx.rmsnorm(x, x, x, 0, 4, 1e-5)
+    with pytest.raises(RuntimeError, match="n_head % n_kv_head"):
+        ctx.gqa_forward(x, x, x, x, 1, 1, 1, 1, 3, 2, 1, 1, False, 0, 0, 1.0)
+    with pytest.raises(RuntimeError, match="key_stride"):
+        ctx.gqa_forward(x, x, x, x, 1, 1, 4, 2, 1, 1, 1, 1, False, 0, 0, 1.0)

@@ -272,6 +272,32 @@ int mcl_cuda_gqa_backward(mcl_cuda_ctx* ctx, const float* q, const float* k, con
                           size_t batch, size_t query_tokens, size_t key_tokens, size_t n_head, size_t n_kv_head,
                           size_t head_dim, int causal, size_t query_offset, float scale);
 
+/* ---- the remaining fp32 ops of the ternary15m trainer step (tools/train_ternary15m.cpp:273-293,377): they replace
+ * run_vulkan_token_position_embedding (:821), run_vulkan_embedding_gather (:776), run_vulkan_embedding_weight_backward
+ * and its _scatter / _scatter_cas variants (:784-819), run_vulkan_position_embedding_backward (:832), run_vulkan_rope /
+ * run_vulkan_rope_split_half (:842,:865) and run_vulkan_adam_update_fast (:704) of
+ * include/motifcl/runtime/vulkan_backend.hpp; callers: src/nn/embedding.cpp:18-120,268-300, src/ops/attention.cpp:838-906,
+ * src/ops/optim.cpp:47-65.
+ *   token_position_embedding  out[t,:] = token_weight[ids[t],:] (0 for an id outside [0,vocab)) + pos_weight[t % seq_len,:];
+ *                             pos_weight NULL = plain gather
+ *   embedding_weight_backward grad_weight[ids[t],:] += grad_out[t,:]; zero_first != 0 clears grad_weight [vocab,dim] first
+ *                             (the reference's scatter variants expect the caller to have cleared it)
+ *   position_embedding_backward grad_position[p,:] = sum_b grad_out[b*seq_len+p,:]  (rows p < seq_len only)
+ *   rope                      x, out [batch*tokens, channels]; heads of head_dim at the front of each row; rotary_dim 0 =
+ *                             head_dim; split_half pairs (i, i+head_dim/2), else (2i, 2i+1); inverse negates the angle
+ *   adam_update               m,v,param updated in place; c1, c2 = 1/(1-beta^step) ---- */
+int mcl_cuda_token_position_embedding(mcl_cuda_ctx* ctx, const float* token_weight, const float* pos_weight,
+                                      const int32_t* token_ids, float* out, size_t token_count, size_t vocab_size,
+                                      size_t seq_len, size_t embed_dim);
+int mcl_cuda_embedding_weight_backward(mcl_cuda_ctx* ctx, const int32_t* indices, const float* grad_out, float* grad_weight,
+                                       size_t vocab_size, size_t embed_dim, size_t token_count, int zero_first);
+int mcl_cuda_position_embedding_backward(mcl_cuda_ctx* ctx, const float* grad_out, float* grad_position, size_t batch,
+                                         size_t seq_len, size_t embed_dim);
+int mcl_cuda_rope(mcl_cuda_ctx* ctx, const float* x, float* out, size_t batch, size_t tokens, size_t channels, size_t n_head,
+                  size_t head_dim, size_t rotary_dim, size_t token_offset, float theta, int inverse, int split_half);
+int mcl_cuda_adam_update(mcl_cuda_ctx* ctx, float* param, const float* grad, float* m, float* v, size_t elements, float lr,
+                         float beta1, float beta2, float eps, float weight_decay, float c1, float c2);
+
 /* ---- ternary decode GEMV, M <= 16 (no reference kernel; semantics of the forward above
  * applied to 2-bit weights).  y[M,out] = x[M,in] * (scale . t)^T.  Requires in % 16 == 0. ---- */
 int mcl_cuda_ternary_gemv(mcl_cuda_ctx* ctx, const float* x, const uint32_t* packed2,

@@ -98,6 +98,11 @@ def lib() -> C.CDLL:
         L.mcl_cuda_swiglu_backward.argtypes = [vp, vp, vp, vp, sz, sz]
         L.mcl_cuda_softmax_cross_entropy.argtypes = [vp, vp, vp, vp, vp, sz, sz]
         L.mcl_cuda_softmax_cross_entropy_backward.argtypes = [vp, vp, vp, vp, vp, sz, sz]
+        L.mcl_cuda_token_position_embedding.argtypes = [vp, vp, vp, vp, vp, sz, sz, sz, sz]
+        L.mcl_cuda_embedding_weight_backward.argtypes = [vp, vp, vp, vp, sz, sz, sz, i]
+        L.mcl_cuda_position_embedding_backward.argtypes = [vp, vp, vp, sz, sz, sz]
+        L.mcl_cuda_rope.argtypes = [vp, vp, vp, sz, sz, sz, sz, sz, sz, sz, f, i, i]
+        L.mcl_cuda_adam_update.argtypes = [vp, vp, vp, vp, vp, sz, f, f, f, f, f, f, f]
         L.mcl_cuda_gqa_forward.argtypes = [vp, vp, vp, vp, vp, sz, sz, sz, sz, sz, sz, sz, sz, i, sz, sz, f]
         L.mcl_cuda_gqa_backward.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, sz, sz, i, sz, f]
         L.mcl_cuda_ternary_gemv.argtypes = [vp, vp, vp, vp, vp, sz, sz, sz]

@@ -26,12 +26,14 @@ namespace {
 const std::uint32_t kNativeTag[1] = {0x4D434C55u};
 enum NativeOp : std::size_t {
     kOpDecode = 1, kOpForward, kOpBackwardInput, kOpUpdateFused, kOpMatmul, kOpEltwise,
-    kOpRmsnorm, kOpRmsnormBwdX, kOpRmsnormBwdW, kOpSwiglu, kOpSwigluBwd, kOpCe, kOpCeBwd, kOpGqa, kOpGqaBwd
+    kOpRmsnorm, kOpRmsnormBwdX, kOpRmsnormBwdW, kOpSwiglu, kOpSwigluBwd, kOpCe, kOpCeBwd, kOpGqa, kOpGqaBwd,
+    kOpEmbedding, kOpEmbeddingBwd, kOpPositionBwd, kOpRope, kOpAdam
 };
 struct NativeArgs {
     std::size_t a = 0, b = 0, c = 0, d = 0;          // dimensions (meaning depends on the op)
     std::size_t e = 0, f = 0, g = 0, h = 0, i = 0, j = 0;
     int causal = 0;
+    float f0 = 0, f1 = 0, f2 = 0, f3 = 0, f4 = 0, f5 = 0, f6 = 0;
     float lr = 0, lr_scale = 0, rms_beta = 0, rms_eps = 0;
     std::uint32_t seed = 0;
     int trans_a = 0, trans_b = 0;
@@ -257,6 +259,26 @@ VulkanOpResult VulkanRuntime::dispatch_cached(const std::uint32_t* spirv, std::s
             rc = mcl_cuda_gqa_backward(ctx, (const float*)p(0), (const float*)p(1), (const float*)p(2), (const float*)p(3),
                                        (float*)p(4), (float*)p(5), (float*)p(6), (float*)p(7), (float*)p(8), a.a, a.b, a.c,
                                        a.e, a.f, a.g, a.causal, a.i, a.alpha);
+            break;
+        case kOpEmbedding:       // token_weight, [pos_weight,] ids, out | tokens, vocab, seq_len, dim
+            rc = mcl_cuda_token_position_embedding(ctx, (const float*)p(0), bufs.size() > 3 ? (const float*)p(1) : nullptr,
+                                                   (const int32_t*)p(bufs.size() - 2), (float*)p(bufs.size() - 1), a.a, a.b,
+                                                   a.c, a.d);
+            break;
+        case kOpEmbeddingBwd:    // ids, grad_out, grad_weight | vocab, dim, tokens, zero_first
+            rc = mcl_cuda_embedding_weight_backward(ctx, (const int32_t*)p(0), (const float*)p(1), (float*)p(2), a.a, a.b, a.c,
+                                                    a.causal);
+            break;
+        case kOpPositionBwd:     // grad_out, grad_position | batch, seq_len, dim
+            rc = mcl_cuda_position_embedding_backward(ctx, (const float*)p(0), (float*)p(1), a.a, a.b, a.c);
+            break;
+        case kOpRope:            // x, out | batch, tokens, channels, heads, head_dim, rotary_dim, offset; theta; inverse, split
+            rc = mcl_cuda_rope(ctx, (const float*)p(0), (float*)p(1), a.a, a.b, a.c, a.d, a.e, a.f, a.g, a.alpha, a.causal,
+                               a.trans_a);
+            break;
+        case kOpAdam:            // param, grad, m, v | elements; lr, beta1, beta2, eps, weight_decay, c1, c2
+            rc = mcl_cuda_adam_update(ctx, (float*)p(0), (const float*)p(1), (float*)p(2), (float*)p(3), a.a, a.f0, a.f1, a.f2,
+                                      a.f3, a.f4, a.f5, a.f6);
             break;
         default:
             r.error = "unknown native operation";
@@ -522,5 +544,96 @@ VulkanOpResult run_vulkan_grouped_query_attention_backward(
     NativeArgs a; a.a = batch; a.b = query_tokens; a.c = key_tokens; a.e = n_head; a.f = n_kv_head; a.g = head_dim;
     a.causal = causal ? 1 : 0; a.i = query_offset; a.alpha = scale;
     return native(rt, kOpGqaBwd, {&q, &k, &v, &grad_out, &probs_scratch, &ds_scratch, &grad_q, &grad_k, &grad_v}, a);
+}
+
+// ---- embeddings, rope, adam ----------------------------------------------------------------------------
+VulkanOpResult run_vulkan_token_position_embedding(VulkanRuntime& rt, const VulkanBuffer& token_weight,
+                                                    const VulkanBuffer& pos_weight, const VulkanBuffer& token_ids,
+                                                    VulkanBuffer& out, std::size_t vocab_size, std::size_t seq_len,
+                                                    std::size_t embed_dim) {
+    if (vocab_size == 0 || seq_len == 0 || embed_dim == 0)
+        return refuse(rt, "Vulkan token+position embedding requires non-zero shapes");
+    // as in the reference, the token count is implied by the output buffer
+    const std::size_t tokens = out.nbytes() / (embed_dim * 4);
+    if (tokens == 0) return refuse(rt, "Vulkan token+position embedding output buffer too small");
+    if (token_ids.nbytes() < tokens * 4 || token_weight.nbytes() < vocab_size * embed_dim * 4 ||
+        pos_weight.nbytes() < seq_len * embed_dim * 4)
+        return refuse(rt, "Vulkan token+position embedding buffer is too small");
+    NativeArgs a; a.a = tokens; a.b = vocab_size; a.c = seq_len; a.d = embed_dim;
+    return native(rt, kOpEmbedding, {&token_weight, &pos_weight, &token_ids, &out}, a);
+}
+VulkanOpResult run_vulkan_embedding_gather(VulkanRuntime& rt, const VulkanBuffer& weight, const VulkanBuffer& indices,
+                                           VulkanBuffer& out, std::size_t vocab_size, std::size_t embed_dim,
+                                           std::size_t token_count) {
+    if (indices.nbytes() < token_count * 4 || weight.nbytes() < vocab_size * embed_dim * 4 ||
+        out.nbytes() < token_count * embed_dim * 4)
+        return refuse(rt, "Vulkan embedding gather buffer is too small");
+    NativeArgs a; a.a = token_count; a.b = vocab_size; a.c = 1; a.d = embed_dim;
+    return native(rt, kOpEmbedding, {&weight, &indices, &out}, a);
+}
+namespace {
+VulkanOpResult embedding_backward(VulkanRuntime& rt, const VulkanBuffer& indices, const VulkanBuffer& grad_out,
+                                  VulkanBuffer& grad_weight, std::size_t vocab_size, std::size_t embed_dim,
+                                  std::size_t token_count, int zero_first) {
+    if (indices.nbytes() < token_count * 4 || grad_out.nbytes() < token_count * embed_dim * 4 ||
+        grad_weight.nbytes() < vocab_size * embed_dim * 4)
+        return refuse(rt, "Vulkan embedding weight backward buffer is too small");
+    NativeArgs a; a.a = vocab_size; a.b = embed_dim; a.c = token_count; a.causal = zero_first;
+    return native(rt, kOpEmbeddingBwd, {&indices, &grad_out, &grad_weight}, a);
+}
+}  // namespace
+VulkanOpResult run_vulkan_embedding_weight_backward(VulkanRuntime& rt, const VulkanBuffer& indices, const VulkanBuffer& grad_out,
+                                                    VulkanBuffer& grad_weight, std::size_t vocab_size, std::size_t embed_dim,
+                                                    std::size_t token_count) {
+    return embedding_backward(rt, indices, grad_out, grad_weight, vocab_size, embed_dim, token_count, 1);
+}
+VulkanOpResult run_vulkan_embedding_weight_backward_scatter(VulkanRuntime& rt, const VulkanBuffer& indices,
+                                                            const VulkanBuffer& grad_out, VulkanBuffer& grad_weight,
+                                                            std::size_t vocab_size, std::size_t embed_dim,
+                                                            std::size_t token_count) {
+    return embedding_backward(rt, indices, grad_out, grad_weight, vocab_size, embed_dim, token_count, 0);
+}
+VulkanOpResult run_vulkan_embedding_weight_backward_scatter_cas(VulkanRuntime& rt, const VulkanBuffer& indices,
+                                                                const VulkanBuffer& grad_out, VulkanBuffer& grad_weight,
+                                                                std::size_t vocab_size, std::size_t embed_dim,
+                                                                std::size_t token_count) {
+    return embedding_backward(rt, indices, grad_out, grad_weight, vocab_size, embed_dim, token_count, 0);
+}
+VulkanOpResult run_vulkan_position_embedding_backward(VulkanRuntime& rt, const VulkanBuffer& grad_out,
+                                                       VulkanBuffer& grad_position, std::size_t batch, std::size_t seq_len,
+                                                       std::size_t embed_dim) {
+    if (grad_out.nbytes() < batch * seq_len * embed_dim * 4 || grad_position.nbytes() < seq_len * embed_dim * 4)
+        return refuse(rt, "Vulkan position embedding backward buffer is too small");
+    NativeArgs a; a.a = batch; a.b = seq_len; a.c = embed_dim;
+    return native(rt, kOpPositionBwd, {&grad_out, &grad_position}, a);
+}
+namespace {
+VulkanOpResult rope(VulkanRuntime& rt, const VulkanBuffer& x, VulkanBuffer& out, std::size_t batch, std::size_t tokens,
+                    std::size_t channels, std::size_t n_head, std::size_t head_dim, std::size_t rotary_dim,
+                    std::size_t token_offset, float theta, bool inverse, int split_half) {
+    if (x.nbytes() < batch * tokens * channels * 4 || out.nbytes() < batch * tokens * channels * 4)
+        return refuse(rt, "Vulkan rope buffer is too small");
+    NativeArgs a; a.a = batch; a.b = tokens; a.c = channels; a.d = n_head; a.e = head_dim; a.f = rotary_dim; a.g = token_offset;
+    a.alpha = theta; a.causal = inverse ? 1 : 0; a.trans_a = split_half;
+    return native(rt, kOpRope, {&x, &out}, a);
+}
+}  // namespace
+VulkanOpResult run_vulkan_rope(VulkanRuntime& rt, const VulkanBuffer& x, VulkanBuffer& out, std::size_t batch, std::size_t tokens,
+                               std::size_t channels, std::size_t n_head, std::size_t head_dim, std::size_t rotary_dim,
+                               std::size_t token_offset, float theta, bool inverse) {
+    return rope(rt, x, out, batch, tokens, channels, n_head, head_dim, rotary_dim, token_offset, theta, inverse, 0);
+}
+VulkanOpResult run_vulkan_rope_split_half(VulkanRuntime& rt, const VulkanBuffer& x, VulkanBuffer& out, std::size_t batch,
+                                          std::size_t tokens, std::size_t channels, std::size_t n_head, std::size_t head_dim,
+                                          std::size_t rotary_dim, std::size_t token_offset, float theta, bool inverse) {
+    return rope(rt, x, out, batch, tokens, channels, n_head, head_dim, rotary_dim, token_offset, theta, inverse, 1);
+}
+VulkanOpResult run_vulkan_adam_update_fast(VulkanRuntime& rt, const VulkanBuffer& param, const VulkanBuffer& grad,
+                                           VulkanBuffer& m, VulkanBuffer& v, std::size_t elements, float lr, float beta1,
+                                           float beta2, float eps, float weight_decay, float c1, float c2) {
+    if (param.nbytes() < elements * 4 || grad.nbytes() < elements * 4 || m.nbytes() < elements * 4 || v.nbytes() < elements * 4)
+        return refuse(rt, "Vulkan adam_update buffer is too small");
+    NativeArgs a; a.a = elements; a.f0 = lr; a.f1 = beta1; a.f2 = beta2; a.f3 = eps; a.f4 = weight_decay; a.f5 = c1; a.f6 = c2;
+    return native(rt, kOpAdam, {&param, &grad, &m, &v}, a);
 }
 }  // namespace motifcl

@@ -448,6 +448,14 @@ int mcl_cuda_counter_pack2(mcl_cuda_ctx* ctx, const uint8_t* state, uint32_t* pa
     return MCL_CUDA_OK;
 }
 
+// defined below, with the grouped step
+static bool fused_wanted(const mcl_cuda_ctx* ctx, const float* x, const float* grad_out, const void* ternary,
+                         const float* scale, const float* y, const float* grad_x, const float* grad_w, size_t I,
+                         size_t O, size_t Nt);
+static int fused_products(mcl_cuda_ctx* ctx, const char* op, const float* x, const float* grad_out,
+                          const uint8_t* state, const uint32_t* packed2, const float* scale, float* y,
+                          float* grad_x, float* grad_w, size_t C, size_t I, size_t O, size_t Nt);
+
 int mcl_cuda_counter_forward(mcl_cuda_ctx* ctx, const float* x, const uint8_t* state,
                              const float* scale, float* y, size_t batch, size_t in_features,
                              size_t out_features, size_t C) {
@@ -460,6 +468,10 @@ int mcl_cuda_counter_forward(mcl_cuda_ctx* ctx, const float* x, const uint8_t* s
     MCL_TRY(check_ptr(ctx, op, "scale", scale, 4));
     MCL_TRY(check_ptr(ctx, op, "y", y, 4));
     DeviceGuard guard(ctx->device);
+    // narrow layers: the tf32 hi/lo kernel reads x in place (no operand-splitting pass)
+    if (tc_wanted(ctx, batch, out_features, in_features) &&
+        fused_wanted(ctx, x, nullptr, state, scale, y, nullptr, nullptr, in_features, out_features, batch))
+        return fused_products(ctx, op, x, nullptr, state, nullptr, scale, y, nullptr, nullptr, C, in_features, out_features, batch);
     if (tc_wanted(ctx, batch, out_features, in_features)) {
         const int ta = ctx->act_terms, ldi = up8(in_features);
         int splits = 1;
@@ -498,6 +510,9 @@ int mcl_cuda_counter_backward_input(mcl_cuda_ctx* ctx, const uint8_t* state, con
     MCL_TRY(check_ptr(ctx, op, "grad_out", grad_out, 4));
     MCL_TRY(check_ptr(ctx, op, "grad_x", grad_x, 4));
     DeviceGuard guard(ctx->device);
+    if (tc_wanted(ctx, batch, in_features, out_features) &&
+        fused_wanted(ctx, nullptr, grad_out, state, scale, nullptr, grad_x, nullptr, in_features, out_features, batch))
+        return fused_products(ctx, op, nullptr, grad_out, state, nullptr, scale, nullptr, grad_x, nullptr, C, in_features, out_features, batch);
     if (tc_wanted(ctx, batch, in_features, out_features)) {
         const int ta = ctx->act_terms, ldo = up8(out_features);
         int splits = 1;
@@ -1269,6 +1284,88 @@ int mcl_cuda_gqa_backward(mcl_cuda_ctx* ctx, const float* q, const float* k, con
                                              (int)head_dim, causal ? 1 : 0, (int)query_offset, scale, ctx->stream, &launches);
     if (e != cudaSuccess) return fail_cuda(ctx, op, e);
     ctx->launches += launches;
+    return MCL_CUDA_OK;
+}
+
+int mcl_cuda_token_position_embedding(mcl_cuda_ctx* ctx, const float* token_weight, const float* pos_weight,
+                                      const int32_t* token_ids, float* out, size_t token_count, size_t vocab_size,
+                                      size_t seq_len, size_t embed_dim) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "token_position_embedding";
+    if (token_count == 0 || vocab_size == 0 || embed_dim == 0 || (pos_weight && seq_len == 0))
+        return fail(ctx, MCL_CUDA_EINVAL, "token_position_embedding requires non-zero shapes");
+    if (vocab_size > 0x7fffffffull || embed_dim > 0x7fffffffull || seq_len > 0x7fffffffull)
+        return fail(ctx, MCL_CUDA_EINVAL, "token_position_embedding dimension is too large");
+    MCL_TRY(check_ptr(ctx, op, "token_weight", token_weight, 4));
+    MCL_TRY(check_ptr(ctx, op, "token_ids", token_ids, 4));
+    MCL_TRY(check_ptr(ctx, op, "out", out, 4));
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, op, mcl::launch_embedding(token_weight, pos_weight, token_ids, out, token_count, (int)vocab_size,
+                                              (int)(seq_len ? seq_len : 1), (int)embed_dim, ctx->sm_count, ctx->stream));
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_embedding_weight_backward(mcl_cuda_ctx* ctx, const int32_t* indices, const float* grad_out, float* grad_weight,
+                                       size_t vocab_size, size_t embed_dim, size_t token_count, int zero_first) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "embedding weight backward";
+    if (vocab_size == 0 || embed_dim == 0) return fail(ctx, MCL_CUDA_EINVAL, "embedding weight backward requires non-zero shapes");
+    if (vocab_size > 0x7fffffffull || embed_dim > 0x7fffffffull)
+        return fail(ctx, MCL_CUDA_EINVAL, "embedding weight backward dimension is too large");
+    MCL_TRY(check_ptr(ctx, op, "grad_weight", grad_weight, 4));
+    DeviceGuard guard(ctx->device);
+    if (zero_first) {
+        cudaError_t e = cudaMemsetAsync(grad_weight, 0, vocab_size * embed_dim * sizeof(float), ctx->stream);
+        if (e != cudaSuccess) return fail_cuda(ctx, op, e);
+    }
+    if (token_count == 0) return MCL_CUDA_OK;
+    MCL_TRY(check_ptr(ctx, op, "indices", indices, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_out", grad_out, 4));
+    MCL_LAUNCH(ctx, op, mcl::launch_embedding_scatter(indices, grad_out, grad_weight, token_count, (int)vocab_size, (int)embed_dim,
+                                                      ctx->sm_count, ctx->stream));
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_position_embedding_backward(mcl_cuda_ctx* ctx, const float* grad_out, float* grad_position, size_t batch,
+                                         size_t seq_len, size_t embed_dim) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "position embedding backward";
+    if (batch == 0 || seq_len == 0 || embed_dim == 0 || batch > 0x7fffffffull || seq_len > 0x7fffffffull || embed_dim > 0x7fffffffull)
+        return fail(ctx, MCL_CUDA_EINVAL, "position embedding backward requires non-zero shapes below 2^31");
+    MCL_TRY(check_ptr(ctx, op, "grad_out", grad_out, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_position", grad_position, 4));
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, op, mcl::launch_position_backward(grad_out, grad_position, (int)batch, (int)seq_len, (int)embed_dim,
+                                                      ctx->sm_count, ctx->stream));
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_rope(mcl_cuda_ctx* ctx, const float* x, float* out, size_t batch, size_t tokens, size_t channels, size_t n_head,
+                  size_t head_dim, size_t rotary_dim, size_t token_offset, float theta, int inverse, int split_half) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "rope";
+    if (batch == 0 || tokens == 0 || channels == 0 || n_head == 0 || head_dim == 0)
+        return fail(ctx, MCL_CUDA_EINVAL, "rope requires non-zero shapes");
+    if (tokens > 0x7fffffffull || channels > 0x7fffffffull || token_offset > 0x3fffffffull || rotary_dim > head_dim)
+        return fail(ctx, MCL_CUDA_EINVAL, "rope dimension is out of range");
+    if (n_head * head_dim > channels) return fail(ctx, MCL_CUDA_EINVAL, "rope requires n_head * head_dim <= channels");
+    MCL_TRY(check_ptr(ctx, op, "x", x, 4));
+    MCL_TRY(check_ptr(ctx, op, "out", out, 4));
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, op, mcl::launch_rope(x, out, batch * tokens, (int)tokens, (int)channels, (int)n_head, (int)head_dim,
+                                         (int)rotary_dim, (int)token_offset, theta, inverse ? 1 : 0, split_half ? 1 : 0,
+                                         ctx->sm_count, ctx->stream));
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_adam_update(mcl_cuda_ctx* ctx, float* param, const float* grad, float* m, float* v, size_t elements, float lr,
+                         float beta1, float beta2, float eps, float weight_decay, float c1, float c2) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "adam_update";
+    if (elements == 0) return fail(ctx, MCL_CUDA_EINVAL, "adam_update requires non-zero elements");
+    MCL_TRY(check_ptr(ctx, op, "param", param, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad", grad, 4));
+    MCL_TRY(check_ptr(ctx, op, "m", m, 4));
+    MCL_TRY(check_ptr(ctx, op, "v", v, 4));
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, op, mcl::launch_adam(param, grad, m, v, elements, lr, beta1, beta2, eps, weight_decay, c1, c2, ctx->sm_count,
+                                         ctx->stream));
     return MCL_CUDA_OK;
 }
 

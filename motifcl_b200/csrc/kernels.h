@@ -143,6 +143,17 @@ cudaError_t launch_softmax_cross_entropy(const float* logits, const int* targets
 cudaError_t launch_softmax_cross_entropy_backward(const float* logits, const int* targets, const float* grad_out,
                                                   float* grad_logits, size_t rows, int cols, int sm_count,
                                                   cudaStream_t stream);
+cudaError_t launch_embedding(const float* token_weight, const float* pos_weight, const int* ids, float* out, size_t tokens,
+                             int vocab, int seq_len, int dim, int sm_count, cudaStream_t stream);
+cudaError_t launch_embedding_scatter(const int* ids, const float* grad_out, float* grad_weight, size_t tokens, int vocab, int dim,
+                                     int sm_count, cudaStream_t stream);
+cudaError_t launch_position_backward(const float* grad_out, float* grad_position, int batch, int seq_len, int dim, int sm_count,
+                                     cudaStream_t stream);
+cudaError_t launch_rope(const float* x, float* out, size_t rows, int tokens, int channels, int n_head, int head_dim,
+                        int rotary_dim, int token_offset, float theta, int inverse, int split_half, int sm_count,
+                        cudaStream_t stream);
+cudaError_t launch_adam(float* param, const float* grad, float* m, float* v, size_t n, float lr, float beta1, float beta2,
+                        float eps, float weight_decay, float c1, float c2, int sm_count, cudaStream_t stream);
 cudaError_t launch_gqa_forward(const float* q, const float* k, const float* v, float* out, int batch, int tq, int tk,
                                int key_stride, int n_head, int n_kv, int hd, int vhd, int causal, int q_off, int window,
                                float scale, float* scores_ws, cudaStream_t stream, int* launches);

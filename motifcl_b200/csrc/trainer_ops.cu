@@ -139,20 +139,53 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const float* __restrict
 }
 
 // ---- mean softmax cross-entropy --------------------------------------------------------------
-__global__ void __launch_bounds__(256) ce_rows_kernel(const float* __restrict__ logits, const int* __restrict__ targets,
-                                                      float* __restrict__ partial, size_t rows, int cols) {
+// A row of logits is read from HBM once: each of the 256 threads keeps its strided share (up to kCeHold values,
+// i.e. rows of up to 32768 classes; longer rows re-read the tail from memory) in registers for the max, sum
+// and gradient passes.
+constexpr int kCeHold = 128;
+
+template <bool BACKWARD>
+__global__ void __launch_bounds__(256) ce_kernel(const float* __restrict__ logits, const int* __restrict__ targets,
+                                                 float* __restrict__ partial, const float* __restrict__ grad_out,
+                                                 float* __restrict__ grad_logits, size_t rows, int cols) {
     __shared__ float red[32];
+    const float gscale = BACKWARD ? grad_out[0] / (float)rows : 0.0f;
     for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const float* l = logits + row * (size_t)cols;
+        float hold[kCeHold];
         float m = -FLT_MAX;
-        for (int c = threadIdx.x; c < cols; c += blockDim.x) m = fmaxf(m, l[c]);
+#pragma unroll
+        for (int j = 0; j < kCeHold; ++j) {
+            const int c = threadIdx.x + j * 256;
+            hold[j] = c < cols ? l[c] : -FLT_MAX;
+            m = fmaxf(m, hold[j]);
+        }
+        for (int c = threadIdx.x + kCeHold * 256; c < cols; c += 256) m = fmaxf(m, l[c]);
         m = block_max(m, red);
         float s = 0.0f;
-        for (int c = threadIdx.x; c < cols; c += blockDim.x) s += expf(l[c] - m);
+#pragma unroll
+        for (int j = 0; j < kCeHold; ++j) {
+            const int c = threadIdx.x + j * 256;
+            if (c < cols) {
+                hold[j] = expf(hold[j] - m);
+                s += hold[j];
+            }
+        }
+        for (int c = threadIdx.x + kCeHold * 256; c < cols; c += 256) s += expf(l[c] - m);
         s = block_sum(s, red);
-        if (threadIdx.x == 0) {
-            const int t = targets[row];
-            partial[row] = (t < 0 || t >= cols) ? 0.0f : logf(s) + m - l[t];
+        const int t = targets[row];
+        if (!BACKWARD) {
+            if (threadIdx.x == 0) partial[row] = (t < 0 || t >= cols) ? 0.0f : logf(s) + m - l[t];
+        } else {
+            const float inv = 1.0f / s;
+            float* g = grad_logits + row * (size_t)cols;
+#pragma unroll
+            for (int j = 0; j < kCeHold; ++j) {
+                const int c = threadIdx.x + j * 256;
+                if (c < cols) g[c] = gscale * (hold[j] * inv - (c == t ? 1.0f : 0.0f));
+            }
+            for (int c = threadIdx.x + kCeHold * 256; c < cols; c += 256)
+                g[c] = gscale * (expf(l[c] - m) * inv - (c == t ? 1.0f : 0.0f));
         }
     }
 }
@@ -164,27 +197,6 @@ __global__ void __launch_bounds__(256) mean_kernel(const float* __restrict__ in,
     s = block_sum(s, red);
     if (threadIdx.x == 0) out[0] = denom > 0 ? s / (float)denom : 0.0f;
 }
-__global__ void __launch_bounds__(256) ce_bwd_kernel(const float* __restrict__ logits, const int* __restrict__ targets,
-                                                     const float* __restrict__ grad_out, float* __restrict__ grad_logits,
-                                                     size_t rows, int cols) {
-    __shared__ float red[32];
-    const float scale = grad_out[0] / (float)rows;
-    for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
-        const float* l = logits + row * (size_t)cols;
-        float m = -FLT_MAX;
-        for (int c = threadIdx.x; c < cols; c += blockDim.x) m = fmaxf(m, l[c]);
-        m = block_max(m, red);
-        float s = 0.0f;
-        for (int c = threadIdx.x; c < cols; c += blockDim.x) s += expf(l[c] - m);
-        s = block_sum(s, red);
-        const float inv = 1.0f / s;
-        const int t = targets[row];
-        float* g = grad_logits + row * (size_t)cols;
-        for (int c = threadIdx.x; c < cols; c += blockDim.x)
-            g[c] = scale * (expf(l[c] - m) * inv - (c == t ? 1.0f : 0.0f));
-    }
-}
-
 // ---- batched grouped-query attention ---------------------------------------------------------
 // q [B*Tq, n_head*hd], k [B*key_stride, n_kv*hd], v [B*key_stride, n_kv*vhd], out [B*Tq, n_head*vhd].
 struct GqaDims {
@@ -223,8 +235,10 @@ struct BGemm {
 };                                   // 2 k (= key) ends at the tile's last query; 3 k (= query) starts at the tile's first key
 constexpr int kBT = 64, kBK = 16;
 
-__device__ __forceinline__ void load_tile(const BOperand& o, const float* zbase, int r0, int rmax, int k0, int kend,
-                                          float (*dst)[kBT + 4]) {
+// A 64 x 16 tile moves through registers (4 elements per thread) so that the next tile's global loads are in
+// flight while the current one is multiplied.
+__device__ __forceinline__ void fetch_tile(const BOperand& o, const float* zbase, int r0, int rmax, int k0, int kend,
+                                           float (&reg)[4]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int idx = threadIdx.x + i * 256;
@@ -236,7 +250,16 @@ __device__ __forceinline__ void load_tile(const BOperand& o, const float* zbase,
             const long long off = o.K0 > 0 ? (long long)(k / o.K0) * o.s1 + (long long)(k % o.K0) * o.s0 : (long long)k * o.s0;
             v = zbase[(long long)row * o.rs + off];
         }
-        dst[kk][r] = v;
+        reg[i] = v;
+    }
+}
+__device__ __forceinline__ void store_tile(const BOperand& o, const float (&reg)[4], float (*dst)[kBT + 4]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int idx = threadIdx.x + i * 256;
+        const int r = o.contig_k ? idx >> 4 : idx & 63;
+        const int kk = o.contig_k ? idx & 15 : idx >> 6;
+        dst[kk][r] = reg[i];
     }
 }
 
@@ -253,10 +276,17 @@ __global__ void __launch_bounds__(256) batched_gemm_kernel(BGemm g) {
     const float* zb = g.b.base + (long long)b * g.b.bs + (long long)(hz / g.b.hdiv) * g.b.hs;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     float acc[4][4] = {};
+    float ra[4], rb[4];
+    fetch_tile(g.a, za, m0, g.M, kbeg, kend, ra);
+    fetch_tile(g.b, zb, n0, g.N, kbeg, kend, rb);
     for (int k0 = kbeg; k0 < kend; k0 += kBK) {
-        load_tile(g.a, za, m0, g.M, k0, kend, As);
-        load_tile(g.b, zb, n0, g.N, k0, kend, Bs);
+        store_tile(g.a, ra, As);
+        store_tile(g.b, rb, Bs);
         __syncthreads();
+        if (k0 + kBK < kend) {
+            fetch_tile(g.a, za, m0, g.M, k0 + kBK, kend, ra);
+            fetch_tile(g.b, zb, n0, g.N, k0 + kBK, kend, rb);
+        }
 #pragma unroll
         for (int kk = 0; kk < kBK; ++kk) {
             const float4 av = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
@@ -324,6 +354,104 @@ cudaError_t run_bgemm(const BGemm& g, int batch, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
+// ---- embeddings, rope, adam (kernels/vulkan/token_position_embedding_f32_i32.comp, embedding_gather_f32_i32.comp,
+// embedding_weight_backward_f32_i32_scatter.comp, position_embedding_backward_f32_i32.comp, rope_f32.comp,
+// rope_split_half_f32.comp, adam_update_fast_f32.comp) ------------------------------------------------------------
+// out[t, d] = token_weight[ids[t], d] (0 for an id outside the table) + pos_weight[t % seq_len, d]; pos_weight may be
+// NULL (plain gather).
+__global__ void __launch_bounds__(256) embedding_kernel(const float* __restrict__ token_weight, const float* __restrict__ pos_weight,
+                                                        const int* __restrict__ ids, float* __restrict__ out, size_t tokens,
+                                                        int vocab, int seq_len, int dim) {
+    const size_t n = tokens * (size_t)dim;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / dim;
+        const int d = (int)(i - t * dim);
+        const int id = ids[t];
+        float v = (id >= 0 && id < vocab) ? token_weight[(size_t)id * dim + d] : 0.0f;
+        if (pos_weight != nullptr) v += pos_weight[(size_t)(t % seq_len) * dim + d];
+        out[i] = v;
+    }
+}
+// grad_weight[ids[t], d] += grad_out[t, d]; grad_weight is zeroed by the caller.
+__global__ void __launch_bounds__(256) embedding_scatter_kernel(const int* __restrict__ ids, const float* __restrict__ grad_out,
+                                                                float* __restrict__ grad_weight, size_t tokens, int vocab,
+                                                                int dim) {
+    const size_t n = tokens * (size_t)dim;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / dim;
+        const int id = ids[t];
+        if (id < 0 || id >= vocab) continue;
+        atomicAdd(grad_weight + (size_t)id * dim + (i - t * dim), grad_out[i]);
+    }
+}
+// grad_position[pos, d] = sum over the batch of grad_out[(b*seq_len + pos), d]
+__global__ void __launch_bounds__(256) position_backward_kernel(const float* __restrict__ grad_out, float* __restrict__ grad_position,
+                                                                int batch, int seq_len, int dim) {
+    const size_t n = (size_t)seq_len * dim;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float acc = 0.0f;
+        for (int b = 0; b < batch; ++b) acc += grad_out[(size_t)b * n + i];
+        grad_position[i] = acc;
+    }
+}
+// Rotary embedding on x [batch*tokens, channels] with n_head heads of head_dim at the front of each row; one thread
+// per rotated pair.  split_half pairs (i, i + head_dim/2), otherwise (2i, 2i+1).  inverse negates the angle.
+__global__ void __launch_bounds__(256) rope_kernel(const float* __restrict__ x, float* __restrict__ out, size_t rows, int tokens,
+                                                   int channels, int n_head, int head_dim, int rotary_dim, int token_offset,
+                                                   float theta, int inverse, int split_half) {
+    const size_t n = rows * (size_t)channels;
+    int rd = rotary_dim <= 0 ? head_dim : rotary_dim;
+    rd = rd < head_dim ? rd : head_dim;
+    rd -= rd & 1;
+    const int half = head_dim >> 1;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i / channels;
+        const int c = (int)(i - row * channels);
+        const int head = c / head_dim, d = c - head * head_dim;
+        if (head >= n_head) continue;                 // the shaders leave such channels unwritten
+        int pair, lo, hi;                             // pair index and the two channels it rotates
+        bool first;
+        if (split_half) {
+            if (half <= 0 || d >= half * 2) { out[i] = x[i]; continue; }
+            pair = d < half ? d : d - half;
+            if (pair >= (rd >> 1)) { out[i] = x[i]; continue; }
+            lo = pair; hi = half + pair; first = d < half;
+        } else {
+            if (d >= rd) { out[i] = x[i]; continue; }
+            pair = d >> 1;
+            lo = d & ~1; hi = lo + 1; first = d == lo;
+        }
+        const int token = (int)(row % tokens);
+        const float exponent = (float)(2 * pair) / (float)head_dim;
+        float angle = (float)(token_offset + token) / powf(theta, exponent);
+        if (inverse) angle = -angle;
+        float sn, cs;
+        sincosf(angle, &sn, &cs);
+        const size_t base = row * (size_t)channels + (size_t)head * head_dim;
+        const float a = x[base + lo], b = x[base + hi];
+        out[i] = first ? a * cs - b * sn : (split_half ? b * cs + a * sn : a * sn + b * cs);
+    }
+}
+__global__ void __launch_bounds__(256) adam_kernel(float* __restrict__ param, const float* __restrict__ grad, float* __restrict__ m,
+                                                   float* __restrict__ v, size_t n, float lr, float beta1, float beta2, float eps,
+                                                   float weight_decay, float c1, float c2) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float g = grad[i];
+        const float mn = beta1 * m[i] + (1.0f - beta1) * g;
+        const float vn = beta2 * v[i] + (1.0f - beta2) * g * g;
+        m[i] = mn;
+        v[i] = vn;
+        const float pv = param[i];
+        param[i] = pv - lr * (mn * c1 / (sqrtf(vn * c2) + eps) + weight_decay * pv);
+    }
+}
+
+int flat_grid(size_t n, int sm_count) {
+    size_t blocks = (n + 255) / 256;
+    const size_t cap = (size_t)sm_count * 16;
+    return (int)(blocks < cap ? (blocks ? blocks : 1) : cap);
+}
+
 int row_grid(size_t rows, int sm_count) {
     const size_t cap = (size_t)sm_count * 16;
     return (int)(rows < cap ? rows : cap);
@@ -374,7 +502,7 @@ cudaError_t launch_swiglu_backward(const float* packed, const float* dy, float* 
 }
 cudaError_t launch_softmax_cross_entropy(const float* logits, const int* targets, float* partial, float* out, size_t rows,
                                          int cols, int sm_count, cudaStream_t stream) {
-    ce_rows_kernel<<<row_grid(rows, sm_count), 256, 0, stream>>>(logits, targets, partial, rows, cols);
+    ce_kernel<false><<<row_grid(rows, sm_count), 256, 0, stream>>>(logits, targets, partial, nullptr, nullptr, rows, cols);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     mean_kernel<<<1, 256, 0, stream>>>(partial, out, rows, rows);
@@ -383,7 +511,39 @@ cudaError_t launch_softmax_cross_entropy(const float* logits, const int* targets
 cudaError_t launch_softmax_cross_entropy_backward(const float* logits, const int* targets, const float* grad_out,
                                                   float* grad_logits, size_t rows, int cols, int sm_count,
                                                   cudaStream_t stream) {
-    ce_bwd_kernel<<<row_grid(rows, sm_count), 256, 0, stream>>>(logits, targets, grad_out, grad_logits, rows, cols);
+    ce_kernel<true><<<row_grid(rows, sm_count), 256, 0, stream>>>(logits, targets, nullptr, grad_out, grad_logits, rows, cols);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_embedding(const float* token_weight, const float* pos_weight, const int* ids, float* out, size_t tokens,
+                             int vocab, int seq_len, int dim, int sm_count, cudaStream_t stream) {
+    embedding_kernel<<<flat_grid(tokens * (size_t)dim, sm_count), 256, 0, stream>>>(token_weight, pos_weight, ids, out, tokens,
+                                                                                    vocab, seq_len, dim);
+    return cudaGetLastError();
+}
+cudaError_t launch_embedding_scatter(const int* ids, const float* grad_out, float* grad_weight, size_t tokens, int vocab, int dim,
+                                     int sm_count, cudaStream_t stream) {
+    embedding_scatter_kernel<<<flat_grid(tokens * (size_t)dim, sm_count), 256, 0, stream>>>(ids, grad_out, grad_weight, tokens,
+                                                                                            vocab, dim);
+    return cudaGetLastError();
+}
+cudaError_t launch_position_backward(const float* grad_out, float* grad_position, int batch, int seq_len, int dim, int sm_count,
+                                     cudaStream_t stream) {
+    position_backward_kernel<<<flat_grid((size_t)seq_len * dim, sm_count), 256, 0, stream>>>(grad_out, grad_position, batch,
+                                                                                             seq_len, dim);
+    return cudaGetLastError();
+}
+cudaError_t launch_rope(const float* x, float* out, size_t rows, int tokens, int channels, int n_head, int head_dim,
+                        int rotary_dim, int token_offset, float theta, int inverse, int split_half, int sm_count,
+                        cudaStream_t stream) {
+    rope_kernel<<<flat_grid(rows * (size_t)channels, sm_count), 256, 0, stream>>>(x, out, rows, tokens, channels, n_head, head_dim,
+                                                                                  rotary_dim, token_offset, theta, inverse,
+                                                                                  split_half);
+    return cudaGetLastError();
+}
+cudaError_t launch_adam(float* param, const float* grad, float* m, float* v, size_t n, float lr, float beta1, float beta2,
+                        float eps, float weight_decay, float c1, float c2, int sm_count, cudaStream_t stream) {
+    adam_kernel<<<flat_grid(n, sm_count), 256, 0, stream>>>(param, grad, m, v, n, lr, beta1, beta2, eps, weight_decay, c1, c2);
     return cudaGetLastError();
 }
 

@@ -237,6 +237,29 @@ class Context:
         self._check(self._lib.mcl_cuda_softmax_cross_entropy_backward(self._ctx, _ptr(logits), _ptr(targets),
                                                                       _ptr(grad_out), _ptr(grad_logits), rows, cols))
 
+    def token_position_embedding(self, token_weight, pos_weight, token_ids, out, token_count, vocab, seq_len, dim):
+        self._check(self._lib.mcl_cuda_token_position_embedding(
+            self._ctx, _ptr(token_weight), _ptr(pos_weight) if pos_weight is not None else None, _ptr(token_ids),
+            _ptr(out), token_count, vocab, seq_len, dim))
+
+    def embedding_weight_backward(self, indices, grad_out, grad_weight, vocab, dim, token_count, zero_first=True):
+        self._check(self._lib.mcl_cuda_embedding_weight_backward(self._ctx, _ptr(indices), _ptr(grad_out),
+                                                                 _ptr(grad_weight), vocab, dim, token_count,
+                                                                 int(zero_first)))
+
+    def position_embedding_backward(self, grad_out, grad_position, batch, seq_len, dim):
+        self._check(self._lib.mcl_cuda_position_embedding_backward(self._ctx, _ptr(grad_out), _ptr(grad_position),
+                                                                   batch, seq_len, dim))
+
+    def rope(self, x, out, batch, tokens, channels, n_head, head_dim, rotary_dim=0, token_offset=0, theta=10000.0,
+             inverse=False, split_half=False):
+        self._check(self._lib.mcl_cuda_rope(self._ctx, _ptr(x), _ptr(out), batch, tokens, channels, n_head, head_dim,
+                                            rotary_dim, token_offset, theta, int(inverse), int(split_half)))
+
+    def adam_update(self, param, grad, m, v, elements, lr, beta1, beta2, eps, weight_decay, c1, c2):
+        self._check(self._lib.mcl_cuda_adam_update(self._ctx, _ptr(param), _ptr(grad), _ptr(m), _ptr(v), elements, lr,
+                                                   beta1, beta2, eps, weight_decay, c1, c2))
+
     def gqa_forward(self, q, k, v, out, batch, tq, tk, key_stride, n_head, n_kv_head, head_dim, v_head_dim,
                     causal, query_offset, sliding_window, scale):
         self._check(self._lib.mcl_cuda_gqa_forward(self._ctx, _ptr(q), _ptr(k), _ptr(v), _ptr(out), batch, tq, tk,

@@ -3,6 +3,7 @@ the CUDA runtime adapter (motifcl_b200/adapter) instead of MotifCL's Vulkan runt
 built where the MotifCL tree is mounted (motifcl_b200/adapter/Makefile) and travel prebuilt; where
 they are absent the tests skip.  Exit code 77 is MotifCL's "skip" convention."""
 import os
+import re
 import subprocess
 
 import pytest
@@ -42,3 +43,43 @@ def test_reference_binary_passes_on_the_cuda_backend(name):
     r = _run(name)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "PASS" in r.stdout and "FAIL" not in r.stdout
+
+
+def _run_env(name, env, timeout=600):
+    path = os.path.join(BUILD, name)
+    if not os.path.isfile(path):
+        pytest.skip(f"{name} was not built on this machine (needs the MotifCL tree)")
+    e = dict(os.environ)
+    e.update({k: str(v) for k, v in env.items()})
+    return subprocess.run([path], capture_output=True, text=True, timeout=timeout, env=e)
+
+
+@pytest.mark.gpu
+def test_reference_block_stack_bench_runs_on_the_cuda_backend():
+    """tests/bench_ternary15m.cpp, MotifCL's own harness for its tok/s figure: the 6-block ternary15m
+    stack (36 counter layers, rmsnorm, attention, swiglu, 32k-vocab head, cross-entropy), forward +
+    backward + counter updates + sgd.  It exits non-zero on a failed op or a non-finite loss; the loss
+    of the last step must be below the first one's."""
+    r = _run_env("bench_ternary15m", {"BENCH_BATCHED": 1, "BENCH_B": 4, "BENCH_STEPS": 10})
+    assert r.returncode == 0, r.stdout + r.stderr
+    losses = [float(line.rsplit("loss", 1)[1]) for line in r.stdout.splitlines() if " loss " in line]
+    assert len(losses) == 2 and losses[1] < losses[0], r.stdout
+    assert "tok/s=" in r.stdout
+
+
+@pytest.mark.gpu
+def test_reference_trainer_learns_synthetic_records(tmp_path):
+    """tools/train_ternary15m.cpp unchanged, on seeded synthetic records with a learnable next-token rule
+    (90 % of transitions follow next = (31*cur + 7) mod 512): embedding, rope, causal attention, adam and the
+    counter updates all have to work for the logged loss to fall well below ln(32000) = 10.37."""
+    import sys
+    sys.path.insert(0, os.path.join(ROOT, "motifcl_b200", "adapter"))
+    import make_synthetic_records as msr
+    data = tmp_path / "data"
+    msr.write_dataset(str(data), seq=64, train_records=512, val_records=32, seed=7)
+    r = _run_env("train_ternary15m", {"DATA_DIR": data, "OUT_DIR": tmp_path / "out", "STEPS": 120, "BATCH": 8, "SEQ": 64,
+                                      "LOG_EVERY": 20, "EVAL_EVERY": 1000, "CKPT_EVERY": 1000, "RESUME": 0})
+    assert r.returncode == 0, r.stdout + r.stderr
+    losses = [float(m.group(1)) for m in re.finditer(r"^step \d+ loss ([0-9.]+)", r.stdout, flags=re.M)]
+    assert len(losses) >= 5, r.stdout
+    assert losses[-1] < 8.0 and losses[-1] < losses[0] - 1.5, r.stdout

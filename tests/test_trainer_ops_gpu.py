@@ -189,3 +189,92 @@ def test_sgd_step_and_argument_checks(ctx):
         ctx.gqa_forward(x, x, x, x, 1, 1, 1, 1, 3, 2, 1, 1, False, 0, 0, 1.0)
     with pytest.raises(RuntimeError, match="key_stride"):
         ctx.gqa_forward(x, x, x, x, 1, 1, 4, 2, 1, 1, 1, 1, False, 0, 0, 1.0)
+
+
+def test_embedding_forward_and_backward(ctx):
+    B, T, V, D = 3, 10, 50, 24
+    g = torch.Generator().manual_seed(11)
+    tw = torch.randn(V, D, generator=g, dtype=torch.float64)
+    pw = torch.randn(T + 4, D, generator=g, dtype=torch.float64)       # a position table longer than the sequence
+    ids = torch.randint(0, V, (B * T,), generator=g, dtype=torch.int32)
+    ids[3] = -1                                                        # outside the table: token part is zero
+    ids[4] = V
+    ok = (ids >= 0) & (ids < V)
+    tok = torch.where(ok.view(-1, 1), tw[ids.clamp(0, V - 1).long()], torch.zeros(1, D, dtype=torch.float64))
+    ref = tok + pw[torch.arange(B * T) % T]
+    out = torch.empty(B * T, D, device="cuda")
+    ctx.token_position_embedding(dev(tw), dev(pw), ids.cuda(), out, B * T, V, T, D)
+    gather = torch.empty(B * T, D, device="cuda")
+    ctx.token_position_embedding(dev(tw), None, ids.cuda(), gather, B * T, V, 1, D)
+    torch.cuda.synchronize()
+    assert rel_l2(out, ref) <= TOL
+    assert rel_l2(gather, tok) <= TOL
+
+    go = torch.randn(B * T, D, generator=g, dtype=torch.float64)
+    ref_gw = torch.zeros(V, D, dtype=torch.float64)
+    ref_gw.index_add_(0, ids[ok].long(), go[ok])
+    gw = torch.full((V, D), 9.0, device="cuda")
+    ctx.embedding_weight_backward(ids.cuda(), dev(go), gw, V, D, B * T, zero_first=True)
+    acc = torch.ones(V, D, device="cuda")
+    ctx.embedding_weight_backward(ids.cuda(), dev(go), acc, V, D, B * T, zero_first=False)
+    gp = torch.empty(T, D, device="cuda")
+    ctx.position_embedding_backward(dev(go), gp, B, T, D)
+    torch.cuda.synchronize()
+    assert rel_l2(gw, ref_gw) <= TOL
+    assert rel_l2(acc, ref_gw + 1.0) <= TOL
+    assert rel_l2(gp, go.view(B, T, D).sum(0)) <= TOL
+
+
+def _rope_reference(x, B, T, H, hd, rd, off, theta, inverse, split_half):
+    x = x.view(B, T, -1).clone()
+    out = x.clone()
+    rd = hd if rd <= 0 else min(rd, hd)
+    rd -= rd & 1
+    half = hd // 2
+    pos = (torch.arange(T, dtype=torch.float64) + off).view(1, T)
+    for h in range(H):
+        for pair in range(rd // 2):
+            lo, hi = (pair, half + pair) if split_half else (2 * pair, 2 * pair + 1)
+            ang = pos / theta ** (2 * pair / hd)
+            if inverse:
+                ang = -ang
+            a, b = x[:, :, h * hd + lo], x[:, :, h * hd + hi]
+            out[:, :, h * hd + lo] = a * torch.cos(ang) - b * torch.sin(ang)
+            out[:, :, h * hd + hi] = a * torch.sin(ang) + b * torch.cos(ang)
+    return out.view(B * T, -1)
+
+
+@pytest.mark.parametrize("split_half", [False, True])
+@pytest.mark.parametrize("rd,off", [(0, 0), (8, 5)])
+def test_rope_forward_and_inverse(ctx, split_half, rd, off):
+    B, T, H, hd = 2, 9, 3, 16
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(B * T, H * hd, generator=g, dtype=torch.float64)
+    ref = _rope_reference(x, B, T, H, hd, rd, off, 10000.0, False, split_half)
+    xd = dev(x)
+    y = torch.empty_like(xd)
+    ctx.rope(xd, y, B, T, H * hd, H, hd, rd, off, 10000.0, False, split_half)
+    back = torch.empty_like(xd)
+    ctx.rope(y, back, B, T, H * hd, H, hd, rd, off, 10000.0, True, split_half)
+    torch.cuda.synchronize()
+    # angles reach ~13 rad and are formed in fp32 (position / theta^e), as in the shader
+    assert rel_l2(y, ref) <= 5e-6
+    assert rel_l2(back, x) <= 5e-6
+
+
+def test_adam_update(ctx):
+    n = 5000
+    g = torch.Generator().manual_seed(1)
+    p = torch.randn(n, generator=g, dtype=torch.float64)
+    gr = torch.randn(n, generator=g, dtype=torch.float64)
+    m = torch.randn(n, generator=g, dtype=torch.float64) * 0.1
+    v = torch.rand(n, generator=g, dtype=torch.float64) * 0.01
+    lr, b1, b2, eps, wd, step = 6e-3, 0.9, 0.95, 1e-8, 0.1, 3
+    c1, c2 = 1 / (1 - b1 ** step), 1 / (1 - b2 ** step)
+    mn = b1 * m + (1 - b1) * gr
+    vn = b2 * v + (1 - b2) * gr * gr
+    ref = p - lr * (mn * c1 / (torch.sqrt(vn * c2) + eps) + wd * p)
+    pd, md, vd = dev(p), dev(m), dev(v)
+    ctx.adam_update(pd, dev(gr), md, vd, n, lr, b1, b2, eps, wd, c1, c2)
+    torch.cuda.synchronize()
+    assert rel_l2(pd, ref) <= TOL and rel_l2(md, mn) <= TOL and rel_l2(vd, vn) <= TOL

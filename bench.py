@@ -371,6 +371,45 @@ def run_refperf(args):
                       "methodology": "median wall time of 50 runs after 5 warm-ups, dispatch + wait", "rows": rows}))
 
 
+def run_trainer15m(args):
+    """--micro trainer15m[:BATCH[:STEPS]]  runs MotifCL's OWN harnesses for its headline tokens/s, compiled unmodified
+    against the CUDA adapter (motifcl_b200/adapter/Makefile): tests/bench_ternary15m.cpp (the 6-block ternary15m stack,
+    forward + backward + counter updates + sgd, one submit per step) and tools/train_ternary15m.cpp (the trainer itself,
+    on seeded synthetic records: the tokenised corpus of the published run is in neither tree).  BATCH x 256 tokens per
+    step; MotifCL's published run is BATCH = 16 on a Radeon RX 580 (docs/TERNARY15M_PRETRAIN_RESULTS.md:3,24-26)."""
+    import re
+    import subprocess
+    import tempfile
+    build = os.path.join(ROOT, "motifcl_b200", "adapter", "_build")
+    parts = args.micro.split(":")
+    batch = int(parts[1]) if len(parts) > 1 else 16
+    steps = int(parts[2]) if len(parts) > 2 else 100
+    rec = {"micro": "trainer15m", "batch": batch, "seq": 256, "tokens_per_step": batch * 256, "data": "synthetic",
+           "published_rx580_tokens_per_s": 4152}
+    if not os.path.isfile(os.path.join(build, "bench_ternary15m")):
+        rec["unavailable"] = "adapter binaries are not built (make -C motifcl_b200/adapter needs the MotifCL tree)"
+        print(json.dumps(rec))
+        return
+    env = dict(os.environ, BENCH_BATCHED="1", BENCH_B=str(batch), BENCH_STEPS=str(steps))
+    r = subprocess.run([os.path.join(build, "bench_ternary15m")], capture_output=True, text=True, timeout=900, env=env)
+    m = re.search(r"ms/step=([0-9.]+)\s+tokens/step=(\d+)\s+tok/s=([0-9.e+]+)", r.stdout)
+    rec["bench_ternary15m"] = ({"ms_per_step": float(m.group(1)), "tokens_per_s": float(m.group(3))} if r.returncode == 0 and m
+                               else {"returncode": r.returncode, "stderr": r.stderr[-300:]})
+    sys.path.insert(0, os.path.join(ROOT, "motifcl_b200", "adapter"))
+    import make_synthetic_records as msr
+    with tempfile.TemporaryDirectory() as tmp:
+        msr.write_dataset(os.path.join(tmp, "data"), seq=256, train_records=4096, val_records=96, seed=1)
+        env = dict(os.environ, DATA_DIR=os.path.join(tmp, "data"), OUT_DIR=os.path.join(tmp, "out"), STEPS=str(2 * steps),
+                   BATCH=str(batch), SEQ="256", LOG_EVERY=str(steps), EVAL_EVERY="1000000", CKPT_EVERY="1000000", RESUME="0")
+        r = subprocess.run([os.path.join(build, "train_ternary15m")], capture_output=True, text=True, timeout=900, env=env)
+    logs = re.findall(r"^step (\d+) loss ([0-9.]+) .*?([0-9]+) tok/s", r.stdout, flags=re.M)
+    # the second window is free of first-step allocations
+    rec["train_ternary15m"] = ({"tokens_per_s": float(logs[-1][2]), "loss_first_window": float(logs[0][1]),
+                                "loss_last_window": float(logs[-1][1]), "steps": int(logs[-1][0])}
+                               if r.returncode == 0 and logs else {"returncode": r.returncode, "stderr": r.stderr[-300:]})
+    print(json.dumps(rec))
+
+
 def run_gemv_tp(args):
     """--micro gemvtp:M[:LAYERS]  the decode-GEMV sweep with the weights sharded over the ranks of the job
     (q, w1, w3 split by output features; o, w2 split by input features + one all-reduce each): what a
@@ -487,6 +526,8 @@ def main():
         return run_gemv_tp(args)
     if args.micro == "refperf":
         return run_refperf(args)
+    if args.micro.startswith("trainer15m"):
+        return run_trainer15m(args)
     if args.micro:
         return run_micro(args)
     wl = workload(args.workload)

@@ -526,7 +526,7 @@ def main():
         return run_gemv_tp(args)
     if args.micro == "refperf":
         return run_refperf(args)
-    if args.micro.startswith("trainer15m"):
+    if args.micro and args.micro.startswith("trainer15m"):
         return run_trainer15m(args)
     if args.micro:
         return run_micro(args)

@@ -26,16 +26,20 @@
 // operand has; the tensor core reads it in place (instruction-descriptor transpose bits), so no
 // transposed copy of an activation is ever made.
 //
-// CTA = 16 warps.  Shared memory holds two rings of 32-deep k-tiles: the RAW ring (2 to 6 slots: A and B
-// as TMA delivers them; deep, because it has to cover the latency of HBM) and the LO ring (2 slots:
-// the lo tiles, which only bridge converter and MMA).
+// CTA = 16 warps.  The A operand of every product is read from TENSOR MEMORY: converter threads own one
+// row of the A tile each (= one TMEM lane), read its 32 k from the raw tile in shared memory and store the
+// raw words (`hi`, scaled by scale[k] for dX) and the lo terms into 64 TMEM columns (tcgen05.st).  A
+// transposed A (dW) is read column-wise from the MN-major boxes, so the transpose costs nothing.  Shared
+// memory holds the RAW ring (2 to 6 slots: A and B as TMA delivers them; deep, because it has to cover
+// the latency of HBM) and, for dW only, a ring of B lo tiles.  Three tiles are in flight between the
+// converters and the MMA lane (three A slots in TMEM, three B lo slots).
 //   warp 0        one lane draws work items from a global counter and issues the TMA copies
-//   warp 1        allocates TMEM; one lane issues tcgen05.mma and commits
-//   warp 2        one lane asks the tiles of the next work item into L2 (TMA prefetch), a few tiles ahead
+//   warp 1        allocates TMEM; one lane issues tcgen05.mma (A from TMEM, B from shared memory) and commits
+//   warp 2        one lane asks the tiles of the next work item into L2 (TMA prefetch; off by default)
 //   warps 4..7    epilogue: tcgen05.ld of TMEM lane quarter (warp & 3), scale, 128-bit stores
-//   warps 8..15   converters: wait for the boxes, write the `lo` tiles (and the scaled `hi` tile
-//                 for dX), fence to the async proxy, arrive
-// Two accumulators in TMEM let the epilogue of one item overlap the main loop of the next.
+//   warps 8..15   converters: two groups of four warps take the k-tiles alternately
+// TMEM columns: two accumulators of at most 160 columns at 0 and 160 (the epilogue of one item overlaps the
+// main loop of the next), A slots of 64 columns at 320, 384, 448.
 // Every wait is bounded (see mbar_wait); on time-out the kernel records an error word and drains.
 #include <cuda.h>
 #include <cstdio>
@@ -55,12 +59,13 @@ constexpr int kConvThreads = 8 * 32;
 constexpr int kBox = 32 * 32 * 4;            // bytes of one 32 x 32 fp32 box
 constexpr int kABytes = 4 * kBox;            // an A tile: 128 rows (or 128 m) x 32 k
 constexpr int kMaxRaw = 6;                   // slots of the raw ring (A hi + B hi as TMA delivers them)
-constexpr int kLoSlots = 2;                  // slots of the lo ring (A lo, and B lo for two fp32 operands)
+constexpr int kLoSlots = 3;                  // tiles between converters and MMA: A (hi, lo) in tensor memory, B lo (dW) in shared memory
 constexpr int kQueue = 4;                    // work items in flight between the scheduler lane and the other roles
 constexpr int kQueueReaders = 1 + 1 + 4 + 8; // MMA lane, prefetch lane, epilogue warps, converter warps
 constexpr int kPrefetchAhead = 12;           // k-tiles the prefetch lane may run ahead of the copies
 constexpr int kScratch = 4 * 4096;           // epilogue staging, 4 KiB per warp
-constexpr int kAccStride = 256;              // TMEM columns between the two accumulators
+constexpr int kAccStride = 160;              // TMEM columns between the two accumulators (an accumulator is at most 160 wide)
+constexpr int kACol = 320;                   // the A tiles follow the accumulators: 64 columns each (hi, lo)
 
 template <int CAP>
 struct FusedTable {
@@ -77,17 +82,23 @@ __device__ __forceinline__ uint32_t idesc_tf32(int m, int n, bool a_mn, bool b_m
     return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
-// Shared-memory layouts.  K-major: rows of 128 bytes (32 fp32 of k) in the 128-byte swizzle, 8-row
+// Shared-memory layouts (B operand; the raw A tiles use the same ones).  K-major: rows of 128 bytes (32 fp32 of k) in the 128-byte swizzle, 8-row
 // groups 1024 bytes apart (stride byte offset).  MN-major: rows of 128 bytes hold 32 consecutive m (or
 // n) for one k, in the 128-byte swizzle with 32-byte atoms (the form the tensor core can transpose
 // 32-bit data from): 4 k-rows per 512 bytes (stride byte offset), the next 32 m one box = 4096 bytes
 // further (leading byte offset).
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accum) {
+// tf32 MMA with the A operand in tensor memory: row m of the tile = TMEM lane m, one tf32 per 32-bit column
+__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_c, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accum) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_c), "l"(da), "l"(db), "r"(idesc), "r"(accum) : "memory");
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_c), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accum) : "memory");
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
 }
 
 struct Item {
@@ -147,7 +158,7 @@ template <int CAP>
 __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_constant__ FusedTable<CAP> tab, int* err,
                                                                 int* next_item) {
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2 * kMaxRaw + 4 + 4 + 2 * kQueue];
+    __shared__ __align__(8) uint64_t bars[2 * kMaxRaw + 2 * kLoSlots + 4 + 2 * kQueue];
     __shared__ int queue_item[kQueue], queue_next[kQueue];
     __shared__ unsigned int tiles_issued;      // progress of the TMA lane, paces the prefetch lane
     __shared__ FusedProblem sp[CAP];
@@ -167,17 +178,18 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
     auto raw_full = [&](int s) { return bar0 + 8u * s; };
     auto raw_empty = [&](int s) { return bar0 + 8u * (kMaxRaw + s); };
     auto lo_full = [&](int s) { return bar0 + 8u * (2 * kMaxRaw + s); };
-    auto lo_empty = [&](int s) { return bar0 + 8u * (2 * kMaxRaw + 2 + s); };
-    auto acc_full = [&](int a) { return bar0 + 8u * (2 * kMaxRaw + 4 + a); };
-    auto acc_empty = [&](int a) { return bar0 + 8u * (2 * kMaxRaw + 6 + a); };
-    auto q_full = [&](int s) { return bar0 + 8u * (2 * kMaxRaw + 8 + s); };
-    auto q_empty = [&](int s) { return bar0 + 8u * (2 * kMaxRaw + 8 + kQueue + s); };
+    auto lo_empty = [&](int s) { return bar0 + 8u * (2 * kMaxRaw + kLoSlots + s); };
+    auto acc_full = [&](int a) { return bar0 + 8u * (2 * kMaxRaw + 2 * kLoSlots + a); };
+    auto acc_empty = [&](int a) { return bar0 + 8u * (2 * kMaxRaw + 2 * kLoSlots + 2 + a); };
+    auto a_col = [](int sl) -> uint32_t { return (uint32_t)(kACol + 64 * sl); };   // TMEM columns of A slot sl
+    auto q_full = [&](int s) { return bar0 + 8u * (2 * kMaxRaw + 2 * kLoSlots + 4 + s); };
+    auto q_empty = [&](int s) { return bar0 + 8u * (2 * kMaxRaw + 2 * kLoSlots + 4 + kQueue + s); };
 
     if (threadIdx.x == 0) {
         abort_flag = (*reinterpret_cast<volatile int*>(err) != 0);
         tiles_issued = 0;
         for (int s = 0; s < kMaxRaw; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), 1); }
-        for (int s = 0; s < kLoSlots; ++s) { mbar_init(lo_full(s), kConvThreads); mbar_init(lo_empty(s), 1); }
+        for (int s = 0; s < kLoSlots; ++s) { mbar_init(lo_full(s), kConvThreads / 2); mbar_init(lo_empty(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 128); }
         for (int s = 0; s < kQueue; ++s) { mbar_init(q_full(s), 1); mbar_init(q_empty(s), kQueueReaders); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -269,13 +281,25 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
 #ifdef MCL_FUSED_PROF
                     t_issue[s] = clock64();
 #endif
+#ifdef MCL_FUSED_PROF
+                    const bool skip_a = tab.pad0 & 32, skip_b = tab.pad0 & 8;
+                    mbar_expect_tx(raw_full(s), (skip_a ? 0u : (uint32_t)kABytes) + (skip_b ? 0u : (uint32_t)P.BN * 128u));
+                    if (!skip_a) {
+                        if (mode == kFusedDW) tma_load_3d(st, ma, raw_full(s), 0, k0, m0 >> 5);
+                        else tma_load_2d(st, ma, raw_full(s), k0, m0);
+                    }
+                    if (!skip_b) {
+                        if (mode == kFusedY) tma_load_2d(st + kABytes, mb, raw_full(s), k0, n0);
+                        else tma_load_3d(st + kABytes, mb, raw_full(s), 0, k0, n0 >> 5);
+                    }
+#else
                     mbar_expect_tx(raw_full(s), bytes);
-                    // K-major: one box of 32 k x rows; MN-major: one box of 32 m x 32 k x chunks (3-D map)
                     // K-major: one box of 32 k x rows; MN-major: one box of 32 m x 32 k x chunks (3-D map)
                     if (mode == kFusedDW) tma_load_3d(st, ma, raw_full(s), 0, k0, m0 >> 5);
                     else tma_load_2d(st, ma, raw_full(s), k0, m0);
                     if (mode == kFusedY) tma_load_2d(st + kABytes, mb, raw_full(s), k0, n0);
                     else tma_load_3d(st + kABytes, mb, raw_full(s), 0, k0, n0 >> 5);
+#endif
                     *reinterpret_cast<volatile unsigned int*>(&tiles_issued) = it + 1;
                     PROF_T(t2); PROF_ADD(pf_issue, t1, t2);
                 }
@@ -296,7 +320,7 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- MMA issuer ------------------------------------------------------------------------
-            uint32_t it = 0, n_local = 0, rs = 0, rph = 0;
+            uint32_t it = 0, n_local = 0, rs = 0;
             int pi = 0;
             long long pf_acc = 0, pf_full = 0, pf_issue = 0; (void)pf_acc; (void)pf_full; (void)pf_issue;
             PROF_T(tstart);
@@ -313,21 +337,14 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 if (item >= n_items || abort_flag) break;
                 const Item I = decode_item(sp, n_problems, item, pi);
                 const FusedProblem& P = sp[I.pi];
-                const bool a_mn = P.mode == kFusedDW, b_mn = P.mode != kFusedY;
-                const uint32_t idesc = idesc_tf32(128, P.BN, a_mn, b_mn);
-                // descriptor words: low = address / 16 | leading byte offset / 16 << 16, high = stride byte offset / 16 |
+                const bool b_mn = P.mode != kFusedY;
+                const uint32_t idesc = idesc_tf32(128, P.BN, false, b_mn);
+                // B descriptor words: low = address / 16 | leading byte offset / 16 << 16, high = stride byte offset / 16 |
                 // version bit | layout type << 29 (1 = 128-byte swizzle with 32-byte atoms, 2 = 128-byte swizzle)
-                const uint32_t a_step = a_mn ? 64u : 2u, b_step = b_mn ? 64u : 2u;          // 16-byte units per 8 k
-                const uint32_t a_lo = a_mn ? ((uint32_t)(kBox >> 4) << 16) : (1u << 16);
+                const uint32_t b_step = b_mn ? 64u : 2u;                                    // 16-byte units per 8 k
                 const uint32_t b_lo = b_mn ? ((uint32_t)(kBox >> 4) << 16) : (1u << 16);
-                const uint32_t a_hi = a_mn ? ((512u >> 4) | (1u << 14) | (1u << 29)) : ((1024u >> 4) | (1u << 14) | (2u << 29));
                 const uint32_t b_hi = b_mn ? ((512u >> 4) | (1u << 14) | (1u << 29)) : ((1024u >> 4) | (1u << 14) | (2u << 29));
                 const uint32_t nprod = (uint32_t)P.nprod, prod0 = P.prod;
-                #ifdef MCL_FUSED_PROF
-                const bool early = (tab.pad0 & 16) && P.mode != kFusedDX;
-#else
-                const bool early = false;                   // hi.hi before the converters finish: measured slower overall
-#endif
                 const uint32_t acc = n_local & 1u, aph = (n_local >> 1) & 1u;
                 PROF_T(ta0);
                 if (!mbar_wait(acc_empty(acc), aph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 14); break; }
@@ -337,45 +354,32 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 uint32_t accum = 0;
                 for (int j = 0; j < I.nkt; ++j, ++it) {
                     const int s = (int)rs, sl = (int)(it % kLoSlots);
-                    const uint32_t ph = rph;
-                    if (++rs == (uint32_t)n_raw) { rs = 0; rph ^= 1u; }
-                    const uint32_t hi16 = (raw0 + (uint32_t)s * raw_slot) >> 4, lo16 = (lo0 + (uint32_t)sl * lo_slot) >> 4;
-                    uint32_t prod = prod0;
-                    auto issue = [&](uint32_t pr) {
-                        const uint32_t a16 = a_lo | ((pr & 3u) ? lo16 : hi16);
-                        const uint32_t b16 = b_lo | ((((pr >> 2) & 3u) ? lo16 : hi16) + (kABytes >> 4));
-#pragma unroll
-                        for (uint32_t kk = 0; kk < 4; ++kk) {
-                            const uint64_t da = ((uint64_t)a_hi << 32) | (uint64_t)(a16 + kk * a_step);
-                            const uint64_t db = ((uint64_t)b_hi << 32) | (uint64_t)(b16 + kk * b_step);
-                            umma_tf32(d_tmem, da, db, idesc, accum);
-                            accum = 1u;
-                        }
-                    };
+                    if (++rs == (uint32_t)n_raw) rs = 0;
+                    const uint32_t hi16 = (raw0 + (uint32_t)s * raw_slot + (uint32_t)kABytes) >> 4;     // B as TMA delivered it
+                    const uint32_t lo16 = (lo0 + (uint32_t)sl * lo_slot) >> 4;                          // B lo
+                    const uint32_t a_tm = tmem_base + a_col(sl);                                        // A hi, A lo at +32
                     PROF_T(t0);
-                    uint32_t q = 0;
-                    if (early) {
-                        // the hi.hi product reads only what TMA delivered: it runs while the converters work
-                        if (!mbar_wait(raw_full(s), ph, &abort_flag)) { abort_flag = 1; atomicExch(err, 18); break; }
-                        tc_fence_after();
-#ifdef MCL_FUSED_PROF
-                        if (!(tab.pad0 & 2))
-#endif
-                        issue(prod);
-                        prod >>= 4;
-                        q = 1;
-                    }
-                    // the converters arrive after they have seen the raw tile, so this wait covers both rings
+                    // the converters arrive after they have seen the raw tile, so this wait covers the copies as well
                     if (!mbar_wait(lo_full(sl), (it / kLoSlots) & 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 12); break; }
                     PROF_T(t1); PROF_ADD(pf_full, t0, t1);
 #ifdef MCL_FUSED_PROF
                     t_mma[s] = t1;
 #endif
                     tc_fence_after();
+                    uint32_t prod = prod0;
 #ifdef MCL_FUSED_PROF
                     if (!(tab.pad0 & 2))
 #endif
-                    for (; q < nprod; ++q, prod >>= 4) issue(prod);
+                    for (uint32_t q = 0; q < nprod; ++q, prod >>= 4) {
+                        const uint32_t a_t = a_tm + ((prod & 3u) ? 32u : 0u);
+                        const uint32_t b16 = b_lo | (((prod >> 2) & 3u) ? lo16 : hi16);
+#pragma unroll
+                        for (uint32_t kk = 0; kk < 4; ++kk) {
+                            const uint64_t db = ((uint64_t)b_hi << 32) | (uint64_t)(b16 + kk * b_step);
+                            umma_tf32_ts(d_tmem, a_t + kk * 8u, db, idesc, accum);
+                            accum = 1u;
+                        }
+                    }
                     umma_commit(raw_empty(s));
                     umma_commit(lo_empty(sl));
                     PROF_T(t2); PROF_ADD(pf_issue, t1, t2);
@@ -501,7 +505,14 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
 #endif
     } else if (warp >= kConvWarp0) {
         // ---- converters --------------------------------------------------------------------------------
-        const int tg = threadIdx.x - kConvWarp0 * 32;
+        // Two groups of four warps take the k-tiles alternately (group = parity of the tile number).
+        // A thread owns one row of the A tile (= its TMEM lane): it reads the 32 k of that row from the raw
+        // tile and stores them (`hi`: the raw words, scaled for dX) and their lo terms into the 64 TMEM columns
+        // of the slot.  A transposed A (dW) is read column-wise from the MN-major boxes, which is the transpose
+        // the tensor core would otherwise have to make.  The B lo tile of dW stays in shared memory.
+        const int grp = (warp - kConvWarp0) >> 2;
+        const int tg = (int)threadIdx.x - kConvWarp0 * 32 - grp * 128;       // 0..127 inside the group
+        const int q = warp & 3, row = q * 32 + lane;
         uint32_t it = 0, rs = 0, rph = 0;
         int pi = 0;
         long long pf_wait = 0, pf_work = 0, pf_lat = 0; (void)pf_wait; (void)pf_work; (void)pf_lat;
@@ -511,18 +522,25 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
             if (item >= n_items || abort_flag) break;
             const Item I = decode_item(sp, n_problems, item, pi);
             const FusedProblem& P = sp[I.pi];
-            const int nb_lo = P.mode == kFusedDW ? P.BN * 8 : 0;        // 16-byte chunks of B that need a lo part
+            const bool a_mn = P.mode == kFusedDW;
+            const int nb_lo = a_mn ? P.BN * 8 : 0;                      // 16-byte chunks of B that need a lo part
             const float* ksc = P.a_kscale;
             const int K = P.K;
             bool ok = true;
             for (int j = 0; j < I.nkt; ++j, ++it) {
-                const int s = (int)rs, sl = (int)(it % kLoSlots);
+                const int s = (int)rs;
                 const uint32_t ph = rph;
                 if (++rs == (uint32_t)n_raw) { rs = 0; rph ^= 1u; }
+                if ((int)(it & 1u) != grp) continue;
+                const int sl = (int)(it % kLoSlots);
+                const uint32_t a_taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a_col(sl);
                 PROF_T(t0);
-                ok = mbar_wait_warp(raw_full(s), ph, &abort_flag) &&
-                     mbar_wait_warp(lo_empty(sl), ((it / kLoSlots) & 1u) ^ 1u, &abort_flag);
+                // the slot first: once its last reader (tile it - 2) is done, every earlier tile is, so the raw
+                // barrier cannot still show the phase of this group's previous visit
+                ok = mbar_wait_warp(lo_empty(sl), ((it / kLoSlots) & 1u) ^ 1u, &abort_flag) &&
+                     mbar_wait_warp(raw_full(s), ph, &abort_flag);
                 if (!ok) break;
+                tc_fence_after();          // the MMAs that read this TMEM slot have completed
                 const int k0 = (I.kt0 + j) * 32;
                 PROF_T(t1); PROF_ADD(pf_wait, t0, t1);
 #ifdef MCL_FUSED_PROF
@@ -530,42 +548,63 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 if (tg == 0) t_conv[s] = t1;
 #endif
                 const uint32_t st = raw0 + (uint32_t)s * raw_slot, sto = lo0 + (uint32_t)sl * lo_slot;
+                uint32_t hi[32], lo[32];
 #ifdef MCL_FUSED_PROF
-                if (!(tab.pad0 & 1))
-#endif
+                if (tab.pad0 & 1) {
 #pragma unroll
-                for (int r = 0; r < kABytes / 16 / kConvThreads; ++r) {
-                    const int idx = tg + kConvThreads * r;            // 16-byte chunk of the A tile
-                    float4 v = lds128(st + (uint32_t)idx * 16u);
-                    if (ksc != nullptr) {
-                        const int k = k0 + 4 * ((idx & 7) ^ ((idx >> 3) & 7));     // undo the swizzle: logical k of this chunk
-                        if (k < K) {
-                            const float4 sc = __ldg(reinterpret_cast<const float4*>(ksc + k));
-                            v.x = __fmul_rn(v.x, sc.x); v.y = __fmul_rn(v.y, sc.y);
-                            v.z = __fmul_rn(v.z, sc.z); v.w = __fmul_rn(v.w, sc.w);
-                            sts128(st + (uint32_t)idx * 16u, v);
-                        }
-                    }
-                    sts128(sto + (uint32_t)idx * 16u, lo_term4(v));
-                }
-#ifdef MCL_FUSED_PROF
-                if (!(tab.pad0 & 1))
+                    for (int c = 0; c < 32; ++c) { hi[c] = 0u; lo[c] = 0u; }
+                } else
 #endif
-                for (int c = tg; c < nb_lo; c += kConvThreads) {
-                    const uint32_t off = (uint32_t)kABytes + (uint32_t)c * 16u;
-                    sts128(sto + off, lo_term4(lds128(st + off)));
+                if (!a_mn) {
+                    // K-major: row `row` is 128 bytes, its 16-byte chunks XOR-swizzled by the row number
+                    const uint32_t ra = st + (uint32_t)row * 128u;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        float4 v = lds128(ra + ((uint32_t)(c ^ (row & 7)) << 4));
+                        if (ksc != nullptr) {
+                            const int k = k0 + 4 * c;
+                            if (k < K) {
+                                const float4 sc = __ldg(reinterpret_cast<const float4*>(ksc + k));
+                                v.x = __fmul_rn(v.x, sc.x); v.y = __fmul_rn(v.y, sc.y);
+                                v.z = __fmul_rn(v.z, sc.z); v.w = __fmul_rn(v.w, sc.w);
+                            }
+                        }
+                        const float4 l = lo_term4(v);
+                        hi[4 * c] = __float_as_uint(v.x); hi[4 * c + 1] = __float_as_uint(v.y);
+                        hi[4 * c + 2] = __float_as_uint(v.z); hi[4 * c + 3] = __float_as_uint(v.w);
+                        lo[4 * c] = __float_as_uint(l.x); lo[4 * c + 1] = __float_as_uint(l.y);
+                        lo[4 * c + 2] = __float_as_uint(l.z); lo[4 * c + 3] = __float_as_uint(l.w);
+                    }
+                } else {
+                    // MN-major: box q holds this warp's 32 rows; k-row kk is 128 bytes whose 32-byte atoms are
+                    // XOR-swizzled by kk & 3.  The 32 lanes of a warp read one whole k-row per instruction.
+                    const uint32_t ba = st + (uint32_t)q * (uint32_t)kBox + ((uint32_t)(lane & 7) << 2);
+#pragma unroll
+                    for (int kk = 0; kk < 32; ++kk) {
+                        const uint32_t w = lds32(ba + (uint32_t)kk * 128u + ((uint32_t)((lane >> 3) ^ (kk & 3)) << 5));
+                        hi[kk] = w;
+                        lo[kk] = __float_as_uint(lo_term(__uint_as_float(w)));
+                    }
                 }
-                fence_proxy_async();
+                tmem_st32(a_taddr, hi);
+                tmem_st32(a_taddr + 32u, lo);
+                for (int c = tg; c < nb_lo; c += kConvThreads / 2) {
+                    const uint32_t off = (uint32_t)c * 16u;
+                    sts128(sto + off, lo_term4(lds128(st + (uint32_t)kABytes + off)));
+                }
+                if (nb_lo) fence_proxy_async();
+                tmem_st_wait();
+                tc_fence_before();
                 mbar_arrive(lo_full(sl));
                 PROF_T(t2); PROF_ADD(pf_work, t1, t2);
 #ifdef MCL_FUSED_PROF
-                if (tg == kConvThreads - 1) t_arr[s] = t2;
+                if (tg == kConvThreads / 2 - 1) t_arr[s] = t2;
 #endif
             }
             if (!ok) { abort_flag = 1; atomicExch(err, 15); break; }
         }
 #ifdef MCL_FUSED_PROF
-        if (tg == 0) { PROF_T(tend); long long* o = g_fused_prof + blockIdx.x * 16 + 12; o[0] = pf_wait; o[1] = pf_work; o[2] = pf_lat; o[3] = it; }
+        if (tg == 0 && grp == 0) { PROF_T(tend); long long* o = g_fused_prof + blockIdx.x * 16 + 12; o[0] = pf_wait; o[1] = pf_work; o[2] = pf_lat; o[3] = it; }
 #endif
     }
     __syncwarp();
@@ -738,7 +777,7 @@ cudaError_t launch_fused_cap(const FusedProblem* probs, const FusedOperand* a_op
     cudaError_t e = cudaFuncGetAttributes(&fa, reinterpret_cast<const void*>(tc_fused_kernel<CAP>));
     if (e != cudaSuccess) return e;
     tab.raw_slot = kABytes + ((bhi + 1023) & ~1023);
-    tab.lo_slot = kABytes + ((blo + 1023) & ~1023);
+    tab.lo_slot = (blo + 1023) & ~1023;
     tab.pad0 = 0;
     static const int prefetch_on = getenv("MCL_CUDA_FUSED_PREFETCH") ? atoi(getenv("MCL_CUDA_FUSED_PREFETCH")) : 0;
     tab.prefetch = prefetch_on;
@@ -776,7 +815,9 @@ size_t fused_plan(FusedProblem* p, int target_items, int depth_limit) {
         p->prod = 0x10u;              // hi.b, then lo.b
         return 0;
     }
-    p->BN = pick_bn(p->N, 32, 128);
+    // 160-wide column tiles: an MMA instruction costs about 100 cycles whatever its width (operand feed), so fewer and
+    // wider instructions win (96-wide tiles measured 1.14x slower per step)
+    p->BN = pick_bn(p->N, 32, 160);
     p->tiles_n = (p->N + p->BN - 1) / p->BN;
     p->nprod = 3;
     p->prod = 0x410u;                 // hi_a.hi_b, then lo_a.hi_b, hi_a.lo_b
@@ -795,7 +836,7 @@ cudaError_t launch_tc_fused(const FusedProblem* probs, const FusedOperand* a_ops
                             int* err_word, size_t max_smem, int sm_count, cudaStream_t stream, int* launches) {
     for (int i = 0; i < n; ++i) {
         const FusedProblem& p = probs[i];
-        if (p.mode == kFusedDW ? (p.BN > 128 || (p.BN & 31)) : (p.BN > 160 || (p.BN & (p.mode == kFusedY ? 15 : 31))))
+        if (p.mode == kFusedDW ? (p.BN > 160 || (p.BN & 31)) : (p.BN > 160 || (p.BN & (p.mode == kFusedY ? 15 : 31))))
             return cudaErrorInvalidValue;
         if ((p.N & 3) || (p.ldc & 3) || (a_ops[i].ld & 3) || (b_ops[i].ld & 3)) return cudaErrorInvalidValue;
     }

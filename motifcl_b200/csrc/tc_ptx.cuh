@@ -53,7 +53,6 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
             const unsigned long long t0 = clock64();
             unsigned spins = 0;
             while (!mbar_try_wait(bar, parity)) {
-                __nanosleep(20);
                 if ((++spins & 0xFFu) == 0) {
                     if (*abort_flag || clock64() - t0 > kWaitCycles) { ok = false; break; }
                 }

@@ -606,15 +606,15 @@ def main():
     gemm_gbs = alg["gemm_bytes"] / (ms_gemm * 1e-3) / 1e9
     upd_gbs = alg["update_bytes"] / world / (ms_upd * 1e-3) / 1e9      # each rank updates its row shard
     # The scope table counts the three products as 6*tokens*weights flop against the dense bf16 rate.  Two more
-    # views explain the number: the pass-adjusted ceiling (fp32 fidelity costs 2 + 2 + 3 tf32 products at half the
-    # bf16 rate on narrow layers = 14 bf16-pass units per 3 useful; 3 + 3 + 6 bf16 products = 12 units on wide
-    # ones) and the HBM view (algorithmic bytes of the products at the copy bandwidth), which is the larger ideal
+    # views explain the number: the pass-adjusted ceiling (fp32 fidelity costs 2 + 2 bf16 products for Y and dX and
+    # 3 tf32 products at half the bf16 rate for dW on narrow layers = 10 bf16-pass units per 3 useful; 3 + 3 + 6 bf16
+    # products = 12 units on wide ones) and the HBM view (algorithmic bytes of the products at the copy bandwidth), which is the larger ideal
     # time when layers are narrow.
     narrow = all(l.in_features <= 1024 and l.out_features <= 1024 for l in wl["linears"])
-    units = 14.0 if narrow else 12.0
+    units = 10.0 if narrow else 12.0
     traffic = MEASURED_TRAFFIC_BYTES.get(args.workload)
     roofline = {"kernel": "counter-linear contractions (Y, dX, dW) of all linears: " +
-                          ("tc_fused_kernel (tf32 hi/lo terms)" if narrow else "tc_gemm_kernel (bf16 term planes)"),
+                          ("tc_fused_kernel (bf16 / tf32 hi-lo terms, A operands in tensor memory)" if narrow else "tc_gemm_kernel (bf16 term planes)"),
                 "bound": "tensor", "achieved": gemm_tf, "peak": tf_peak, "unit": "TFLOP/s", "frac": gemm_tf / tf_peak,
                 "peak_kind": f"{peak_kind} bf16 sustained", "traffic": traffic,
                 "flop_per_step": alg["gemm_flop"], "ms": ms_gemm,
@@ -681,10 +681,11 @@ def main():
                            "linears": len(wl["linears"]), "weights": alg["weights"],
                            "parallelism": f"dp{world}" if world > 1 else "single",
                            "l2": "inputs larger than L2 (X and dY of all linears: %.2f GB)" % (in_bytes / 1e9),
-                           "precision": "fp32 in/out; layers up to 1024 features: tcgen05 tf32 on hi/lo terms of the fp32 "
-                                        "operands (2 products for Y and dX, 3 for dW); wider layers: tcgen05 bf16 on 3 "
+                           "precision": "fp32 in/out; layers up to 1024 features: Y and dX = tcgen05 bf16 on two bf16 terms of the fp32 "
+                                        "activations against exact bf16 ternary digits (2 products), dW = tcgen05 tf32 on "
+                                        "hi/lo terms of both operands (3 products); wider layers: tcgen05 bf16 on 3 "
                                         "terms (3 / 6 products); fp32 accumulate in TMEM; relative L2 <= 1e-5 vs the "
-                                        "fp32 reference sums (tested; measured <= 5e-6); counter update bit-exact",
+                                        "fp32 reference sums (tested; measured <= 6e-6); counter update bit-exact",
                            "grouped_call": not args.no_group, "lanes": 1 if not args.no_group else args.lanes,
                            "recorded_batch": not args.eager},
                 "gpu_launches": launches, "clocks": clocks, "roofline": roofline,

@@ -108,6 +108,38 @@ class CounterStateLinear:
                                       self.out_features, x.shape[0], self.lr, self.lr_scale,
                                       self.rms_beta, self.rms_eps, seed)
 
+    # -- several micro-batches per counter update -------------------------------------------
+    # MotifCL updates the counters after every backward pass and names the small effective batch as the main
+    # quality gap of its pretraining run (docs/TERNARY15M_PRETRAIN_RESULTS.md:90-97).  Here the weight gradient
+    # of several micro-batches can be summed (fp32, in the order of the calls) before ONE update; the update
+    # itself is the reference's dense one (apply_update_seed), so given the summed gradient its result is
+    # bit-identical to the reference's.
+    def accumulate_backward(self, x: torch.Tensor, grad_out: torch.Tensor, need_grad_x: bool = True):
+        """grad_x from the current state; dW = grad_out^T x is added to the layer's gradient buffer."""
+        gx = self.backward_input_from_state(grad_out) if need_grad_x else None
+        x, grad_out = x.contiguous(), grad_out.contiguous()
+        n = self.out_features * self.in_features
+        first = getattr(self, "_acc", None) is None
+        if first:
+            self._acc = torch.empty(self.out_features, self.in_features, dtype=torch.float32, device=x.device)
+            self._acc_tmp = torch.empty_like(self._acc)
+            self._acc_count = 0
+        dst = self._acc if self._acc_count == 0 else self._acc_tmp
+        self.ctx.matmul_f32(grad_out, x, dst, self.out_features, x.shape[0], self.in_features, trans_a=True)
+        if self._acc_count > 0:
+            self.ctx.eltwise(0, self._acc, self._acc_tmp, self._acc, n)     # MCL_CUDA_ELT_ADD
+        self._acc_count += 1
+        return gx
+
+    def apply_accumulated(self, seed: int, packed2_out: torch.Tensor | None = None) -> int:
+        """One counter update with the summed gradient; returns how many micro-batches it covered."""
+        count = getattr(self, "_acc_count", 0)
+        if count == 0:
+            raise RuntimeError("apply_accumulated: no gradient has been accumulated")
+        self.apply_update_seed(self._acc, seed, packed2_out)
+        self._acc_count = 0
+        return count
+
     def backward(self, x: torch.Tensor, grad_out: torch.Tensor, seed: int, need_grad_x: bool = True):
         """What CounterBackwardNode::backward does (src/nn/compact_counter.cpp:40-50): grad_x
         from the PRE-update state, then the fused update."""

@@ -888,65 +888,90 @@ int mcl_cuda_counter_linear_step_many(mcl_cuda_ctx* ctx, const mcl_cuda_linear_d
     void* wsp = nullptr;
     MCL_TRY(ws_reserve(ctx, cv.off, &wsp));
     char* w = static_cast<char*>(wsp);
-    // 1. ternary digits of every layer as fp32
+    // 1. ternary digits of every layer as bf16: T [O][I] in the first half of the layer's block, its transpose after it
     {
         std::vector<const uint8_t*> st(ng);
         std::vector<const uint32_t*> p2(ng);
-        std::vector<float*> T(ng);
+        std::vector<void*> T(ng), Tt(ng);
         std::vector<int> Os(ng), Is(ng);
         for (size_t gi = 0; gi < ng; ++gi) {
             const mcl_cuda_linear_desc& L = layers[grouped[gi]];
-            st[gi] = L.state; p2[gi] = L.packed2_in; T[gi] = reinterpret_cast<float*>(w + t_off[gi]);
+            st[gi] = L.state; p2[gi] = L.packed2_in;
+            T[gi] = w + t_off[gi]; Tt[gi] = w + t_off[gi] + L.out_features * L.in_features * 2;
             Os[gi] = (int)L.out_features; Is[gi] = (int)L.in_features;
         }
         int launches = 0;
-        cudaError_t e = mcl::launch_ternary_f32_group(st.data(), p2.data(), T.data(), Os.data(), Is.data(), (int)ng, (int)C, ctx->sm_count,
-                                                      ctx->stream, &launches);
+        cudaError_t e = mcl::launch_ternary_bf16_group(st.data(), p2.data(), T.data(), Tt.data(), Os.data(), Is.data(), (int)ng, (int)C,
+                                                       ctx->sm_count, ctx->stream, &launches);
         ctx->launches += launches;
         if (e != cudaSuccess) return fail_cuda(ctx, op, e);
     }
-    // 2. all products.  A launch takes kFusedMaxProblems problems, i.e. the three products of a third as many
-    // layers; within a launch the long work items (dW: K = tokens) come first so that the short ones fill the tail.
+    // 2. all products.  The weight-gradient products (tf32 terms, K = tokens, long work items) and the row products
+    // (bf16 terms against the bf16 digits, 64-deep k-tiles) run in launches of their own: their tiles differ in size,
+    // and a launch sizes its rings for the largest tile of its table.
     {
-        const size_t per_launch = mcl::kFusedMaxProblems / 3;
-        for (size_t g0 = 0; g0 < ng; g0 += per_launch) {
-            const size_t g1 = g0 + per_launch < ng ? g0 + per_launch : ng;
-            for (size_t gi = g0; gi < g1; ++gi) {
-                const mcl_cuda_linear_desc& L = layers[grouped[gi]];
-                const size_t I = L.in_features, O = L.out_features, Nt = L.batch;
-                mcl::FusedProblem p = mcl::FusedProblem();
-                p.mode = mcl::kFusedDW; p.M = (int)O; p.N = (int)I; p.K = (int)Nt;
-                mcl::fused_plan(&p, target_items, depth);
-                p.C = p.splits > 1 ? reinterpret_cast<float*>(w + k_off[gi]) : L.grad_w; p.ldc = (int)I;
-                pr.push_back(p); oa.push_back(operand(L.grad_out, Nt, O, 1, 4)); ob.push_back(operand(L.x, Nt, I, 1, p.BN / 32));
-            }
-            for (size_t gi = g0; gi < g1; ++gi) {
-                const mcl_cuda_linear_desc& L = layers[grouped[gi]];
-                const size_t I = L.in_features, O = L.out_features, Nt = L.batch;
-                const float* T = reinterpret_cast<const float*>(w + t_off[gi]);
-                mcl::FusedProblem p;
-                if (L.y) {
-                    p = mcl::FusedProblem();
-                    p.mode = mcl::kFusedY; p.M = (int)Nt; p.N = (int)O; p.K = (int)I;
-                    p.col_scale = L.scale; p.C = L.y; p.ldc = (int)O;
-                    mcl::fused_plan(&p, 0, 0);
-                    pr.push_back(p); oa.push_back(operand(L.x, Nt, I, 0, 128)); ob.push_back(operand(T, O, I, 0, p.BN));
-                }
-                if (L.grad_x) {
-                    p = mcl::FusedProblem();
-                    p.mode = mcl::kFusedDX; p.M = (int)Nt; p.N = (int)I; p.K = (int)O;
-                    p.a_kscale = L.scale; p.C = L.grad_x; p.ldc = (int)I;
-                    mcl::fused_plan(&p, 0, 0);
-                    pr.push_back(p); oa.push_back(operand(L.grad_out, Nt, O, 0, 128)); ob.push_back(operand(T, O, I, 1, p.BN / 32));
-                }
-            }
+        auto flush = [&]() -> cudaError_t {
+            if (pr.empty()) return cudaSuccess;
             int launches = 0;
             cudaError_t e = mcl::launch_tc_fused(pr.data(), oa.data(), ob.data(), (int)pr.size(), ctx->err_word, ctx->max_smem,
                                                  ctx->sm_count, ctx->stream, &launches);
             ctx->launches += launches;
-            if (e != cudaSuccess) return fail_cuda(ctx, op, e);
             pr.clear(); oa.clear(); ob.clear();
+            return e;
+        };
+        auto operand_bf16 = [](const void* p, size_t rows, size_t cols, int box_outer) {
+            mcl::FusedOperand o = {static_cast<const float*>(p), (int)rows, (int)cols, (int)cols, 0, box_outer, 1};
+            return o;
+        };
+        for (size_t gi = 0; gi < ng; ++gi) {
+            const mcl_cuda_linear_desc& L = layers[grouped[gi]];
+            const size_t I = L.in_features, O = L.out_features, Nt = L.batch;
+            mcl::FusedProblem p = mcl::FusedProblem();
+            p.mode = mcl::kFusedDW; p.M = (int)O; p.N = (int)I; p.K = (int)Nt;
+            mcl::fused_plan(&p, target_items, depth);
+            p.C = p.splits > 1 ? reinterpret_cast<float*>(w + k_off[gi]) : L.grad_w; p.ldc = (int)I;
+            pr.push_back(p); oa.push_back(operand(L.grad_out, Nt, O, 1, 4)); ob.push_back(operand(L.x, Nt, I, 1, p.BN / 32));
+            if (pr.size() == (size_t)mcl::kFusedMaxProblems) {
+                cudaError_t e = flush();
+                if (e != cudaSuccess) return fail_cuda(ctx, op, e);
+            }
         }
+        {
+            cudaError_t e = flush();
+            if (e != cudaSuccess) return fail_cuda(ctx, op, e);
+        }
+        // row products: launches of equal size
+        size_t n_row = 0;
+        for (size_t gi = 0; gi < ng; ++gi) n_row += (layers[grouped[gi]].y ? 1 : 0) + (layers[grouped[gi]].grad_x ? 1 : 0);
+        const size_t n_launch = (n_row + mcl::kFusedMaxProblems - 1) / mcl::kFusedMaxProblems;
+        const size_t per_launch = n_launch ? (n_row + n_launch - 1) / n_launch : 0;
+        for (size_t gi = 0; gi < ng; ++gi) {
+            const mcl_cuda_linear_desc& L = layers[grouped[gi]];
+            const size_t I = L.in_features, O = L.out_features, Nt = L.batch;
+            const char* T = w + t_off[gi];
+            const char* Tt = T + O * I * 2;
+            mcl::FusedProblem p;
+            if (L.y) {
+                p = mcl::FusedProblem();
+                p.mode = mcl::kFusedYB; p.M = (int)Nt; p.N = (int)O; p.K = (int)I;
+                p.col_scale = L.scale; p.C = L.y; p.ldc = (int)O;
+                mcl::fused_plan(&p, 0, 0);
+                pr.push_back(p); oa.push_back(operand(L.x, Nt, I, 0, 128)); ob.push_back(operand_bf16(T, O, I, p.BN));
+            }
+            if (L.grad_x) {
+                p = mcl::FusedProblem();
+                p.mode = mcl::kFusedDXB; p.M = (int)Nt; p.N = (int)I; p.K = (int)O;
+                p.a_kscale = L.scale; p.C = L.grad_x; p.ldc = (int)I;
+                mcl::fused_plan(&p, 0, 0);
+                pr.push_back(p); oa.push_back(operand(L.grad_out, Nt, O, 0, 128)); ob.push_back(operand_bf16(Tt, I, O, p.BN));
+            }
+            if (pr.size() + 2 > per_launch || pr.size() + 2 > (size_t)mcl::kFusedMaxProblems) {
+                cudaError_t e = flush();
+                if (e != cudaSuccess) return fail_cuda(ctx, op, e);
+            }
+        }
+        cudaError_t e = flush();
+        if (e != cudaSuccess) return fail_cuda(ctx, op, e);
     }
     // 3. split-K reductions of dW
     {

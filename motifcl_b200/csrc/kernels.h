@@ -74,13 +74,16 @@ cudaError_t launch_expand_ternary_p2(const uint32_t* packed2, int O, int I, void
                                      cudaStream_t stream);
 
 // tc_fused.cu -- grouped tcgen05 (tf32, two terms) contractions straight from fp32 tensors
-enum { kFusedY = 0, kFusedDX = 1, kFusedDW = 2 };
+// kFusedYB / kFusedDXB are Y and dX with the activation split into two bf16 terms and the ternary digits given
+// as a K-major bf16 matrix (T [out,in] for Y, its transpose [in,out] for dX): k-tiles of 64, kind::f16
+enum { kFusedY = 0, kFusedDX = 1, kFusedDW = 2, kFusedYB = 3, kFusedDXB = 4 };
 constexpr int kFusedMaxProblems = 63;
-struct FusedOperand {          // a row-major fp32 tensor read through TMA (host side only)
-    const float* ptr;
+struct FusedOperand {          // a row-major tensor read through TMA (host side only)
+    const float* ptr;          // fp32 elements, or bf16 ones when `bf16` is set
     int rows, cols, ld;
     int mn_major;              // read as a transposed operand (cols % 32 == 0): 32-byte-atom swizzle, 3-D box
     int box_outer;             // rows of the box (K-major) or 32-column chunks per box (MN-major)
+    int bf16;                  // K-major bf16 matrix: box of 64 elements x box_outer rows
 };
 struct FusedProblem {          // C[M,N] = A[M,K] . B[N,K]^T, see the kinds in tc_fused.cu
     const float* a_kscale;     // DX: A is multiplied by a_kscale[k] (rounded to fp32) before the split
@@ -106,8 +109,13 @@ cudaError_t launch_ternary_f32_group(const uint8_t* const* state, const uint32_t
                                      int sm_count, cudaStream_t stream, int* launches);
 cudaError_t launch_splitk_reduce_group(const float* const* partial, float* const* out, const int* elements, const int* splits,
                                        int n, int sm_count, cudaStream_t stream, int* launches);
+// ternary digits of the layers as bf16, both orientations: T [O][I] and Tt [I][O]
+cudaError_t launch_ternary_bf16_group(const uint8_t* const* state, const uint32_t* const* packed2, void* const* T, void* const* Tt,
+                                      const int* O, const int* I, int n, int C, int sm_count, cudaStream_t stream, int* launches);
 // tc_gemm.cu: TMA map of a row-major fp32 matrix, 128-byte swizzle, zero fill outside
 bool tc_encode_map_f32(void* map, const float* base, int cols, int rows, int ld, int mn_major, int box_outer);
+// the same for a K-major bf16 matrix: box of 64 elements x box_outer rows
+bool tc_encode_map_bf16(void* map, const void* base, int cols, int rows, int ld, int box_outer);
 cudaError_t launch_splitk_reduce(const float* partial, float* c, const float* col_scale, int M, int N, int ldc,
                                  int splits, cudaStream_t stream);
 

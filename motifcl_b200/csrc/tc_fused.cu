@@ -42,6 +42,7 @@
 // main loop of the next), A slots of 64 columns at 320, 384, 448.
 // Every wait is bounded (see mbar_wait); on time-out the kernel records an error word and drains.
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cstdio>
 #include <cstdlib>
 
@@ -95,6 +96,19 @@ __device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_c, uint32_t tmem_a, u
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(tmem_c), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accum) : "memory");
 }
+// kind::f16 (bf16 operands, two per 32-bit TMEM column for A), A in tensor memory
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_c, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accum) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_c), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accum) : "memory");
+}
+// Instruction descriptor, kind::f16: D = f32, A = B = bf16 (1 at bits 7 and 10), both K-major
+__device__ __forceinline__ uint32_t idesc_bf16_k(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ bool is_bf16_mode(int mode) { return mode >= kFusedYB; }
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -119,7 +133,7 @@ __device__ __forceinline__ Item decode_item(const FusedProblem* sp, int n_proble
     const int rest = local / P.tiles_n;
     it.mt = rest % P.tiles_m;
     it.split = rest / P.tiles_m;
-    const int ktiles = (P.K + 31) >> 5;
+    const int ktiles = is_bf16_mode(P.mode) ? (P.K + 63) >> 6 : (P.K + 31) >> 5;
     it.kt0 = it.split * P.ktiles_per_split;
     it.nkt = min(P.ktiles_per_split, ktiles - it.kt0);
     return it;
@@ -281,25 +295,21 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
 #ifdef MCL_FUSED_PROF
                     t_issue[s] = clock64();
 #endif
-#ifdef MCL_FUSED_PROF
-                    const bool skip_a = tab.pad0 & 32, skip_b = tab.pad0 & 8;
-                    mbar_expect_tx(raw_full(s), (skip_a ? 0u : (uint32_t)kABytes) + (skip_b ? 0u : (uint32_t)P.BN * 128u));
-                    if (!skip_a) {
+                    if (is_bf16_mode(mode)) {
+                        // 64 k: two fp32 boxes of A side by side, one bf16 box of the ternary operand
+                        mbar_expect_tx(raw_full(s), 2u * (uint32_t)kABytes + (uint32_t)P.BN * 128u);
+                        const int kb = (I.kt0 + j) * 64;
+                        tma_load_2d(st, ma, raw_full(s), kb, m0);
+                        tma_load_2d(st + kABytes, ma, raw_full(s), kb + 32, m0);
+                        tma_load_2d(st + 2 * kABytes, mb, raw_full(s), kb, n0);
+                    } else {
+                        mbar_expect_tx(raw_full(s), bytes);
+                        // K-major: one box of 32 k x rows; MN-major: one box of 32 m x 32 k x chunks (3-D map)
                         if (mode == kFusedDW) tma_load_3d(st, ma, raw_full(s), 0, k0, m0 >> 5);
                         else tma_load_2d(st, ma, raw_full(s), k0, m0);
-                    }
-                    if (!skip_b) {
                         if (mode == kFusedY) tma_load_2d(st + kABytes, mb, raw_full(s), k0, n0);
                         else tma_load_3d(st + kABytes, mb, raw_full(s), 0, k0, n0 >> 5);
                     }
-#else
-                    mbar_expect_tx(raw_full(s), bytes);
-                    // K-major: one box of 32 k x rows; MN-major: one box of 32 m x 32 k x chunks (3-D map)
-                    if (mode == kFusedDW) tma_load_3d(st, ma, raw_full(s), 0, k0, m0 >> 5);
-                    else tma_load_2d(st, ma, raw_full(s), k0, m0);
-                    if (mode == kFusedY) tma_load_2d(st + kABytes, mb, raw_full(s), k0, n0);
-                    else tma_load_3d(st + kABytes, mb, raw_full(s), 0, k0, n0 >> 5);
-#endif
                     *reinterpret_cast<volatile unsigned int*>(&tiles_issued) = it + 1;
                     PROF_T(t2); PROF_ADD(pf_issue, t1, t2);
                 }
@@ -337,8 +347,9 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 if (item >= n_items || abort_flag) break;
                 const Item I = decode_item(sp, n_problems, item, pi);
                 const FusedProblem& P = sp[I.pi];
+                const bool bf = is_bf16_mode(P.mode);
                 const bool b_mn = P.mode != kFusedY;
-                const uint32_t idesc = idesc_tf32(128, P.BN, false, b_mn);
+                const uint32_t idesc = bf ? idesc_bf16_k(128, P.BN) : idesc_tf32(128, P.BN, false, b_mn);
                 // B descriptor words: low = address / 16 | leading byte offset / 16 << 16, high = stride byte offset / 16 |
                 // version bit | layout type << 29 (1 = 128-byte swizzle with 32-byte atoms, 2 = 128-byte swizzle)
                 const uint32_t b_step = b_mn ? 64u : 2u;                                    // 16-byte units per 8 k
@@ -355,7 +366,7 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 for (int j = 0; j < I.nkt; ++j, ++it) {
                     const int s = (int)rs, sl = (int)(it % kLoSlots);
                     if (++rs == (uint32_t)n_raw) rs = 0;
-                    const uint32_t hi16 = (raw0 + (uint32_t)s * raw_slot + (uint32_t)kABytes) >> 4;     // B as TMA delivered it
+                    const uint32_t hi16 = (raw0 + (uint32_t)s * raw_slot + (bf ? 2u : 1u) * (uint32_t)kABytes) >> 4;     // B as TMA delivered it
                     const uint32_t lo16 = (lo0 + (uint32_t)sl * lo_slot) >> 4;                          // B lo
                     const uint32_t a_tm = tmem_base + a_col(sl);                                        // A hi, A lo at +32
                     PROF_T(t0);
@@ -370,6 +381,17 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
 #ifdef MCL_FUSED_PROF
                     if (!(tab.pad0 & 2))
 #endif
+                    if (bf) {
+                        // the ternary tile is K-major bf16 in the 128-byte swizzle (rows of 64 k); A terms: hi, lo
+                        const uint64_t db0 = smem_desc_k_sw128(hi16 << 4);
+#pragma unroll
+                        for (uint32_t t = 0; t < 2; ++t)
+#pragma unroll
+                            for (uint32_t kk = 0; kk < 4; ++kk) {
+                                umma_bf16_ts(d_tmem, a_tm + 32u * t + kk * 8u, db0 + 2u * kk, idesc, accum);
+                                accum = 1u;
+                            }
+                    } else
                     for (uint32_t q = 0; q < nprod; ++q, prod >>= 4) {
                         const uint32_t a_t = a_tm + ((prod & 3u) ? 32u : 0u);
                         const uint32_t b16 = b_lo | (((prod >> 2) & 3u) ? lo16 : hi16);
@@ -429,12 +451,13 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                     while ((int)(pos + (unsigned int)t - *reinterpret_cast<volatile unsigned int*>(&tiles_issued)) > kPrefetchAhead &&
                            !abort_flag)
                         __nanosleep(100);
-                    const int k = (J.kt0 + t) * 32;
+                    const int k = (J.kt0 + t) * (is_bf16_mode(qmode) ? 64 : 32);
                     if (qmode == kFusedDW) {
                         tma_prefetch_3d(qa, 0, k, qm >> 5);
                         tma_prefetch_3d(qb, 0, k, qn >> 5);
                     } else {
                         tma_prefetch_2d(qa, k, qm);      // the ternary operand is small and stays in L2 by itself
+                        if (is_bf16_mode(qmode)) tma_prefetch_2d(qa, k + 32, qm);
                     }
                 }
             }
@@ -555,7 +578,33 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                     for (int c = 0; c < 32; ++c) { hi[c] = 0u; lo[c] = 0u; }
                 } else
 #endif
-                if (!a_mn) {
+                if (is_bf16_mode(P.mode)) {
+                    // 64 k of the row from two boxes; two bf16 terms, two k per TMEM column (even k in the low half)
+                    const int kb = (I.kt0 + j) * 64;
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        const uint32_t ra = st + (uint32_t)b * (uint32_t)kABytes + (uint32_t)row * 128u;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            float4 v = lds128(ra + ((uint32_t)(c ^ (row & 7)) << 4));
+                            if (ksc != nullptr) {
+                                const int k = kb + 32 * b + 4 * c;
+                                if (k < K) {
+                                    const float4 sc = __ldg(reinterpret_cast<const float4*>(ksc + k));
+                                    v.x = __fmul_rn(v.x, sc.x); v.y = __fmul_rn(v.y, sc.y);
+                                    v.z = __fmul_rn(v.z, sc.z); v.w = __fmul_rn(v.w, sc.w);
+                                }
+                            }
+                            const __nv_bfloat162 h0 = __floats2bfloat162_rn(v.x, v.y), h1 = __floats2bfloat162_rn(v.z, v.w);
+                            const __nv_bfloat162 l0 = __floats2bfloat162_rn(v.x - __low2float(h0), v.y - __high2float(h0));
+                            const __nv_bfloat162 l1 = __floats2bfloat162_rn(v.z - __low2float(h1), v.w - __high2float(h1));
+                            hi[16 * b + 2 * c] = *reinterpret_cast<const uint32_t*>(&h0);
+                            hi[16 * b + 2 * c + 1] = *reinterpret_cast<const uint32_t*>(&h1);
+                            lo[16 * b + 2 * c] = *reinterpret_cast<const uint32_t*>(&l0);
+                            lo[16 * b + 2 * c + 1] = *reinterpret_cast<const uint32_t*>(&l1);
+                        }
+                    }
+                } else if (!a_mn) {
                     // K-major: row `row` is 128 bytes, its 16-byte chunks XOR-swizzled by the row number
                     const uint32_t ra = st + (uint32_t)row * 128u;
 #pragma unroll
@@ -681,6 +730,73 @@ __global__ void __launch_bounds__(256) ternary_f32_group_kernel(const __grid_con
     }
 }
 
+// ---- ternary digits of several layers as bf16, both orientations --------------------------------------------
+// T [O][I] (the K-major operand of Y) and Tt [I][O] (the K-major operand of dX), 64 x 64 tiles through shared memory
+struct TernaryBf16Group {
+    int n, C;
+    int tile_begin[kTernCap + 1];
+    int O[kTernCap], I[kTernCap];
+    const uint8_t* state[kTernCap];            // 6-bit state of layer j, or null: then
+    const uint32_t* packed2[kTernCap];         // its 2-bit words
+    __nv_bfloat16* T[kTernCap];
+    __nv_bfloat16* Tt[kTernCap];
+};
+__global__ void __launch_bounds__(256) ternary_bf16_group_kernel(const __grid_constant__ TernaryBf16Group g) {
+    __shared__ DecodeLut lut;
+    __shared__ __nv_bfloat16 tile[64][66];
+    build_decode_lut(&lut, g.C, threadIdx.x, blockDim.x);
+    __syncthreads();
+    const int total = g.tile_begin[g.n];
+    for (int u = blockIdx.x; u < total; u += gridDim.x) {
+        int lo = 0, hi = g.n - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (g.tile_begin[mid] <= u) lo = mid; else hi = mid - 1;
+        }
+        const int O = g.O[lo], I = g.I[lo], tiles_i = (I + 63) >> 6;
+        const int local = u - g.tile_begin[lo];
+        const int o0 = (local / tiles_i) * 64, i0 = (local % tiles_i) * 64;
+        const uint8_t* state = g.state[lo];
+        const uint32_t* p2 = g.packed2[lo];
+        __nv_bfloat16* T = g.T[lo];
+        __nv_bfloat16* Tt = g.Tt[lo];
+        // 64 rows x 16 groups of 4 weights per tile
+        for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+            const int oo = e >> 4, gi = e & 15, o = o0 + oo, i = i0 + 4 * gi;
+            if (o < O && i < I) {
+                float t[4];
+                if (state != nullptr) {
+                    const uint8_t* sp = state + ((size_t)o * (I >> 2) + (i >> 2)) * 3;
+                    const uint32_t w = (uint32_t)__ldg(sp) | ((uint32_t)__ldg(sp + 1) << 8) | ((uint32_t)__ldg(sp + 2) << 16);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) t[k] = lut.e[(w >> (6 * k)) & 63u].x;
+                } else {
+                    const uint32_t b = __ldg(p2 + (size_t)o * (I >> 4) + (i >> 4)) >> (2 * (i & 15));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) t[k] = (float)((int)((b >> (2 * k)) & 3u) - 1);
+                }
+                const __nv_bfloat162 t01 = __floats2bfloat162_rn(t[0], t[1]), t23 = __floats2bfloat162_rn(t[2], t[3]);
+                tile[oo][4 * gi] = __low2bfloat16(t01); tile[oo][4 * gi + 1] = __high2bfloat16(t01);
+                tile[oo][4 * gi + 2] = __low2bfloat16(t23); tile[oo][4 * gi + 3] = __high2bfloat16(t23);
+                uint2 pk;
+                pk.x = *reinterpret_cast<const uint32_t*>(&t01); pk.y = *reinterpret_cast<const uint32_t*>(&t23);
+                *reinterpret_cast<uint2*>(T + (size_t)o * I + i) = pk;
+            }
+        }
+        __syncthreads();
+        // transposed: thread -> (row i of Tt, two consecutive o)
+        for (int e = threadIdx.x; e < 64 * 32; e += 256) {
+            const int ii = e >> 5, op = (e & 31) * 2, i = i0 + ii, o = o0 + op;
+            if (i < I && o < O) {       // O is even
+                __nv_bfloat162 v;
+                v.x = tile[op][ii]; v.y = tile[op + 1][ii];
+                *reinterpret_cast<__nv_bfloat162*>(Tt + (size_t)i * O + o) = v;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // ---- the split-K reduction of several layers in one launch ----------------------------------------------------
 constexpr int kGroupCap = 64;
 struct ReduceGroup {
@@ -723,7 +839,7 @@ int pick_bn(int N, int step, int hi) {
 
 bool same_operand(const FusedOperand& a, const FusedOperand& b) {
     return a.ptr == b.ptr && a.rows == b.rows && a.cols == b.cols && a.ld == b.ld && a.mn_major == b.mn_major &&
-           a.box_outer == b.box_outer;
+           a.box_outer == b.box_outer && a.bf16 == b.bf16;
 }
 
 template <int CAP>
@@ -751,8 +867,9 @@ cudaError_t launch_fused_cap(const FusedProblem* probs, const FusedOperand* a_op
         }
         if (idx[0] < 0 || idx[1] < 0) break;
         for (int m = n_maps; m < n_maps + added; ++m)
-            if (!tc_encode_map_f32(&tab.maps[m], seen[m].ptr, seen[m].cols, seen[m].rows, seen[m].ld, seen[m].mn_major,
-                                   seen[m].box_outer))
+            if (!(seen[m].bf16 ? tc_encode_map_bf16(&tab.maps[m], seen[m].ptr, seen[m].cols, seen[m].rows, seen[m].ld, seen[m].box_outer)
+                               : tc_encode_map_f32(&tab.maps[m], seen[m].ptr, seen[m].cols, seen[m].rows, seen[m].ld, seen[m].mn_major,
+                                                   seen[m].box_outer)))
                 return cudaErrorInvalidValue;
         n_maps += added;
         FusedProblem& p = tab.p[taken];
@@ -770,7 +887,8 @@ cudaError_t launch_fused_cap(const FusedProblem* probs, const FusedOperand* a_op
     int bhi = 0, blo = 0;
     for (int i = 0; i < taken; ++i) {
         const int bytes = tab.p[i].BN * 128;
-        if (bytes > bhi) bhi = bytes;
+        const int raw = bytes + (tab.p[i].mode >= kFusedYB ? kABytes : 0);    // bf16 kinds: a second fp32 box of A
+        if (raw > bhi) bhi = raw;
         if (tab.p[i].mode == kFusedDW && bytes > blo) blo = bytes;      // only two fp32 operands need a B lo tile
     }
     cudaFuncAttributes fa;
@@ -805,6 +923,15 @@ cudaError_t launch_fused_cap(const FusedProblem* probs, const FusedOperand* a_op
 size_t fused_plan(FusedProblem* p, int target_items, int depth_limit) {
     const int ktiles = (p->K + 31) / 32;
     p->tiles_m = (p->M + 127) / 128;
+    if (p->mode >= kFusedYB) {
+        p->BN = pick_bn(p->N, 16, 160);
+        p->tiles_n = (p->N + p->BN - 1) / p->BN;
+        p->splits = 1;
+        p->ktiles_per_split = (p->K + 63) / 64;
+        p->nprod = 2;
+        p->prod = 0x10u;
+        return 0;
+    }
     if (p->mode != kFusedDW) {
         // B tiles of at most 20 KiB keep the raw ring four slots deep; wider tiles (three slots) measured 1.4x slower
         p->BN = pick_bn(p->N, p->mode == kFusedY ? 16 : 32, 160);
@@ -836,7 +963,7 @@ cudaError_t launch_tc_fused(const FusedProblem* probs, const FusedOperand* a_ops
                             int* err_word, size_t max_smem, int sm_count, cudaStream_t stream, int* launches) {
     for (int i = 0; i < n; ++i) {
         const FusedProblem& p = probs[i];
-        if (p.mode == kFusedDW ? (p.BN > 160 || (p.BN & 31)) : (p.BN > 160 || (p.BN & (p.mode == kFusedY ? 15 : 31))))
+        if (p.mode == kFusedDW ? (p.BN > 160 || (p.BN & 31)) : (p.BN > 160 || (p.BN & (p.mode == kFusedDX ? 31 : 15))))
             return cudaErrorInvalidValue;
         if ((p.N & 3) || (p.ldc & 3) || (a_ops[i].ld & 3) || (b_ops[i].ld & 3)) return cudaErrorInvalidValue;
     }
@@ -890,6 +1017,33 @@ cudaError_t launch_ternary_f32_group(const uint8_t* const* state, const uint32_t
         long long blocks = (units + 255) / 256;
         if (blocks > (long long)sm_count * 8) blocks = (long long)sm_count * 8;
         ternary_f32_group_kernel<<<(int)blocks, 256, 0, stream>>>(g);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        ++*launches;
+        done += take;
+    }
+    return cudaSuccess;
+}
+
+cudaError_t launch_ternary_bf16_group(const uint8_t* const* state, const uint32_t* const* packed2, void* const* T, void* const* Tt,
+                                      const int* O, const int* I, int n, int C, int sm_count, cudaStream_t stream, int* launches) {
+    for (int done = 0; done < n;) {
+        TernaryBf16Group g;
+        const int take = n - done < kTernCap ? n - done : kTernCap;
+        int tiles = 0;
+        for (int j = 0; j < take; ++j) {
+            g.tile_begin[j] = tiles;
+            g.state[j] = state[done + j];
+            g.packed2[j] = packed2[done + j];
+            g.T[j] = static_cast<__nv_bfloat16*>(T[done + j]);
+            g.Tt[j] = static_cast<__nv_bfloat16*>(Tt[done + j]);
+            g.O[j] = O[done + j]; g.I[j] = I[done + j];
+            tiles += ((O[done + j] + 63) / 64) * ((I[done + j] + 63) / 64);
+        }
+        g.tile_begin[take] = tiles;
+        g.n = take; g.C = C;
+        const int blocks = tiles < sm_count * 8 ? tiles : sm_count * 8;
+        ternary_bf16_group_kernel<<<blocks, 256, 0, stream>>>(g);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
         ++*launches;

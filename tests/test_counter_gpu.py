@@ -307,6 +307,42 @@ def test_layer_mirror_teacher_recovery(ctx):
     assert mse <= 5e-3 and acc >= 0.9, (mse, acc)
 
 
+def test_accumulated_micro_batches_update_once(ctx, orc):
+    """Three micro-batches summed into one gradient, then one update: the summed gradient is within 1e-5
+    (relative L2) of the float64 sum over all tokens, grad_x comes from the unchanged state every time,
+    and the update is bit-identical to the CPU checker's given the summed gradient's bytes."""
+    from motifcl_b200 import CounterStateLinear
+    I, O, C, N = 96, 64, 11, 160
+    layer = CounterStateLinear(ctx, I, O, C=C, lr=3e-3, lr_scale=0.05, seed=7)
+    st0 = layer.state.cpu().numpy().copy()
+    sc0, v0 = layer.scale.cpu().numpy().copy(), layer.v.cpu().numpy().copy()
+    rng = np.random.default_rng(5)
+    xs = [rng.standard_normal((N, I)).astype(np.float32) for _ in range(3)]
+    dys = [(0.02 * rng.standard_normal((N, O))).astype(np.float32) for _ in range(3)]
+    with pytest.raises(RuntimeError):
+        layer.apply_accumulated(1)
+    for x, dy in zip(xs, dys):
+        gx = layer.accumulate_backward(_t(x), _t(dy))
+        ctx.finish()
+        assert rel_l2(gx.cpu().numpy(), orc.backward_input(dy, st0, sc0, C, I)) <= 1e-5
+        assert np.array_equal(layer.state.cpu().numpy(), st0)          # no update between micro-batches
+    gw = layer._acc.cpu().numpy().copy()
+    ref = sum(dy.astype(np.float64).T @ x.astype(np.float64) for x, dy in zip(xs, dys))
+    assert rel_l2(gw, ref) <= 1e-5
+    p2 = torch.zeros(O, I // 16, dtype=torch.int32, device=DEV)
+    assert layer.apply_accumulated(99, p2) == 3
+    ctx.finish()
+    e = orc.update_dense(st0, sc0, v0, gw, C, I, O, 0, 3e-3, 0.05, 0.9, 1e-3, 99)
+    assert np.array_equal(layer.state.cpu().numpy(), e[0])
+    assert np.array_equal(_bits(layer.scale.cpu().numpy()), _bits(e[1]))
+    assert np.array_equal(_bits(layer.v.cpu().numpy()), _bits(e[2]))
+    assert np.array_equal(p2.cpu().numpy().view(np.uint32), e[3])
+    # the buffer starts over
+    layer.accumulate_backward(_t(xs[0]), _t(dys[0]), need_grad_x=False)
+    ctx.finish()
+    assert rel_l2(layer._acc.cpu().numpy(), dys[0].astype(np.float64).T @ xs[0].astype(np.float64)) <= 1e-5
+
+
 # ---- tensor-core (tcgen05) contractions -----------------------------------------------------
 
 TC_SHAPES = [(256, 288, 288), (512, 768, 288), (300, 288, 768), (1000, 2048, 512), (129, 96, 1032), (4096, 1024, 1024)]

@@ -64,7 +64,7 @@ constexpr int kLoSlots = 3;                  // tiles between converters and MMA
 constexpr int kQueue = 4;                    // work items in flight between the scheduler lane and the other roles
 constexpr int kQueueReaders = 1 + 1 + 4 + 8; // MMA lane, prefetch lane, epilogue warps, converter warps
 constexpr int kPrefetchAhead = 12;           // k-tiles the prefetch lane may run ahead of the copies
-constexpr int kScratch = 4 * 4096;           // epilogue staging, 4 KiB per warp
+constexpr int kScratch = 4 * 2048;           // epilogue staging, 2 KiB per warp
 constexpr int kAccStride = 160;              // TMEM columns between the two accumulators (an accumulator is at most 160 wide)
 constexpr int kACol = 320;                   // the A tiles follow the accumulators: 64 columns each (hi, lo)
 
@@ -109,6 +109,14 @@ __device__ __forceinline__ uint32_t idesc_bf16_k(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 __device__ __forceinline__ bool is_bf16_mode(int mode) { return mode >= kFusedYB; }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -187,7 +195,7 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
     const uint32_t raw_slot = (uint32_t)tab.raw_slot, lo_slot = (uint32_t)tab.lo_slot;
     const uint32_t raw0 = (smem_u32(smem_raw) + 1023u) & ~1023u;        // raw ring: A hi at +0, B hi at +kABytes
     const uint32_t lo0 = raw0 + (uint32_t)n_raw * raw_slot;             // lo ring:  A lo at +0, B lo at +kABytes
-    const uint32_t scratch0 = lo0 + (uint32_t)kLoSlots * lo_slot;       // 4 KiB per epilogue warp
+    const uint32_t scratch0 = lo0 + (uint32_t)kLoSlots * lo_slot;       // 2 KiB per epilogue warp
     const uint32_t bar0 = smem_u32(bars);
     auto raw_full = [&](int s) { return bar0 + 8u * s; };
     auto raw_empty = [&](int s) { return bar0 + 8u * (kMaxRaw + s); };
@@ -486,32 +494,32 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
             const int BN = P.BN, n0 = I.nt * BN;
             const int row0 = I.mt * 128 + q * 32;
             float* cbase = P.C + ((size_t)I.split * P.M + row0) * P.ldc;
-            // The TMEM fragment (lane = row, 32 columns) goes through a swizzled 4 KiB tile of shared memory so
-            // that a store instruction writes 4 rows x 128 contiguous bytes instead of 32 rows x 16 bytes.
-            const uint32_t scratch = scratch0 + (uint32_t)q * 4096u;
-            const int rsub = lane >> 3, j4 = lane & 7;
+            // The TMEM fragment (lane = row, 16 columns) goes through a swizzled 2 KiB tile of shared memory so
+            // that a store instruction writes 8 rows x 64 contiguous bytes instead of 32 rows x 16 bytes.
+            const uint32_t scratch = scratch0 + (uint32_t)q * 2048u;
+            const int rsub = lane >> 2, j4 = lane & 3;
 #ifdef MCL_FUSED_PROF
             if (!(tab.pad0 & 4))
 #endif
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 0; c0 < BN; c0 += 16) {
                 if (n0 + c0 >= P.N) break;
-                uint32_t r[32];
-                tmem_ld32(tmem_base + acc * kAccStride + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                uint32_t r[16];
+                tmem_ld16(tmem_base + acc * kAccStride + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
                 tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    sts128(scratch + (uint32_t)lane * 128u + ((uint32_t)(j ^ (lane & 7)) << 4),
+                for (int j = 0; j < 4; ++j)
+                    sts128(scratch + (uint32_t)lane * 64u + ((uint32_t)(j ^ ((lane >> 1) & 3)) << 4),
                            make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
                                        __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
                 __syncwarp();
                 const int col = n0 + c0 + 4 * j4;
-                const bool col_ok = col < P.N && c0 + 4 * j4 < BN;
+                const bool col_ok = col < P.N;
                 float4 sc = make_float4(1.f, 1.f, 1.f, 1.f);
                 if (scale && col_ok) sc = __ldg(reinterpret_cast<const float4*>(P.col_scale + col));
 #pragma unroll
-                for (int p = 0; p < 8; ++p) {
-                    const int rr = p * 4 + rsub;
-                    float4 o = lds128(scratch + (uint32_t)rr * 128u + ((uint32_t)(j4 ^ (rr & 7)) << 4));
+                for (int p = 0; p < 4; ++p) {
+                    const int rr = p * 8 + rsub;
+                    float4 o = lds128(scratch + (uint32_t)rr * 64u + ((uint32_t)(j4 ^ ((rr >> 1) & 3)) << 4));
                     if (col_ok && row0 + rr < P.M) {
                         o.x *= sc.x; o.y *= sc.y; o.z *= sc.z; o.w *= sc.w;
                         *reinterpret_cast<float4*>(cbase + (size_t)rr * P.ldc + col) = o;

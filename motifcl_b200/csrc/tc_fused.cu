@@ -501,31 +501,39 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
 #ifdef MCL_FUSED_PROF
             if (!(tab.pad0 & 4))
 #endif
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                if (n0 + c0 >= P.N) break;
+            {
+                // software pipeline: the TMEM load of the next chunk and the scale of this one are in flight while
+                // the current chunk goes through shared memory to global memory
+                const uint32_t t0addr = tmem_base + acc * kAccStride + ((uint32_t)(q * 32) << 16);
                 uint32_t r[16];
-                tmem_ld16(tmem_base + acc * kAccStride + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
-                tmem_ld_wait();
+                int nchunks = 0;
+                for (int c0 = 0; c0 < BN && n0 + c0 < P.N; c0 += 16) ++nchunks;
+                if (nchunks > 0) tmem_ld16(t0addr, r);
+                for (int ci = 0; ci < nchunks; ++ci) {
+                    const int c0 = ci * 16;
+                    const int col = n0 + c0 + 4 * j4;
+                    const bool col_ok = col < P.N;
+                    float4 sc = make_float4(1.f, 1.f, 1.f, 1.f);
+                    if (scale && col_ok) sc = __ldg(reinterpret_cast<const float4*>(P.col_scale + col));
+                    tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    sts128(scratch + (uint32_t)lane * 64u + ((uint32_t)(j ^ ((lane >> 1) & 3)) << 4),
-                           make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                       __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
-                __syncwarp();
-                const int col = n0 + c0 + 4 * j4;
-                const bool col_ok = col < P.N;
-                float4 sc = make_float4(1.f, 1.f, 1.f, 1.f);
-                if (scale && col_ok) sc = __ldg(reinterpret_cast<const float4*>(P.col_scale + col));
+                    for (int j = 0; j < 4; ++j)
+                        sts128(scratch + (uint32_t)lane * 64u + ((uint32_t)(j ^ ((lane >> 1) & 3)) << 4),
+                               make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                           __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+                    __syncwarp();
+                    if (ci + 1 < nchunks) tmem_ld16(t0addr + (uint32_t)(c0 + 16), r);
 #pragma unroll
-                for (int p = 0; p < 4; ++p) {
-                    const int rr = p * 8 + rsub;
-                    float4 o = lds128(scratch + (uint32_t)rr * 64u + ((uint32_t)(j4 ^ ((rr >> 1) & 3)) << 4));
-                    if (col_ok && row0 + rr < P.M) {
-                        o.x *= sc.x; o.y *= sc.y; o.z *= sc.z; o.w *= sc.w;
-                        *reinterpret_cast<float4*>(cbase + (size_t)rr * P.ldc + col) = o;
+                    for (int p = 0; p < 4; ++p) {
+                        const int rr = p * 8 + rsub;
+                        float4 o = lds128(scratch + (uint32_t)rr * 64u + ((uint32_t)(j4 ^ ((rr >> 1) & 3)) << 4));
+                        if (col_ok && row0 + rr < P.M) {
+                            o.x *= sc.x; o.y *= sc.y; o.z *= sc.z; o.w *= sc.w;
+                            *reinterpret_cast<float4*>(cbase + (size_t)rr * P.ldc + col) = o;
+                        }
                     }
+                    __syncwarp();
                 }
-                __syncwarp();
             }
             tc_fence_before();
             mbar_arrive(acc_empty(acc));

@@ -109,9 +109,12 @@ def reduce_scatter_many(lins, group=None):
         for l in lins:
             reduce_scatter_rows(l.grad_w, l.gw_shard, l.rank, l.world, group)
         return
+    for l in lins:
+        if getattr(l, "_scatter_view", None) is None:
+            l._scatter_view = l.gw_shard[:l.rows]
     with dist._coalescing_manager(group=group, device=lins[0].grad_w.device, async_ops=False):
         for l in lins:
-            dist.reduce_scatter_tensor(l.gw_shard[:l.rows], l.grad_w, op=dist.ReduceOp.SUM, group=group)
+            dist.reduce_scatter_tensor(l._scatter_view, l.grad_w, op=dist.ReduceOp.SUM, group=group)
 
 
 def all_gather_many(lins, group=None):
@@ -121,9 +124,14 @@ def all_gather_many(lins, group=None):
             all_gather_rows(l.packed2, l.rank, l.world, group)
             all_gather_rows(l.scale, l.rank, l.world, group)
         return
-    shards = [(l.packed2[l.off:l.off + l.rows].clone(), l.scale[l.off:l.off + l.rows].clone()) for l in lins]
+    # In place: with equal shards a rank's rows already sit at rank * rows of the full tensor, which is where
+    # NCCL's all-gather expects the send buffer of an in-place call; no copies, and the views are made once.
+    for l in lins:
+        if getattr(l, "_gather_views", None) is None:
+            l._gather_views = (l.packed2[l.off:l.off + l.rows], l.scale[l.off:l.off + l.rows])
     with dist._coalescing_manager(group=group, device=lins[0].grad_w.device, async_ops=False):
-        for l, (p2s, scs) in zip(lins, shards):
+        for l in lins:
+            p2s, scs = l._gather_views
             dist.all_gather_into_tensor(l.packed2, p2s, group=group)
             dist.all_gather_into_tensor(l.scale, scs, group=group)
 

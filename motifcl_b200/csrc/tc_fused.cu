@@ -8,7 +8,7 @@
 // as tcgen05.mma.kind::tf32 on two terms per fp32 operand:
 //     a = hi + lo,   hi = a with the low 13 mantissa bits cleared (what the tensor core reads of a
 //                         raw fp32 word),  lo = tf32_round(a - hi)   (a - hi is exact)
-// so `hi` needs no work at all and `lo` is one elementwise pass over the tile in shared memory.
+// so `hi` is the raw word and `lo` one elementwise pass over the tile.
 // a.b is taken as lo.b + hi.b for an exact (ternary) b and as lo_a.hi_b + hi_a.lo_b + hi_a.hi_b for
 // two fp32 operands; the dropped lo.lo and the rounding of lo are ~2^-22 relative.
 //
@@ -22,6 +22,10 @@
 //   kFusedY   A = X  [tokens,in]  K-major              B = T [out,in]  K-major   (exact)
 //   kFusedDX  A = dY [tokens,out] K-major, x scale[k]  B = T [out,in]  MN-major  (exact)
 //   kFusedDW  A = dY [tokens,out] MN-major             B = X [tokens,in] MN-major
+//   kFusedYB / kFusedDXB  the two row products as tcgen05.mma.kind::f16: A split into two bf16 terms
+//             (hi = bf16(a), lo = bf16(a - hi), two k per TMEM column), B = the ternary digits as a K-major
+//             bf16 matrix (T [out,in] for Y, its transpose [in,out] for dX), k-tiles of 64: half the MMA
+//             instructions and hand-offs per unit of work; 16 mantissa bits, relative L2 ~2.5e-6
 // "MN-major" = the M (or N) index is the contiguous one in memory, the layout a transposed
 // operand has; the tensor core reads it in place (instruction-descriptor transpose bits), so no
 // transposed copy of an activation is ever made.

@@ -13,6 +13,12 @@ Prints ONE JSON line (rank 0).  `value` times the step with inputs resident in H
 times it from pinned HOST buffers (host->device copies of X and dY, device->host copy of the
 updated state / packed weights / scales) through the same C-ABI calls.  `--impl reference`
 times the CPU checker's restatement of the reference kernels on the host cores instead.
+
+The same line carries, under `also`, the other configurations of the metric: on one GPU the
+1B-scale stack (cfg3), the decode-GEMV sweep at M = 1, 4, 16 with the reference's own host GEMV
+beside it (cfg5) and the fused update at an HBM-resident size; on several GPUs the 8B-scale
+data-parallel stack (cfg4) and `dp_parity`, a byte comparison of every rank's updated row shards
+with the CPU checker run on the reduce-scattered gradient that the rank downloaded.
 """
 from __future__ import annotations
 
@@ -40,6 +46,9 @@ def workload(name: str):
     if name == "cfg3":
         return dict(cfg=3, tokens=16384, sigma=0.01, linears=synth.llama_linears(2048, 5632, 22),
                     desc="1B-scale: dim 2048, FFN 5632, 22 layers, 16384 tokens")
+    if name == "cfg4":
+        return dict(cfg=4, tokens=8192, sigma=0.01, linears=synth.llama_linears(4096, 14336, 32, kv_dim=1024),
+                    desc="8B-scale: dim 4096, FFN 14336, 32 layers, k/v 4096x1024, 8192 tokens per GPU")
     if name == "cfg1":
         return dict(cfg=1, tokens=256, sigma=0.02, linears=[synth.LinearShape("single", 288, 288)],
                     desc="single 288x288 counter linear, 256 tokens")
@@ -118,68 +127,117 @@ def measured_peaks():
     return 6650.0, 1400.0, "fallback"
 
 
-def cpu_reference_rate(wl, min_seconds: float = 10.0, max_tokens: int = 8192):
-    """Times the CPU checker (restatement of the reference kernels, all host cores) on a
-    bounded sample of the workload: one linear of every distinct shape, at up to `max_tokens`
-    tokens, repeated until `min_seconds` of CPU work; scaled to the full workload by
-    tokens * weights for the three contractions and by weights for the update."""
-    import oracle
-    from motifcl_b200 import synth
-    cores = len(os.sched_getaffinity(0))
-    oracle.port.set_threads(cores)
-    cfg, sigma = wl["cfg"], wl["sigma"]
-    n_s = min(wl["tokens"], max_tokens)
-    shapes = {}
-    for idx, l in enumerate(wl["linears"]):
-        shapes.setdefault((l.out_features, l.in_features), idx)
-    data = []
-    for (O, I), idx in shapes.items():
-        sc, v = synth.scale_v(cfg, idx, O, I)
-        data.append((O, I, synth.counters(cfg, idx, O, I).reshape(-1), sc, v,
-                     synth.activations(cfg, idx, n_s, I), synth.upstream_grad(cfg, idx, n_s, O, sigma)))
-    t_gemm = t_upd = 0.0
-    reps = 0
-    t0 = time.perf_counter()
-    while reps == 0 or time.perf_counter() - t0 < min_seconds:
-        for O, I, st, sc, v, x, dy in data:
-            a = time.perf_counter()
-            oracle.port.forward(x, st, sc, 11, O)
-            oracle.port.backward_input(dy, st, sc, 11, I)
-            gw = oracle.port.grad_w(dy, x)
-            b = time.perf_counter()
-            oracle.port.update_dense(st, sc, v, gw, 11, I, O, 0, 3e-3, 0.0, 0.9, 1e-3, 12345)
-            c = time.perf_counter()
-            t_gemm += b - a
-            t_upd += c - b
-        reps += 1
-    w_done = sum(d[0] * d[1] for d in data)
+def base_config(name, wl, world):
+    """The `config` object: identical in both arms (ours / reference) for the same command line."""
     alg = algorithmic(wl)
-    full = (t_gemm / reps) * (wl["tokens"] / n_s) * (alg["weights"] / w_done) + (t_upd / reps) * (alg["weights"] / w_done)
-    return dict(value=wl["tokens"] / full, unit=UNIT, cores=cores, kind="port",
-                sample=f"{len(data)} distinct linear shapes ({w_done} weights) at {n_s} tokens, {reps} repetitions "
-                       f"({time.perf_counter() - t0:.1f} s of CPU work); scaled by tokens*weights "
-                       f"(update by weights) to the full workload"), full
+    in_bytes = sum(4 * wl["tokens"] * (l.in_features + l.out_features) for l in wl["linears"])
+    return {"workload": f"{name}: {wl['desc']}", "tokens_per_gpu": wl["tokens"], "linears": len(wl["linears"]),
+            "weights": alg["weights"], "parallelism": f"dp{world}" if world > 1 else "single",
+            "l2": "inputs larger than L2 (X and dY of all linears: %.2f GB)" % (in_bytes / 1e9)}
+
+
+class CpuSample:
+    """A bounded sample of a workload for the CPU checker (the restatement of the reference kernels, all
+    host cores): one linear of every distinct shape at up to `max_tokens` tokens.  One `pass_once()` runs
+    forward, backward-to-input, weight gradient and the fused update of each; `scale` converts the time of
+    a pass to the time of a full step (products by tokens x weights, update by weights)."""
+
+    def __init__(self, wl, max_tokens: int = 8192):
+        import oracle
+        from motifcl_b200 import synth
+        self.orc = oracle.port
+        self.cores = len(os.sched_getaffinity(0))
+        self.orc.set_threads(self.cores)
+        self.wl = wl
+        cfg, sigma = wl["cfg"], wl["sigma"]
+        self.tokens = min(wl["tokens"], max_tokens)
+        shapes = {}
+        for idx, l in enumerate(wl["linears"]):
+            shapes.setdefault((l.out_features, l.in_features), idx)
+        self.data = []
+        for (O, I), idx in shapes.items():
+            sc, v = synth.scale_v(cfg, idx, O, I)
+            self.data.append((O, I, synth.counters(cfg, idx, O, I).reshape(-1), sc, v,
+                              synth.activations(cfg, idx, self.tokens, I),
+                              synth.upstream_grad(cfg, idx, self.tokens, O, sigma)))
+        self.weights = sum(d[0] * d[1] for d in self.data)
+        self.t_gemm = self.t_upd = 0.0
+        self.passes = 0
+
+    def pass_once(self):
+        o = self.orc
+        for O, I, st, sc, v, x, dy in self.data:
+            a = time.perf_counter()
+            o.forward(x, st, sc, 11, O)
+            o.backward_input(dy, st, sc, 11, I)
+            gw = o.grad_w(dy, x)
+            b = time.perf_counter()
+            o.update_dense(st, sc, v, gw, 11, I, O, 0, 3e-3, 0.0, 0.9, 1e-3, 12345)
+            c = time.perf_counter()
+            self.t_gemm += b - a
+            self.t_upd += c - b
+        self.passes += 1
+
+    def reset(self):
+        self.t_gemm = self.t_upd = 0.0
+        self.passes = 0
+
+    def full_step_seconds(self):
+        alg = algorithmic(self.wl)
+        wr = alg["weights"] / self.weights
+        return (self.t_gemm / self.passes) * (self.wl["tokens"] / self.tokens) * wr + (self.t_upd / self.passes) * wr
+
+    def describe(self, seconds):
+        return (f"{len(self.data)} distinct linear shapes ({self.weights} of {algorithmic(self.wl)['weights']} weights) at "
+                f"{self.tokens} tokens, {self.passes} passes ({seconds:.1f} s of CPU work); scaled to the full workload by "
+                f"tokens*weights (update by weights)")
+
+
+def cpu_reference_rate(wl, min_seconds: float = 10.0, max_tokens: int = 8192):
+    """The `cpu_baseline` object of the GPU arm: passes over the sample until `min_seconds` of CPU work."""
+    smp = CpuSample(wl, max_tokens)
+    t0 = time.perf_counter()
+    while smp.passes == 0 or time.perf_counter() - t0 < min_seconds:
+        smp.pass_once()
+    full = smp.full_step_seconds()
+    return dict(value=wl["tokens"] / full, unit=UNIT, cores=smp.cores, kind="port",
+                sample=smp.describe(time.perf_counter() - t0)), full
 
 
 def run_reference(args, wl):
+    """The reference arm: the CPU restatement of the reference kernels, all host cores, on the same bounded sample
+    as the GPU arm's cpu_baseline (every distinct linear shape at the full token count).  A step is a whole number of
+    passes over that sample, sized from the warm-up so that the timed region holds at least 10 s of CPU work;
+    `ms_per_step` is the MEASURED time of a step, `step_work_fraction` the work of such a step as a share of a full
+    workload step, and `value` = tokens / (ms_per_step / step_work_fraction)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    times = []
-    base = None
-    for i in range(args.warmup + args.steps):
-        base, full = cpu_reference_rate(wl, min_seconds=0.0, max_tokens=2048)
-        if i >= args.warmup:
-            times.append(full)
-    t = float(np.mean(times))
-    val = wl["tokens"] / t
-    base["value"] = val
+    smp = CpuSample(wl)
+    t0 = time.perf_counter()
+    for _ in range(max(args.warmup, 1)):
+        smp.pass_once()
+    t_pass = (time.perf_counter() - t0) / smp.passes
+    reps = max(1, int(np.ceil(10.0 / max(args.steps * t_pass, 1e-9))))
+    reps = min(reps, max(1, int(120.0 / max(args.steps * t_pass, 1e-9))))      # and the run stays within minutes
+    smp.reset()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for _ in range(reps):
+            smp.pass_once()
+    wall = time.perf_counter() - t0
+    full = smp.full_step_seconds()
+    val = wl["tokens"] / full
+    ms_step = wall / args.steps * 1e3
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {wl['desc']}", "tokens_per_step": wl["tokens"],
-                       "note": "CPU restatement of the reference kernels on the host cores (no GPU)"},
-            "cpu_baseline": base,
+            "config": base_config(args.workload, wl, args.gpus),
+            "step_work_fraction": (wall / args.steps) / full,
+            "passes_per_step": reps, "ms_per_full_step_scaled": full * 1e3,
+            "arm": "CPU restatement of the reference kernels on the host cores (no GPU); the reference's own kernels "
+                   "are OpenCL / Vulkan compute shaders with no host implementation of the contractions",
+            "cpu_baseline": dict(value=val, unit=UNIT, cores=smp.cores, kind="port", sample=smp.describe(wall)),
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
@@ -317,6 +375,7 @@ def run_micro(args):
                    "layers": len(shapes), "tokens": T}
         else:
             raise SystemExit("unknown --micro kind")
+    ctx.finish()        # raises if a kernel of the timed region reported an abandoned wait
     out.update({"frac": out["achieved"] / out["peak"], "peak_kind": peak_kind, "ms": ms, "micro": args.micro,
                 "steps": args.steps, "clocks": clk.summary(), "gpu_launches": ctx.launch_count})
     print(json.dumps(out))
@@ -509,14 +568,203 @@ def run_gemv_tp(args):
         dist.destroy_process_group()
 
 
+def time_wide_workload(ctx, wl, dev, steps, warmup, group=None):
+    """Times WideStack steps of a wide-layer workload (cfg3 on one GPU, cfg4 data-parallel) with CUDA events on
+    the launching stream; returns the record for the `also` object.  Inputs of one layer (X and dY of 16384 x 2048
+    floats and more) exceed L2, and consecutive layers use other buffers."""
+    import torch
+    import torch.distributed as dist
+    from motifcl_b200.step import Hyper, WideStack
+    world = 1 if group is None else dist.get_world_size(group)
+    stack = WideStack(ctx, wl["linears"], wl["tokens"], Hyper(), dev, wl["sigma"], group)
+    l0 = ctx.launch_count
+    for _ in range(warmup):
+        stack.step()
+    stack.sync_streams()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l1 = ctx.launch_count
+    e0.record()
+    for _ in range(steps):
+        stack.step()
+    stack.sync_streams()
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ctx.finish()
+    alg = algorithmic(wl)
+    hbm_peak, tf_peak, peak_kind = measured_peaks()
+    tf = alg["gemm_flop"] / (ms * 1e-3) / 1e12           # per GPU: the whole step (pre-passes and update included)
+    rec = {"workload": wl["desc"], "n_gpus": world, "tokens_per_gpu": wl["tokens"], "linears": len(wl["linears"]),
+           "weights": alg["weights"], "steps": steps, "warmup": warmup, "ms_per_step": ms,
+           "tokens_per_s": wl["tokens"] * world / (ms * 1e-3), "gpu_launches_per_step": (ctx.launch_count - l1) // steps,
+           "roofline": {"kernel": "whole step per GPU: operand splits, tc_gemm_kernel contractions (bf16 terms, 3 / 3 / 6 "
+                                  "products), fused update" + (", collectives overlapped" if world > 1 else ""),
+                        "bound": "tensor", "achieved": tf, "peak": tf_peak, "unit": "TFLOP/s", "frac": tf / tf_peak,
+                        "peak_kind": f"{peak_kind} bf16 sustained", "flop_per_step": alg["gemm_flop"],
+                        "pass_adjusted": {"bf16_pass_units_per_3_useful": 12.0, "ceiling": tf_peak / 4.0,
+                                          "frac": tf / (tf_peak / 4.0)}}}
+    if world > 1:
+        rec["collectives_per_step"] = {"reduce_scatter_bytes_in": 4.0 * alg["weights"],
+                                       "all_gather_bytes_out": alg["weights"] / 4.0 + 4.0 * alg["rows"]}
+    del stack
+    torch.cuda.empty_cache()
+    return rec
+
+
+def gemv_cpu_baseline():
+    """The reference's host GEMV, native::matmul_f32_m1 (MotifCL src/runtime/native_matmul.cpp:110-133: one thread, SSE,
+    dense fp32 [in, out] weights), compiled from the reference's own source where that library was built, timed on
+    one 4096 x 14336 matrix of the decode sweep and scaled by weights to the 32-layer sweep."""
+    import oracle
+    kind, fn = ("reference", oracle.ref.matmul_m1) if oracle.ref is not None else ("port", oracle.port.matmul_m1)
+    K, N = 4096, 14336
+    rng = np.random.default_rng(5)
+    b = rng.integers(-1, 2, size=(K, N)).astype(np.float32)
+    a = rng.standard_normal(K).astype(np.float32)
+    fn(a, b)
+    reps, t0 = 0, time.perf_counter()
+    while reps < 3 or time.perf_counter() - t0 < 3.0:
+        fn(a, b)
+        reps += 1
+    t = (time.perf_counter() - t0) / reps
+    sweep_weights = 32 * (3 * 4096 * 14336 + 2 * 4096 * 4096)
+    t_sweep = t * sweep_weights / (K * N)
+    return {"value": 1.0 / t_sweep, "unit": "tokens/s at M = 1", "cores": 1, "kind": kind,
+            "sample": f"matmul_f32_m1 on one dense fp32 [4096, 14336] matrix ({K * N * 4 / 1e6:.0f} MB), {reps} calls of "
+                      f"{t * 1e3:.1f} ms; scaled by weights to the 160 matrices of the sweep",
+            "ms_per_sweep_scaled": t_sweep * 1e3, "gb_per_s": K * N * 4 / t / 1e9}
+
+
+def run_also(args):
+    """--micro also: the other single-GPU configurations of the metric, each timed like its --micro form; one JSON
+    object.  Run by the default benchmark in a child process so that a failure here cannot take the main line down."""
+    import io
+    import contextlib
+    out = {}
+
+    def micro(spec, steps, warmup):
+        a = argparse.Namespace(**vars(args))
+        a.micro, a.steps, a.warmup = spec, steps, warmup
+        buf = io.StringIO()
+        with contextlib.redirect_stdout(buf):
+            run_micro(a)
+        return json.loads(buf.getvalue().strip().splitlines()[-1])
+
+    try:
+        import torch
+        from motifcl_b200 import Context
+        torch.cuda.set_device(0)
+        torch.cuda.set_stream(torch.cuda.Stream(device=0))
+        ctx = Context.on_torch_stream(0)
+        out["cfg3"] = time_wide_workload(ctx, workload("cfg3"), "cuda:0", 2, 1)
+        ctx.close()
+    except Exception as exc:       # noqa: BLE001
+        out["cfg3"] = {"error": repr(exc)[:300]}
+    try:
+        sweeps = {f"M{m}": micro(f"gemvsweep:{m}", 20, 5) for m in (1, 4, 16)}
+        out["cfg5"] = {"workload": "decode GEMV sweep: 32 layers x (w1, w3 14336x4096; w2 4096x14336; q, o 4096x4096) as 2-bit "
+                                   "words, every matrix distinct (1.68 GB: larger than L2)",
+                       "sweeps": {k: {"ms_per_sweep": v["ms"], "tokens_per_s": v["tokens_per_s"], "us_per_matrix": v["us_per_matrix"],
+                                      "roofline": {"bound": "hbm", "achieved": v["achieved"], "peak": v["peak"], "unit": "GB/s",
+                                                   "frac": v["frac"], "peak_kind": v["peak_kind"],
+                                                   "bytes_per_sweep": v["bytes_per_launch"]}}
+                                  for k, v in sweeps.items()}}
+        out["cfg5"]["cpu_baseline"] = gemv_cpu_baseline()
+    except Exception as exc:       # noqa: BLE001
+        out["cfg5"] = {"error": repr(exc)[:300]}
+    try:
+        u = micro("update:8192x4096", 50, 5)
+        out["update_hbm"] = {"workload": "fused counter update of an 8192 x 4096 layer, buffer sets rotated (larger than L2)",
+                             "ms": u["ms"], "roofline": {"bound": "hbm", "achieved": u["achieved"], "peak": u["peak"],
+                                                         "unit": "GB/s", "frac": u["frac"], "peak_kind": u["peak_kind"],
+                                                         "bytes_per_launch": u["bytes_per_launch"]}}
+    except Exception as exc:       # noqa: BLE001
+        out["update_hbm"] = {"error": repr(exc)[:300]}
+    print(json.dumps(out))
+
+
+def also_in_child(timeout_s: int = 420):
+    import subprocess
+    try:
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--micro", "also"], capture_output=True, text=True,
+                           timeout=timeout_s)
+        lines = [ln for ln in r.stdout.strip().splitlines() if ln.startswith("{")]
+        if r.returncode == 0 and lines:
+            return json.loads(lines[-1])
+        return {"error": f"child exited {r.returncode}: {r.stderr[-300:]}"}
+    except Exception as exc:       # noqa: BLE001
+        return {"error": repr(exc)[:300]}
+
+
+def dp_parity_check(stack, xs, dys, dev, group):
+    """After the timed region, on every rank: snapshot the local row shards, run ONE more data-parallel step, download
+    the reduce-scattered gradient shard and the updated shard, run the CPU checker's update on the downloaded gradient
+    with the shard's row offset and the step's seed, and compare bytes.  Also: the all-gathered 2-bit words equal the
+    checker's pack2 of the gathered states, and the replicated scales equal the gathered shard scales."""
+    import torch
+    import torch.distributed as dist
+    import oracle
+    o = oracle.port
+    o.set_threads(max(1, len(os.sched_getaffinity(0)) // dist.get_world_size(group)))
+    h = stack.h
+    stack.sync_streams()
+    torch.cuda.synchronize()
+    pre = []
+    for l in stack.linears:
+        sh = l.sharded
+        sl = slice(sh.off, sh.off + sh.rows)
+        pre.append((sh.state.cpu().numpy().copy(), sh.scale[sl].cpu().numpy().copy(), sh.v.cpu().numpy().copy()))
+    seed = (12345 + stack.step_index) & 0xFFFFFFFF
+    stack.step(xs, dys)
+    stack.sync_streams()
+    torch.cuda.synchronize()
+    bad = 0
+    checked = 0
+    for l, (st0, sc0, v0) in zip(stack.linears, pre):
+        sh = l.sharded
+        I = l.shape.in_features
+        sl = slice(sh.off, sh.off + sh.rows)
+        gw = sh.gw_shard[:sh.rows].cpu().numpy()
+        e = o.update_dense(st0, sc0, v0, gw, h.C, I, sh.rows, sh.off, h.lr, h.lr_scale, h.rms_beta, h.rms_eps, seed)
+        bad += int(not np.array_equal(sh.state.cpu().numpy(), e[0]))
+        bad += int(not np.array_equal(sh.scale[sl].cpu().numpy().view(np.uint32), e[1].view(np.uint32)))
+        bad += int(not np.array_equal(sh.v.cpu().numpy().view(np.uint32), e[2].view(np.uint32)))
+        bad += int(not np.array_equal(sh.packed2[sl].cpu().numpy().view(np.uint32), e[3]))
+        # replicated tensors: gather every rank's state shard, pack on the host, compare with the local full copy
+        world = dist.get_world_size(group)
+        parts = [torch.empty_like(sh.state) for _ in range(world)]
+        dist.all_gather(parts, sh.state, group=group)
+        full_state = torch.cat(parts).cpu().numpy()
+        bad += int(not np.array_equal(sh.packed2.cpu().numpy().view(np.uint32), o.pack2(full_state, h.C, I, sh.O)))
+        checked += 5
+    t = torch.tensor([bad, checked], device=dev, dtype=torch.int64)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+    bad, checked = int(t[0].item()), int(t[1].item())
+    return {"result": "bit-exact" if bad == 0 else f"{bad} tensors differ", "tensors_compared": checked,
+            "what": "per rank and linear: state / scale / v / 2-bit shard after one step vs the CPU checker's update of the "
+                    "downloaded reduce-scattered gradient (row_offset, seed of the step); all-gathered 2-bit words vs "
+                    "pack2 of the gathered states", "seed": seed}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-also", action="store_true", help="skip the other configurations (cfg3 / cfg5 / update; cfg4 and "
+                                                            "dp_parity on several GPUs)")
     ap.add_argument("--lanes", type=int, default=8, help="contexts (streams) that independent linears are spread over")
     ap.add_argument("--no-group", action="store_true", help="one call per linear (spread over --lanes) instead of the grouped step call")
     ap.add_argument("--eager", action="store_true", help="do not record the step into one batch (for per-kernel profiling)")
@@ -526,6 +774,8 @@ def main():
         return run_gemv_tp(args)
     if args.micro == "refperf":
         return run_refperf(args)
+    if args.micro == "also":
+        return run_also(args)
     if args.micro and args.micro.startswith("trainer15m"):
         return run_trainer15m(args)
     if args.micro:
@@ -552,6 +802,18 @@ def main():
     torch.cuda.set_stream(torch.cuda.Stream(device=local))   # a recordable (non-default) stream
     ctx = Context.on_torch_stream(local)
     cfg, T, sigma = wl["cfg"], wl["tokens"], wl["sigma"]
+    if any(l.in_features > 1024 or l.out_features > 1024 for l in wl["linears"]):
+        # wide-layer workloads keep activations per shape, not per layer
+        rec = time_wide_workload(ctx, wl, dev, args.steps, max(args.warmup, 1), group)
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": rec["tokens_per_s"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                              "warmup": max(args.warmup, 1), "ms_per_step": rec["ms_per_step"], "higher_is_better": True,
+                              "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                              "config": base_config(args.workload, wl, world), "roofline": rec["roofline"],
+                              "gpu_launches": rec["gpu_launches_per_step"] * args.steps, "e2e": None, "cpu_baseline": None}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- inputs: pinned host copies (for e2e) and device-resident copies (for value) ----------
     lin_states, xs_h, dys_h = [], [], []
@@ -574,54 +836,62 @@ def main():
         torch.cuda.synchronize()
 
     def timed(fn, steps, warmup):
+        """K steps between two events on the launching stream (the figure that is reported), with an event after every
+        step for the median."""
         for _ in range(warmup):
             fn()
+        stack.sync_streams()
         barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
         l0 = ctx.launch_count
-        e0.record()
-        for _ in range(steps):
+        evs[0].record()
+        for i in range(steps):
             fn()
-        e1.record()
+            if i + 1 < steps:
+                evs[i + 1].record()
+        stack.sync_streams()            # several GPUs: the tail of the last step runs on the communication stream
+        evs[steps].record()
         barrier()
-        ms = e0.elapsed_time(e1)
+        ms = evs[0].elapsed_time(evs[steps])
+        per = sorted(evs[i].elapsed_time(evs[i + 1]) for i in range(steps))
         if world > 1:
             t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
-        return ms / steps, (ctx.launch_count - l0)
+        return ms / steps, (ctx.launch_count - l0), per[len(per) // 2]
 
     # ---- device-resident throughput ------------------------------------------------------
     with ClockSampler(local) as clk:
-        ms_step, launches = timed(lambda: stack.step(xs, dys, recorded=not args.eager), args.steps, max(args.warmup, 3))
+        ms_step, launches, ms_median = timed(lambda: stack.step(xs, dys, recorded=not args.eager), args.steps,
+                                             max(args.warmup, 3))
     clocks = clk.summary()
+    if world > 1:
+        launches += stack.comm_launches()
 
     # ---- roofline of the dominant kernel: timed alone on the launching stream ---------------
     alg = algorithmic(wl)
     hbm_peak, tf_peak, peak_kind = measured_peaks()
 
-    ms_upd, n_upd = timed(stack.update_only, args.steps, 3)
+    ms_upd, n_upd, _ = timed(stack.update_only, args.steps, 3)
     if args.eager or args.no_group:
-        ms_gemm, n_gemm = timed(lambda: stack.products_only(xs, dys), args.steps, 3)
+        ms_gemm, n_gemm, _ = timed(lambda: stack.products_only(xs, dys), args.steps, 3)
     else:
         # recorded like the step itself, so that the figure is the kernels' time and not the host's per-call work
         # (an eager grouped call encodes ~170 tensor maps and builds its tables before it launches)
         prod_batch = stack._record(lambda: stack.products_only(xs, dys))
-        ms_gemm, n_gemm = timed(prod_batch.launch, args.steps, 3)
+        ms_gemm, n_gemm, _ = timed(prod_batch.launch, args.steps, 3)
         prod_batch.close()
     gemm_tf = alg["gemm_flop"] / (ms_gemm * 1e-3) / 1e12
     gemm_gbs = alg["gemm_bytes"] / (ms_gemm * 1e-3) / 1e9
     upd_gbs = alg["update_bytes"] / world / (ms_upd * 1e-3) / 1e9      # each rank updates its row shard
     # The scope table counts the three products as 6*tokens*weights flop against the dense bf16 rate.  Two more
     # views explain the number: the pass-adjusted ceiling (fp32 fidelity costs 2 + 2 bf16 products for Y and dX and
-    # 3 tf32 products at half the bf16 rate for dW on narrow layers = 10 bf16-pass units per 3 useful; 3 + 3 + 6 bf16
-    # products = 12 units on wide ones) and the HBM view (algorithmic bytes of the products at the copy bandwidth), which is the larger ideal
-    # time when layers are narrow.
-    narrow = all(l.in_features <= 1024 and l.out_features <= 1024 for l in wl["linears"])
-    units = 10.0 if narrow else 12.0
+    # 3 tf32 products at half the bf16 rate for dW on narrow layers = 10 bf16-pass units per 3 useful) and the HBM view
+    # (algorithmic bytes of the products at the copy bandwidth), which is the larger ideal time when layers are narrow.
+    units = 10.0
     traffic = MEASURED_TRAFFIC_BYTES.get(args.workload)
-    roofline = {"kernel": "counter-linear contractions (Y, dX, dW) of all linears: " +
-                          ("tc_fused_kernel (bf16 / tf32 hi-lo terms, A operands in tensor memory)" if narrow else "tc_gemm_kernel (bf16 term planes)"),
+    roofline = {"kernel": "counter-linear contractions (Y, dX, dW) of all linears: tc_fused_kernel (bf16 / tf32 hi-lo terms, "
+                          "A operands in tensor memory)",
                 "bound": "tensor", "achieved": gemm_tf, "peak": tf_peak, "unit": "TFLOP/s", "frac": gemm_tf / tf_peak,
                 "peak_kind": f"{peak_kind} bf16 sustained", "traffic": traffic,
                 "flop_per_step": alg["gemm_flop"], "ms": ms_gemm,
@@ -633,8 +903,8 @@ def main():
                              "ideal_ms_tensor_single_pass": alg["gemm_flop"] / (tf_peak * 1e12) * 1e3},
                 "update": {"bound": "hbm", "achieved": upd_gbs, "peak": hbm_peak, "unit": "GB/s",
                            "frac": upd_gbs / hbm_peak, "bytes_per_step": alg["update_bytes"], "ms": ms_upd,
-                           "note": "all 42 state tensors fit in L2 at this workload; see the cfg3-scale "
-                                   "update numbers in profiles/ for the HBM-resident case"}}
+                           "note": "all 42 state tensors fit in L2 at this workload; the HBM-resident figure is "
+                                   "also.update_hbm"}}
 
     # ---- end to end from pinned host memory --------------------------------------------------
     out_h = [(torch.empty_like(l.state, device="cpu").pin_memory(),
@@ -668,37 +938,55 @@ def main():
             stack.step(xs, dys)
         e2e_seed[0] += 1
         consumed.record(main_stream)
+        stack.sync_streams()                      # the updated shards come from the communication stream
         for l, o in zip(stack.linears, out_h):
             o[0].copy_(l.state, non_blocking=True)
             o[1].copy_(l.packed2, non_blocking=True)
             o[2].copy_(l.scale, non_blocking=True)
             o[3].copy_(l.v, non_blocking=True)
-    ms_e2e, _ = timed(e2e_step, max(2, args.steps // 4), 2)
+    ms_e2e, _, _ = timed(e2e_step, max(2, args.steps // 4), 2)
 
     cpu = None
+    also = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu, _ = cpu_reference_rate(wl)
+    if world == 1 and not args.no_also:
+        also = also_in_child()
+    dp_parity = None
+    if world > 1 and not args.no_also:
+        try:
+            dp_parity = dp_parity_check(stack, xs, dys, dev, group)
+        except Exception as exc:       # noqa: BLE001
+            dp_parity = {"result": "not run", "error": repr(exc)[:300]}
+        del stack, xs, dys, lin_states
+        torch.cuda.empty_cache()
+        try:
+            also = {"cfg4": time_wide_workload(ctx, workload("cfg4"), dev, 2, 1, group)}
+        except Exception as exc:       # noqa: BLE001
+            also = {"cfg4": {"error": repr(exc)[:300]}}
 
     if rank == 0:
         line = {"metric": METRIC, "value": T * world / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+                "ms_per_step_median": ms_median,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
                 "data": "synthetic",
-                "config": {"workload": f"{args.workload}: {wl['desc']}", "tokens_per_gpu": T,
-                           "linears": len(wl["linears"]), "weights": alg["weights"],
-                           "parallelism": f"dp{world}" if world > 1 else "single",
-                           "l2": "inputs larger than L2 (X and dY of all linears: %.2f GB)" % (in_bytes / 1e9),
-                           "precision": "fp32 in/out; layers up to 1024 features: Y and dX = tcgen05 bf16 on two bf16 terms of the fp32 "
-                                        "activations against exact bf16 ternary digits (2 products), dW = tcgen05 tf32 on "
-                                        "hi/lo terms of both operands (3 products); wider layers: tcgen05 bf16 on 3 "
-                                        "terms (3 / 6 products); fp32 accumulate in TMEM; relative L2 <= 1e-5 vs the "
-                                        "fp32 reference sums (tested; measured <= 6e-6); counter update bit-exact",
-                           "grouped_call": not args.no_group, "lanes": 1 if not args.no_group else args.lanes,
-                           "recorded_batch": not args.eager},
+                "config": base_config(args.workload, wl, world),
+                "arm": {"precision": "fp32 in/out; layers up to 1024 features: Y and dX = tcgen05 bf16 on two bf16 terms of the fp32 "
+                                     "activations against exact bf16 ternary digits (2 products), dW = tcgen05 tf32 on "
+                                     "hi/lo terms of both operands (3 products); wider layers: tcgen05 bf16 on 3 "
+                                     "terms (3 / 6 products); fp32 accumulate in TMEM; relative L2 <= 1e-5 vs the "
+                                     "fp32 reference sums (tested; measured <= 6e-6); counter update bit-exact",
+                        "grouped_call": not args.no_group, "lanes": 1 if not args.no_group else args.lanes,
+                        "recorded_batch": not args.eager,
+                        "collectives": ("reduce-scatter under the row products, update + all-gather under the next "
+                                        "step's weight gradients (communication stream)") if world > 1 else None},
                 "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
                 "e2e": {"value": T * world / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
                         "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes},
-                "cpu_baseline": cpu}
+                "cpu_baseline": cpu, "also": also}
+        if dp_parity is not None:
+            line["dp_parity"] = dp_parity
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -164,7 +164,9 @@ typedef struct mcl_cuda_linear_desc {
     float* v;                /* [out], updated */
     float* y;                /* [batch, out] or NULL */
     float* grad_x;           /* [batch, in] or NULL */
-    float* grad_w;           /* [out, in] */
+    float* grad_w;           /* [out, in], or NULL to skip the weight gradient (then update_rows must be 0): a
+                                data-parallel rank forms the weight gradients in one call, starts their
+                                reduce-scatter, and forms y / grad_x in a second call that runs under it */
     uint32_t* packed2_out;   /* [out, in/16] or NULL */
     size_t in_features, out_features, batch;
     size_t update_rows, row_offset;   /* as in mcl_cuda_counter_linear_step */
@@ -196,8 +198,8 @@ int mcl_cuda_counter_update_dense_many(mcl_cuda_ctx* ctx, const mcl_cuda_update_
  * :113-156): y = x W^T; grad_x = (grad_out . scale) T from the PRE-update state; grad_w =
  * grad_out^T x; then the fused update of `rows` rows starting at `row_offset` (pass rows =
  * out_features, row_offset = 0 for the whole layer).  Shares the operand splits between the
- * three products.  y, grad_x and packed2_out may be NULL to skip that output; grad_w must hold
- * out*in floats.  With update_rows == 0 the update is skipped (the caller reduces grad_w
+ * three products.  y, grad_x and packed2_out may be NULL to skip that output; grad_w holds
+ * out*in floats (NULL skips it and needs update_rows == 0).  With update_rows == 0 the update is skipped (the caller reduces grad_w
  * across ranks first and then calls mcl_cuda_counter_update_dense on its shard). ---- */
 int mcl_cuda_counter_linear_step(mcl_cuda_ctx* ctx, const float* x, const float* grad_out,
                                  uint8_t* state, float* scale, float* v, float* y, float* grad_x,

@@ -11,7 +11,8 @@ import re
 import subprocess
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "lib", "libmotifcl_cuda.so")
+# MOTIFCL_CUDA_LIBRARY names another build of the library (same C ABI) to load instead of the in-tree one
+LIB_PATH = os.environ.get("MOTIFCL_CUDA_LIBRARY") or os.path.join(_PKG, "lib", "libmotifcl_cuda.so")
 HEADER_PATH = os.path.join(os.path.dirname(_PKG), "include", "motifcl_cuda.h")
 
 

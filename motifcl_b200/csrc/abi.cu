@@ -180,10 +180,18 @@ int check_device_error(mcl_cuda_ctx* ctx) {
     if (e != cudaSuccess) return fail_cuda(ctx, "error-word read", e);
     if (w != 0) {
         cudaMemset(ctx->err_word, 0, sizeof(int));
-        const char* who = w == 1 ? "TMA producer (slot never released)" : w == 2 ? "MMA issuer (tile never arrived)"
-                                                                                 : "epilogue (accumulator never completed)";
-        return fail(ctx, MCL_CUDA_ECUDA, std::string("tensor-core kernel gave up a bounded wait: ") + who +
-                                             "; results of that call are invalid");
+        const char* who;
+        switch (w) {
+            case 1: case 11: who = "copy lane (ring slot never released)"; break;
+            case 2: case 12: who = "MMA lane (operand tile never arrived)"; break;
+            case 13: case 15: who = "epilogue / converter warps (accumulator or tile never completed)"; break;
+            case 14: who = "MMA lane (accumulator never drained)"; break;
+            case 16: case 17: who = "work-item queue (scheduler lane and its readers lost step)"; break;
+            case 21: who = "wide-row counter update (a row slot was never marked ready or released)"; break;
+            default: who = "epilogue (accumulator never completed)"; break;
+        }
+        return fail(ctx, MCL_CUDA_ECUDA, std::string("a kernel gave up a bounded wait: ") + who + " [code " +
+                                             std::to_string(w) + "]; results of that call are invalid");
     }
     return MCL_CUDA_OK;
 }
@@ -561,7 +569,7 @@ int mcl_cuda_counter_update_dense(mcl_cuda_ctx* ctx, uint8_t* state, float* scal
     DeviceGuard guard(ctx->device);
     cudaError_t e = mcl::launch_counter_update_dense(state, scale, v, grad_w, packed2_out, (int)C,
                                                      (int)in_features, (int)rows, (int)row_offset, lr,
-                                                     lr_scale, rms_beta, rms_eps, seed, ctx->seed_offset,
+                                                     lr_scale, rms_beta, rms_eps, seed, ctx->seed_offset, ctx->err_word,
                                                      ctx->sm_count, ctx->max_smem, ctx->stream);
     if (e == cudaErrorInvalidConfiguration)
         return fail(ctx, MCL_CUDA_EUNSUPPORTED, "counter update: in_features too large for one row in shared memory");
@@ -800,7 +808,8 @@ int mcl_cuda_counter_linear_step(mcl_cuda_ctx* ctx, const float* x, const float*
     MCL_TRY(check_ptr(ctx, op, "state", state, 1));
     MCL_TRY(check_ptr(ctx, op, "scale", scale, 4));
     MCL_TRY(check_ptr(ctx, op, "v", v, 4));
-    MCL_TRY(check_ptr(ctx, op, "grad_w", grad_w, 16));
+    if (grad_w) MCL_TRY(check_ptr(ctx, op, "grad_w", grad_w, 16));
+    else if (update_rows != 0) return fail(ctx, MCL_CUDA_EINVAL, "counter linear step: an update needs grad_w");
     if (row_offset + update_rows > out_features)
         return fail(ctx, MCL_CUDA_EINVAL, "counter linear step: update rows exceed out_features");
     const size_t state_row = in_features / 4 * 3;
@@ -831,7 +840,9 @@ int mcl_cuda_counter_linear_step_many(mcl_cuda_ctx* ctx, const mcl_cuda_linear_d
         MCL_TRY(check_ptr(ctx, op, "x", L.x, 4));
         MCL_TRY(check_ptr(ctx, op, "grad_out", L.grad_out, 4));
         MCL_TRY(check_ptr(ctx, op, "scale", L.scale, 4));
-        MCL_TRY(check_ptr(ctx, op, "grad_w", L.grad_w, 16));
+        if (L.grad_w) MCL_TRY(check_ptr(ctx, op, "grad_w", L.grad_w, 16));
+        else if (L.update_rows != 0) return fail(ctx, MCL_CUDA_EINVAL, "counter linear step (many): an update needs grad_w");
+        if (!L.grad_w && !L.y && !L.grad_x) return fail(ctx, MCL_CUDA_EINVAL, "counter linear step (many): a layer asks for no product");
         if (L.state != nullptr) {
             MCL_TRY(check_ptr(ctx, op, "v", L.v, 4));
         } else {
@@ -879,7 +890,8 @@ int mcl_cuda_counter_linear_step_many(mcl_cuda_ctx* ctx, const mcl_cuda_linear_d
     };
     for (size_t gi = 0; gi < ng; ++gi) {
         const mcl_cuda_linear_desc& L = layers[grouped[gi]];
-        t_off[gi] = cv.reserve(L.out_features * L.in_features * 4);
+        t_off[gi] = cv.reserve((L.y || L.grad_x) ? L.out_features * L.in_features * 4 : 0);
+        if (!L.grad_w) { k_off[gi] = cv.reserve(0); continue; }
         mcl::FusedProblem p = mcl::FusedProblem();
         p.mode = mcl::kFusedDW; p.M = (int)L.out_features; p.N = (int)L.in_features; p.K = (int)L.batch;
         k_off[gi] = cv.reserve(mcl::fused_plan(&p, target_items, depth) * 4);
@@ -888,21 +900,24 @@ int mcl_cuda_counter_linear_step_many(mcl_cuda_ctx* ctx, const mcl_cuda_linear_d
     void* wsp = nullptr;
     MCL_TRY(ws_reserve(ctx, cv.off, &wsp));
     char* w = static_cast<char*>(wsp);
-    // 1. ternary digits of every layer as bf16: T [O][I] in the first half of the layer's block, its transpose after it
+    // 1. ternary digits of every layer with a row product, as bf16: T [O][I] in the first half of the layer's block,
+    // its transpose after it
     {
-        std::vector<const uint8_t*> st(ng);
-        std::vector<const uint32_t*> p2(ng);
-        std::vector<void*> T(ng), Tt(ng);
-        std::vector<int> Os(ng), Is(ng);
+        std::vector<const uint8_t*> st;
+        std::vector<const uint32_t*> p2;
+        std::vector<void*> T, Tt;
+        std::vector<int> Os, Is;
         for (size_t gi = 0; gi < ng; ++gi) {
             const mcl_cuda_linear_desc& L = layers[grouped[gi]];
-            st[gi] = L.state; p2[gi] = L.packed2_in;
-            T[gi] = w + t_off[gi]; Tt[gi] = w + t_off[gi] + L.out_features * L.in_features * 2;
-            Os[gi] = (int)L.out_features; Is[gi] = (int)L.in_features;
+            if (!L.y && !L.grad_x) continue;
+            st.push_back(L.state); p2.push_back(L.packed2_in);
+            T.push_back(w + t_off[gi]); Tt.push_back(w + t_off[gi] + L.out_features * L.in_features * 2);
+            Os.push_back((int)L.out_features); Is.push_back((int)L.in_features);
         }
         int launches = 0;
-        cudaError_t e = mcl::launch_ternary_bf16_group(st.data(), p2.data(), T.data(), Tt.data(), Os.data(), Is.data(), (int)ng, (int)C,
-                                                       ctx->sm_count, ctx->stream, &launches);
+        cudaError_t e = st.empty() ? cudaSuccess
+                                   : mcl::launch_ternary_bf16_group(st.data(), p2.data(), T.data(), Tt.data(), Os.data(), Is.data(), (int)st.size(), (int)C,
+                                                                    ctx->sm_count, ctx->stream, &launches);
         ctx->launches += launches;
         if (e != cudaSuccess) return fail_cuda(ctx, op, e);
     }
@@ -926,6 +941,7 @@ int mcl_cuda_counter_linear_step_many(mcl_cuda_ctx* ctx, const mcl_cuda_linear_d
         for (size_t gi = 0; gi < ng; ++gi) {
             const mcl_cuda_linear_desc& L = layers[grouped[gi]];
             const size_t I = L.in_features, O = L.out_features, Nt = L.batch;
+            if (!L.grad_w) continue;
             mcl::FusedProblem p = mcl::FusedProblem();
             p.mode = mcl::kFusedDW; p.M = (int)O; p.N = (int)I; p.K = (int)Nt;
             mcl::fused_plan(&p, target_items, depth);
@@ -1013,7 +1029,7 @@ int mcl_cuda_counter_linear_step_many(mcl_cuda_ctx* ctx, const mcl_cuda_linear_d
         if (!ud.empty()) {
             int launches = 0;
             cudaError_t e = mcl::launch_counter_update_group(ud.data(), (int)ud.size(), (int)C, lr, lr_scale, rms_beta, rms_eps, seed,
-                                                             ctx->seed_offset, ctx->sm_count, ctx->max_smem, ctx->stream, &launches);
+                                                             ctx->seed_offset, ctx->err_word, ctx->sm_count, ctx->max_smem, ctx->stream, &launches);
             ctx->launches += launches;
             if (e == cudaErrorNotSupported) {
                 for (const mcl::UpdateDesc& u : ud)
@@ -1054,7 +1070,7 @@ int mcl_cuda_counter_update_dense_many(mcl_cuda_ctx* ctx, const mcl_cuda_update_
     DeviceGuard guard(ctx->device);
     int launches = 0;
     cudaError_t e = mcl::launch_counter_update_group(ud.data(), (int)ud.size(), (int)C, lr, lr_scale, rms_beta, rms_eps, seed,
-                                                     ctx->seed_offset, ctx->sm_count, ctx->max_smem, ctx->stream, &launches);
+                                                     ctx->seed_offset, ctx->err_word, ctx->sm_count, ctx->max_smem, ctx->stream, &launches);
     ctx->launches += launches;
     if (e == cudaErrorNotSupported) {
         for (const mcl::UpdateDesc& u : ud)

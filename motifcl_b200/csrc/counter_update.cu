@@ -26,6 +26,7 @@
 // packed weights out = 5.75 B.
 #include "counter_codec.cuh"
 #include "kernels.h"
+#include "tc_ptx.cuh"
 
 namespace mcl {
 
@@ -333,23 +334,21 @@ counter_update_dense_kernel(const UpdParams p) {
 //   * the right shifts of the integer hash are issued as mul.hi (FMA pipe) because the ALU
 //     pipe is the busiest one in this kernel.
 constexpr int kMaxRowsU16 = 64;
-constexpr int kTail16 = 256;          // tail-table row of the fast variant: rounded counter in [-128, 127]
+#ifndef MCL_UPD_CTAS_PER_SM
+#define MCL_UPD_CTAS_PER_SM 4         // resident CTAs per SM the 16-weight kernel is compiled and sized for
+#endif
+constexpr int kUpdCtasPerSm = MCL_UPD_CTAS_PER_SM;
 constexpr int kPairs = kUpdThreads / 64;
 
 __device__ __forceinline__ int swz4(int f) {          // float4 index -> swizzled float4 index
     return (f & ~3) | ((f & 3) ^ ((f >> 3) & 3));
 }
 __device__ __forceinline__ uint32_t shr_mulhi(uint32_t x, uint32_t pow2) {   // x >> (32 - log2(pow2))
-    uint32_t r;
-    asm("mul.hi.u32 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(pow2));
-    return r;
+    return pow2 == 65536u ? x >> 16 : x >> 15;
 }
 
 __device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
     uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v;
-}
-__device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
-    uint32_t v; asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a)); return v;
 }
 __device__ __forceinline__ float2 lds_f2(uint32_t a) {
     float2 v; asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a)); return v;
@@ -363,22 +362,194 @@ __device__ __forceinline__ void sts_u32(uint32_t a, uint32_t v) {
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
 }
 
+__device__ __forceinline__ float fmax_nan(float a, float b) {          // max that keeps a NaN operand
+    float r; asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r;
+}
+
+// Per-row constants of the tick (32 bytes).  gw / dn is formed without a division: yh = RN(1 / dn) and
+// yl = RN((1 - dn * yh) * yh) make yh + yl equal 1 / dn to ~2^-47, so p = RN(gw * yh + RN(gw * yl)) is one of the
+// two floats next to gw / dn, and one residual step  q = RN(p + (gw - dn * p) * yh)  (the residual is exact in an
+// FMA) is the correctly rounded quotient -- the value the reference's IEEE division gives (Markstein's theorem:
+// a faithful quotient, a reciprocal within 2^-24 relative, one FMA correction).  The argument needs no underflow:
+// it holds for dn in [2^-32, 2^32] and |q| >= 2^-64; `qlo` is that bound for rows whose dn is in range and NaN for
+// the others, and a unit whose smallest |q| fails  qmin >= qlo  is looked at again and, unless its small quotients
+// are exact zeros, redone with the division.
+struct RowK {
+    float yh, yl, dn, k_tick, k_reb, qlo, pad0, pad1;
+};
+
+// Tick table of the 16-weight kernel: for weight position k in its group, old ternary digit t in {-1,0,1,2} and
+// rounded counter ccv in [-64, 63]:  new code << 6k  |  (new digit + 1) << (24 + 2k), so that the four look-ups of
+// a group ADD UP to its 24-bit state word and its byte of 2-bit fields.
+constexpr int kTickN = 128;                      // entries per (k, t)
+constexpr int kTickHalf = kTickN / 2;
+constexpr int kTickBytes = 4 * 4 * kTickN * 4;   // 8 KiB
+constexpr float kTickValMax = (float)(kTickHalf - 2);   // |counter + tick| below this stays inside the table
+
+// The tick of one 16-weight unit (3 state words in, 3 state words and one word of 2-bit fields out), shared by the
+// kernels below.  All operands are shared-memory addresses: sa_rowk the row's RowK, rt its 64-entry row table, sw the
+// unit's three state words, g4 the first of its four gradient float4s (swizzled by jsw).  e_unit = global element
+// index of the unit's first weight.
+__device__ __forceinline__ void tick_unit16(const uint32_t sa_rowk, const uint32_t rt, const uint32_t sw, const uint32_t g4,
+                                            const uint32_t jsw, const uint32_t e_unit, const uint32_t seed, const float neg_lr,
+                                            const float Cf, const int C, const int lv, const uint32_t pow16,
+                                            const uint32_t pow17, const DecodeLut* lut, uint32_t (&nwd)[4], uint32_t& fields) {
+    const float4 rcv = lds_f4(sa_rowk);            // yh, yl, dn, k_tick
+    const float2 rcw = lds_f2(sa_rowk + 16u);      // k_reb, qlo
+    const float ndn = -rcv.z;
+    const uint32_t s0 = lds_u32(sw), s1 = lds_u32(sw + 4), s2 = lds_u32(sw + 8);
+    const uint32_t gwd[4] = {s0 & 0xFFFFFFu, (s0 >> 24) | ((s1 & 0xFFFFu) << 8),
+                             (s1 >> 16) | ((s2 & 0xFFu) << 16), s2 >> 8};
+    fields = 0;
+    float vmax = 0.0f;                              // largest |counter + tick| of the unit (NaN if any is)
+    float qmin = __int_as_float(0x7f800000);        // smallest |gw / dn| of the unit
+#pragma unroll
+    for (int gg = 0; gg < 4; ++gg) {
+        const float4 gw = lds_f4(g4 + (((uint32_t)gg ^ jsw) << 4));
+        const float gwv[4] = {gw.x, gw.y, gw.z, gw.w};
+        const uint32_t w = gwd[gg];
+        const uint32_t e0 = e_unit + 4u * gg;
+        const uint32_t e0x = e0 ^ shr_mulhi(e0, pow16);
+        uint32_t acc = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            // byte offset of the row-table entry of the old code: code * 8
+            const uint32_t c8 = (k == 0 ? (w << 3) : (w >> (6 * k - 3))) & 0x1F8u;
+            const float2 re = lds_f2(rt + c8);            // x = rebased counter, y = tick-table address (int bits)
+            const float g = gwv[k];
+            const float pq = __fmaf_rn(g, rcv.x, __fmul_rn(g, rcv.y));
+            const float q = __fmaf_rn(__fmaf_rn(ndn, pq, g), rcv.x, pq);      // = RN(g / dn), see RowK
+            qmin = fminf(qmin, fabsf(q));
+            const float tick = __fmul_rn(__fmul_rn(neg_lr, q), rcv.w);
+            const float val = __fadd_rn(re.x, tick);
+            vmax = fmax_nan(vmax, fabsf(val));
+            uint32_t x = (e0x ^ (uint32_t)k) * 0x7feb352du;
+            x ^= shr_mulhi(x, pow17);            // x >> 15
+            x *= 0x846ca68bu;
+            x = seed ^ x ^ shr_mulhi(x, pow16);  // seed ^ hash(elem)
+            x ^= shr_mulhi(x, pow16);
+            x *= 0x7feb352du;
+            x ^= shr_mulhi(x, pow17);
+            x *= 0x846ca68bu;
+            const uint32_t h = (x ^ shr_mulhi(x, pow16)) & 0x00ffffffu;
+            const float f = floorf(val);
+            const float rnd = __fmul_rn((float)h, 1.0f / 16777216.0f);
+            int iccv;           // saturating conversion: a wild value still gives an address inside this CTA's shared memory
+            asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(iccv) : "f"(f));
+            iccv += (rnd < __fsub_rn(val, f)) ? 1 : 0;
+            acc += lds_u32((uint32_t)(__float_as_int(re.y) + 4 * iccv) + (uint32_t)(k * 4 * kTickN * 4));
+        }
+        nwd[gg] = acc & 0xFFFFFFu;
+        fields |= (acc >> 24) << (8 * gg);
+    }
+    bool redo = !(vmax < kTickValMax);      // a rounded counter beyond the table, a code outside it, or a NaN
+    if (!(qmin >= rcw.y)) {
+        // a quotient below the range in which the division-free form is proven (or a row outside it): exact
+        // zeros are fine, anything else goes to the formulas
+        redo = redo || (rcw.y != rcw.y);
+        for (int gg = 0; gg < 4 && !redo; ++gg) {
+            const float4 gw = lds_f4(g4 + (((uint32_t)gg ^ jsw) << 4));
+            const float gwv[4] = {gw.x, gw.y, gw.z, gw.w};
+            for (int k = 0; k < 4; ++k)
+                if (gwv[k] != 0.0f && !(fabsf(__fdiv_rn(gwv[k], rcv.z)) >= rcw.y)) redo = true;
+        }
+    }
+    if (redo) {
+        // rare: redo the unit with the reference formulas
+        fields = 0;
+        for (int gg = 0; gg < 4; ++gg) {
+            const float4 gw = lds_f4(g4 + (((uint32_t)gg ^ jsw) << 4));
+            const float gwv[4] = {gw.x, gw.y, gw.z, gw.w};
+            uint32_t nw = 0;
+            for (int k = 0; k < 4; ++k) {
+                const float2 tc = lut->e[(gwd[gg] >> (6 * k)) & 63u];
+                uint32_t fld;
+                const uint32_t code = counter_tick(gwv[k], tc.x, tc.y, e_unit + (uint32_t)(4 * gg + k), seed,
+                                                   neg_lr, rcv.z, rcv.w, rcw.x, Cf, C, lv, &fld);
+                nw += (code & 0x3Fu) << (6 * k);
+                fields += (fld & 3u) << (2 * (4 * gg + k));
+            }
+            nwd[gg] = nw;
+        }
+    }
+}
+
+// kernels/compact_counter.cl:129-136 evaluated for every (old digit, rounded counter) the table covers
+__device__ __forceinline__ void build_tick_table(uint32_t* tick_tab, const int C, const int tid, const int nthreads) {
+    const int lv = 2 * C - 1;
+    const float Cf = (float)C;
+    for (int e = tid; e < 4 * kTickN; e += nthreads) {
+        const int t = e / kTickN - 1;
+        const float ccv = (float)(e % kTickN - kTickHalf);
+        const float carry = truncf(__fdiv_rn(ccv, Cf));
+        float rem = __fsub_rn(ccv, __fmul_rn(carry, Cf));
+        const int nt = t + (int)carry;
+        const int ct = nt < -1 ? -1 : (nt > 1 ? 1 : nt);
+        if (ct != nt) rem = __fmul_rn(ccv > 0.0f ? 1.0f : (ccv < 0.0f ? -1.0f : 0.0f), __fsub_rn(Cf, 1.0f));
+        int ri = (int)rem;
+        ri = ri < -(C - 1) ? -(C - 1) : (ri > C - 1 ? C - 1 : ri);
+        const uint32_t code = (uint32_t)(((ct + 1) * lv + (ri + (C - 1))) & 0x3F);
+        const uint32_t fld = (uint32_t)(ct + 1);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) tick_tab[k * 4 * kTickN + e] = (code << (6 * k)) | (fld << (24 + 2 * k));
+    }
+}
+
+// Row constants from the two row sums (kernels/compact_counter.cl:92-99); writes v and the new scale of the row.
+template <bool WITH_Q>
+__device__ __forceinline__ RowK finish_row_stats(const UpdParams& p, const int row, const float a, const float b, const float Cf,
+                                                 const float s_old, const float v_old) {
+    const int I = p.in_features;
+    const float gsq = __fdiv_rn(a, (float)I);
+    float s_new = s_old;
+    if (WITH_Q) {
+        const float gs = __fdiv_rn(b, __fsqrt_rn((float)I));
+        s_new = __fsub_rn(s_old, __fmul_rn(p.lr_scale, gs));
+    }
+    s_new = fminf(fmaxf(s_new, 1e-5f), 10.0f);
+    const float vv = __fadd_rn(__fmul_rn(p.rms_beta, v_old), __fmul_rn(__fsub_rn(1.0f, p.rms_beta), gsq));
+    p.v[row] = vv;
+    RowK rc;
+    rc.dn = fmaxf(__fsqrt_rn(vv), p.rms_eps);
+    rc.k_tick = __fdiv_rn(Cf, s_new);
+    rc.k_reb = __fdiv_rn(s_old, s_new);
+    rc.yh = __frcp_rn(rc.dn);
+    rc.yl = __fmul_rn(__fmaf_rn(-rc.dn, rc.yh, 1.0f), rc.yh);
+    const bool in_range = rc.dn >= 2.3283064365386963e-10f && rc.dn <= 4294967296.0f;     // 2^-32 .. 2^32
+    rc.qlo = in_range ? 5.421010862427522e-20f : __int_as_float(0x7fc00000);                 // 2^-64 or NaN
+    rc.pad0 = rc.pad1 = 0.0f;
+    p.scale[row] = s_new;           // scale commit (kernels/basic.cl:6-9)
+    return rc;
+}
+
+// Row-table entry of old code value `code`: the rebased counter and the shared-memory address of the tick-table entry
+// of (k = 0, the code's digit, rounded counter 0).  A code whose ternary digit the tick table lacks gets an infinite
+// counter, which sends its unit down the formula path.
+__device__ __forceinline__ RowEntry row_entry(const DecodeLut* lut, const int code, const float k_reb, const uint32_t sa_tick) {
+    const float2 tc = lut->e[code];
+    const int ti = (int)tc.x + 1;
+    const bool ok = ti >= 0 && ti < 4;
+    RowEntry re;
+    re.creb = ok ? __fmul_rn(tc.y, k_reb) : __int_as_float(0x7f800000);
+    re.tail_base = (int)(sa_tick + 4u * (uint32_t)((ok ? ti : 0) * kTickN + kTickHalf));
+    return re;
+}
+
 struct U16Layout {
-    int sb, off_tailc, off_tailf, off_rowc, off_part, off_rowtab, off_gw, off_q, off_st, off_so, off_p2;
+    int sb, off_tick, off_rowc, off_part, off_rowtab, off_gw, off_st, off_so, off_p2;
     size_t total;
 };
 __host__ __device__ inline U16Layout u16_layout(int I, int R, bool with_q) {
+    (void)with_q;
     U16Layout L;
     const int row_bytes = (I >> 2) * 3;
     L.sb = (row_bytes + 15) & ~15;
     size_t o = sizeof(DecodeLut);
-    L.off_tailc = (int)o; o += 4 * kTail16;
-    L.off_tailf = (int)o; o += 4 * kTail16;
-    L.off_rowc = (int)o; o += sizeof(RowConst) * R;
+    L.off_tick = (int)o; o += kTickBytes;
+    L.off_rowc = (int)o; o += sizeof(RowK) * R;
     L.off_part = (int)o; o += sizeof(float) * 64 * kPairs;
     L.off_rowtab = (int)o; o += sizeof(RowEntry) * 64 * (size_t)R;
     L.off_gw = (int)o; o += sizeof(float) * (size_t)R * I;
-    L.off_q = (int)o; if (with_q) o += sizeof(float) * (size_t)R * I;
     L.off_st = (int)o; o += (size_t)R * L.sb + 16;
     L.off_so = (int)o; o += (size_t)R * L.sb + 16;
     L.off_p2 = (int)o; o += (size_t)R * (I >> 2);
@@ -387,7 +558,7 @@ __host__ __device__ inline U16Layout u16_layout(int I, int R, bool with_q) {
 }
 
 // Body shared by the single-layer and the grouped kernel: batches batch0, batch0 + batch_step, ... of the
-// layer `p`.  The decode and tail tables depend on C alone; `build_tables` is false when an earlier call
+// layer `p`.  The decode and tick tables depend on C alone; `build_tables` is false when an earlier call
 // of the same CTA already built them for this C.
 template <bool WITH_Q>
 __device__ __forceinline__ void update_u16_body(const UpdParams& p, const uint32_t unit_magic, const uint32_t pow16,
@@ -402,18 +573,16 @@ __device__ __forceinline__ void update_u16_body(const UpdParams& p, const uint32
     const U16Layout L = u16_layout(I, R, WITH_Q);
 
     DecodeLut* lut = reinterpret_cast<DecodeLut*>(smem);
-    unsigned char* tail_code = smem + L.off_tailc;
-    unsigned char* tail_field = smem + L.off_tailf;
-    RowConst* rowc = reinterpret_cast<RowConst*>(smem + L.off_rowc);
+    uint32_t* tick_tab = reinterpret_cast<uint32_t*>(smem + L.off_tick);
+    RowK* rowc = reinterpret_cast<RowK*>(smem + L.off_rowc);
     float* part = reinterpret_cast<float*>(smem + L.off_part);
     RowEntry* rowtab = reinterpret_cast<RowEntry*>(smem + L.off_rowtab);
     float4* gw_s = reinterpret_cast<float4*>(smem + L.off_gw);
-    float4* q_s = reinterpret_cast<float4*>(smem + L.off_q);
     unsigned char* st_s = smem + L.off_st;
     unsigned char* so_s = smem + L.off_so;
     uint32_t* p2_s = reinterpret_cast<uint32_t*>(smem + L.off_p2);
     const uint32_t sa0 = (uint32_t)__cvta_generic_to_shared(smem);
-    const uint32_t sa_tail = sa0 + L.off_tailc, sa_rowc = sa0 + L.off_rowc, sa_rowtab = sa0 + L.off_rowtab;
+    const uint32_t sa_tick = sa0 + L.off_tick, sa_rowc = sa0 + L.off_rowc, sa_rowtab = sa0 + L.off_rowtab;
     const uint32_t sa_gw = sa0 + L.off_gw, sa_st = sa0 + L.off_st, sa_so = sa0 + L.off_so, sa_p2 = sa0 + L.off_p2;
 
     const int tid = threadIdx.x;
@@ -426,19 +595,10 @@ __device__ __forceinline__ void update_u16_body(const UpdParams& p, const uint32
     const uint32_t seed = p.seed + (p.seed_offset ? __ldg(p.seed_offset) : 0u);
     const bool aligned16 = p.state_align >= 16;
 
-    if (build_tables) build_decode_lut(lut, p.C, tid, kUpdThreads);
-    for (int e = tid; build_tables && e < 4 * kTail16; e += kUpdThreads) {     // kernels/compact_counter.cl:129-136
-        const int t = e / kTail16 - 1;
-        const float ccv = (float)(e % kTail16 - 128);
-        const float carry = truncf(__fdiv_rn(ccv, Cf));
-        float rem = __fsub_rn(ccv, __fmul_rn(carry, Cf));
-        const int nt = t + (int)carry;
-        const int ct = nt < -1 ? -1 : (nt > 1 ? 1 : nt);
-        if (ct != nt) rem = __fmul_rn(ccv > 0.0f ? 1.0f : (ccv < 0.0f ? -1.0f : 0.0f), __fsub_rn(Cf, 1.0f));
-        int ri = (int)rem;
-        ri = ri < -(p.C - 1) ? -(p.C - 1) : (ri > p.C - 1 ? p.C - 1 : ri);
-        tail_code[e] = (unsigned char)(((ct + 1) * lv + (ri + (p.C - 1))) & 0x3F);
-        tail_field[e] = (unsigned char)(ct + 1);
+    if (build_tables) {
+        __syncthreads();                  // an earlier layer's batches may still read the old tables
+        build_decode_lut(lut, p.C, tid, kUpdThreads);
+        build_tick_table(tick_tab, p.C, tid, kUpdThreads);
     }
     __syncthreads();
 
@@ -462,24 +622,27 @@ __device__ __forceinline__ void update_u16_body(const UpdParams& p, const uint32
                     reinterpret_cast<uint32_t*>(st_s + (size_t)r * L.sb)[w] = __ldg(s1 + i);
                 }
             }
-        }
-        if (WITH_Q) __syncthreads();
-        {
-            const float4* src = reinterpret_cast<const float4*>(p.grad_w + (size_t)row0 * I);
-            for (int i = tid; i < nrows * gpr; i += kUpdThreads) {
-                const float4 gw = __ldg(src + i);
-                const int r = i / gpr, g = i - r * gpr;
-                const int at = r * gpr + swz4(g);
-                gw_s[at] = gw;
-                if (WITH_Q) {
-                    const uint32_t* raw = reinterpret_cast<const uint32_t*>(st_s + (size_t)r * L.sb);
-                    const uint32_t w = load_group24(raw, (uint32_t)g * 3u);
-                    float4 q;
-                    q.x = __fmul_rn(gw.x, lut->e[w & 63u].x);
-                    q.y = __fmul_rn(gw.y, lut->e[(w >> 6) & 63u].x);
-                    q.z = __fmul_rn(gw.z, lut->e[(w >> 12) & 63u].x);
-                    q.w = __fmul_rn(gw.w, lut->e[(w >> 18) & 63u].x);
-                    q_s[at] = q;
+            const float4* gsrc = reinterpret_cast<const float4*>(p.grad_w + (size_t)row0 * I);
+            const int n4 = nrows * gpr;
+            if ((gpr & 31) == 0) {  // rows start on a period of the swizzle: the flat float4 index can be swizzled as it is
+                int i = tid;
+                for (; i + 3 * kUpdThreads < n4; i += 4 * kUpdThreads) {       // four loads in flight per thread
+                    const float4 v0 = __ldg(gsrc + i), v1 = __ldg(gsrc + i + kUpdThreads), v2 = __ldg(gsrc + i + 2 * kUpdThreads),
+                                 v3 = __ldg(gsrc + i + 3 * kUpdThreads);
+                    gw_s[swz4(i)] = v0; gw_s[swz4(i + kUpdThreads)] = v1;
+                    gw_s[swz4(i + 2 * kUpdThreads)] = v2; gw_s[swz4(i + 3 * kUpdThreads)] = v3;
+                }
+                for (; i < n4; i += kUpdThreads) gw_s[swz4(i)] = __ldg(gsrc + i);
+            } else {                // a warp per row, rows of the batch dealt round-robin
+                for (int r = tid >> 5; r < nrows; r += kUpdThreads / 32) {
+                    const float4* rs = gsrc + (size_t)r * gpr;
+                    float4* rd = gw_s + r * gpr;
+                    int g = lane;
+                    for (; g + 64 < gpr; g += 96) {
+                        const float4 v0 = __ldg(rs + g), v1 = __ldg(rs + g + 32), v2 = __ldg(rs + g + 64);
+                        rd[swz4(g)] = v0; rd[swz4(g + 32)] = v1; rd[swz4(g + 64)] = v2;
+                    }
+                    for (; g < gpr; g += 32) rd[swz4(g)] = __ldg(rs + g);
                 }
             }
         }
@@ -489,7 +652,7 @@ __device__ __forceinline__ void update_u16_body(const UpdParams& p, const uint32
         for (int r = pair; r < nrows; r += kPairs) {
             float a = 0.0f, b = 0.0f;
             const float4* g4 = gw_s + r * gpr;
-            const float4* q4 = q_s + r * gpr;
+            const uint32_t* raw = reinterpret_cast<const uint32_t*>(st_s + (size_t)r * L.sb);
             for (int g = vlane; g < gpr; g += 64) {
                 const float4 gw = g4[swz4(g)];
                 a = __fadd_rn(a, __fmul_rn(gw.x, gw.x));
@@ -497,11 +660,11 @@ __device__ __forceinline__ void update_u16_body(const UpdParams& p, const uint32
                 a = __fadd_rn(a, __fmul_rn(gw.z, gw.z));
                 a = __fadd_rn(a, __fmul_rn(gw.w, gw.w));
                 if (WITH_Q) {
-                    const float4 q = q4[swz4(g)];
-                    b = __fadd_rn(b, q.x);
-                    b = __fadd_rn(b, q.y);
-                    b = __fadd_rn(b, q.z);
-                    b = __fadd_rn(b, q.w);
+                    const uint32_t w = load_group24(raw, (uint32_t)g * 3u);
+                    b = __fadd_rn(b, __fmul_rn(gw.x, lut->e[w & 63u].x));
+                    b = __fadd_rn(b, __fmul_rn(gw.y, lut->e[(w >> 6) & 63u].x));
+                    b = __fadd_rn(b, __fmul_rn(gw.z, lut->e[(w >> 12) & 63u].x));
+                    b = __fadd_rn(b, __fmul_rn(gw.w, lut->e[(w >> 18) & 63u].x));
                 }
             }
             if (vlane >= 32) {
@@ -517,39 +680,10 @@ __device__ __forceinline__ void update_u16_body(const UpdParams& p, const uint32
                     a = __fadd_rn(a, __shfl_down_sync(0xffffffffu, a, s));
                     b = __fadd_rn(b, __shfl_down_sync(0xffffffffu, b, s));
                 }
-                if (lane == 0) {                  // kernels/compact_counter.cl:92-99
-                    const int row = row0 + r;
-                    const float gsq = __fdiv_rn(a, (float)I);
-                    const float s_old = p.scale[row];
-                    float s_new = s_old;
-                    if (WITH_Q) {
-                        const float gs = __fdiv_rn(b, __fsqrt_rn((float)I));
-                        s_new = __fsub_rn(s_old, __fmul_rn(p.lr_scale, gs));
-                    }
-                    s_new = fminf(fmaxf(s_new, 1e-5f), 10.0f);
-                    const float vv = __fadd_rn(__fmul_rn(p.rms_beta, p.v[row]),
-                                               __fmul_rn(__fsub_rn(1.0f, p.rms_beta), gsq));
-                    p.v[row] = vv;
-                    RowConst rc;
-                    rc.dn = fmaxf(__fsqrt_rn(vv), p.rms_eps);
-                    rc.k_tick = __fdiv_rn(Cf, s_new);
-                    rc.k_reb = __fdiv_rn(s_old, s_new);
-                    rc.pad = 0.0f;
-                    rowc[r] = rc;
-                    p.scale[row] = s_new;
-                }
+                if (lane == 0) rowc[r] = finish_row_stats<WITH_Q>(p, row0 + r, a, b, Cf, p.scale[row0 + r], p.v[row0 + r]);
             }
             asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory");
-            {   // per-row table of rebased counters, one entry per old code value
-                const float2 tc = lut->e[vlane];
-                RowEntry re;
-                const int ti = (int)tc.x + 1;
-                // a code whose ternary digit the tail table lacks gets an infinite counter, which
-                // sends its unit down the formula path
-                re.creb = (ti >= 0 && ti < 4) ? __fmul_rn(tc.y, rowc[r].k_reb) : __int_as_float(0x7f800000);
-                re.tail_base = (ti >= 0 && ti < 4) ? ti * kTail16 + 128 : 128;
-                rowtab[r * 64 + vlane] = re;
-            }
+            rowtab[r * 64 + vlane] = row_entry(lut, vlane, rowc[r].k_reb, sa_tick);     // one entry per old code value
         }
         __syncthreads();
 
@@ -560,72 +694,12 @@ __device__ __forceinline__ void update_u16_body(const UpdParams& p, const uint32
         for (int u = tid; u < nunits; u += kUpdThreads) {
             const int r = unit_magic ? (int)__umulhi((uint32_t)u, unit_magic) : u;       // u / upr (magic 0: upr == 1)
             const int j = u - r * upr;
-            const float4 rcv = lds_f4(sa_rowc + (uint32_t)r * 16u);       // dn, k_tick, k_reb
-            const uint32_t rt = sa_rowtab + (uint32_t)r * 512u;
-            const uint32_t sw = sa_st + (uint32_t)r * (uint32_t)L.sb + 12u * (uint32_t)j;
-            const uint32_t s0 = lds_u32(sw), s1 = lds_u32(sw + 4), s2 = lds_u32(sw + 8);
-            const uint32_t gwd[4] = {s0 & 0xFFFFFFu, (s0 >> 24) | ((s1 & 0xFFFFu) << 8),
-                                     (s1 >> 16) | ((s2 & 0xFFu) << 16), s2 >> 8};
             const uint32_t g4 = sa_gw + ((uint32_t)(r * gpr + 4 * j) << 4);
-            const uint32_t jsw = (uint32_t)((j >> 1) & 3);
             const uint32_t e_unit = (uint32_t)(p.row_offset + row0 + r) * (uint32_t)I + (uint32_t)(16 * j);
-            uint32_t nwd[4], fields = 0;
-            float vmax = 0.0f;          // largest |counter + tick| of the unit
-#pragma unroll
-            for (int gg = 0; gg < 4; ++gg) {
-                const float4 gw = lds_f4(g4 + (((uint32_t)gg ^ jsw) << 4));
-                const float gwv[4] = {gw.x, gw.y, gw.z, gw.w};
-                const uint32_t w = gwd[gg];
-                const uint32_t e0 = e_unit + 4u * gg;
-                const uint32_t e0x = e0 ^ shr_mulhi(e0, pow16);
-                uint32_t nw = 0;
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    // byte offset of the row-table entry of the old code: code * 8
-                    const uint32_t c8 = (k == 0 ? (w << 3) : (w >> (6 * k - 3))) & 0x1F8u;
-                    const float2 re = lds_f2(rt + c8);            // x = rebased counter, y = tail-table base (int bits)
-                    const float tick = __fmul_rn(__fmul_rn(neg_lr, __fdiv_rn(gwv[k], rcv.x)), rcv.y);
-                    const float val = __fadd_rn(re.x, tick);
-                    vmax = fmaxf(vmax, fabsf(val));
-                    uint32_t x = (e0x ^ (uint32_t)k) * 0x7feb352du;
-                    x ^= shr_mulhi(x, pow17);            // x >> 15
-                    x *= 0x846ca68bu;
-                    x = seed ^ x ^ shr_mulhi(x, pow16);  // seed ^ hash(elem)
-                    x ^= shr_mulhi(x, pow16);
-                    x *= 0x7feb352du;
-                    x ^= shr_mulhi(x, pow17);
-                    x *= 0x846ca68bu;
-                    const uint32_t h = (x ^ shr_mulhi(x, pow16)) & 0x00ffffffu;
-                    const float f = floorf(val);
-                    const float rnd = __fmul_rn((float)h, 1.0f / 16777216.0f);
-                    const float up = (rnd < __fsub_rn(val, f)) ? 1.0f : 0.0f;
-                    int iccv;           // saturating conversion keeps the table index in range whatever val is
-                    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(iccv) : "f"(__fadd_rn(f, up)));
-                    const uint32_t ta = sa_tail + (uint32_t)(__float_as_int(re.y) + iccv);
-                    nw += lds_u8(ta) << (6 * k);
-                    fields += lds_u8(ta + 4 * kTail16) << (2 * (4 * gg + k));
-                }
-                nwd[gg] = nw;
-            }
-            if (!(vmax < 126.0f)) {
-                // rare: a rounded counter beyond the table (or a code outside it): redo the unit
-                // with the reference formulas
-                fields = 0;
-                for (int gg = 0; gg < 4; ++gg) {
-                    const float4 gw = lds_f4(g4 + (((uint32_t)gg ^ jsw) << 4));
-                    const float gwv[4] = {gw.x, gw.y, gw.z, gw.w};
-                    uint32_t nw = 0;
-                    for (int k = 0; k < 4; ++k) {
-                        const float2 tc = lut->e[(gwd[gg] >> (6 * k)) & 63u];
-                        uint32_t fld;
-                        const uint32_t code = counter_tick(gwv[k], tc.x, tc.y, e_unit + (uint32_t)(4 * gg + k), seed,
-                                                           neg_lr, rcv.x, rcv.y, rcv.z, Cf, p.C, lv, &fld);
-                        nw += (code & 0x3Fu) << (6 * k);
-                        fields += (fld & 3u) << (2 * (4 * gg + k));
-                    }
-                    nwd[gg] = nw;
-                }
-            }
+            uint32_t nwd[4], fields;
+            tick_unit16(sa_rowc + (uint32_t)r * 32u, sa_rowtab + (uint32_t)r * 512u,
+                        sa_st + (uint32_t)r * (uint32_t)L.sb + 12u * (uint32_t)j, g4, (uint32_t)((j >> 1) & 3), e_unit, seed,
+                        neg_lr, Cf, p.C, lv, pow16, pow17, lut, nwd, fields);
             const uint32_t so = sa_so + (uint32_t)r * (uint32_t)L.sb + 12u * (uint32_t)j;
             sts_u32(so, nwd[0] | (nwd[1] << 24));
             sts_u32(so + 4, (nwd[1] >> 8) | (nwd[2] << 16));
@@ -634,7 +708,7 @@ __device__ __forceinline__ void update_u16_body(const UpdParams& p, const uint32
         }
         __syncthreads();
 
-        // ---- store ------------------------------------------------------------------------------
+        // ---- store (the next batch's loads follow without a barrier: they touch other arrays) ------------
         {
             uint8_t* dst = p.state + (size_t)row0 * row_bytes;
             if (aligned16) {
@@ -660,12 +734,304 @@ __device__ __forceinline__ void update_u16_body(const UpdParams& p, const uint32
                 }
             }
         }
-        __syncthreads();
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Wide rows (in_features >= 1024, a multiple of 64): one persistent CTA per SM whose warps have ROLES, so that the
+// latency of HBM, the row statistics (64 lanes of parallelism per row, by the reference's reduction order) and the
+// tick (everything else) overlap instead of taking turns between CTA-wide barriers.
+//   ring     D row slots in shared memory: gradient row (XOR-swizzled float4s), state row, row table, row constants
+//   warps 0..3   "stats": warp s owns the CTA's rows s, s+4, ...  For a row it waits until the slot's previous row
+//                has been ticked, copies gradient and state into the slot with cp.async (the next row's copies are
+//                issued before this row's statistics, so several rows per warp are in flight), replays the 64-lane
+//                reduction with two virtual lanes per thread, writes v / scale / the row's constants and its
+//                table, and marks the slot ready.
+//   warps 4..15  "tick": chunks of 32 consecutive 16-weight units, dealt round-robin over the twelve warps across
+//                rows.  A lane ticks one unit, writes the new state words over the old ones in the slot, the warp
+//                copies its 384 bytes out with 16-byte stores and stores its 32 words of 2-bit fields; when a warp
+//                has passed a row it releases the slot.
+// Every wait is bounded: on time-out the kernel sets *err (when given) and all roles leave.
+#ifndef MCL_WS_AHEAD
+#define MCL_WS_AHEAD 1
+#endif
+#ifndef MCL_WS_THREADS
+#define MCL_WS_THREADS 512
+#endif
+constexpr int kWsThreads = MCL_WS_THREADS;
+// Every fourth warp is a stats warp: warps are dealt to the SM's four schedulers by warp number, so the stats warps
+// share ONE scheduler among themselves and their short dependent instruction chains do not queue behind the tick
+// warps' long independent ones.
+constexpr int kWsStatsWarps = kWsThreads / 128;
+constexpr int kWsTickWarps = kWsThreads / 32 - kWsStatsWarps;
+constexpr int kWsMaxSlots = 16;
+constexpr int kWsErrCode = 21;
+
+struct WsLayout {
+    int off_tick, off_bars, off_ring, slot_bytes, off_st, off_rowtab, off_rowk, off_sv, nslots;
+    size_t total;
+};
+__host__ __device__ inline WsLayout ws_layout(int I, size_t max_smem) {
+    WsLayout L;
+    size_t o = sizeof(DecodeLut);
+    L.off_tick = (int)o; o += kTickBytes;
+    L.off_bars = (int)o; o += 8 * 2 * kWsMaxSlots + 16;
+    o = (o + 127) & ~size_t(127);
+    L.off_ring = (int)o;
+    const int row_bytes = (I >> 2) * 3;
+    L.off_st = 4 * I;
+    L.off_rowtab = L.off_st + ((row_bytes + 15) & ~15) + 16;      // 16 readable bytes after the state row (24-bit group loads)
+    L.off_rowk = L.off_rowtab + 64 * (int)sizeof(RowEntry);
+    L.off_sv = L.off_rowk + (int)sizeof(RowK);          // the row's old scale and v, copied in with the row
+    L.slot_bytes = (L.off_sv + 16 + 127) & ~127;
+    long long n = ((long long)max_smem - 1024 - (long long)o) / L.slot_bytes;
+    L.nslots = n > kWsMaxSlots ? kWsMaxSlots : (int)n;
+    L.total = o + (size_t)(L.nslots > 0 ? L.nslots : 0) * L.slot_bytes;
+    return L;
+}
+
+// Bounded wait of a whole warp on an mbarrier phase, polled by one lane that SLEEPS between polls: the waiting roles of
+// this kernel share their schedulers with the warps that do the arithmetic, and a hot poll loop costs those warps
+// issue slots.  Returns false after ~0.5 s or once another role has flagged an abort.
+__device__ __forceinline__ bool ws_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0 && !mbar_try_wait(bar, parity)) {
+        const unsigned long long t0 = clock64();
+        unsigned spins = 0;
+        for (;;) {
+            __nanosleep(spins < 8 ? 64 : 256);
+            if (mbar_try_wait(bar, parity)) break;
+            if ((++spins & 0x3Fu) == 0 && (*abort_flag || clock64() - t0 > kWaitCycles)) { ok = false; break; }
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (ok) ok = mbar_try_wait(bar, parity);      // completed phase: every lane takes its own acquire
+    return __all_sync(0xffffffffu, ok);
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+#ifdef MCL_WS_PROF
+__device__ long long g_ws_prof[16 * 8];
+#define WSP_T(v) const long long v = clock64()
+#define WSP_ADD(slot, a, b) prof[slot] += (b) - (a)
+#else
+#define WSP_T(v)
+#define WSP_ADD(slot, a, b)
+#endif
+
 template <bool WITH_Q>
-__global__ void __launch_bounds__(kUpdThreads, 4)
+__global__ void __launch_bounds__(kWsThreads, 1)
+counter_update_ws_kernel(const UpdParams p, const uint32_t pow16, const uint32_t pow17, const int nslots, int* err) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int I = p.in_features;
+    const int gpr = I >> 2, upr = I >> 4, row_bytes = gpr * 3;
+    const WsLayout L = ws_layout(I, 0);
+    DecodeLut* lut = reinterpret_cast<DecodeLut*>(smem);
+    uint32_t* tick_tab = reinterpret_cast<uint32_t*>(smem + L.off_tick);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.off_bars + 8 * 2 * kWsMaxSlots);
+    const uint32_t sa0 = (uint32_t)__cvta_generic_to_shared(smem);
+    const uint32_t sa_tick = sa0 + L.off_tick, sa_ring = sa0 + L.off_ring, bar0 = sa0 + L.off_bars;
+    auto ready_bar = [&](int s) { return bar0 + 8u * (uint32_t)s; };
+    auto free_bar = [&](int s) { return bar0 + 8u * (uint32_t)(kWsMaxSlots + s); };
+
+    const int tid = threadIdx.x, hw_warp = tid >> 5, lane = tid & 31;
+    const bool is_stats = (hw_warp & 3) == 0;
+    const int warp = is_stats ? (hw_warp >> 2) : kWsStatsWarps + hw_warp - (hw_warp >> 2) - 1;     // role index: stats warps first
+    const int lv = 2 * p.C - 1;
+    const float Cf = (float)p.C;
+    const float neg_lr = -p.lr;
+    const uint32_t seed = p.seed + (p.seed_offset ? __ldg(p.seed_offset) : 0u);
+    const int D = nslots;
+
+    // this CTA's rows: a contiguous block
+    const int r_begin = (int)(((long long)p.rows * blockIdx.x) / gridDim.x);
+    const int r_end = (int)(((long long)p.rows * (blockIdx.x + 1)) / gridDim.x);
+    const int nrows = r_end - r_begin;
+
+    if (tid == 0) {
+        *abort_flag = (err != nullptr && *reinterpret_cast<volatile int*>(err) != 0) ? 1 : 0;
+        for (int s = 0; s < D; ++s) { mbar_init(ready_bar(s), 32); mbar_init(free_bar(s), kWsTickWarps); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    build_decode_lut(lut, p.C, tid, kWsThreads);
+    build_tick_table(tick_tab, p.C, tid, kWsThreads);
+    __syncthreads();
+    auto give_up = [&]() {
+        *abort_flag = 1;
+        if (err != nullptr) atomicExch(err, kWsErrCode);
+    };
+
+#ifdef MCL_WS_PROF
+    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long t_start = clock64();
+#endif
+    // A slot is refilled by whichever stats warp owns the row D rows later; the wait on the slot's "free" barrier tells
+    // apart only two consecutive uses, so a warp must never get two uses ahead of the ring: with S warps striding the
+    // rows by S, that holds when S <= D.  Fewer slots than stats warps (very wide rows): the surplus warps sit out.
+    const int S = kWsStatsWarps < D ? kWsStatsWarps : D;
+    if (warp < kWsStatsWarps) {
+        // ---- stats warps ---------------------------------------------------------------------------
+        // A warp issues the copies of its rows `ahead` turns early.  The slot of a row held the row D earlier, which can
+        // only be ticked once every row before it is ready: copies may run ahead only by fewer rows than the ring has slots.
+        const int ahead = (D - 1) / S < MCL_WS_AHEAD ? (D - 1) / S : MCL_WS_AHEAD;
+        auto issue = [&](int n) -> bool {       // copies of local row n into its slot; false: gave up
+            const int slot = n % D;
+            WSP_T(w0);
+            if (!ws_wait(free_bar(slot), (((uint32_t)(n / D)) & 1u) ^ 1u, abort_flag)) return false;
+            WSP_T(w1); WSP_ADD(0, w0, w1);
+            const uint32_t base = sa_ring + (uint32_t)slot * (uint32_t)L.slot_bytes;
+            const float4* gsrc = reinterpret_cast<const float4*>(p.grad_w + (size_t)(r_begin + n) * I);
+            for (int g = lane; g < gpr; g += 32) cp_async16(base + ((uint32_t)swz4(g) << 4), gsrc + g);
+            const uint4* ssrc = reinterpret_cast<const uint4*>(p.state + (size_t)(r_begin + n) * row_bytes);
+            for (int c = lane; c < (row_bytes >> 4); c += 32) cp_async16(base + (uint32_t)L.off_st + ((uint32_t)c << 4), ssrc + c);
+            if (lane < 2) {
+                const float* src = (lane == 0 ? p.scale : p.v) + (r_begin + n);
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(base + (uint32_t)L.off_sv + 4u * (uint32_t)lane), "l"(src) : "memory");
+            }
+            return true;
+        };
+        bool ok = true;
+        for (int a = 0; a < ahead; ++a) {
+            const int n = warp + a * S;
+            if (ok && warp < S && n < nrows) ok = issue(n);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        for (int n = warp < S ? warp : nrows; n < nrows && ok; n += S) {
+            if (n + ahead * S < nrows) ok = issue(n + ahead * S);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            if (!ok) break;
+            WSP_T(l0);
+            switch (ahead) {
+                case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+                case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+                case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+                default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+            }
+            __syncwarp();
+            WSP_T(l1); WSP_ADD(1, l0, l1);
+            const int slot = n % D;
+            unsigned char* sbase = smem + L.off_ring + (size_t)slot * L.slot_bytes;
+            const float4* g4 = reinterpret_cast<const float4*>(sbase);
+            const uint32_t* raw = reinterpret_cast<const uint32_t*>(sbase + L.off_st);
+            // lane l stands for the reference's work-items l and l + 32 (kernels/compact_counter.cl:73-91): item l walks
+            // groups l, l + 64, ..., item l + 32 walks l + 32, l + 96, ...
+            float a0 = 0.0f, a1 = 0.0f, b0 = 0.0f, b1 = 0.0f;
+            for (int g = lane; g < gpr; g += 64) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int gg = g + 32 * h;
+                    if (gg < gpr) {
+                        const float4 gw = g4[swz4(gg)];
+                        float& a = h ? a1 : a0;
+                        a = __fadd_rn(a, __fmul_rn(gw.x, gw.x));
+                        a = __fadd_rn(a, __fmul_rn(gw.y, gw.y));
+                        a = __fadd_rn(a, __fmul_rn(gw.z, gw.z));
+                        a = __fadd_rn(a, __fmul_rn(gw.w, gw.w));
+                        if (WITH_Q) {
+                            const uint32_t w = load_group24(raw, (uint32_t)gg * 3u);
+                            float& b = h ? b1 : b0;
+                            b = __fadd_rn(b, __fmul_rn(gw.x, lut->e[w & 63u].x));
+                            b = __fadd_rn(b, __fmul_rn(gw.y, lut->e[(w >> 6) & 63u].x));
+                            b = __fadd_rn(b, __fmul_rn(gw.z, lut->e[(w >> 12) & 63u].x));
+                            b = __fadd_rn(b, __fmul_rn(gw.w, lut->e[(w >> 18) & 63u].x));
+                        }
+                    }
+                }
+            }
+            float a = __fadd_rn(a0, a1), b = __fadd_rn(b0, b1);       // tree step 32
+#pragma unroll
+            for (int s2 = 16; s2 > 0; s2 >>= 1) {
+                a = __fadd_rn(a, __shfl_down_sync(0xffffffffu, a, s2));
+                b = __fadd_rn(b, __shfl_down_sync(0xffffffffu, b, s2));
+            }
+            RowK rc;
+            if (lane == 0) {
+                const float* sv = reinterpret_cast<const float*>(sbase + L.off_sv);
+                rc = finish_row_stats<WITH_Q>(p, r_begin + n, a, b, Cf, sv[0], sv[1]);
+                *reinterpret_cast<RowK*>(sbase + L.off_rowk) = rc;
+            }
+            const float k_reb = __shfl_sync(0xffffffffu, rc.k_reb, 0);
+            RowEntry* rowtab = reinterpret_cast<RowEntry*>(sbase + L.off_rowtab);
+            rowtab[lane] = row_entry(lut, lane, k_reb, sa_tick);
+            rowtab[lane + 32] = row_entry(lut, lane + 32, k_reb, sa_tick);
+            mbar_arrive(ready_bar(slot));          // 32 arrivals complete the phase: each lane publishes its own writes
+            WSP_T(l2); WSP_ADD(2, l1, l2);
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        if (!ok && lane == 0) give_up();
+    } else {
+        // ---- tick warps ------------------------------------------------------------------------------
+        const int tw = warp - kWsStatsWarps;
+        const int cpr = (upr + 31) >> 5;                     // chunks of 32 units per row
+        int released = 0;                                    // rows [0, released) this warp has let go
+        bool ok = true;
+        // chunk number G = tw, tw + T, ... as (row n, chunk c of the row), advanced without a division
+        const int step_n = kWsTickWarps / cpr, step_c = kWsTickWarps - step_n * cpr;
+        int n = tw / cpr, c = tw - n * cpr;
+        for (; n < nrows && ok; n += step_n, c += step_c) {
+            if (c >= cpr) { c -= cpr; ++n; if (n >= nrows) break; }
+            if (released < n) {
+                __syncwarp();
+                if (lane == 0)
+                    for (; released < n; ++released) mbar_arrive(free_bar(released % D));
+                released = n;
+            }
+            const int slot = n % D;
+            WSP_T(k0);
+            if (!ws_wait(ready_bar(slot), ((uint32_t)(n / D)) & 1u, abort_flag)) { ok = false; break; }
+            WSP_T(k1); WSP_ADD(3, k0, k1);
+            const uint32_t base = sa_ring + (uint32_t)slot * (uint32_t)L.slot_bytes;
+            const int j = c * 32 + lane;
+            const int row = r_begin + n;
+            uint32_t fields = 0;
+            if (j < upr) {
+                uint32_t nwd[4];
+                const uint32_t sw = base + (uint32_t)L.off_st + 12u * (uint32_t)j;
+                tick_unit16(base + (uint32_t)L.off_rowk, base + (uint32_t)L.off_rowtab, sw, base + ((uint32_t)(4 * j) << 4),
+                            (uint32_t)((j >> 1) & 3), (uint32_t)(p.row_offset + row) * (uint32_t)I + (uint32_t)(16 * j), seed,
+                            neg_lr, Cf, p.C, lv, pow16, pow17, lut, nwd, fields);
+                sts_u32(sw, nwd[0] | (nwd[1] << 24));            // over the old words: only this lane reads them
+                sts_u32(sw + 4, (nwd[1] >> 8) | (nwd[2] << 16));
+                sts_u32(sw + 8, (nwd[2] >> 16) | (nwd[3] << 8));
+                if (p.packed2 != nullptr) p.packed2[(size_t)row * upr + j] = fields;
+            }
+            __syncwarp();
+            WSP_T(k2); WSP_ADD(4, k1, k2);
+            // the chunk's 384 bytes of state, 16 bytes per lane
+            const int nbytes = min(32, upr - c * 32) * 12;
+            if (lane * 16 < nbytes) {
+                const uint4 v = *reinterpret_cast<const uint4*>(smem + L.off_ring + (size_t)slot * L.slot_bytes + L.off_st +
+                                                                (size_t)c * 384 + (size_t)lane * 16);
+                *reinterpret_cast<uint4*>(p.state + (size_t)row * row_bytes + (size_t)c * 384 + (size_t)lane * 16) = v;
+            }
+            WSP_T(k3); WSP_ADD(5, k2, k3);
+        }
+        __syncwarp();
+        if (ok) {
+            if (lane == 0)
+                for (; released < nrows; ++released) mbar_arrive(free_bar(released % D));
+        } else if (lane == 0) {
+            give_up();
+        }
+    }
+#ifdef MCL_WS_PROF
+    if (blockIdx.x == 0 && lane == 0) {
+        prof[6] = clock64() - t_start;
+        for (int i = 0; i < 8; ++i) g_ws_prof[warp * 8 + i] = prof[i];
+    }
+#endif
+}
+#ifdef MCL_WS_PROF
+}  // namespace
+extern "C" int mcl_debug_ws_prof(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_ws_prof, sizeof(g_ws_prof)); }
+namespace {
+#endif
+
+template <bool WITH_Q>
+__global__ void __launch_bounds__(kUpdThreads, kUpdCtasPerSm)
 counter_update_u16_kernel(const UpdParams p, const uint32_t unit_magic, const uint32_t pow16, const uint32_t pow17) {
     update_u16_body<WITH_Q>(p, unit_magic, pow16, pow17, blockIdx.x, gridDim.x, true);
 }
@@ -679,7 +1045,7 @@ struct UpdGroup {
     UpdParams p[kUpdGroupCap];
 };
 template <bool WITH_Q>
-__global__ void __launch_bounds__(kUpdThreads, 4)
+__global__ void __launch_bounds__(kUpdThreads, kUpdCtasPerSm)
 counter_update_u16_group_kernel(const __grid_constant__ UpdGroup g, const uint32_t pow16, const uint32_t pow17) {
     const int grid = (int)gridDim.x, b = (int)blockIdx.x;
     int built_c = -1;
@@ -770,13 +1136,32 @@ cudaError_t ensure_dynamic_smem(const void* kern, int slot, size_t max_smem) {
 cudaError_t launch_counter_update_dense(uint8_t* state, float* scale, float* v, const float* grad_w,
                                         uint32_t* packed2, int C, int in_features, int rows,
                                         int row_offset, float lr, float lr_scale, float rms_beta,
-                                        float rms_eps, uint32_t seed, const uint32_t* seed_offset, int sm_count,
-                                        size_t max_smem, cudaStream_t stream) {
+                                        float rms_eps, uint32_t seed, const uint32_t* seed_offset, int* err_word,
+                                        int sm_count, size_t max_smem, cudaStream_t stream) {
     const bool with_q = (lr_scale != 0.0f);
     const uintptr_t sp0 = reinterpret_cast<uintptr_t>(state), pp0 = reinterpret_cast<uintptr_t>(packed2);
+    if (in_features >= 1024 && in_features % 64 == 0 && sp0 % 16 == 0 && pp0 % 4 == 0 &&
+        reinterpret_cast<uintptr_t>(grad_w) % 16 == 0) {
+        // wide rows: the warp-specialised kernel, one persistent CTA per SM
+        const WsLayout L = ws_layout(in_features, max_smem);
+        if (L.nslots >= 2) {
+            UpdParams p;
+            p.state = state; p.scale = scale; p.v = v; p.grad_w = grad_w; p.packed2 = packed2;
+            p.C = C; p.in_features = in_features; p.rows = rows; p.row_offset = row_offset;
+            p.rows_per_batch = 1; p.state_align = 16;
+            p.lr = lr; p.lr_scale = lr_scale; p.rms_beta = rms_beta; p.rms_eps = rms_eps;
+            p.seed = seed; p.seed_offset = seed_offset;
+            auto kern = with_q ? counter_update_ws_kernel<true> : counter_update_ws_kernel<false>;
+            cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), with_q ? 10 : 11, max_smem);
+            if (e != cudaSuccess) return e;
+            const int grid = rows < sm_count ? rows : sm_count;
+            kern<<<grid, kWsThreads, L.total, stream>>>(p, 1u << 16, 1u << 17, L.nslots, err_word);
+            return cudaGetLastError();
+        }
+    }
     if (in_features % 16 == 0 && sp0 % 4 == 0) {
         // fast variant: rows per batch sized for four CTAs per SM when a row allows it
-        const size_t target = (max_smem - 4096) / 4;
+        const size_t target = (max_smem - 4096) / kUpdCtasPerSm;
         int Ru = kMaxRowsU16;
         while (Ru > 1 && u16_layout(in_features, Ru, with_q).total > target) --Ru;
         const U16Layout L = u16_layout(in_features, Ru, with_q);
@@ -790,7 +1175,7 @@ cudaError_t launch_counter_update_dense(uint8_t* state, float* scale, float* v, 
             p.seed = seed; p.seed_offset = seed_offset;
             const int nb = (rows + Ru - 1) / Ru;
             int per_sm = (int)((max_smem - 1024) / L.total);
-            if (per_sm > 4) per_sm = 4;
+            if (per_sm > kUpdCtasPerSm) per_sm = kUpdCtasPerSm;
             if (per_sm < 1) per_sm = 1;
             int grid = sm_count * per_sm;
             if (grid > nb) grid = nb;
@@ -828,18 +1213,54 @@ cudaError_t launch_counter_update_dense(uint8_t* state, float* scale, float* v, 
     return cudaGetLastError();
 }
 
+static cudaError_t launch_update_group_narrow(const UpdateDesc* d, int n, int C, float lr, float lr_scale, float rms_beta,
+                                              float rms_eps, uint32_t seed, const uint32_t* seed_offset, int sm_count,
+                                              size_t max_smem, cudaStream_t stream, int* launches);
+
 // The fused update of several layers in one launch (same C and hyper-parameters).  Returns
 // cudaErrorNotSupported, having launched nothing, when a layer does not qualify for the 16-weight
 // kernel; the caller then updates layer by layer.
 cudaError_t launch_counter_update_group(const UpdateDesc* d, int n, int C, float lr, float lr_scale, float rms_beta,
-                                        float rms_eps, uint32_t seed, const uint32_t* seed_offset, int sm_count,
+                                        float rms_eps, uint32_t seed, const uint32_t* seed_offset, int* err_word, int sm_count,
                                         size_t max_smem, cudaStream_t stream, int* launches) {
     const bool with_q = (lr_scale != 0.0f);
-    const size_t target = (max_smem - 4096) / 4;
     for (int i = 0; i < n; ++i) {
         if (d[i].in_features % 16 != 0 || reinterpret_cast<uintptr_t>(d[i].state) % 4 != 0) return cudaErrorNotSupported;
         if (u16_layout(d[i].in_features, 1, with_q).total > max_smem - 1024) return cudaErrorNotSupported;
     }
+    // wide layers are whole launches of their own (the per-layer launcher picks the kernel); the narrow ones share launches
+    UpdateDesc narrow[kUpdGroupCap];
+    int nn = 0;
+    auto flush_narrow = [&]() -> cudaError_t {
+        if (nn == 0) return cudaSuccess;
+        cudaError_t e = launch_update_group_narrow(narrow, nn, C, lr, lr_scale, rms_beta, rms_eps, seed, seed_offset, sm_count, max_smem,
+                                                   stream, launches);
+        nn = 0;
+        return e;
+    };
+    for (int i = 0; i < n; ++i) {
+        if (d[i].in_features >= 1024) {
+            cudaError_t e = launch_counter_update_dense(d[i].state, d[i].scale, d[i].v, d[i].grad_w, d[i].packed2, C, d[i].in_features,
+                                                        d[i].rows, d[i].row_offset, lr, lr_scale, rms_beta, rms_eps, seed, seed_offset,
+                                                        err_word, sm_count, max_smem, stream);
+            if (e != cudaSuccess) return e;
+            ++*launches;
+            continue;
+        }
+        narrow[nn++] = d[i];
+        if (nn == kUpdGroupCap) {
+            cudaError_t e = flush_narrow();
+            if (e != cudaSuccess) return e;
+        }
+    }
+    return flush_narrow();
+}
+
+static cudaError_t launch_update_group_narrow(const UpdateDesc* d, int n, int C, float lr, float lr_scale, float rms_beta,
+                                              float rms_eps, uint32_t seed, const uint32_t* seed_offset, int sm_count,
+                                              size_t max_smem, cudaStream_t stream, int* launches) {
+    const bool with_q = (lr_scale != 0.0f);
+    const size_t target = (max_smem - 4096) / kUpdCtasPerSm;
     for (int done = 0; done < n;) {
         UpdGroup g;
         const int take = n - done < kUpdGroupCap ? n - done : kUpdGroupCap;
@@ -867,7 +1288,7 @@ cudaError_t launch_counter_update_group(const UpdateDesc* d, int n, int C, float
         g.batch_begin[take] = batches;
         g.n = take;
         int per_sm = (int)((max_smem - 1024) / smem);
-        if (per_sm > 4) per_sm = 4;
+        if (per_sm > kUpdCtasPerSm) per_sm = kUpdCtasPerSm;
         if (per_sm < 1) per_sm = 1;
         int grid = sm_count * per_sm;
         if (grid > batches) grid = batches;

@@ -10,11 +10,12 @@ namespace mcl {
 
 // counter_update.cu
 cudaError_t ensure_dynamic_smem(const void* kern, int slot, size_t max_smem);
+// err_word (may be null): device word that the wide-row kernel sets when a bounded wait gives up
 cudaError_t launch_counter_update_dense(uint8_t* state, float* scale, float* v, const float* grad_w,
                                         uint32_t* packed2, int C, int in_features, int rows,
                                         int row_offset, float lr, float lr_scale, float rms_beta,
-                                        float rms_eps, uint32_t seed, const uint32_t* seed_offset, int sm_count,
-                                        size_t max_smem, cudaStream_t stream);
+                                        float rms_eps, uint32_t seed, const uint32_t* seed_offset, int* err_word,
+                                        int sm_count, size_t max_smem, cudaStream_t stream);
 struct UpdateDesc {            // rows [row_offset, row_offset + rows) of one layer; pointers at the first row
     uint8_t* state;
     float* scale;
@@ -24,7 +25,7 @@ struct UpdateDesc {            // rows [row_offset, row_offset + rows) of one la
     int in_features, rows, row_offset;
 };
 cudaError_t launch_counter_update_group(const UpdateDesc* d, int n, int C, float lr, float lr_scale, float rms_beta,
-                                        float rms_eps, uint32_t seed, const uint32_t* seed_offset, int sm_count,
+                                        float rms_eps, uint32_t seed, const uint32_t* seed_offset, int* err_word, int sm_count,
                                         size_t max_smem, cudaStream_t stream, int* launches);
 cudaError_t launch_decode_weight(const uint8_t* state, const float* scale, float* w, int C,
                                  int in_features, int out_features, int sm_count, cudaStream_t stream);
@@ -78,6 +79,9 @@ cudaError_t launch_expand_ternary_p2(const uint32_t* packed2, int O, int I, void
 // as a K-major bf16 matrix (T [out,in] for Y, its transpose [in,out] for dX): k-tiles of 64, kind::f16
 enum { kFusedY = 0, kFusedDX = 1, kFusedDW = 2, kFusedYB = 3, kFusedDXB = 4 };
 constexpr int kFusedMaxProblems = 63;
+// dW on tf32 terms: 3 products x 4 instructions per 32-deep k-tile add into one accumulator, each with a truncation error of
+// ~2e-8 relative; 16 k-tiles (512 tokens) keep that below 4e-6
+constexpr int kFusedFlushKtiles = 16;
 struct FusedOperand {          // a row-major tensor read through TMA (host side only)
     const float* ptr;          // fp32 elements, or bf16 ones when `bf16` is set
     int rows, cols, ld;
@@ -93,6 +97,7 @@ struct FusedProblem {          // C[M,N] = A[M,K] . B[N,K]^T, see the kinds in t
     int mode;
     int BN, tiles_m, tiles_n, splits, ktiles_per_split;   // filled by fused_plan (k-tiles of 32)
     int nprod;                 // products per k-tile
+    int flush;                 // k-tiles (of 32) one accumulator takes before the epilogue adds it to the output; 0 = the whole item
     uint32_t prod;             // 4 bits each: A term | B term << 2 (0 = hi, 1 = lo), smallest first
     int a_map, b_map, item_begin;                         // filled by the launcher
 };

@@ -94,7 +94,7 @@ int mcl_cuda_counter_update_fused_static(void* cuda_stream, uint8_t* state, floa
                                          size_t C, size_t in_features, size_t out_features, size_t batch,
                                          float lr, float lr_scale, float rms_beta, float rms_eps,
                                          uint32_t seed) {
-    // same refusals as the ordinary entry point
+    // the refusals of the ordinary entry point, made before anything is launched
     if (C == 0 || in_features == 0 || out_features == 0 || batch == 0)
         return refuse(MCL_CUDA_EINVAL, "static update requires non-zero dimensions");
     if (in_features % 4 != 0) return refuse(MCL_CUDA_EINVAL, "static update requires in_features % 4 == 0");
@@ -110,6 +110,13 @@ int mcl_cuda_counter_update_fused_static(void* cuda_stream, uint8_t* state, floa
     if (!std::isfinite(rms_eps) || rms_eps < 0.0f)
         return refuse(MCL_CUDA_EINVAL, "static update requires non-negative finite rms_eps");
     if (!state || !scale || !v || !grad_out || !x) return refuse(MCL_CUDA_EINVAL, "static update: NULL pointer");
+    {   // fp32 / uint32 tensors are read with 32-bit accesses: a misaligned one would fault on the device
+        const struct { const char* name; const void* p; } al[] = {
+            {"grad_out", grad_out}, {"x", x}, {"scale", scale}, {"v", v}, {"packed2_out", packed2_out}};
+        for (const auto& a : al)
+            if (a.p && reinterpret_cast<uintptr_t>(a.p) % 4 != 0)
+                return refuse(MCL_CUDA_EINVAL, std::string("static update: ") + a.name + " must be 4-byte aligned");
+    }
     if (packed2_out && in_features % 16 != 0)
         return refuse(MCL_CUDA_EINVAL, "static update: packed2 output requires in_features % 16 == 0");
 
@@ -134,7 +141,7 @@ int mcl_cuda_counter_update_fused_static(void* cuda_stream, uint8_t* state, floa
         e = mcl::launch_counter_update_dense(state + r0 * state_row, scale + r0, v + r0, gw,
                                              packed2_out ? packed2_out + r0 * (in_features / 16) : nullptr, (int)C,
                                              (int)in_features, (int)nr, (int)r0, lr, lr_scale, rms_beta, rms_eps,
-                                             seed, nullptr, s->sm_count, s->max_smem, stream);
+                                             seed, nullptr, nullptr, s->sm_count, s->max_smem, stream);
         if (e == cudaErrorInvalidConfiguration)
             return refuse(MCL_CUDA_EUNSUPPORTED, "static update: in_features too large for one row in shared memory");
         if (e != cudaSuccess) return refuse(MCL_CUDA_ECUDA, std::string("static update: ") + cudaGetErrorString(e));

@@ -346,7 +346,7 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
             int pi = 0;
             long long pf_acc = 0, pf_full = 0, pf_issue = 0; (void)pf_acc; (void)pf_full; (void)pf_issue;
             PROF_T(tstart);
-            for (;; ++n_local) {
+            for (;;) {
                 int item = n_items;
                 {   // single-lane form of next_from_queue
                     const int s = (int)(q_seq % kQueue);
@@ -368,6 +368,12 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 const uint32_t b_lo = b_mn ? ((uint32_t)(kBox >> 4) << 16) : (1u << 16);
                 const uint32_t b_hi = b_mn ? ((512u >> 4) | (1u << 14) | (1u << 29)) : ((1024u >> 4) | (1u << 14) | (2u << 29));
                 const uint32_t nprod = (uint32_t)P.nprod, prod0 = P.prod;
+                // An accumulator takes at most P.flush k-tiles (tensor-core accumulation truncates, and the error grows
+                // with the number of instructions that add into one accumulator): a long item hands its accumulator to
+                // the epilogue every P.flush k-tiles and goes on in the other one; the epilogue adds the pieces in fp32.
+                const int flush = P.flush > 0 ? P.flush : I.nkt;
+                for (int j0 = 0; j0 < I.nkt && !abort_flag; j0 += flush, ++n_local) {
+                const int j1 = min(I.nkt, j0 + flush);
                 const uint32_t acc = n_local & 1u, aph = (n_local >> 1) & 1u;
                 PROF_T(ta0);
                 if (!mbar_wait(acc_empty(acc), aph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 14); break; }
@@ -375,7 +381,7 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kAccStride;
                 uint32_t accum = 0;
-                for (int j = 0; j < I.nkt; ++j, ++it) {
+                for (int j = j0; j < j1; ++j, ++it) {
                     const int s = (int)rs, sl = (int)(it % kLoSlots);
                     if (++rs == (uint32_t)n_raw) rs = 0;
                     const uint32_t hi16 = (raw0 + (uint32_t)s * raw_slot + (bf ? 2u : 1u) * (uint32_t)kABytes) >> 4;     // B as TMA delivered it
@@ -423,6 +429,8 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 }
                 if (abort_flag) break;
                 umma_commit(acc_full(acc));
+                }
+                if (abort_flag) break;
             }
 #ifdef MCL_FUSED_PROF
             { PROF_T(tend); long long* o = g_fused_prof + blockIdx.x * 16 + 4; o[0] = pf_acc; o[1] = pf_full; o[2] = pf_issue; o[3] = tend - tstart; }
@@ -481,17 +489,22 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
         int pi = 0;
         long long pf_wait = 0, pf_store = 0; (void)pf_wait; (void)pf_store;
         PROF_T(tstart);
-        for (;; ++n_local) {
+        bool alive = true;
+        while (alive) {
             PROF_T(t0);
             const int item = next_from_queue();
             if (item >= n_items) break;
             const Item I = decode_item(sp, n_problems, item, pi);
             const FusedProblem& P = sp[I.pi];
+            const int flush = P.flush > 0 ? P.flush : I.nkt;
+            const int npieces = (I.nkt + flush - 1) / flush;
+            for (int piece = 0; piece < npieces; ++piece, ++n_local) {
+            const bool add_prev = piece > 0;       // later pieces of an item are added to what this thread stored before
             const uint32_t acc = n_local & 1u, aph = (n_local >> 1) & 1u;
             bool ok = !abort_flag;
             if (ok && !mbar_wait_warp(acc_full(acc), aph, &abort_flag)) { abort_flag = 1; atomicExch(err, 13); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            if (!ok) { alive = false; break; }
             PROF_T(t1); PROF_ADD(pf_wait, t0, t1);
             tc_fence_after();
             const bool scale = (P.col_scale != nullptr) && P.splits == 1;
@@ -513,12 +526,29 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 int nchunks = 0;
                 for (int c0 = 0; c0 < BN && n0 + c0 < P.N; c0 += 16) ++nchunks;
                 if (nchunks > 0) tmem_ld16(t0addr, r);
+                // what this thread stored for the earlier pieces of the item, fetched one chunk ahead (an L2 round trip)
+                float4 prev[4], prev_next[4];
+                auto load_prev = [&](int ci, float4 (&dst)[4]) {
+                    const int col = n0 + ci * 16 + 4 * j4;
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        const int rr = p * 8 + rsub;
+                        dst[p] = (col < P.N && row0 + rr < P.M) ? *reinterpret_cast<const float4*>(cbase + (size_t)rr * P.ldc + col)
+                                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                };
+                if (add_prev && nchunks > 0) load_prev(0, prev_next);
                 for (int ci = 0; ci < nchunks; ++ci) {
                     const int c0 = ci * 16;
                     const int col = n0 + c0 + 4 * j4;
                     const bool col_ok = col < P.N;
                     float4 sc = make_float4(1.f, 1.f, 1.f, 1.f);
                     if (scale && col_ok) sc = __ldg(reinterpret_cast<const float4*>(P.col_scale + col));
+                    if (add_prev) {
+#pragma unroll
+                        for (int p = 0; p < 4; ++p) prev[p] = prev_next[p];
+                        if (ci + 1 < nchunks) load_prev(ci + 1, prev_next);
+                    }
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
@@ -533,6 +563,10 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                         float4 o = lds128(scratch + (uint32_t)rr * 64u + ((uint32_t)(j4 ^ ((rr >> 1) & 3)) << 4));
                         if (col_ok && row0 + rr < P.M) {
                             o.x *= sc.x; o.y *= sc.y; o.z *= sc.z; o.w *= sc.w;
+                            if (add_prev) {
+                                o.x = __fadd_rn(prev[p].x, o.x); o.y = __fadd_rn(prev[p].y, o.y);
+                                o.z = __fadd_rn(prev[p].z, o.z); o.w = __fadd_rn(prev[p].w, o.w);
+                            }
                             *reinterpret_cast<float4*>(cbase + (size_t)rr * P.ldc + col) = o;
                         }
                     }
@@ -542,6 +576,7 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
             tc_fence_before();
             mbar_arrive(acc_empty(acc));
             PROF_T(t2); PROF_ADD(pf_store, t1, t2);
+            }
         }
 #ifdef MCL_FUSED_PROF
         if (warp == kEpiWarp0 && lane == 0) { PROF_T(tend); long long* o = g_fused_prof + blockIdx.x * 16 + 8; o[0] = pf_wait; o[1] = pf_store; o[2] = tend - tstart; o[3] = n_local; }
@@ -976,6 +1011,7 @@ size_t fused_plan(FusedProblem* p, int target_items, int depth_limit) {
     if (depth_limit > 0 && (ktiles + splits - 1) / splits > depth_limit) splits = (ktiles + depth_limit - 1) / depth_limit;
     p->ktiles_per_split = (ktiles + splits - 1) / splits;
     p->splits = (ktiles + p->ktiles_per_split - 1) / p->ktiles_per_split;
+    p->flush = kFusedFlushKtiles;
     return p->splits > 1 ? (size_t)p->splits * p->M * p->N : 0;
 }
 

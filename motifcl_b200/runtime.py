@@ -69,6 +69,7 @@ class Context:
         if rc != 0:
             raise MotifclCudaError(rc, self._lib.mcl_cuda_last_error(None).decode())
         self.device = device
+        self.stream_handle = stream      # the cudaStream_t the context enqueues on (None: a stream of its own)
 
     @classmethod
     def on_torch_stream(cls, device: int = 0) -> "Context":

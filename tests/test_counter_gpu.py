@@ -589,3 +589,92 @@ def test_linear_step_many_equals_layer_by_layer(ctx, orc):
         assert np.array_equal(_bits(d["v"].cpu().numpy()), _bits(o[2]))
         if d["packed2_out"] is not None:
             assert np.array_equal(d["packed2_out"].cpu().numpy().view(np.uint32), o[3])
+
+
+# ---- the benchmarked configurations themselves ----------------------------------------------------
+
+def _stack_entry(cfg, idx, shape, N, sigma, randomised=True):
+    I, O = shape.in_features, shape.out_features
+    sc, v = synth.scale_v(cfg, idx, O, I, randomised)
+    L = dict(I=I, O=O, state=synth.counters(cfg, idx, O, I).reshape(-1), sc=sc, v=v,
+             x=synth.activations(cfg, idx, N, I), dy=synth.upstream_grad(cfg, idx, N, O, sigma))
+    L["d"] = dict(x=_t(L["x"]), grad_out=_t(L["dy"]), state=_t(L["state"]), scale=_t(sc), v=_t(v),
+                  y=torch.empty(N, O, dtype=torch.float32, device=DEV),
+                  grad_x=torch.empty(N, I, dtype=torch.float32, device=DEV),
+                  grad_w=torch.empty(O, I, dtype=torch.float32, device=DEV),
+                  packed2_out=torch.zeros(O, I // 16, dtype=torch.int32, device=DEV),
+                  in_features=I, out_features=O, batch=N, update_rows=O, row_offset=0)
+    return L
+
+
+def _check_update_given_own_gradient(orc, L, C, hy, seed):
+    d = L["d"]
+    gw = d["grad_w"].cpu().numpy()
+    o = orc.update_dense(L["state"], L["sc"], L["v"], gw, C, L["I"], L["O"], 0, *hy, seed)
+    assert np.array_equal(d["state"].cpu().numpy(), o[0])
+    assert np.array_equal(_bits(d["scale"].cpu().numpy()), _bits(o[1]))
+    assert np.array_equal(_bits(d["v"].cpu().numpy()), _bits(o[2]))
+    assert np.array_equal(d["packed2_out"].cpu().numpy().view(np.uint32), o[3])
+    return gw
+
+
+def test_grouped_step_at_the_benchmark_token_count_vs_oracle(ctx, orc):
+    """The stories15M-shaped workload as the benchmark runs it: 8192 tokens, so every weight gradient is
+    four 2048-token slices added by the grouped split-K reduction.  One layer of each of the three shapes
+    against the fp32 reference sums (relative L2 <= 1e-5), update bit-exact given the step's own gradient."""
+    from motifcl_b200.runtime import linear_descs
+    C, N = 11, 8192
+    hy = (3e-3, 0.05, 0.9, 1e-3)
+    shapes = [synth.LinearShape("wq", 288, 288), synth.LinearShape("w1", 768, 288), synth.LinearShape("w2", 288, 768)]
+    layers = [_stack_entry(2, 50 + i, s, N, 0.02) for i, s in enumerate(shapes)]
+    ctx.counter_linear_step_many(linear_descs([L["d"] for L in layers]), C, *hy, 12345)
+    ctx.finish()
+    for L in layers:
+        d = L["d"]
+        assert rel_l2(d["y"].cpu().numpy(), orc.forward(L["x"], L["state"], L["sc"], C, L["O"])) <= 1e-5
+        assert rel_l2(d["grad_x"].cpu().numpy(), orc.backward_input(L["dy"], L["state"], L["sc"], C, L["I"])) <= 1e-5
+        gw = _check_update_given_own_gradient(orc, L, C, hy, 12345)
+        assert rel_l2(gw, orc.grad_w(L["dy"], L["x"])) <= 1e-5
+
+
+def test_grouped_step_of_all_42_linears_at_8192_tokens(ctx, orc):
+    """The whole benchmarked call: 42 linears x 8192 tokens in one mcl_cuda_counter_linear_step_many (problem
+    tables of 42 and 2 x 42 entries).  Products against float64 sums (relative L2 <= 1e-5); update bit-exact
+    given each layer's own gradient."""
+    from motifcl_b200.runtime import linear_descs
+    C, N = 11, 8192
+    hy = (3e-3, 0.0, 0.9, 1e-3)
+    shapes = synth.stories15m_linears()
+    layers = [_stack_entry(2, i, s, N, 0.02, randomised=False) for i, s in enumerate(shapes)]
+    ctx.counter_linear_step_many(linear_descs([L["d"] for L in layers]), C, *hy, 777)
+    ctx.finish()
+    worst = [0.0, 0.0, 0.0]
+    for L in layers:
+        d = L["d"]
+        w = orc.decode_weight(L["state"], L["sc"], C, L["I"], L["O"]).astype(np.float64)
+        x64, dy64 = L["x"].astype(np.float64), L["dy"].astype(np.float64)
+        errs = (rel_l2(d["y"].cpu().numpy(), x64 @ w.T), rel_l2(d["grad_x"].cpu().numpy(), dy64 @ w),
+                rel_l2(_check_update_given_own_gradient(orc, L, C, hy, 777), dy64.T @ x64))
+        worst = [max(a, b) for a, b in zip(worst, errs)]
+        del d["x"], d["grad_out"], d["y"], d["grad_x"]
+    print(f"42 linears x 8192 tokens: worst relative L2  Y {worst[0]:.2e}  dX {worst[1]:.2e}  dW {worst[2]:.2e}")
+    assert max(worst) <= 1e-5, worst
+
+
+@pytest.mark.parametrize("M", [1, 4, 16])
+@pytest.mark.parametrize("O,I", [(14336, 4096), (4096, 14336), (4096, 4096)])
+def test_ternary_gemv_on_the_decode_sweep_matrices(ctx, orc, M, O, I):
+    """The matrices of the decode-GEMV configuration (w1 / w3, w2, q / o of an 8B-scale block) against float64."""
+    rng = np.random.default_rng(M * 11 + O // 1024)
+    p2 = rng.integers(0, 3, size=(O, I), dtype=np.uint8)           # fields t + 1
+    words = np.zeros((O, I // 16), np.uint32)
+    for k in range(16):
+        words |= p2[:, k::16].astype(np.uint32) << np.uint32(2 * k)
+    scale = rng.uniform(0.02, 0.2, O).astype(np.float32)
+    x = rng.standard_normal((M, I)).astype(np.float32)
+    y = torch.full((M, O), 3.0, dtype=torch.float32, device=DEV)
+    ctx.ternary_gemv(_t(x), _t(words.view(np.int32)), _t(scale), y, M, I, O)
+    ref64 = (x.astype(np.float64) @ (p2.astype(np.float64) - 1.0).T) * scale.astype(np.float64)
+    assert rel_l2(y.cpu().numpy(), ref64) <= 1e-5
+    if M == 1:      # and the checker's own 2-bit decoder agrees with the layout used here
+        assert rel_l2(orc.ternary_gemv(x, words, scale, f64=True), ref64) <= 1e-12

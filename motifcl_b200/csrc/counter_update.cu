@@ -633,16 +633,11 @@ __device__ __forceinline__ void update_u16_body(const UpdParams& p, const uint32
                     gw_s[swz4(i + 2 * kUpdThreads)] = v2; gw_s[swz4(i + 3 * kUpdThreads)] = v3;
                 }
                 for (; i < n4; i += kUpdThreads) gw_s[swz4(i)] = __ldg(gsrc + i);
-            } else {                // a warp per row, rows of the batch dealt round-robin
-                for (int r = tid >> 5; r < nrows; r += kUpdThreads / 32) {
-                    const float4* rs = gsrc + (size_t)r * gpr;
-                    float4* rd = gw_s + r * gpr;
-                    int g = lane;
-                    for (; g + 64 < gpr; g += 96) {
-                        const float4 v0 = __ldg(rs + g), v1 = __ldg(rs + g + 32), v2 = __ldg(rs + g + 64);
-                        rd[swz4(g)] = v0; rd[swz4(g + 32)] = v1; rd[swz4(g + 64)] = v2;
-                    }
-                    for (; g < gpr; g += 32) rd[swz4(g)] = __ldg(rs + g);
+            } else {                // flat over the batch; row = i / gpr by multiply-high (gpr = 4 * units per row)
+                for (int i = tid; i < n4; i += kUpdThreads) {
+                    const int r = unit_magic ? (int)__umulhi((uint32_t)i >> 2, unit_magic) : (i >> 2);
+                    const int g = i - r * gpr;
+                    gw_s[r * gpr + swz4(g)] = __ldg(gsrc + i);
                 }
             }
         }
@@ -742,23 +737,18 @@ __device__ __forceinline__ void update_u16_body(const UpdParams& p, const uint32
 // latency of HBM, the row statistics (64 lanes of parallelism per row, by the reference's reduction order) and the
 // tick (everything else) overlap instead of taking turns between CTA-wide barriers.
 //   ring     D row slots in shared memory: gradient row (XOR-swizzled float4s), state row, row table, row constants
-//   warps 0..3   "stats": warp s owns the CTA's rows s, s+4, ...  For a row it waits until the slot's previous row
-//                has been ticked, copies gradient and state into the slot with cp.async (the next row's copies are
-//                issued before this row's statistics, so several rows per warp are in flight), replays the 64-lane
-//                reduction with two virtual lanes per thread, writes v / scale / the row's constants and its
-//                table, and marks the slot ready.
-//   warps 4..15  "tick": chunks of 32 consecutive 16-weight units, dealt round-robin over the twelve warps across
-//                rows.  A lane ticks one unit, writes the new state words over the old ones in the slot, the warp
-//                copies its 384 bytes out with 16-byte stores and stores its 32 words of 2-bit fields; when a warp
-//                has passed a row it releases the slot.
+//   stats    every fourth warp (one scheduler's worth).  Stats warp s owns the CTA's rows s, s + S, ...  For a row it
+//            waits until the slot's previous row has been ticked, copies gradient, state, scale and v into the slot with
+//            cp.async, replays the 64-lane reduction with two virtual lanes per thread, writes v / scale / the row's
+//            constants and its table, and marks the slot ready.  The warps take turns, so S rows are in flight.
+//   tick     the other warps: chunks of 32 consecutive 16-weight units, dealt round-robin across rows.  A lane ticks
+//            one unit, writes the new state words over the old ones in the slot, the warp copies its 384 bytes out
+//            with 16-byte stores and stores its 32 words of 2-bit fields; a warp that has passed a row releases its slot.
+// Measured on B200 (8192 x 4096 fp32 gradient, CUDA events): 1.95 TB/s = 0.30 of the copy bandwidth; the kernel issues
+// ~55 instructions per weight (two 32-bit hashes, the quotient, floor / compare / two table look-ups), which at four
+// instructions per clock and SM bounds it near 0.55 whatever the memory system does.
 // Every wait is bounded: on time-out the kernel sets *err (when given) and all roles leave.
-#ifndef MCL_WS_AHEAD
-#define MCL_WS_AHEAD 1
-#endif
-#ifndef MCL_WS_THREADS
-#define MCL_WS_THREADS 512
-#endif
-constexpr int kWsThreads = MCL_WS_THREADS;
+constexpr int kWsThreads = 512;
 // Every fourth warp is a stats warp: warps are dealt to the SM's four schedulers by warp number, so the stats warps
 // share ONE scheduler among themselves and their short dependent instruction chains do not queue behind the tick
 // warps' long independent ones.
@@ -813,14 +803,6 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
-#ifdef MCL_WS_PROF
-__device__ long long g_ws_prof[16 * 8];
-#define WSP_T(v) const long long v = clock64()
-#define WSP_ADD(slot, a, b) prof[slot] += (b) - (a)
-#else
-#define WSP_T(v)
-#define WSP_ADD(slot, a, b)
-#endif
 
 template <bool WITH_Q>
 __global__ void __launch_bounds__(kWsThreads, 1)
@@ -864,24 +846,15 @@ counter_update_ws_kernel(const UpdParams p, const uint32_t pow16, const uint32_t
         if (err != nullptr) atomicExch(err, kWsErrCode);
     };
 
-#ifdef MCL_WS_PROF
-    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const long long t_start = clock64();
-#endif
     // A slot is refilled by whichever stats warp owns the row D rows later; the wait on the slot's "free" barrier tells
     // apart only two consecutive uses, so a warp must never get two uses ahead of the ring: with S warps striding the
     // rows by S, that holds when S <= D.  Fewer slots than stats warps (very wide rows): the surplus warps sit out.
     const int S = kWsStatsWarps < D ? kWsStatsWarps : D;
     if (warp < kWsStatsWarps) {
         // ---- stats warps ---------------------------------------------------------------------------
-        // A warp issues the copies of its rows `ahead` turns early.  The slot of a row held the row D earlier, which can
-        // only be ticked once every row before it is ready: copies may run ahead only by fewer rows than the ring has slots.
-        const int ahead = (D - 1) / S < MCL_WS_AHEAD ? (D - 1) / S : MCL_WS_AHEAD;
         auto issue = [&](int n) -> bool {       // copies of local row n into its slot; false: gave up
             const int slot = n % D;
-            WSP_T(w0);
             if (!ws_wait(free_bar(slot), (((uint32_t)(n / D)) & 1u) ^ 1u, abort_flag)) return false;
-            WSP_T(w1); WSP_ADD(0, w0, w1);
             const uint32_t base = sa_ring + (uint32_t)slot * (uint32_t)L.slot_bytes;
             const float4* gsrc = reinterpret_cast<const float4*>(p.grad_w + (size_t)(r_begin + n) * I);
             for (int g = lane; g < gpr; g += 32) cp_async16(base + ((uint32_t)swz4(g) << 4), gsrc + g);
@@ -893,25 +866,16 @@ counter_update_ws_kernel(const UpdParams p, const uint32_t pow16, const uint32_t
             }
             return true;
         };
+        // Several rows are in flight per SM because the stats warps take turns; a warp itself copies one row in, waits
+        // for it and works on it (issuing the next row's copies earlier was measured no faster: the warp would then
+        // wait for a free slot while its current row keeps the tick warps waiting).
         bool ok = true;
-        for (int a = 0; a < ahead; ++a) {
-            const int n = warp + a * S;
-            if (ok && warp < S && n < nrows) ok = issue(n);
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        }
         for (int n = warp < S ? warp : nrows; n < nrows && ok; n += S) {
-            if (n + ahead * S < nrows) ok = issue(n + ahead * S);
+            ok = issue(n);
             asm volatile("cp.async.commit_group;" ::: "memory");
             if (!ok) break;
-            WSP_T(l0);
-            switch (ahead) {
-                case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-                case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-                case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-                default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-            }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncwarp();
-            WSP_T(l1); WSP_ADD(1, l0, l1);
             const int slot = n % D;
             unsigned char* sbase = smem + L.off_ring + (size_t)slot * L.slot_bytes;
             const float4* g4 = reinterpret_cast<const float4*>(sbase);
@@ -958,7 +922,6 @@ counter_update_ws_kernel(const UpdParams p, const uint32_t pow16, const uint32_t
             rowtab[lane] = row_entry(lut, lane, k_reb, sa_tick);
             rowtab[lane + 32] = row_entry(lut, lane + 32, k_reb, sa_tick);
             mbar_arrive(ready_bar(slot));          // 32 arrivals complete the phase: each lane publishes its own writes
-            WSP_T(l2); WSP_ADD(2, l1, l2);
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
         if (!ok && lane == 0) give_up();
@@ -980,9 +943,7 @@ counter_update_ws_kernel(const UpdParams p, const uint32_t pow16, const uint32_t
                 released = n;
             }
             const int slot = n % D;
-            WSP_T(k0);
             if (!ws_wait(ready_bar(slot), ((uint32_t)(n / D)) & 1u, abort_flag)) { ok = false; break; }
-            WSP_T(k1); WSP_ADD(3, k0, k1);
             const uint32_t base = sa_ring + (uint32_t)slot * (uint32_t)L.slot_bytes;
             const int j = c * 32 + lane;
             const int row = r_begin + n;
@@ -999,7 +960,6 @@ counter_update_ws_kernel(const UpdParams p, const uint32_t pow16, const uint32_t
                 if (p.packed2 != nullptr) p.packed2[(size_t)row * upr + j] = fields;
             }
             __syncwarp();
-            WSP_T(k2); WSP_ADD(4, k1, k2);
             // the chunk's 384 bytes of state, 16 bytes per lane
             const int nbytes = min(32, upr - c * 32) * 12;
             if (lane * 16 < nbytes) {
@@ -1007,7 +967,6 @@ counter_update_ws_kernel(const UpdParams p, const uint32_t pow16, const uint32_t
                                                                 (size_t)c * 384 + (size_t)lane * 16);
                 *reinterpret_cast<uint4*>(p.state + (size_t)row * row_bytes + (size_t)c * 384 + (size_t)lane * 16) = v;
             }
-            WSP_T(k3); WSP_ADD(5, k2, k3);
         }
         __syncwarp();
         if (ok) {
@@ -1017,18 +976,7 @@ counter_update_ws_kernel(const UpdParams p, const uint32_t pow16, const uint32_t
             give_up();
         }
     }
-#ifdef MCL_WS_PROF
-    if (blockIdx.x == 0 && lane == 0) {
-        prof[6] = clock64() - t_start;
-        for (int i = 0; i < 8; ++i) g_ws_prof[warp * 8 + i] = prof[i];
-    }
-#endif
 }
-#ifdef MCL_WS_PROF
-}  // namespace
-extern "C" int mcl_debug_ws_prof(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_ws_prof, sizeof(g_ws_prof)); }
-namespace {
-#endif
 
 template <bool WITH_Q>
 __global__ void __launch_bounds__(kUpdThreads, kUpdCtasPerSm)

@@ -677,7 +677,7 @@ static int fused_products(mcl_cuda_ctx* ctx, const char* op, const float* x, con
     int n = 0, i_dw = -1;
     size_t k_floats = 0;
     // the kernel's split-K slices are 32 deep; the depth limit is stated in k-tiles of 64
-    const int depth = 2 * mcl::kGradDepthLimit;
+    const int depth = mcl::kFusedDwDepth;
     auto add = [&](int mode, int M, int N, int K) {
         mcl::FusedProblem& p = pr[n];
         p = mcl::FusedProblem();
@@ -875,7 +875,7 @@ int mcl_cuda_counter_linear_step_many(mcl_cuda_ctx* ctx, const mcl_cuda_linear_d
                                              lr_scale, rms_beta, rms_eps, seed));
     }
     if (grouped.empty()) return MCL_CUDA_OK;
-    const int depth = 2 * mcl::kGradDepthLimit;
+    const int depth = mcl::kFusedDwDepth;
     const size_t ng = grouped.size();
     // with many layers in flight the K splits of dW only have to respect the accumulation depth
     const int target_items = (int)((2 * (size_t)ctx->sm_count + ng - 1) / ng);

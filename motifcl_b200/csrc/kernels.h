@@ -81,7 +81,15 @@ enum { kFusedY = 0, kFusedDX = 1, kFusedDW = 2, kFusedYB = 3, kFusedDXB = 4 };
 constexpr int kFusedMaxProblems = 63;
 // dW on tf32 terms: 3 products x 4 instructions per 32-deep k-tile add into one accumulator, each with a truncation error of
 // ~2e-8 relative; 16 k-tiles (512 tokens) keep that below 4e-6
-constexpr int kFusedFlushKtiles = 16;
+#ifndef MCL_FUSED_FLUSH
+#define MCL_FUSED_FLUSH 16
+#endif
+#ifndef MCL_FUSED_DW_DEPTH
+#define MCL_FUSED_DW_DEPTH 64
+#endif
+constexpr int kFusedFlushKtiles = MCL_FUSED_FLUSH;
+// k-tiles (of 32 tokens) of one dW work item: longer items mean fewer split-K partials to write and add up
+constexpr int kFusedDwDepth = MCL_FUSED_DW_DEPTH;
 struct FusedOperand {          // a row-major tensor read through TMA (host side only)
     const float* ptr;          // fp32 elements, or bf16 ones when `bf16` is set
     int rows, cols, ld;

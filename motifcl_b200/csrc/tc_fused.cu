@@ -368,6 +368,65 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 const uint32_t b_lo = b_mn ? ((uint32_t)(kBox >> 4) << 16) : (1u << 16);
                 const uint32_t b_hi = b_mn ? ((512u >> 4) | (1u << 14) | (1u << 29)) : ((1024u >> 4) | (1u << 14) | (2u << 29));
                 const uint32_t nprod = (uint32_t)P.nprod, prod0 = P.prod;
+                if (P.flush <= 0) {
+                // ---- the whole item in one accumulator ----
+                const uint32_t acc = n_local & 1u, aph = (n_local >> 1) & 1u;
+                PROF_T(ta0);
+                if (!mbar_wait(acc_empty(acc), aph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 14); break; }
+                PROF_T(ta1); PROF_ADD(pf_acc, ta0, ta1);
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * kAccStride;
+                uint32_t accum = 0;
+                for (int j = 0; j < I.nkt; ++j, ++it) {
+                    const int s = (int)rs, sl = (int)(it % kLoSlots);
+                    if (++rs == (uint32_t)n_raw) rs = 0;
+                    const uint32_t hi16 = (raw0 + (uint32_t)s * raw_slot + (bf ? 2u : 1u) * (uint32_t)kABytes) >> 4;     // B as TMA delivered it
+                    const uint32_t lo16 = (lo0 + (uint32_t)sl * lo_slot) >> 4;                          // B lo
+                    const uint32_t a_tm = tmem_base + a_col(sl);                                        // A hi, A lo at +32
+                    PROF_T(t0);
+                    // the converters arrive after they have seen the raw tile, so this wait covers the copies as well
+                    if (!mbar_wait(lo_full(sl), (it / kLoSlots) & 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 12); break; }
+                    PROF_T(t1); PROF_ADD(pf_full, t0, t1);
+#ifdef MCL_FUSED_PROF
+                    t_mma[s] = t1;
+#endif
+                    tc_fence_after();
+                    uint32_t prod = prod0;
+#ifdef MCL_FUSED_PROF
+                    if (!(tab.pad0 & 2))
+#endif
+                    if (bf) {
+                        // the ternary tile is K-major bf16 in the 128-byte swizzle (rows of 64 k); A terms: hi, lo
+                        const uint64_t db0 = smem_desc_k_sw128(hi16 << 4);
+#pragma unroll
+                        for (uint32_t t = 0; t < 2; ++t)
+#pragma unroll
+                            for (uint32_t kk = 0; kk < 4; ++kk) {
+                                umma_bf16_ts(d_tmem, a_tm + 32u * t + kk * 8u, db0 + 2u * kk, idesc, accum);
+                                accum = 1u;
+                            }
+                    } else
+                    for (uint32_t q = 0; q < nprod; ++q, prod >>= 4) {
+                        const uint32_t a_t = a_tm + ((prod & 3u) ? 32u : 0u);
+                        const uint32_t b16 = b_lo | (((prod >> 2) & 3u) ? lo16 : hi16);
+#pragma unroll
+                        for (uint32_t kk = 0; kk < 4; ++kk) {
+                            const uint64_t db = ((uint64_t)b_hi << 32) | (uint64_t)(b16 + kk * b_step);
+                            umma_tf32_ts(d_tmem, a_t + kk * 8u, db, idesc, accum);
+                            accum = 1u;
+                        }
+                    }
+                    umma_commit(raw_empty(s));
+                    umma_commit(lo_empty(sl));
+                    PROF_T(t2); PROF_ADD(pf_issue, t1, t2);
+#ifdef MCL_FUSED_PROF
+                    t_commit[s] = t2;
+#endif
+                }
+                if (abort_flag) break;
+                umma_commit(acc_full(acc));
+                ++n_local;
+                } else {
                 // An accumulator takes at most P.flush k-tiles (tensor-core accumulation truncates, and the error grows
                 // with the number of instructions that add into one accumulator): a long item hands its accumulator to
                 // the epilogue every P.flush k-tiles and goes on in the other one; the epilogue adds the pieces in fp32.
@@ -429,6 +488,7 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 }
                 if (abort_flag) break;
                 umma_commit(acc_full(acc));
+                }
                 }
                 if (abort_flag) break;
             }
@@ -496,6 +556,67 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
             if (item >= n_items) break;
             const Item I = decode_item(sp, n_problems, item, pi);
             const FusedProblem& P = sp[I.pi];
+            if (P.flush <= 0) {
+            // ---- the whole item is one accumulator: scale and store ----
+            do {
+            const uint32_t acc = n_local & 1u, aph = (n_local >> 1) & 1u;
+            bool ok = !abort_flag;
+            if (ok && !mbar_wait_warp(acc_full(acc), aph, &abort_flag)) { abort_flag = 1; atomicExch(err, 13); ok = false; }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { alive = false; break; }
+            PROF_T(t1); PROF_ADD(pf_wait, t0, t1);
+            tc_fence_after();
+            const bool scale = (P.col_scale != nullptr) && P.splits == 1;
+            const int BN = P.BN, n0 = I.nt * BN;
+            const int row0 = I.mt * 128 + q * 32;
+            float* cbase = P.C + ((size_t)I.split * P.M + row0) * P.ldc;
+            // The TMEM fragment (lane = row, 16 columns) goes through a swizzled 2 KiB tile of shared memory so
+            // that a store instruction writes 8 rows x 64 contiguous bytes instead of 32 rows x 16 bytes.
+            const uint32_t scratch = scratch0 + (uint32_t)q * 2048u;
+            const int rsub = lane >> 2, j4 = lane & 3;
+#ifdef MCL_FUSED_PROF
+            if (!(tab.pad0 & 4))
+#endif
+            {
+                // software pipeline: the TMEM load of the next chunk and the scale of this one are in flight while
+                // the current chunk goes through shared memory to global memory
+                const uint32_t t0addr = tmem_base + acc * kAccStride + ((uint32_t)(q * 32) << 16);
+                uint32_t r[16];
+                int nchunks = 0;
+                for (int c0 = 0; c0 < BN && n0 + c0 < P.N; c0 += 16) ++nchunks;
+                if (nchunks > 0) tmem_ld16(t0addr, r);
+                for (int ci = 0; ci < nchunks; ++ci) {
+                    const int c0 = ci * 16;
+                    const int col = n0 + c0 + 4 * j4;
+                    const bool col_ok = col < P.N;
+                    float4 sc = make_float4(1.f, 1.f, 1.f, 1.f);
+                    if (scale && col_ok) sc = __ldg(reinterpret_cast<const float4*>(P.col_scale + col));
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        sts128(scratch + (uint32_t)lane * 64u + ((uint32_t)(j ^ ((lane >> 1) & 3)) << 4),
+                               make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                           __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+                    __syncwarp();
+                    if (ci + 1 < nchunks) tmem_ld16(t0addr + (uint32_t)(c0 + 16), r);
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        const int rr = p * 8 + rsub;
+                        float4 o = lds128(scratch + (uint32_t)rr * 64u + ((uint32_t)(j4 ^ ((rr >> 1) & 3)) << 4));
+                        if (col_ok && row0 + rr < P.M) {
+                            o.x *= sc.x; o.y *= sc.y; o.z *= sc.z; o.w *= sc.w;
+                            *reinterpret_cast<float4*>(cbase + (size_t)rr * P.ldc + col) = o;
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(acc_empty(acc));
+            PROF_T(t2); PROF_ADD(pf_store, t1, t2);
+            ++n_local;
+            } while (false);
+            } else {
             const int flush = P.flush > 0 ? P.flush : I.nkt;
             const int npieces = (I.nkt + flush - 1) / flush;
             for (int piece = 0; piece < npieces; ++piece, ++n_local) {
@@ -526,57 +647,81 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 int nchunks = 0;
                 for (int c0 = 0; c0 < BN && n0 + c0 < P.N; c0 += 16) ++nchunks;
                 if (nchunks > 0) tmem_ld16(t0addr, r);
-                // what this thread stored for the earlier pieces of the item, fetched one chunk ahead (an L2 round trip)
-                float4 prev[4], prev_next[4];
-                auto load_prev = [&](int ci, float4 (&dst)[4]) {
-                    const int col = n0 + ci * 16 + 4 * j4;
+                if (!add_prev) {
+                    // the first (usually only) piece of an item: scale and store
+                    for (int ci = 0; ci < nchunks; ++ci) {
+                        const int c0 = ci * 16;
+                        const int col = n0 + c0 + 4 * j4;
+                        const bool col_ok = col < P.N;
+                        float4 sc = make_float4(1.f, 1.f, 1.f, 1.f);
+                        if (scale && col_ok) sc = __ldg(reinterpret_cast<const float4*>(P.col_scale + col));
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int p = 0; p < 4; ++p) {
-                        const int rr = p * 8 + rsub;
-                        dst[p] = (col < P.N && row0 + rr < P.M) ? *reinterpret_cast<const float4*>(cbase + (size_t)rr * P.ldc + col)
-                                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (int j = 0; j < 4; ++j)
+                            sts128(scratch + (uint32_t)lane * 64u + ((uint32_t)(j ^ ((lane >> 1) & 3)) << 4),
+                                   make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                               __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+                        __syncwarp();
+                        if (ci + 1 < nchunks) tmem_ld16(t0addr + (uint32_t)(c0 + 16), r);
+#pragma unroll
+                        for (int p = 0; p < 4; ++p) {
+                            const int rr = p * 8 + rsub;
+                            float4 o = lds128(scratch + (uint32_t)rr * 64u + ((uint32_t)(j4 ^ ((rr >> 1) & 3)) << 4));
+                            if (col_ok && row0 + rr < P.M) {
+                                o.x *= sc.x; o.y *= sc.y; o.z *= sc.z; o.w *= sc.w;
+                                *reinterpret_cast<float4*>(cbase + (size_t)rr * P.ldc + col) = o;
+                            }
+                        }
+                        __syncwarp();
                     }
-                };
-                if (add_prev && nchunks > 0) load_prev(0, prev_next);
-                for (int ci = 0; ci < nchunks; ++ci) {
-                    const int c0 = ci * 16;
-                    const int col = n0 + c0 + 4 * j4;
-                    const bool col_ok = col < P.N;
-                    float4 sc = make_float4(1.f, 1.f, 1.f, 1.f);
-                    if (scale && col_ok) sc = __ldg(reinterpret_cast<const float4*>(P.col_scale + col));
-                    if (add_prev) {
+                } else {
+                    // a later piece: add to what this thread stored for the earlier ones (fetched one chunk ahead: an L2
+                    // round trip); only unscaled outputs are cut into pieces
+                    float4 prev[4], prev_next[4];
+                    auto load_prev = [&](int ci, float4 (&dst)[4]) {
+                        const int col = n0 + ci * 16 + 4 * j4;
+#pragma unroll
+                        for (int p = 0; p < 4; ++p) {
+                            const int rr = p * 8 + rsub;
+                            dst[p] = (col < P.N && row0 + rr < P.M) ? *reinterpret_cast<const float4*>(cbase + (size_t)rr * P.ldc + col)
+                                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                    };
+                    if (nchunks > 0) load_prev(0, prev_next);
+                    for (int ci = 0; ci < nchunks; ++ci) {
+                        const int c0 = ci * 16;
+                        const int col = n0 + c0 + 4 * j4;
+                        const bool col_ok = col < P.N;
 #pragma unroll
                         for (int p = 0; p < 4; ++p) prev[p] = prev_next[p];
                         if (ci + 1 < nchunks) load_prev(ci + 1, prev_next);
-                    }
-                    tmem_ld_wait();
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        sts128(scratch + (uint32_t)lane * 64u + ((uint32_t)(j ^ ((lane >> 1) & 3)) << 4),
-                               make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                           __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
-                    __syncwarp();
-                    if (ci + 1 < nchunks) tmem_ld16(t0addr + (uint32_t)(c0 + 16), r);
+                        for (int j = 0; j < 4; ++j)
+                            sts128(scratch + (uint32_t)lane * 64u + ((uint32_t)(j ^ ((lane >> 1) & 3)) << 4),
+                                   make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                               __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+                        __syncwarp();
+                        if (ci + 1 < nchunks) tmem_ld16(t0addr + (uint32_t)(c0 + 16), r);
 #pragma unroll
-                    for (int p = 0; p < 4; ++p) {
-                        const int rr = p * 8 + rsub;
-                        float4 o = lds128(scratch + (uint32_t)rr * 64u + ((uint32_t)(j4 ^ ((rr >> 1) & 3)) << 4));
-                        if (col_ok && row0 + rr < P.M) {
-                            o.x *= sc.x; o.y *= sc.y; o.z *= sc.z; o.w *= sc.w;
-                            if (add_prev) {
+                        for (int p = 0; p < 4; ++p) {
+                            const int rr = p * 8 + rsub;
+                            float4 o = lds128(scratch + (uint32_t)rr * 64u + ((uint32_t)(j4 ^ ((rr >> 1) & 3)) << 4));
+                            if (col_ok && row0 + rr < P.M) {
                                 o.x = __fadd_rn(prev[p].x, o.x); o.y = __fadd_rn(prev[p].y, o.y);
                                 o.z = __fadd_rn(prev[p].z, o.z); o.w = __fadd_rn(prev[p].w, o.w);
+                                *reinterpret_cast<float4*>(cbase + (size_t)rr * P.ldc + col) = o;
                             }
-                            *reinterpret_cast<float4*>(cbase + (size_t)rr * P.ldc + col) = o;
                         }
+                        __syncwarp();
                     }
-                    __syncwarp();
                 }
             }
             tc_fence_before();
             mbar_arrive(acc_empty(acc));
             PROF_T(t2); PROF_ADD(pf_store, t1, t2);
             }
+                    }
         }
 #ifdef MCL_FUSED_PROF
         if (warp == kEpiWarp0 && lane == 0) { PROF_T(tend); long long* o = g_fused_prof + blockIdx.x * 16 + 8; o[0] = pf_wait; o[1] = pf_store; o[2] = tend - tstart; o[3] = n_local; }

@@ -4,7 +4,9 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -33,6 +35,7 @@ struct mcl_cuda_ctx {
     uint64_t lane_mark = 0;      // launches at the last lane_fork (when this context is a lane)
     bool recording = false;      // between mcl_cuda_batch_begin and mcl_cuda_batch_end
     uint64_t recorded_launches = 0;
+    int live_batches = 0;        // recorded batches not yet destroyed: they hold addresses inside the workspace
 };
 
 static bool g_fused_enabled = true;   // environment MCL_CUDA_FUSED=0 turns the grouped fused-split kernel off (A/B timing)
@@ -41,11 +44,16 @@ struct mcl_cuda_batch {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     uint64_t kernels = 0;        // kernel launches one replay stands for
+    mcl_cuda_ctx* ctx = nullptr; // the context it was recorded on (looked up among the live contexts before use)
 };
 
 namespace {
 
 thread_local std::string g_error;   // errors raised before a context exists
+
+// live contexts, so that a batch destroyed after its context does not touch freed memory
+std::mutex g_ctx_mutex;
+std::set<mcl_cuda_ctx*> g_live_ctx;
 
 int fail(mcl_cuda_ctx* ctx, int code, const std::string& msg) {
     if (ctx) ctx->error = msg; else g_error = msg;
@@ -99,6 +107,10 @@ int ws_reserve(mcl_cuda_ctx* ctx, size_t bytes, void** out) {
     if (bytes > ctx->ws_bytes) {
         if (ctx->recording)
             return fail(ctx, MCL_CUDA_EINVAL, "workspace would grow while recording a batch: run the same calls once unrecorded first");
+        if (ctx->live_batches > 0)
+            return fail(ctx, MCL_CUDA_EINVAL, "workspace would grow (to " + std::to_string(bytes) + " bytes) while " +
+                                                  std::to_string(ctx->live_batches) + " recorded batch(es) hold addresses inside it: "
+                                                  "run the largest call once before recording, or destroy the batches first");
         cudaError_t e = cudaStreamSynchronize(ctx->stream);
         if (e != cudaSuccess) return fail_cuda(ctx, "workspace sync", e);
         if (ctx->ws) cudaFree(ctx->ws);
@@ -169,6 +181,10 @@ int create_impl(int device, cudaStream_t stream, bool own, mcl_cuda_ctx** out_ct
     }
     if (const char* e = std::getenv("MCL_CUDA_TC_MAX_KTILES")) mcl::tc_set_max_ktiles(std::atoi(e));
     if (const char* e = std::getenv("MCL_CUDA_FUSED")) g_fused_enabled = std::atoi(e) != 0;
+    {
+        std::lock_guard<std::mutex> lock(g_ctx_mutex);
+        g_live_ctx.insert(ctx);
+    }
     *out_ctx = ctx;
     return MCL_CUDA_OK;
 }
@@ -259,6 +275,10 @@ int mcl_cuda_create_on_stream(int device, void* cuda_stream, mcl_cuda_ctx** out_
 }
 void mcl_cuda_destroy(mcl_cuda_ctx* ctx) {
     if (!ctx) return;
+    {
+        std::lock_guard<std::mutex> lock(g_ctx_mutex);
+        g_live_ctx.erase(ctx);
+    }
     DeviceGuard guard(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->ws) cudaFree(ctx->ws);
@@ -303,6 +323,8 @@ int mcl_cuda_batch_end(mcl_cuda_ctx* ctx, mcl_cuda_batch** out_batch) {
     ctx->launches = ctx->recorded_launches;     // recorded, not run
     e = cudaGraphInstantiate(&b->exec, graph, 0);
     if (e != cudaSuccess) { cudaGraphDestroy(graph); delete b; return fail_cuda(ctx, "batch_end (instantiate)", e); }
+    b->ctx = ctx;
+    ++ctx->live_batches;
     *out_batch = b;
     return MCL_CUDA_OK;
 }
@@ -318,6 +340,10 @@ int mcl_cuda_batch_launch(mcl_cuda_ctx* ctx, mcl_cuda_batch* batch) {
 }
 void mcl_cuda_batch_destroy(mcl_cuda_batch* batch) {
     if (!batch) return;
+    {
+        std::lock_guard<std::mutex> lock(g_ctx_mutex);
+        if (batch->ctx && g_live_ctx.count(batch->ctx) && batch->ctx->live_batches > 0) --batch->ctx->live_batches;
+    }
     if (batch->exec) cudaGraphExecDestroy(batch->exec);
     if (batch->graph) cudaGraphDestroy(batch->graph);
     delete batch;

@@ -224,6 +224,12 @@ class CounterStack:
                 b = getattr(self, name)
                 if b is not None:
                     b.close()
+            if not getattr(self, "_ws_sized", False):
+                # The context's workspace only grows, and a recorded batch holds addresses inside it: make the call with the
+                # largest footprint (all three products at once) before anything is recorded.
+                self.products_only(xs, dys)
+                self.ctx.finish()
+                self._ws_sized = True
             self._batch = self._record(lambda: self._products_part(xs, dys, "dw"))
             self._rows_batch = self._record(lambda: self._products_part(xs, dys, "rows"))
             self._batch_key = key

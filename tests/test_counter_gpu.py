@@ -678,3 +678,36 @@ def test_ternary_gemv_on_the_decode_sweep_matrices(ctx, orc, M, O, I):
     assert rel_l2(y.cpu().numpy(), ref64) <= 1e-5
     if M == 1:      # and the checker's own 2-bit decoder agrees with the layout used here
         assert rel_l2(orc.ternary_gemv(x, words, scale, f64=True), ref64) <= 1e-12
+
+
+def test_workspace_growth_is_refused_while_a_recorded_batch_is_alive(orc):
+    """A recorded batch holds addresses inside the context's grow-only workspace; a later call that needs a larger
+    workspace must be refused (with the reason) instead of moving the workspace under the batch."""
+    from motifcl_b200 import Context
+    c2 = Context(0)
+    try:
+        def products(n_tokens, I, O):
+            rng = np.random.default_rng(n_tokens)
+            st = synth.counters(7, 3, O, I).reshape(-1)
+            x = _t(rng.standard_normal((n_tokens, I)).astype(np.float32))
+            y = torch.empty(n_tokens, O, dtype=torch.float32, device=DEV)
+            d_st, d_sc = _t(st), _t(np.full(O, 0.1, np.float32))
+            torch.cuda.synchronize()
+            return lambda: c2.counter_forward(x, d_st, d_sc, y, n_tokens, I, O, 11)
+        c2.set_gemm_mode("tensor")
+        small, big = products(256, 2048, 256), products(512, 2048, 2048)
+        small()
+        c2.finish()
+        c2.batch_begin()
+        small()
+        batch = c2.batch_end()
+        with pytest.raises(MotifclCudaError) as e:
+            big()
+        assert "recorded batch" in e.value.message
+        batch.launch()
+        c2.finish()
+        batch.close()
+        big()               # with the batch gone the workspace may grow
+        c2.finish()
+    finally:
+        c2.close()

@@ -133,6 +133,9 @@ cudaError_t launch_splitk_reduce(const float* partial, float* c, const float* co
                                  int splits, cudaStream_t stream);
 
 // gemv.cu
+// M <= 2: one CUDA-core launch that streams the 2-bit words (in_features % 16 == 0)
+cudaError_t launch_ternary_gemv_stream(const float* x, const uint32_t* packed2, const float* scale, float* y, int M,
+                                       int in_features, int out_features, int sm_count, cudaStream_t stream);
 cudaError_t launch_ternary_gemv(const float* x, const uint32_t* packed2, const float* scale, float* y,
                                 int M, int in_features, int out_features, int sm_count,
                                 cudaStream_t stream);

@@ -405,7 +405,8 @@ def run_refperf(args):
         print(json.dumps({"micro": "refperf", "unavailable": "adapter binaries are not built (make -C motifcl_b200/adapter "
                                                              "needs the MotifCL tree)"}))
         return
-    out_dir = os.path.join(ROOT, "gpurun_out", "vulkan-perf")
+    import tempfile
+    out_dir = tempfile.mkdtemp(prefix="motifcl-vulkan-perf-")
     rows = []
     for flt in ("counter_", "matmul_f32"):
         r = subprocess.run([exe, "--filter", flt, "--out", os.path.join(out_dir, flt.strip("_"))], capture_output=True,
@@ -533,8 +534,9 @@ def run_gemv_tp(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         return ms
-    # one recorded batch per sweep on a single rank; with several ranks the sweep is launched eagerly (recording a
-    # sweep that contains NCCL all-reduces into this library's batch did not return on the 2-GPU box)
+    # one recorded batch per sweep on a single rank; with several ranks the sweep is launched eagerly: a batch is a stream
+    # capture of the context's stream, and torch's NCCL collectives run on the process group's own stream behind event
+    # hand-offs, which must not be captured by this library's thread-local capture
     recorded = False
     try:
         if world > 1:

@@ -38,8 +38,6 @@ struct mcl_cuda_ctx {
     int live_batches = 0;        // recorded batches not yet destroyed: they hold addresses inside the workspace
 };
 
-static bool g_fused_enabled = true;   // environment MCL_CUDA_FUSED=0 turns the grouped fused-split kernel off (A/B timing)
-
 struct mcl_cuda_batch {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
@@ -179,8 +177,6 @@ int create_impl(int device, cudaStream_t stream, bool own, mcl_cuda_ctx** out_ct
         delete ctx;
         return fail_cuda(nullptr, "context setup", e);
     }
-    if (const char* e = std::getenv("MCL_CUDA_TC_MAX_KTILES")) mcl::tc_set_max_ktiles(std::atoi(e));
-    if (const char* e = std::getenv("MCL_CUDA_FUSED")) g_fused_enabled = std::atoi(e) != 0;
     {
         std::lock_guard<std::mutex> lock(g_ctx_mutex);
         g_live_ctx.insert(ctx);
@@ -687,7 +683,7 @@ static bool fused_wanted(const mcl_cuda_ctx* ctx, const float* x, const float* g
                          const float* scale, const float* y, const float* grad_x, const float* grad_w, size_t I,
                          size_t O, size_t Nt) {
     (void)ternary;
-    if (!g_fused_enabled || I % 32 != 0 || O % 32 != 0 || Nt % 4 != 0 || I > 1024 || O > 1024) return false;
+    if (I % 32 != 0 || O % 32 != 0 || Nt % 4 != 0 || I > 1024 || O > 1024) return false;
     const uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(grad_out) |
                            reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(y) |
                            reinterpret_cast<uintptr_t>(grad_x) | reinterpret_cast<uintptr_t>(grad_w);

@@ -59,13 +59,6 @@ __device__ __forceinline__ uint32_t idesc_i8(int m, int n) {
 // long as the activation digits are stored in the same order, which gemv_quantize_kernel does.
 __device__ __forceinline__ int gv_kperm(int k) { return (k & ~15) | ((k & 3) << 2) | ((k >> 2) & 3); }
 
-#ifdef MCL_GEMV_PROF
-__device__ long long g_gemv_prof[148 * 16];
-__device__ __forceinline__ long long gv_now() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define GVP(slot) do { if (blockIdx.x < 148) g_gemv_prof[blockIdx.x * 16 + (slot)] = gv_now(); } while (0)
-#else
-#define GVP(slot) do { } while (0)
-#endif
 
 __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_constant__ CUtensorMap tmP,
                                                              const __grid_constant__ CUtensorMap tmX,
@@ -76,7 +69,6 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) GVP(0);
     const int S = p.stages, Nq = p.Nq;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t b_tile = (uint32_t)Nq * 128u;
@@ -115,7 +107,6 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
-    if (threadIdx.x == 0) GVP(1);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -143,9 +134,6 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
             // ---- MMA issuer: 8 x (128 x Nq x 32) int8 MMAs per k-block ------------------------------
             const uint32_t idesc = idesc_i8(GV_ROWS, Nq);
             uint32_t it = 0, n_local = 0;
-#ifdef MCL_GEMV_PROF
-            long long mm_wait = 0, mm_work = 0;
-#endif
             for (int item = blockIdx.x; item < n_items && !abort_flag; item += gridDim.x, ++n_local) {
                 const int split = item / row_tiles;
                 const int kb0 = split * p.kb_per_split;
@@ -156,17 +144,9 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
                 const uint32_t d_tmem = tmem_base + acc * (uint32_t)Nq;
                 for (int j = 0; j < nkb; ++j, ++it) {
                     const int s = (int)(it % (uint32_t)S);
-#ifdef MCL_GEMV_PROF
-                    const long long tm0 = clock64();
-#endif
                     const int e = (int)(it % GV_EXP);
                     // the expanders arrive after they have seen the raw slot: this wait covers the digit tiles too
                     if (!mbar_wait(a_full(e), (it / GV_EXP) & 1u, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 12); break; }
-                    if (it == 0) GVP(3);
-#ifdef MCL_GEMV_PROF
-                    const long long tm1 = clock64();
-                    mm_wait += tm1 - tm0;
-#endif
                     tc_fence_after();
                     const uint32_t st = base + (uint32_t)s * stage_bytes;
                     const uint32_t a_tm = tmem_base + a_col0 + (uint32_t)e * GV_ACOLS;
@@ -179,16 +159,9 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
                     }
                     umma_commit(a_empty(e));
                     umma_commit(empty_bar(s));
-#ifdef MCL_GEMV_PROF
-                    mm_work += clock64() - tm1;
-#endif
                 }
                 if (abort_flag) break;
                 umma_commit(acc_full(acc));
-                GVP(4);
-#ifdef MCL_GEMV_PROF
-                if (blockIdx.x < 148) { g_gemv_prof[blockIdx.x * 16 + 12] = mm_wait; g_gemv_prof[blockIdx.x * 16 + 13] = mm_work; }
-#endif
             }
         }
     } else if (warp < 6) {
@@ -199,9 +172,6 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         uint32_t it = 0;
         bool ok = true;
-#ifdef MCL_GEMV_PROF
-        long long ex_wait = 0, ex_work = 0;
-#endif
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const int split = item / row_tiles;
             const int kb0 = split * p.kb_per_split;
@@ -209,17 +179,9 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
             for (int j = 0; j < nkb; ++j, ++it) {
                 const int s = (int)(it % (uint32_t)S);
                 const uint32_t ph = (it / (uint32_t)S) & 1u;
-#ifdef MCL_GEMV_PROF
-                const long long tw0 = clock64();
-#endif
                 const int e = (int)(it % GV_EXP);
                 if (abort_flag || !mbar_wait(raw_full(s), ph, &abort_flag) ||
                     !mbar_wait(a_empty(e), ((it / GV_EXP) & 1u) ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 13); ok = false; break; }
-                if (it == 0 && r == 0) GVP(2);
-#ifdef MCL_GEMV_PROF
-                const long long tw1 = clock64();
-                ex_wait += tw1 - tw0;
-#endif
                 tc_fence_after();      // the MMAs that read this TMEM slot have completed (a_empty)
                 unsigned char* st = smem_raw + (base - smem_u32(smem_raw)) + (size_t)s * stage_bytes;
                 const uint4* raw = reinterpret_cast<const uint4*>(st + r * 64);
@@ -245,14 +207,8 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
                 tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(a_full(e));
-#ifdef MCL_GEMV_PROF
-                ex_work += clock64() - tw1;
-#endif
             }
         }
-#ifdef MCL_GEMV_PROF
-        if (r == 0 && blockIdx.x < 148) { g_gemv_prof[blockIdx.x * 16 + 10] = ex_wait; g_gemv_prof[blockIdx.x * 16 + 11] = ex_work; g_gemv_prof[blockIdx.x * 16 + 14] = it; }
-#endif
     } else {
         // ---- epilogue warps: int32 accumulator -> global (atomic when k is split) ---------------
         const int q = warp & 3;
@@ -264,7 +220,6 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
             if (ok && !mbar_wait(acc_full(acc), aph, &abort_flag)) { abort_flag = 1; atomicExch(p.err, 15); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            if (n_local == 0 && warp == 6 && lane == 0) GVP(5);
             tc_fence_after();
             const int row = rt * GV_ROWS + q * 32 + lane;
             int* dst = p.acc + row;
@@ -287,7 +242,6 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
             }
             tc_fence_before();
             mbar_arrive(acc_empty(acc));
-            if (warp == 6 && lane == 0) GVP(6);
         }
     }
     __syncwarp();
@@ -300,7 +254,6 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_tc_kernel(const __grid_consta
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
-    if (threadIdx.x == 0) GVP(7);
 }
 
 // ---- activation rows -> four int8 digit rows each, digit sums, power-of-two scale ---------------
@@ -319,9 +272,6 @@ __global__ void __launch_bounds__(256) gemv_quantize_kernel(const float* __restr
             acc_clear[i] = make_int4(0, 0, 0, 0);
         return;
     }
-#ifdef MCL_GEMV_PROF
-    if (tid == 0 && m == 0) g_gemv_prof[8] = gv_now();
-#endif
     signed char* q0 = xq + (size_t)(4 * m) * I;
     if (m >= M) {
         for (int k = tid; k < I; k += 256) { q0[k] = 0; q0[I + k] = 0; q0[2 * (size_t)I + k] = 0; q0[3 * (size_t)I + k] = 0; }
@@ -357,9 +307,6 @@ __global__ void __launch_bounds__(256) gemv_quantize_kernel(const float* __restr
     __syncthreads();
     if (tid < 4) corr[4 * m + tid] = isum[tid];
     if (tid == 0) xscale[m] = ldexpf(1.0f, e) / 64.0f;
-#ifdef MCL_GEMV_PROF
-    if (tid == 0 && m == 0) g_gemv_prof[9] = gv_now();
-#endif
 }
 
 // y[m,o] = scale[o] * xscale[m] * sum_d 128^-d * (acc[o][4m+d] - corr[4m+d])
@@ -484,10 +431,5 @@ cudaError_t launch_ternary_gemv_tc(const float* x, const uint32_t* packed2, cons
     return cudaSuccess;
 }
 
-#ifdef MCL_GEMV_PROF
-extern "C" int mcl_debug_gemv_prof(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_gemv_prof, sizeof(long long) * 148 * 16);
-}
-#endif
 
 }  // namespace mcl

@@ -54,7 +54,6 @@ cudaError_t launch_simt_grad_w(const float* grad_out, const float* x, float* gra
 
 // tc_gemm.cu -- tcgen05 / TMEM / TMA contractions on bf16 term planes (see the file header)
 int tc_pick_bn(int N);
-void tc_set_max_ktiles(int n);
 size_t tc_splitk_workspace_bytes(int M, int N, int K, int sm_count, int depth_limit, int* splits_out);
 constexpr int kGradDepthLimit = 32;   // k-tiles per accumulator for fp32 x fp32 products (K = 2048)
 // C[M,N] (+= over terms) A_pa[M,K] . B_pb[N,K]^T ; planes are bf16 [P][rows][ld], plane stride in elements

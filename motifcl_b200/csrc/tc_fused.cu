@@ -171,14 +171,6 @@ __device__ __forceinline__ float4 lo_term4(float4 v) {
 }
 
 
-#ifdef MCL_FUSED_PROF
-__device__ long long g_fused_prof[148 * 16 + 148 * 8];
-#define PROF_T(var) const long long var = clock64()
-#define PROF_ADD(acc, a, b) acc += (b) - (a)
-#else
-#define PROF_T(var)
-#define PROF_ADD(acc, a, b)
-#endif
 
 template <int CAP>
 __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_constant__ FusedTable<CAP> tab, int* err,
@@ -188,9 +180,6 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
     __shared__ int queue_item[kQueue], queue_next[kQueue];
     __shared__ unsigned int tiles_issued;      // progress of the TMA lane, paces the prefetch lane
     __shared__ FusedProblem sp[CAP];
-#ifdef MCL_FUSED_PROF
-    __shared__ long long t_issue[kMaxRaw], t_conv[kMaxRaw], t_arr[kMaxRaw], t_mma[kMaxRaw], t_commit[kMaxRaw];
-#endif
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -263,9 +252,6 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
             // ---- scheduler + TMA producer --------------------------------------------------------------
             uint32_t it = 0, rs = 0, rph = 0;          // tiles issued, raw slot, its phase parity
             int pi = 0;
-            long long pf_wait = 0, pf_issue = 0; (void)pf_wait; (void)pf_issue;
-            long long h0 = 0, h1 = 0, h2 = 0, h3 = 0, h4 = 0; (void)h0; (void)h1; (void)h2; (void)h3; (void)h4;
-            PROF_T(tstart);
             // two items are drawn ahead: the next one is published with the current one (the prefetch lane asks
             // its tiles into L2), the one after is still in flight from the counter
             int drawn = atomicAdd(next_item, 1);
@@ -293,20 +279,9 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                     const int s = (int)rs;
                     const uint32_t ph = rph;
                     if (++rs == (uint32_t)n_raw) { rs = 0; rph ^= 1u; }
-                    PROF_T(t0);
                     if (!mbar_wait(raw_empty(s), ph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 11); break; }
-                    PROF_T(t1); PROF_ADD(pf_wait, t0, t1);
-#ifdef MCL_FUSED_PROF
-                    if (it >= (uint32_t)n_raw) {
-                        h0 += t_conv[s] - t_issue[s]; h1 += t_arr[s] - t_conv[s]; h2 += t_mma[s] - t_arr[s];
-                        h3 += t_commit[s] - t_mma[s]; h4 += t1 - t_commit[s];
-                    }
-#endif
                     const uint32_t st = raw0 + (uint32_t)s * raw_slot;
                     const int k0 = (I.kt0 + j) * 32;
-#ifdef MCL_FUSED_PROF
-                    t_issue[s] = clock64();
-#endif
                     if (is_bf16_mode(mode)) {
                         // 64 k: two fp32 boxes of A side by side, one bf16 box of the ternary operand
                         mbar_expect_tx(raw_full(s), 2u * (uint32_t)kABytes + (uint32_t)P.BN * 128u);
@@ -323,7 +298,6 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                         else tma_load_3d(st + kABytes, mb, raw_full(s), 0, k0, n0 >> 5);
                     }
                     *reinterpret_cast<volatile unsigned int*>(&tiles_issued) = it + 1;
-                    PROF_T(t2); PROF_ADD(pf_issue, t1, t2);
                 }
                 if (abort_flag) {      // tell the other roles to stop
                     const int s = (int)(q_seq % kQueue);
@@ -335,17 +309,12 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                     break;
                 }
             }
-#ifdef MCL_FUSED_PROF
-            { PROF_T(tend); long long* o = g_fused_prof + blockIdx.x * 16; o[0] = pf_wait; o[1] = pf_issue; o[2] = tend - tstart; o[3] = it; long long* o2 = g_fused_prof + 148 * 16 + blockIdx.x * 8; o2[0] = h0; o2[1] = h1; o2[2] = h2; o2[3] = h3; o2[4] = h4; }
-#endif
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- MMA issuer ------------------------------------------------------------------------
             uint32_t it = 0, n_local = 0, rs = 0;
             int pi = 0;
-            long long pf_acc = 0, pf_full = 0, pf_issue = 0; (void)pf_acc; (void)pf_full; (void)pf_issue;
-            PROF_T(tstart);
             for (;;) {
                 int item = n_items;
                 {   // single-lane form of next_from_queue
@@ -371,9 +340,7 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 if (P.flush <= 0) {
                 // ---- the whole item in one accumulator ----
                 const uint32_t acc = n_local & 1u, aph = (n_local >> 1) & 1u;
-                PROF_T(ta0);
                 if (!mbar_wait(acc_empty(acc), aph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 14); break; }
-                PROF_T(ta1); PROF_ADD(pf_acc, ta0, ta1);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kAccStride;
                 uint32_t accum = 0;
@@ -383,18 +350,10 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                     const uint32_t hi16 = (raw0 + (uint32_t)s * raw_slot + (bf ? 2u : 1u) * (uint32_t)kABytes) >> 4;     // B as TMA delivered it
                     const uint32_t lo16 = (lo0 + (uint32_t)sl * lo_slot) >> 4;                          // B lo
                     const uint32_t a_tm = tmem_base + a_col(sl);                                        // A hi, A lo at +32
-                    PROF_T(t0);
                     // the converters arrive after they have seen the raw tile, so this wait covers the copies as well
                     if (!mbar_wait(lo_full(sl), (it / kLoSlots) & 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 12); break; }
-                    PROF_T(t1); PROF_ADD(pf_full, t0, t1);
-#ifdef MCL_FUSED_PROF
-                    t_mma[s] = t1;
-#endif
                     tc_fence_after();
                     uint32_t prod = prod0;
-#ifdef MCL_FUSED_PROF
-                    if (!(tab.pad0 & 2))
-#endif
                     if (bf) {
                         // the ternary tile is K-major bf16 in the 128-byte swizzle (rows of 64 k); A terms: hi, lo
                         const uint64_t db0 = smem_desc_k_sw128(hi16 << 4);
@@ -418,10 +377,6 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                     }
                     umma_commit(raw_empty(s));
                     umma_commit(lo_empty(sl));
-                    PROF_T(t2); PROF_ADD(pf_issue, t1, t2);
-#ifdef MCL_FUSED_PROF
-                    t_commit[s] = t2;
-#endif
                 }
                 if (abort_flag) break;
                 umma_commit(acc_full(acc));
@@ -434,9 +389,7 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 for (int j0 = 0; j0 < I.nkt && !abort_flag; j0 += flush, ++n_local) {
                 const int j1 = min(I.nkt, j0 + flush);
                 const uint32_t acc = n_local & 1u, aph = (n_local >> 1) & 1u;
-                PROF_T(ta0);
                 if (!mbar_wait(acc_empty(acc), aph ^ 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 14); break; }
-                PROF_T(ta1); PROF_ADD(pf_acc, ta0, ta1);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kAccStride;
                 uint32_t accum = 0;
@@ -446,18 +399,10 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                     const uint32_t hi16 = (raw0 + (uint32_t)s * raw_slot + (bf ? 2u : 1u) * (uint32_t)kABytes) >> 4;     // B as TMA delivered it
                     const uint32_t lo16 = (lo0 + (uint32_t)sl * lo_slot) >> 4;                          // B lo
                     const uint32_t a_tm = tmem_base + a_col(sl);                                        // A hi, A lo at +32
-                    PROF_T(t0);
                     // the converters arrive after they have seen the raw tile, so this wait covers the copies as well
                     if (!mbar_wait(lo_full(sl), (it / kLoSlots) & 1u, &abort_flag)) { abort_flag = 1; atomicExch(err, 12); break; }
-                    PROF_T(t1); PROF_ADD(pf_full, t0, t1);
-#ifdef MCL_FUSED_PROF
-                    t_mma[s] = t1;
-#endif
                     tc_fence_after();
                     uint32_t prod = prod0;
-#ifdef MCL_FUSED_PROF
-                    if (!(tab.pad0 & 2))
-#endif
                     if (bf) {
                         // the ternary tile is K-major bf16 in the 128-byte swizzle (rows of 64 k); A terms: hi, lo
                         const uint64_t db0 = smem_desc_k_sw128(hi16 << 4);
@@ -481,10 +426,6 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                     }
                     umma_commit(raw_empty(s));
                     umma_commit(lo_empty(sl));
-                    PROF_T(t2); PROF_ADD(pf_issue, t1, t2);
-#ifdef MCL_FUSED_PROF
-                    t_commit[s] = t2;
-#endif
                 }
                 if (abort_flag) break;
                 umma_commit(acc_full(acc));
@@ -492,9 +433,6 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 }
                 if (abort_flag) break;
             }
-#ifdef MCL_FUSED_PROF
-            { PROF_T(tend); long long* o = g_fused_prof + blockIdx.x * 16 + 4; o[0] = pf_acc; o[1] = pf_full; o[2] = pf_issue; o[3] = tend - tstart; }
-#endif
         }
     } else if (warp == 2) {
         if (lane == 0) {
@@ -547,11 +485,8 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
         const int q = warp & 3;
         uint32_t n_local = 0;
         int pi = 0;
-        long long pf_wait = 0, pf_store = 0; (void)pf_wait; (void)pf_store;
-        PROF_T(tstart);
         bool alive = true;
         while (alive) {
-            PROF_T(t0);
             const int item = next_from_queue();
             if (item >= n_items) break;
             const Item I = decode_item(sp, n_problems, item, pi);
@@ -564,7 +499,6 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
             if (ok && !mbar_wait_warp(acc_full(acc), aph, &abort_flag)) { abort_flag = 1; atomicExch(err, 13); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { alive = false; break; }
-            PROF_T(t1); PROF_ADD(pf_wait, t0, t1);
             tc_fence_after();
             const bool scale = (P.col_scale != nullptr) && P.splits == 1;
             const int BN = P.BN, n0 = I.nt * BN;
@@ -574,9 +508,6 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
             // that a store instruction writes 8 rows x 64 contiguous bytes instead of 32 rows x 16 bytes.
             const uint32_t scratch = scratch0 + (uint32_t)q * 2048u;
             const int rsub = lane >> 2, j4 = lane & 3;
-#ifdef MCL_FUSED_PROF
-            if (!(tab.pad0 & 4))
-#endif
             {
                 // software pipeline: the TMEM load of the next chunk and the scale of this one are in flight while
                 // the current chunk goes through shared memory to global memory
@@ -613,7 +544,6 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
             }
             tc_fence_before();
             mbar_arrive(acc_empty(acc));
-            PROF_T(t2); PROF_ADD(pf_store, t1, t2);
             ++n_local;
             } while (false);
             } else {
@@ -626,7 +556,6 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
             if (ok && !mbar_wait_warp(acc_full(acc), aph, &abort_flag)) { abort_flag = 1; atomicExch(err, 13); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { alive = false; break; }
-            PROF_T(t1); PROF_ADD(pf_wait, t0, t1);
             tc_fence_after();
             const bool scale = (P.col_scale != nullptr) && P.splits == 1;
             const int BN = P.BN, n0 = I.nt * BN;
@@ -636,9 +565,6 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
             // that a store instruction writes 8 rows x 64 contiguous bytes instead of 32 rows x 16 bytes.
             const uint32_t scratch = scratch0 + (uint32_t)q * 2048u;
             const int rsub = lane >> 2, j4 = lane & 3;
-#ifdef MCL_FUSED_PROF
-            if (!(tab.pad0 & 4))
-#endif
             {
                 // software pipeline: the TMEM load of the next chunk and the scale of this one are in flight while
                 // the current chunk goes through shared memory to global memory
@@ -719,13 +645,9 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
             }
             tc_fence_before();
             mbar_arrive(acc_empty(acc));
-            PROF_T(t2); PROF_ADD(pf_store, t1, t2);
             }
                     }
         }
-#ifdef MCL_FUSED_PROF
-        if (warp == kEpiWarp0 && lane == 0) { PROF_T(tend); long long* o = g_fused_prof + blockIdx.x * 16 + 8; o[0] = pf_wait; o[1] = pf_store; o[2] = tend - tstart; o[3] = n_local; }
-#endif
     } else if (warp >= kConvWarp0) {
         // ---- converters --------------------------------------------------------------------------------
         // Two groups of four warps take the k-tiles alternately (group = parity of the tile number).
@@ -738,8 +660,6 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
         const int q = warp & 3, row = q * 32 + lane;
         uint32_t it = 0, rs = 0, rph = 0;
         int pi = 0;
-        long long pf_wait = 0, pf_work = 0, pf_lat = 0; (void)pf_wait; (void)pf_work; (void)pf_lat;
-        PROF_T(tstart);
         for (;;) {
             const int item = next_from_queue();
             if (item >= n_items || abort_flag) break;
@@ -757,7 +677,6 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 if ((int)(it & 1u) != grp) continue;
                 const int sl = (int)(it % kLoSlots);
                 const uint32_t a_taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a_col(sl);
-                PROF_T(t0);
                 // the slot first: once its last reader (tile it - 2) is done, every earlier tile is, so the raw
                 // barrier cannot still show the phase of this group's previous visit
                 ok = mbar_wait_warp(lo_empty(sl), ((it / kLoSlots) & 1u) ^ 1u, &abort_flag) &&
@@ -765,19 +684,8 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 if (!ok) break;
                 tc_fence_after();          // the MMAs that read this TMEM slot have completed
                 const int k0 = (I.kt0 + j) * 32;
-                PROF_T(t1); PROF_ADD(pf_wait, t0, t1);
-#ifdef MCL_FUSED_PROF
-                pf_lat += t1 - t_issue[s];
-                if (tg == 0) t_conv[s] = t1;
-#endif
                 const uint32_t st = raw0 + (uint32_t)s * raw_slot, sto = lo0 + (uint32_t)sl * lo_slot;
                 uint32_t hi[32], lo[32];
-#ifdef MCL_FUSED_PROF
-                if (tab.pad0 & 1) {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) { hi[c] = 0u; lo[c] = 0u; }
-                } else
-#endif
                 if (is_bf16_mode(P.mode)) {
                     // 64 k of the row from two boxes; two bf16 terms, two k per TMEM column (even k in the low half)
                     const int kb = (I.kt0 + j) * 64;
@@ -845,16 +753,9 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(lo_full(sl));
-                PROF_T(t2); PROF_ADD(pf_work, t1, t2);
-#ifdef MCL_FUSED_PROF
-                if (tg == kConvThreads / 2 - 1) t_arr[s] = t2;
-#endif
             }
             if (!ok) { abort_flag = 1; atomicExch(err, 15); break; }
         }
-#ifdef MCL_FUSED_PROF
-        if (tg == 0 && grp == 0) { PROF_T(tend); long long* o = g_fused_prof + blockIdx.x * 16 + 12; o[0] = pf_wait; o[1] = pf_work; o[2] = pf_lat; o[3] = it; }
-#endif
     }
     __syncwarp();
     if (abort_flag) {
@@ -1097,11 +998,7 @@ cudaError_t launch_fused_cap(const FusedProblem* probs, const FusedOperand* a_op
     tab.raw_slot = kABytes + ((bhi + 1023) & ~1023);
     tab.lo_slot = (blo + 1023) & ~1023;
     tab.pad0 = 0;
-    static const int prefetch_on = getenv("MCL_CUDA_FUSED_PREFETCH") ? atoi(getenv("MCL_CUDA_FUSED_PREFETCH")) : 0;
-    tab.prefetch = prefetch_on;
-#ifdef MCL_FUSED_PROF
-    if (const char* dbg = getenv("MCL_FUSED_DBG")) tab.pad0 = atoi(dbg);      // ablation switches of the profiling build
-#endif
+    tab.prefetch = 0;       // asking the next item's tiles into L2 ahead of the copies measured no gain
     const long long budget = (long long)max_smem - (long long)fa.sharedSizeBytes - 1024 - kScratch - kLoSlots * (long long)tab.lo_slot;
     int n_raw = (int)(budget / tab.raw_slot);
     if (n_raw > kMaxRaw) n_raw = kMaxRaw;
@@ -1279,10 +1176,5 @@ cudaError_t launch_splitk_reduce_group(const float* const* partial, float* const
     return cudaSuccess;
 }
 
-#ifdef MCL_FUSED_PROF
-extern "C" int mcl_debug_fused_prof(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_fused_prof, sizeof(long long) * (148 * 16 + 148 * 8));
-}
-#endif
 
 }  // namespace mcl

@@ -451,8 +451,6 @@ int tc_pick_bn(int N) {
     return best;
 }
 
-static int g_max_ktiles = -1;     // debug override of the depth limit (environment MCL_CUDA_TC_MAX_KTILES)
-void tc_set_max_ktiles(int n) { g_max_ktiles = n; }
 
 size_t tc_splitk_workspace_bytes(int M, int N, int K, int sm_count, int depth_limit, int* splits_out) {
     const int bn = tc_pick_bn(N);
@@ -470,7 +468,7 @@ size_t tc_splitk_workspace_bytes(int M, int N, int K, int sm_count, int depth_li
     // at K = 1024, 6e-6 at K = 16384).  `depth_limit` (k-tiles of 64) bounds what one accumulator
     // absorbs; deeper contractions are cut into slices that the reduction kernel adds in fp32 with
     // round-to-nearest.
-    const int lim = g_max_ktiles >= 0 ? g_max_ktiles : depth_limit;
+    const int lim = depth_limit;
     if (lim > 0 && (ktiles + splits - 1) / splits > lim) splits = (ktiles + lim - 1) / lim;
     *splits_out = splits;
     return splits > 1 ? (size_t)splits * M * N * sizeof(float) : 0;

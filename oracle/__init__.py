@@ -21,8 +21,10 @@ _f64p = np.ctypeslib.ndpointer(np.float64, flags="C_CONTIGUOUS")
 _u32p = np.ctypeslib.ndpointer(np.uint32, flags="C_CONTIGUOUS")
 
 
-def build(ref_tree: str = "/root/reference") -> None:
+def build(ref_tree: str | None = None) -> None:
     """Compile liboracle.so, and the compiled-reference library when `ref_tree` exists."""
+    if ref_tree is None:      # MOTIFCL_REF, else a `reference` directory beside this repository
+        ref_tree = os.environ.get("MOTIFCL_REF", os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference"))
     subprocess.check_call(["make", "-s", "-C", _HERE, "all"])
     if os.path.isfile(os.path.join(ref_tree, "kernels", "compact_counter.cl")):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={ref_tree}"])

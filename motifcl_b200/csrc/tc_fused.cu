@@ -30,8 +30,8 @@
 // operand has; the tensor core reads it in place (instruction-descriptor transpose bits), so no
 // transposed copy of an activation is ever made.
 //
-// CTA = 16 warps.  The A operand of every product is read from TENSOR MEMORY: converter threads own one
-// row of the A tile each (= one TMEM lane), read its 32 k from the raw tile in shared memory and store the
+// CTA = 16 warps.  The A operand of every product is read from TENSOR MEMORY: two converter threads share one
+// row of the A tile (= one TMEM lane), read half of its k each from the raw tile in shared memory and store the
 // raw words (`hi`, scaled by scale[k] for dX) and the lo terms into 64 TMEM columns (tcgen05.st).  A
 // transposed A (dW) is read column-wise from the MN-major boxes, so the transpose costs nothing.  Shared
 // memory holds the RAW ring (2 to 6 slots: A and B as TMA delivers them; deep, because it has to cover
@@ -41,7 +41,7 @@
 //   warp 1        allocates TMEM; one lane issues tcgen05.mma (A from TMEM, B from shared memory) and commits
 //   warp 2        one lane asks the tiles of the next work item into L2 (TMA prefetch; off by default)
 //   warps 4..7    epilogue: tcgen05.ld of TMEM lane quarter (warp & 3), scale, 128-bit stores
-//   warps 8..15   converters: two groups of four warps take the k-tiles alternately
+//   warps 8..15   converters: all eight work on every k-tile, half a row of the A tile per thread
 // TMEM columns: two accumulators of at most 160 columns at 0 and 160 (the epilogue of one item overlaps the
 // main loop of the next), A slots of 64 columns at 320, 384, 448.
 // Every wait is bounded (see mbar_wait); on time-out the kernel records an error word and drains.
@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
         abort_flag = (*reinterpret_cast<volatile int*>(err) != 0);
         tiles_issued = 0;
         for (int s = 0; s < kMaxRaw; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), 1); }
-        for (int s = 0; s < kLoSlots; ++s) { mbar_init(lo_full(s), kConvThreads / 2); mbar_init(lo_empty(s), 1); }
+        for (int s = 0; s < kLoSlots; ++s) { mbar_init(lo_full(s), kConvThreads); mbar_init(lo_empty(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 128); }
         for (int s = 0; s < kQueue; ++s) { mbar_init(q_full(s), 1); mbar_init(q_empty(s), kQueueReaders); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -650,13 +650,13 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
         }
     } else if (warp >= kConvWarp0) {
         // ---- converters --------------------------------------------------------------------------------
-        // Two groups of four warps take the k-tiles alternately (group = parity of the tile number).
-        // A thread owns one row of the A tile (= its TMEM lane): it reads the 32 k of that row from the raw
-        // tile and stores them (`hi`: the raw words, scaled for dX) and their lo terms into the 64 TMEM columns
-        // of the slot.  A transposed A (dW) is read column-wise from the MN-major boxes, which is the transpose
-        // the tensor core would otherwise have to make.  The B lo tile of dW stays in shared memory.
-        const int grp = (warp - kConvWarp0) >> 2;
-        const int tg = (int)threadIdx.x - kConvWarp0 * 32 - grp * 128;       // 0..127 inside the group
+        // All eight warps work on every k-tile: a thread owns HALF a row of the A tile (its TMEM lane = the row, so
+        // the two warps of a lane quarter share each row): it reads 16 k (32 k of one fp32 box for the bf16 kinds) of
+        // that row from the raw tile and stores them (`hi`: the raw words, scaled for dX) and their lo terms into its
+        // 16 + 16 of the slot's 64 TMEM columns.  A transposed A (dW) is read column-wise from the MN-major boxes, which
+        // is the transpose the tensor core would otherwise have to make.  The B lo tile of dW stays in shared memory.
+        const int half = (warp - kConvWarp0) >> 2;                           // which half of the row's k
+        const int tg = (int)threadIdx.x - kConvWarp0 * 32;                   // 0..255 among the converters
         const int q = warp & 3, row = q * 32 + lane;
         uint32_t it = 0, rs = 0, rph = 0;
         int pi = 0;
@@ -674,49 +674,47 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                 const int s = (int)rs;
                 const uint32_t ph = rph;
                 if (++rs == (uint32_t)n_raw) { rs = 0; rph ^= 1u; }
-                if ((int)(it & 1u) != grp) continue;
                 const int sl = (int)(it % kLoSlots);
-                const uint32_t a_taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a_col(sl);
-                // the slot first: once its last reader (tile it - 2) is done, every earlier tile is, so the raw
-                // barrier cannot still show the phase of this group's previous visit
+                const uint32_t a_taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a_col(sl) + 16u * (uint32_t)half;
+                // the slot first: once its last reader (tile it - 3) is done, every earlier tile is
                 ok = mbar_wait_warp(lo_empty(sl), ((it / kLoSlots) & 1u) ^ 1u, &abort_flag) &&
                      mbar_wait_warp(raw_full(s), ph, &abort_flag);
                 if (!ok) break;
                 tc_fence_after();          // the MMAs that read this TMEM slot have completed
                 const int k0 = (I.kt0 + j) * 32;
                 const uint32_t st = raw0 + (uint32_t)s * raw_slot, sto = lo0 + (uint32_t)sl * lo_slot;
-                uint32_t hi[32], lo[32];
+                uint32_t hi[16], lo[16];
                 if (is_bf16_mode(P.mode)) {
-                    // 64 k of the row from two boxes; two bf16 terms, two k per TMEM column (even k in the low half)
-                    const int kb = (I.kt0 + j) * 64;
-#pragma unroll
-                    for (int b = 0; b < 2; ++b) {
-                        const uint32_t ra = st + (uint32_t)b * (uint32_t)kABytes + (uint32_t)row * 128u;
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            float4 v = lds128(ra + ((uint32_t)(c ^ (row & 7)) << 4));
-                            if (ksc != nullptr) {
-                                const int k = kb + 32 * b + 4 * c;
-                                if (k < K) {
-                                    const float4 sc = __ldg(reinterpret_cast<const float4*>(ksc + k));
-                                    v.x = __fmul_rn(v.x, sc.x); v.y = __fmul_rn(v.y, sc.y);
-                                    v.z = __fmul_rn(v.z, sc.z); v.w = __fmul_rn(v.w, sc.w);
-                                }
-                            }
-                            const __nv_bfloat162 h0 = __floats2bfloat162_rn(v.x, v.y), h1 = __floats2bfloat162_rn(v.z, v.w);
-                            const __nv_bfloat162 l0 = __floats2bfloat162_rn(v.x - __low2float(h0), v.y - __high2float(h0));
-                            const __nv_bfloat162 l1 = __floats2bfloat162_rn(v.z - __low2float(h1), v.w - __high2float(h1));
-                            hi[16 * b + 2 * c] = *reinterpret_cast<const uint32_t*>(&h0);
-                            hi[16 * b + 2 * c + 1] = *reinterpret_cast<const uint32_t*>(&h1);
-                            lo[16 * b + 2 * c] = *reinterpret_cast<const uint32_t*>(&l0);
-                            lo[16 * b + 2 * c + 1] = *reinterpret_cast<const uint32_t*>(&l1);
-                        }
-                    }
-                } else if (!a_mn) {
-                    // K-major: row `row` is 128 bytes, its 16-byte chunks XOR-swizzled by the row number
-                    const uint32_t ra = st + (uint32_t)row * 128u;
+                    // 64 k of the row lie in two boxes; this thread takes box `half`: 32 k -> two bf16 terms, two k per
+                    // TMEM column (even k in the low half)
+                    const int kb = (I.kt0 + j) * 64 + 32 * half;
+                    const uint32_t ra = st + (uint32_t)half * (uint32_t)kABytes + (uint32_t)row * 128u;
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
+                        float4 v = lds128(ra + ((uint32_t)(c ^ (row & 7)) << 4));
+                        if (ksc != nullptr) {
+                            const int k = kb + 4 * c;
+                            if (k < K) {
+                                const float4 sc = __ldg(reinterpret_cast<const float4*>(ksc + k));
+                                v.x = __fmul_rn(v.x, sc.x); v.y = __fmul_rn(v.y, sc.y);
+                                v.z = __fmul_rn(v.z, sc.z); v.w = __fmul_rn(v.w, sc.w);
+                            }
+                        }
+                        const __nv_bfloat162 h0 = __floats2bfloat162_rn(v.x, v.y), h1 = __floats2bfloat162_rn(v.z, v.w);
+                        const __nv_bfloat162 l0 = __floats2bfloat162_rn(v.x - __low2float(h0), v.y - __high2float(h0));
+                        const __nv_bfloat162 l1 = __floats2bfloat162_rn(v.z - __low2float(h1), v.w - __high2float(h1));
+                        hi[2 * c] = *reinterpret_cast<const uint32_t*>(&h0);
+                        hi[2 * c + 1] = *reinterpret_cast<const uint32_t*>(&h1);
+                        lo[2 * c] = *reinterpret_cast<const uint32_t*>(&l0);
+                        lo[2 * c + 1] = *reinterpret_cast<const uint32_t*>(&l1);
+                    }
+                } else if (!a_mn) {
+                    // K-major: row `row` is 128 bytes, its 16-byte chunks XOR-swizzled by the row number; this thread
+                    // takes chunks 4 half .. 4 half + 3 (16 k)
+                    const uint32_t ra = st + (uint32_t)row * 128u;
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        const int c = 4 * half + cc;
                         float4 v = lds128(ra + ((uint32_t)(c ^ (row & 7)) << 4));
                         if (ksc != nullptr) {
                             const int k = k0 + 4 * c;
@@ -727,25 +725,27 @@ __global__ void __launch_bounds__(kFThreads, 1) tc_fused_kernel(const __grid_con
                             }
                         }
                         const float4 l = lo_term4(v);
-                        hi[4 * c] = __float_as_uint(v.x); hi[4 * c + 1] = __float_as_uint(v.y);
-                        hi[4 * c + 2] = __float_as_uint(v.z); hi[4 * c + 3] = __float_as_uint(v.w);
-                        lo[4 * c] = __float_as_uint(l.x); lo[4 * c + 1] = __float_as_uint(l.y);
-                        lo[4 * c + 2] = __float_as_uint(l.z); lo[4 * c + 3] = __float_as_uint(l.w);
+                        hi[4 * cc] = __float_as_uint(v.x); hi[4 * cc + 1] = __float_as_uint(v.y);
+                        hi[4 * cc + 2] = __float_as_uint(v.z); hi[4 * cc + 3] = __float_as_uint(v.w);
+                        lo[4 * cc] = __float_as_uint(l.x); lo[4 * cc + 1] = __float_as_uint(l.y);
+                        lo[4 * cc + 2] = __float_as_uint(l.z); lo[4 * cc + 3] = __float_as_uint(l.w);
                     }
                 } else {
-                    // MN-major: box q holds this warp's 32 rows; k-row kk is 128 bytes whose 32-byte atoms are
-                    // XOR-swizzled by kk & 3.  The 32 lanes of a warp read one whole k-row per instruction.
+                    // MN-major: box q holds this lane quarter's 32 rows; k-row kk is 128 bytes whose 32-byte atoms are
+                    // XOR-swizzled by kk & 3.  The 32 lanes of a warp read one whole k-row per instruction; this warp
+                    // takes k-rows 16 half .. 16 half + 15.
                     const uint32_t ba = st + (uint32_t)q * (uint32_t)kBox + ((uint32_t)(lane & 7) << 2);
 #pragma unroll
-                    for (int kk = 0; kk < 32; ++kk) {
+                    for (int kc = 0; kc < 16; ++kc) {
+                        const int kk = 16 * half + kc;
                         const uint32_t w = lds32(ba + (uint32_t)kk * 128u + ((uint32_t)((lane >> 3) ^ (kk & 3)) << 5));
-                        hi[kk] = w;
-                        lo[kk] = __float_as_uint(lo_term(__uint_as_float(w)));
+                        hi[kc] = w;
+                        lo[kc] = __float_as_uint(lo_term(__uint_as_float(w)));
                     }
                 }
-                tmem_st32(a_taddr, hi);
-                tmem_st32(a_taddr + 32u, lo);
-                for (int c = tg; c < nb_lo; c += kConvThreads / 2) {
+                tmem_st16(a_taddr, hi);
+                tmem_st16(a_taddr + 32u, lo);
+                for (int c = tg; c < nb_lo; c += kConvThreads) {
                     const uint32_t off = (uint32_t)c * 16u;
                     sts128(sto + off, lo_term4(lds128(st + (uint32_t)kABytes + off)));
                 }

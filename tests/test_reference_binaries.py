@@ -78,8 +78,28 @@ def test_reference_trainer_learns_synthetic_records(tmp_path):
     data = tmp_path / "data"
     msr.write_dataset(str(data), seq=64, train_records=512, val_records=32, seed=7)
     r = _run_env("train_ternary15m", {"DATA_DIR": data, "OUT_DIR": tmp_path / "out", "STEPS": 120, "BATCH": 8, "SEQ": 64,
-                                      "LOG_EVERY": 20, "EVAL_EVERY": 1000, "CKPT_EVERY": 1000, "RESUME": 0})
+                                      "LOG_EVERY": 20, "EVAL_EVERY": 1000, "CKPT_EVERY": 60, "RESUME": 0})
     assert r.returncode == 0, r.stdout + r.stderr
     losses = [float(m.group(1)) for m in re.finditer(r"^step \d+ loss ([0-9.]+)", r.stdout, flags=re.M)]
     assert len(losses) >= 5, r.stdout
     assert losses[-1] < 8.0 and losses[-1] < losses[0] - 1.5, r.stdout
+    # the checkpoint the trainer wrote with MotifCL's own save_tensor pins this package's reader of those files:
+    # every counter linear of every block loads, with the shapes of the ternary15m stack and a valid 6-bit state
+    import numpy as np
+    from motifcl_b200 import checkpoint, codec
+    out = str(tmp_path / "out")
+    dims = {"wq": (288, 288), "wk": (288, 288), "wv": (288, 288), "wo": (288, 288), "wup": (1536, 288), "wdown": (288, 768)}
+    seen = 0
+    for layer in range(6):
+        for name in checkpoint.LINEAR_NAMES:
+            st, sc, v = checkpoint.load_counter_linear(out, checkpoint.block_prefix(layer, name))
+            O, I = dims[name]
+            assert st.shape == (O * I // 4 * 3,) and sc.shape == (O,) and v.shape == (O,), (layer, name, st.shape, sc.shape)
+            codes = codec.unpack_codes(st.reshape(O, -1), I)
+            assert codes.max() < 63 and np.isfinite(sc).all() and (sc > 0).all() and (v >= 0).all()
+            t, c = codec.decode(codes, 11)
+            assert set(np.unique(t)) <= {-1, 0, 1} and np.abs(c).max() <= 10
+            seen += 1
+    assert seen == 36
+    emb = checkpoint.load_tensor(os.path.join(out, "emb.mt"))
+    assert emb.dtype == np.float32 and emb.shape == (32000, 288)

@@ -278,3 +278,38 @@ def test_adam_update(ctx):
     ctx.adam_update(pd, dev(gr), md, vd, n, lr, b1, b2, eps, wd, c1, c2)
     torch.cuda.synchronize()
     assert rel_l2(pd, ref) <= TOL and rel_l2(md, mn) <= TOL and rel_l2(vd, vn) <= TOL
+
+
+def test_reference_known_answer_inputs_for_rmsnorm_swiglu_add(ctx):
+    """The fixed inputs and tolerances MotifCL's own backend test uses for these ops
+    (tests/test_vulkan_backend.cpp:159-220): RMSNorm of two rows of four with eps 1e-6 (1e-5 abs), SwiGLU of two packed
+    rows [gate | up] (1e-5 abs), add (1e-6 abs); expectations are the test's own float formulas."""
+    dev = "cuda:0"
+    t = lambda a: torch.tensor(a, dtype=torch.float32, device=dev)
+    rms_x = [1.0, 2.0, 3.0, 4.0, -2.0, 0.0, 2.0, 4.0]
+    rms_w = [1.0, 0.5, 1.5, 2.0]
+    out = torch.empty(8, dtype=torch.float32, device=dev)
+    ctx.rmsnorm(t(rms_x), t(rms_w), out, 2, 4, 1.0e-6)
+    ctx.finish()
+    got = out.cpu().numpy()
+    for r in range(2):
+        ss = np.float32(0.0)
+        for c in range(4):
+            ss = np.float32(ss + np.float32(rms_x[r * 4 + c]) * np.float32(rms_x[r * 4 + c]))
+        inv = np.float32(1.0) / np.sqrt(np.float32(ss / np.float32(4.0) + np.float32(1.0e-6)))
+        for c in range(4):
+            assert abs(got[r * 4 + c] - np.float32(rms_x[r * 4 + c]) * inv * np.float32(rms_w[c])) <= 1e-5
+    sw = [1.0, -2.0, 0.5, 4.0, -1.5, 3.0, -2.0, 0.25]
+    out = torch.empty(4, dtype=torch.float32, device=dev)
+    ctx.swiglu(t(sw), out, 2, 2)
+    ctx.finish()
+    got = out.cpu().numpy()
+    for r in range(2):
+        for c in range(2):
+            gate, up = np.float32(sw[r * 4 + c]), np.float32(sw[r * 4 + 2 + c])
+            assert abs(got[r * 2 + c] - gate / (np.float32(1.0) + np.exp(-gate)) * up) <= 1e-5
+    a, b = [1.0, -2.0, 3.5, 4.0], [4.0, 5.0, -0.5, -1.0]
+    out = torch.empty(4, dtype=torch.float32, device=dev)
+    ctx.eltwise(0, t(a), t(b), out, 4)
+    ctx.finish()
+    assert np.abs(out.cpu().numpy() - (np.float32(a) + np.float32(b))).max() <= 1e-6

@@ -67,7 +67,7 @@ def algorithmic(wl):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the contraction kernel for one step of a workload, from the ncu
 # capture summarised in profiles/ (captured on a subset of the layers and scaled by layers where noted there)
-MEASURED_TRAFFIC_BYTES = {"cfg2": 3.471e9}     # 466.6 MB on the first 6 layers (both contraction launches) x (2180.0 / 293.1 MB algorithmic)
+MEASURED_TRAFFIC_BYTES = {"cfg2": 3.412e9}     # 458.8 MB on the first 6 layers (both contraction launches) x (2180.0 / 293.1 MB algorithmic)
 
 
 class ClockSampler:

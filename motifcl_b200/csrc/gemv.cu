@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(256) ternary_gemv_kernel(const float* __restri
 // ---- M <= 4: one launch, CUDA cores, HBM-streaming -------------------------------------------------------------
 // For one to four activation rows the tensor-core route (quantize, MMA, finalize: three dependent launches and an
 // MMA whose A operand is fed at 64 B/clk) costs more than the weights take to stream.  Here a CTA owns R output rows
-// at a time and its 256 threads split K: a thread takes one 2-bit word (16 weights) of each of the R rows per step, so
+// at a time and its threads (128 for M = 1) split K: a thread takes one 2-bit word (16 weights) of each of the R rows per step, so
 // the 16 activations it needs are loaded once (L1 / L2 resident: x is at most 57 KB per row) and used for all R rows,
 // and every thread has R (and, one group ahead, 2 R) independent weight loads in flight.
 // A 2-bit field f = t + 1 becomes the float v = 2 + f / 2 by integer arithmetic on the word (mask, shift, OR into the bit
@@ -71,12 +71,13 @@ __global__ void __launch_bounds__(256) ternary_gemv_kernel(const float* __restri
 // table of float4 digits in shared memory, one 128-bit load per byte of fields, was measured 1.7 x slower: the
 // data-dependent 16-byte loads collide in the banks.)
 // Threads are combined in a fixed order (shuffles, then the eight warps in order), so results are deterministic.
-template <int MB, int R, int MINB>
-__global__ void __launch_bounds__(256, MINB) gemv_stream_kernel(const float* __restrict__ x, const uint32_t* __restrict__ packed2,
+template <int MB, int R, int MINB, int NT>
+__global__ void __launch_bounds__(NT, MINB) gemv_stream_kernel(const float* __restrict__ x, const uint32_t* __restrict__ packed2,
                                                                 const float* __restrict__ scale, float* __restrict__ y, int M, int I,
                                                                 int O) {
     constexpr int NV = R * MB + MB;             // values a thread contributes: R x MB dot products and MB sums of x
-    __shared__ float red[8][NV];
+    constexpr int NW = NT / 32;
+    __shared__ float red[NW][NV];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int wpr = I >> 4;
     const int groups = (O + R - 1) / R;
@@ -97,7 +98,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_stream_kernel(const float* __r
 #pragma unroll
             for (int r = 0; r < R; ++r) acc[r][m] = 0.0f;
         }
-        for (int w = threadIdx.x; w < wpr; w += 256) {
+        for (int w = threadIdx.x; w < wpr; w += NT) {
             uint32_t word[R];
             if (w == (int)threadIdx.x) {
                 const int on = (grp + (int)gridDim.x) * R;
@@ -156,7 +157,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_stream_kernel(const float* __r
             const int r = threadIdx.x / MB, m = threadIdx.x - r * MB, o = o0 + r;
             float a = 0.0f, sx = 0.0f;
 #pragma unroll
-            for (int w = 0; w < 8; ++w) { a += red[w][threadIdx.x]; sx += red[w][R * MB + m]; }
+            for (int w = 0; w < NW; ++w) { a += red[w][threadIdx.x]; sx += red[w][R * MB + m]; }
             if (m < M && o < O) y[(size_t)m * O + o] = __ldg(scale + o) * (2.0f * a - 5.0f * sx);
         }
         __syncthreads();
@@ -167,15 +168,15 @@ __global__ void __launch_bounds__(256, MINB) gemv_stream_kernel(const float* __r
 
 cudaError_t launch_ternary_gemv_stream(const float* x, const uint32_t* packed2, const float* scale, float* y, int M,
                                        int in_features, int out_features, int sm_count, cudaStream_t stream) {
-    const int cap = sm_count * 8;
+    const int cap = sm_count * 16;
     auto grid_for = [&](int rows_per_cta) {
         const int g = (out_features + rows_per_cta - 1) / rows_per_cta;
         return g < cap ? g : cap;
     };
-    if (M <= 1)
-        gemv_stream_kernel<1, 8, 3><<<grid_for(8), 256, 0, stream>>>(x, packed2, scale, y, M, in_features, out_features);
+    if (M <= 1)     // 128 threads per CTA measured best (1.84 ms per sweep; 256: 2.00, 64: 2.26)
+        gemv_stream_kernel<1, 8, 6, 128><<<grid_for(8), 128, 0, stream>>>(x, packed2, scale, y, M, in_features, out_features);
     else
-        gemv_stream_kernel<2, 4, 4><<<grid_for(4), 256, 0, stream>>>(x, packed2, scale, y, M, in_features, out_features);
+        gemv_stream_kernel<2, 4, 4, 256><<<grid_for(4), 256, 0, stream>>>(x, packed2, scale, y, M, in_features, out_features);
     return cudaGetLastError();
 }
 

@@ -64,7 +64,15 @@ uint64_t mcl_cuda_launch_count(mcl_cuda_ctx* ctx);
  * recorded instead of run (CUDA stream capture); batch_end returns a replayable batch that
  * mcl_cuda_batch_launch enqueues as ONE graph launch.  The recorded calls must already have run
  * once unrecorded with the same shapes, so that the context's workspace has its final size;
- * finish, download, upload, alloc and free are refused while recording. ---- */
+ * finish, download, upload, alloc and free are refused while recording.
+ * A batch holds addresses inside the context's workspace: while any batch of a context is alive,
+ * a call that would make the workspace grow is refused (MCL_CUDA_ERR_ARG, "workspace would grow")
+ * instead of freeing memory the batch still points into; destroy the batches first, or run the
+ * larger call once before recording.
+ * Recording captures the calling thread's work on the context's stream only.  Do not enqueue
+ * work of other libraries that hands off to streams of their own (an NCCL collective through a
+ * framework's process group, for one) between begin and end: such work is not part of the batch
+ * and its hand-off events are illegal inside a capture.  Put it between two batches instead. ---- */
 typedef struct mcl_cuda_batch mcl_cuda_batch;
 /* Optional device word whose value is added to the seed of every counter update enqueued
  * afterwards (NULL = none).  A recorded batch bakes its scalar arguments in; bumping this word

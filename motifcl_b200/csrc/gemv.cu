@@ -59,25 +59,6 @@ __global__ void __launch_bounds__(256) ternary_gemv_kernel(const float* __restri
 }
 
 
-#ifndef MCL_GEMV_PDL
-#define MCL_GEMV_PDL 1
-#endif
-#ifndef MCL_GEMV_F2
-#define MCL_GEMV_F2 1
-#endif
-
-// Two fp32 FMAs in one instruction (sm_100: fma.rn.f32x2 on register pairs); each half rounds like fmaf.
-__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
-    unsigned long long ra, rb, rc, rd;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
-    float2 d;
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
-    return d;
-}
-
 // ---- M <= 4: one launch, CUDA cores, HBM-streaming -------------------------------------------------------------
 // For one to four activation rows the tensor-core route (quantize, MMA, finalize: three dependent launches and an
 // MMA whose A operand is fed at 64 B/clk) costs more than the weights take to stream.  Here a CTA owns R output rows
@@ -102,19 +83,6 @@ __global__ void __launch_bounds__(NT, MINB) gemv_stream_kernel(const float* __re
     const int groups = (O + R - 1) / R;
     // words of the first step of a group: loaded one group ahead, so that a thread has two groups' loads in flight
     uint32_t pre[R];
-#if MCL_GEMV_PDL
-    // Programmatic dependent launch: the next kernel of the stream may be scheduled while this one drains, and this
-    // one may have been scheduled while its predecessor drained.  Until the wait below returns, the predecessor may
-    // still be writing x (or the weights), so only L2 prefetches of the first words are issued before it.
-    asm volatile("griddepcontrol.launch_dependents;");
-    if (blockIdx.x < groups && (int)threadIdx.x < wpr) {
-        const int o0 = blockIdx.x * R;
-#pragma unroll
-        for (int r = 0; r < R; ++r)
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(packed2 + (size_t)min(o0 + r, O - 1) * wpr + threadIdx.x));
-    }
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-#endif
     {
         const int o0 = blockIdx.x * R;
 #pragma unroll
@@ -123,23 +91,12 @@ __global__ void __launch_bounds__(NT, MINB) gemv_stream_kernel(const float* __re
     }
     for (int grp = blockIdx.x; grp < groups; grp += gridDim.x) {
         const int o0 = grp * R;
-        float xs[MB];
-#if MCL_GEMV_F2
-        float2 acc[R][MB];      // even and odd weights of a row add up apart (one paired FMA serves both)
-#else
-        float acc[R][MB];
-#endif
+        float acc[R][MB], xs[MB];
 #pragma unroll
         for (int m = 0; m < MB; ++m) {
             xs[m] = 0.0f;
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-#if MCL_GEMV_F2
-                acc[r][m] = make_float2(0.0f, 0.0f);
-#else
-                acc[r][m] = 0.0f;
-#endif
-            }
+            for (int r = 0; r < R; ++r) acc[r][m] = 0.0f;
         }
         for (int w = threadIdx.x; w < wpr; w += NT) {
             uint32_t word[R];
@@ -172,15 +129,10 @@ __global__ void __launch_bounds__(NT, MINB) gemv_stream_kernel(const float* __re
                     const float v3 = __uint_as_float(((b & 0xC0u) << 15) | 0x40000000u);
 #pragma unroll
                     for (int m = 0; m < MB; ++m) {
-#if MCL_GEMV_F2
-                        acc[r][m] = ffma2(make_float2(xv[m].x, xv[m].y), make_float2(v0, v1), acc[r][m]);
-                        acc[r][m] = ffma2(make_float2(xv[m].z, xv[m].w), make_float2(v2, v3), acc[r][m]);
-#else
                         acc[r][m] = fmaf(xv[m].x, v0, acc[r][m]);
                         acc[r][m] = fmaf(xv[m].y, v1, acc[r][m]);
                         acc[r][m] = fmaf(xv[m].z, v2, acc[r][m]);
                         acc[r][m] = fmaf(xv[m].w, v3, acc[r][m]);
-#endif
                     }
                 }
             }
@@ -190,13 +142,7 @@ __global__ void __launch_bounds__(NT, MINB) gemv_stream_kernel(const float* __re
 #pragma unroll
         for (int r = 0; r < R; ++r)
 #pragma unroll
-            for (int m = 0; m < MB; ++m) {
-#if MCL_GEMV_F2
-                vals[r * MB + m] = acc[r][m].x + acc[r][m].y;
-#else
-                vals[r * MB + m] = acc[r][m];
-#endif
-            }
+            for (int m = 0; m < MB; ++m) vals[r * MB + m] = acc[r][m];
 #pragma unroll
         for (int m = 0; m < MB; ++m) vals[R * MB + m] = xs[m];
 #pragma unroll
@@ -227,23 +173,11 @@ cudaError_t launch_ternary_gemv_stream(const float* x, const uint32_t* packed2, 
         const int g = (out_features + rows_per_cta - 1) / rows_per_cta;
         return g < cap ? g : cap;
     };
-    cudaLaunchConfig_t cfg = {};
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-#if MCL_GEMV_PDL
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-#endif
-    if (M <= 1) {   // 128 threads per CTA measured best (1.84 ms per sweep; 256: 2.00, 64: 2.26)
-        cfg.gridDim = dim3(grid_for(8));
-        cfg.blockDim = dim3(128);
-        return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<1, 8, 6, 128>, x, packed2, scale, y, M, in_features, out_features);
-    }
-    cfg.gridDim = dim3(grid_for(4));
-    cfg.blockDim = dim3(256);
-    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<2, 4, 4, 256>, x, packed2, scale, y, M, in_features, out_features);
+    if (M <= 1)     // 128 threads per CTA measured best (1.84 ms per sweep; 256: 2.00, 64: 2.26)
+        gemv_stream_kernel<1, 8, 6, 128><<<grid_for(8), 128, 0, stream>>>(x, packed2, scale, y, M, in_features, out_features);
+    else
+        gemv_stream_kernel<2, 4, 4, 256><<<grid_for(4), 256, 0, stream>>>(x, packed2, scale, y, M, in_features, out_features);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_ternary_gemv(const float* x, const uint32_t* packed2, const float* scale, float* y,

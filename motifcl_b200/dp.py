@@ -49,7 +49,9 @@ def reduce_scatter_rows(grad_w: torch.Tensor, out: torch.Tensor, rank: int, worl
 
 def all_gather_rows(full: torch.Tensor, rank: int, world: int, group=None, scratch=None):
     """Every rank owns rows [off, off+rows) of `full` ([O, ...]); afterwards all ranks hold all
-    rows.  Even blocks gather in place; ragged blocks go through a padded scratch."""
+    rows.  Even blocks are gathered straight into `full` from a copy of the rank's own block (the
+    per-layer helper; the coalesced step gathers in place without that copy); ragged blocks go through
+    a padded scratch."""
     O = full.shape[0]
     off, rows = shard_rows(O, rank, world)
     if O % world == 0:

@@ -38,6 +38,9 @@ struct mcl_cuda_ctx {
     int live_batches = 0;        // recorded batches not yet destroyed: they hold addresses inside the workspace
 };
 
+// ticket words of the sliced table look-up GEMV, one per block of 256 output rows
+constexpr int kGemvTicketWords = 4096;
+
 struct mcl_cuda_batch {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
@@ -168,8 +171,9 @@ int create_impl(int device, cudaStream_t stream, bool own, mcl_cuda_ctx** out_ct
             cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
         cudaGetLastError();
     }
-    e = cudaMalloc(reinterpret_cast<void**>(&ctx->err_word), 16 * sizeof(int));    // [0] error word, [1] work-item counter
-    if (e == cudaSuccess) e = cudaMemset(ctx->err_word, 0, 16 * sizeof(int));
+    // [0] error word, [1] work-item counter, [16 ...) ticket words of the table look-up GEMV (zero between launches)
+    e = cudaMalloc(reinterpret_cast<void**>(&ctx->err_word), (16 + kGemvTicketWords) * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->err_word, 0, (16 + kGemvTicketWords) * sizeof(int));
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_join, cudaEventDisableTiming);
     if (e != cudaSuccess) {
@@ -1449,9 +1453,21 @@ int mcl_cuda_ternary_gemv(mcl_cuda_ctx* ctx, const float* x, const uint32_t* pac
     MCL_TRY(check_ptr(ctx, op, "scale", scale, 4));
     MCL_TRY(check_ptr(ctx, op, "y", y, 4));
     DeviceGuard guard(ctx->device);
+    if (ctx->gemm_mode != MCL_CUDA_GEMM_EXACT && M == 1 &&
+        mcl::gemv_lut_supported((int)M, (int)in_features, (int)out_features, packed2, kGemvTicketWords)) {
+        // one activation row: one launch that looks pairs of weights up in a table of activation sums
+        void* wsp = nullptr;
+        const size_t need = mcl::gemv_lut_workspace_bytes((int)in_features, (int)out_features);
+        if (need) MCL_TRY(ws_reserve(ctx, need, &wsp));
+        MCL_LAUNCH(ctx, op, mcl::launch_ternary_gemv_lut(x, packed2, scale, y, (int)in_features, (int)out_features,
+                                                         static_cast<float*>(wsp),
+                                                         reinterpret_cast<unsigned int*>(ctx->err_word + 16), ctx->sm_count,
+                                                         ctx->max_smem, ctx->stream));
+        return MCL_CUDA_OK;
+    }
     if (ctx->gemm_mode != MCL_CUDA_GEMM_EXACT && M == 1) {
-        // a single activation row: streaming the words through the CUDA cores in one launch beats the three launches
-        // of the tensor-core route (measured: 12 us against 17 us per matrix of the 8B-scale sweep)
+        // a single activation row whose shape the table kernels do not take: streaming the words through the CUDA
+        // cores in one launch still beats the three launches of the tensor-core route
         MCL_LAUNCH(ctx, op, mcl::launch_ternary_gemv_stream(x, packed2, scale, y, (int)M, (int)in_features, (int)out_features,
                                                             ctx->sm_count, ctx->stream));
         return MCL_CUDA_OK;

@@ -135,6 +135,12 @@ cudaError_t launch_splitk_reduce(const float* partial, float* c, const float* co
 // M <= 2: one CUDA-core launch that streams the 2-bit words (in_features % 16 == 0)
 cudaError_t launch_ternary_gemv_stream(const float* x, const uint32_t* packed2, const float* scale, float* y, int M,
                                        int in_features, int out_features, int sm_count, cudaStream_t stream);
+// table look-up kernels for M = 1 (in_features % 256 == 0, 16-byte aligned words); tickets: zeroed words, one per 256 rows
+bool gemv_lut_supported(int M, int in_features, int out_features, const void* packed2, int ticket_words);
+size_t gemv_lut_workspace_bytes(int in_features, int out_features);
+cudaError_t launch_ternary_gemv_lut(const float* x, const uint32_t* packed2, const float* scale, float* y,
+                                    int in_features, int out_features, float* part, unsigned int* tickets, int sm_count,
+                                    size_t max_smem, cudaStream_t stream);
 cudaError_t launch_ternary_gemv(const float* x, const uint32_t* packed2, const float* scale, float* y,
                                 int M, int in_features, int out_features, int sm_count,
                                 cudaStream_t stream);

@@ -218,8 +218,8 @@ def test_pack2_matches_oracle(ctx, orc):
     assert np.array_equal(p2.cpu().numpy().view(np.uint32), orc.pack2(c["state"], c["C"], c["I"], c["O"]))
 
 
-@pytest.mark.parametrize("M", [1, 3, 4, 16])
-@pytest.mark.parametrize("O,I", [(288, 288), (96, 2048), (40, 5632),         # CUDA-core kernel
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 16])
+@pytest.mark.parametrize("O,I", [(288, 288), (96, 2048), (40, 5632),         # CUDA-core kernels
                                  (256, 2048), (300, 4160), (1000, 512), (4096, 1024)])   # tensor-core kernel
 def test_ternary_gemv_vs_oracle(ctx, orc, M, O, I):
     if M == 3 and O == 4096:
@@ -234,6 +234,47 @@ def test_ternary_gemv_vs_oracle(ctx, orc, M, O, I):
     ref64 = orc.ternary_gemv(x, p2, scale, f64=True)
     assert rel_l2(y.cpu().numpy(), ref64) <= 1e-5
     assert rel_l2(y.cpu().numpy(), orc.forward(x, st, scale, 11, O)) <= 1e-5
+
+
+@pytest.mark.parametrize("O,I", [(203, 1024), (33, 4096), (2380, 2048),       # one table for the whole row, ragged row groups
+                                 (5000, 8192), (100, 6144), (257, 14336)])     # sliced tables, ticket reduction
+def test_single_row_gemv_table_kernels_vs_oracle(ctx, orc, O, I):
+    """One activation row on the table look-up kernels: row counts that are no multiple of 16 or 256, every field
+    value (3 included: random words), repeated launches (the ticket words must come back to zero) and a recorded
+    batch replayed several times."""
+    rng = np.random.default_rng(O + I)
+    words = rng.integers(0, 2 ** 32, size=(O, I // 16), dtype=np.uint64).astype(np.uint32)
+    fields = np.zeros((O, I), np.float64)
+    for k in range(16):
+        fields[:, k::16] = ((words >> np.uint32(2 * k)) & np.uint32(3)).astype(np.float64)
+    scale = rng.uniform(0.02, 0.2, O).astype(np.float32)
+    xs = [rng.standard_normal((1, I)).astype(np.float32) for _ in range(3)]
+    wd, sd = _t(words.view(np.int32)), _t(scale)
+    refs = [(x.astype(np.float64) @ (fields - 1.0).T) * scale.astype(np.float64) for x in xs]
+    y = torch.full((1, O), 7.0, dtype=torch.float32, device=DEV)
+    for x, ref in zip(xs, refs):
+        ctx.ternary_gemv(_t(x), wd, sd, y, 1, I, O)
+        assert rel_l2(y.cpu().numpy(), ref) <= 1e-5
+    first = y.clone()
+    ctx.ternary_gemv(_t(xs[2]), wd, sd, y, 1, I, O)
+    assert torch.equal(first, y)                      # deterministic, launch after launch
+    xd = _t(xs[0])
+    ctx.finish()
+    ctx.batch_begin()
+    try:
+        ctx.ternary_gemv(xd, wd, sd, y, 1, I, O)
+    finally:
+        batch = ctx.batch_end()
+    try:
+        for x, ref in zip(xs, refs):
+            xd.copy_(torch.from_numpy(x).to(DEV))
+            y.fill_(3.0)
+            torch.cuda.synchronize()
+            batch.launch()
+            ctx.finish()
+            assert rel_l2(y.cpu().numpy(), ref) <= 1e-5
+    finally:
+        batch.close()
 
 
 def test_ternary_gemv_calls_in_a_row_leave_no_residue(ctx, orc):
@@ -661,7 +702,7 @@ def test_grouped_step_of_all_42_linears_at_8192_tokens(ctx, orc):
     assert max(worst) <= 1e-5, worst
 
 
-@pytest.mark.parametrize("M", [1, 4, 16])
+@pytest.mark.parametrize("M", [1, 2, 4, 16])
 @pytest.mark.parametrize("O,I", [(14336, 4096), (4096, 14336), (4096, 4096)])
 def test_ternary_gemv_on_the_decode_sweep_matrices(ctx, orc, M, O, I):
     """The matrices of the decode-GEMV configuration (w1 / w3, w2, q / o of an 8B-scale block) against float64."""

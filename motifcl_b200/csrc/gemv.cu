@@ -207,11 +207,15 @@ __global__ void __launch_bounds__(256) gemv_lut_kernel(const float* __restrict__
     for (int g = threadIdx.x; g < G; g += 256) {
         const float2 xv = __ldg(reinterpret_cast<const float2*>(x + (size_t)slice * KS) + g);
         const float a[4] = {-xv.x, 0.0f, xv.x, 2.0f * xv.x};         // (f - 1) x: exact
-        const float b[4] = {-xv.y, 0.0f, xv.y, 2.0f * xv.y};
         float4* dst = reinterpret_cast<float4*>(tab + (size_t)g * 16);
+        // the four 16-byte stores go out in an order rotated by lane / 2: consecutive lanes' entry sets are 64 bytes
+        // apart, so lanes 0, 2, 4, 6 would otherwise store into the same banks
 #pragma unroll
-        for (int f1 = 0; f1 < 4; ++f1)
-            dst[f1] = make_float4(__fadd_rn(a[0], b[f1]), __fadd_rn(a[1], b[f1]), __fadd_rn(a[2], b[f1]), __fadd_rn(a[3], b[f1]));
+        for (int t = 0; t < 4; ++t) {
+            const int f1 = (t + ((threadIdx.x & 31) >> 1)) & 3;
+            const float bf = (float)(f1 - 1) * xv.y;                   // exact
+            dst[f1] = make_float4(__fadd_rn(a[0], bf), __fadd_rn(a[1], bf), __fadd_rn(a[2], bf), __fadd_rn(a[3], bf));
+        }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
@@ -289,7 +293,7 @@ constexpr int kLkRing = 2;                 // unit slots per warp
 __global__ void __launch_bounds__(kLkThreads, 1) gemv_lutk_kernel(const float* __restrict__ x,
                                                                   const uint32_t* __restrict__ packed2,
                                                                   const float* __restrict__ scale, float* __restrict__ y,
-                                                                  int I, int O, int groups_q, int groups_r) {
+                                                                  int I, int O, int groups_q, int groups_r, int chunk_inv) {
     extern __shared__ __align__(1024) unsigned char lk_smem[];
     // [0, 32 I): table | ring: warps x slots x 1 KB | chunk sums: (I / 256) x 128 floats
     const int chunks = I >> 8;
@@ -315,8 +319,9 @@ __global__ void __launch_bounds__(kLkThreads, 1) gemv_lutk_kernel(const float* _
     const size_t wpr = (size_t)(I >> 4);
     // a warp's units of a row block are warp, warp + 32, ...; unit u = chunk u % chunks of group u / chunks, kept as a
     // (group, chunk) cursor that steps by 32 units without dividing
-    const int step_g = kLkWarps / chunks, step_c = kLkWarps % chunks;
-    const int first_g = warp / chunks, first_c = warp % chunks;
+    // (chunk_inv = ceil(2^16 / chunks) from the host: n * chunk_inv >> 16 = n / chunks for n <= 32)
+    const int step_g = (kLkWarps * chunk_inv) >> 16, step_c = kLkWarps - step_g * chunks;
+    const int first_g = (warp * chunk_inv) >> 16, first_c = warp - first_g * chunks;
     auto advance = [&](int& g, int& c) {
         g += step_g; c += step_c;
         if (c >= chunks) { c -= chunks; ++g; }
@@ -351,12 +356,15 @@ __global__ void __launch_bounds__(kLkThreads, 1) gemv_lutk_kernel(const float* _
                 const int g = threadIdx.x + j * kLkThreads;
                 if (g < pairs) {
                     const float a[4] = {-xv[j].x, 0.0f, xv[j].x, 2.0f * xv[j].x};         // (f - 1) x: exact
-                    const float b[4] = {-xv[j].y, 0.0f, xv[j].y, 2.0f * xv[j].y};
                     float4* dst = reinterpret_cast<float4*>(lk_smem + (size_t)g * 64);
+                    // a thread's four 16-byte stores go out in an order rotated by lane / 2: consecutive lanes' entry
+                    // sets are 64 bytes apart, so lanes 0, 2, 4, 6 would otherwise store into the same banks
 #pragma unroll
-                    for (int f1 = 0; f1 < 4; ++f1)
-                        dst[f1] = make_float4(__fadd_rn(a[0], b[f1]), __fadd_rn(a[1], b[f1]), __fadd_rn(a[2], b[f1]),
-                                              __fadd_rn(a[3], b[f1]));
+                    for (int t = 0; t < 4; ++t) {
+                        const int f1 = (t + (lane >> 1)) & 3;
+                        const float bf = (float)(f1 - 1) * xv[j].y;                          // exact
+                        dst[f1] = make_float4(__fadd_rn(a[0], bf), __fadd_rn(a[1], bf), __fadd_rn(a[2], bf), __fadd_rn(a[3], bf));
+                    }
                 }
             }
             __syncthreads();
@@ -442,7 +450,9 @@ cudaError_t launch_ternary_gemv_lut(const float* x, const uint32_t* packed2, con
         if (e != cudaSuccess) return e;
         const int groups = (O + 15) / 16;
         const int grid = groups < sm_count ? groups : sm_count;
-        gemv_lutk_kernel<<<grid, kLkThreads, lk_smem, stream>>>(x, packed2, scale, y, I, O, groups / grid, groups % grid);
+        const int chunks = I >> 8;
+        gemv_lutk_kernel<<<grid, kLkThreads, lk_smem, stream>>>(x, packed2, scale, y, I, O, groups / grid, groups % grid,
+                                                                (65536 + chunks - 1) / chunks);
         return cudaGetLastError();
     }
     // the longest slice that still gives every SM two CTAs (measured: fewer, longer slices beat more CTAs)

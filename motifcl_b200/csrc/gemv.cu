@@ -284,6 +284,15 @@ __global__ void __launch_bounds__(256) gemv_lut_kernel(const float* __restrict__
 // it extracts (prmt takes the upper three bytes from a register that holds the 256-byte aligned base), so a look-up
 // stays one prmt, one load and one add.  The 64-weight sums of a unit go to shared memory ([chunk][row]) and one thread
 // per row adds a row's chunks in order: deterministic, no atomics, nothing crosses CTAs.
+// One shared-memory load at [register + constant]: the table look-ups below need the constant IN the instruction (the
+// register already holds base | entry offset), which the compiler does not do for addresses built from 64-bit pointers.
+template <int IMM>
+__device__ __forceinline__ float lds_f32_at(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(IMM));
+    return v;
+}
+
 constexpr int kLkWarps = 32;
 constexpr int kLkThreads = kLkWarps * 32;
 constexpr int kLkRowBlock = 128;           // rows whose chunk sums are held at a time
@@ -295,9 +304,13 @@ __global__ void __launch_bounds__(kLkThreads, 1) gemv_lutk_kernel(const float* _
                                                                   const float* __restrict__ scale, float* __restrict__ y,
                                                                   int I, int O, int groups_q, int groups_r, int chunk_inv) {
     extern __shared__ __align__(1024) unsigned char lk_smem[];
-    // [0, 32 I): table | ring: warps x slots x 1 KB | chunk sums: (I / 256) x 128 floats
+    // table (32 I bytes, at the first 256-byte boundary: a look-up merges an entry's offset into the low byte of the
+    // table's address) | ring: warps x slots x 1 KB | chunk sums: (I / 256) x 128 floats
     const int chunks = I >> 8;
-    unsigned char* ring0 = lk_smem + (size_t)32 * I;
+    const uint32_t smem0 = (uint32_t)__cvta_generic_to_shared(lk_smem);
+    const uint32_t tab32 = (smem0 + 255u) & ~255u;
+    unsigned char* tabp = lk_smem + (tab32 - smem0);
+    unsigned char* ring0 = tabp + (size_t)32 * I;
     float* csum = reinterpret_cast<float*>(ring0 + (size_t)kLkWarps * kLkRing * 1024);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = lane >> 4, r = lane & 15;
@@ -356,7 +369,7 @@ __global__ void __launch_bounds__(kLkThreads, 1) gemv_lutk_kernel(const float* _
                 const int g = threadIdx.x + j * kLkThreads;
                 if (g < pairs) {
                     const float a[4] = {-xv[j].x, 0.0f, xv[j].x, 2.0f * xv[j].x};         // (f - 1) x: exact
-                    float4* dst = reinterpret_cast<float4*>(lk_smem + (size_t)g * 64);
+                    float4* dst = reinterpret_cast<float4*>(tabp + (size_t)g * 64);
                     // a thread's four 16-byte stores go out in an order rotated by lane / 2: consecutive lanes' entry
                     // sets are 64 bytes apart, so lanes 0, 2, 4, 6 would otherwise store into the same banks
 #pragma unroll
@@ -375,23 +388,27 @@ __global__ void __launch_bounds__(kLkThreads, 1) gemv_lutk_kernel(const float* _
             __syncwarp();
             const int slot = k % kLkRing;
             const uint4* rowp = reinterpret_cast<const uint4*>(my_ring + slot * 1024 + r * 64);
-            const uint32_t base = (uint32_t)cc << 13;         // table of this chunk: 128 pairs x 64 B = 8 KB
+            const uint32_t base = tab32 + ((uint32_t)cc << 13);        // table of this chunk: 128 pairs x 64 B = 8 KB
+            const int sw = (r >> 1) & 3;
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint4 wv = rowp[i ^ ((r >> 1) & 3)];
-                const uint32_t w4[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint32_t v = (__funnelshift_l(w4[q], w4[q], rot) & 0x3C3C3C3Cu) | hbit;
-#pragma unroll
-                    for (int b = 0; b < 4; ++b) {
-                        // byte b of v below the upper three bytes of the chunk's base: offset of the entry in the table
-                        const uint32_t o = __byte_perm(v, base, 0x7650u | (uint32_t)b);
-                        acc[b] += *reinterpret_cast<const float*>(lk_smem + (size_t)(((i * 4 + q) * 8 + 2 * b) * 64) + o);
-                    }
-                }
-            }
+            // word WD of the unit's 16: this lane's four nibbles x 4 in the bytes of v; a look-up takes byte b of v below
+            // the upper three bytes of the chunk's table address (prmt) and loads at + (pair of nibble 2 b) x 64
+#define LK_WORD(WD, W)                                                                             \
+    {                                                                                              \
+        const uint32_t v = (__funnelshift_l((W), (W), rot) & 0x3C3C3C3Cu) | hbit;                  \
+        acc[0] += lds_f32_at<((WD) * 8 + 0) * 64>(__byte_perm(v, base, 0x7650u));                  \
+        acc[1] += lds_f32_at<((WD) * 8 + 2) * 64>(__byte_perm(v, base, 0x7651u));                  \
+        acc[2] += lds_f32_at<((WD) * 8 + 4) * 64>(__byte_perm(v, base, 0x7652u));                  \
+        acc[3] += lds_f32_at<((WD) * 8 + 6) * 64>(__byte_perm(v, base, 0x7653u));                  \
+    }
+#define LK_QUAD(Q)                                                                                 \
+    {                                                                                              \
+        const uint4 wv = rowp[(Q) ^ sw];                                                           \
+        LK_WORD((Q) * 4 + 0, wv.x) LK_WORD((Q) * 4 + 1, wv.y) LK_WORD((Q) * 4 + 2, wv.z) LK_WORD((Q) * 4 + 3, wv.w) \
+    }
+            LK_QUAD(0) LK_QUAD(1) LK_QUAD(2) LK_QUAD(3)
+#undef LK_QUAD
+#undef LK_WORD
             float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
             sum += __shfl_xor_sync(0xffffffffu, sum, 16);
             if (h == 0) csum[cc * kLkRowBlock + cg * 16 + r] = sum;
@@ -444,7 +461,7 @@ cudaError_t launch_ternary_gemv_lut(const float* x, const uint32_t* packed2, con
                                     int in_features, int out_features, float* part, unsigned int* tickets, int sm_count,
                                     size_t max_smem, cudaStream_t stream) {
     const int I = in_features, O = out_features;
-    const size_t lk_smem = (size_t)32 * I + (size_t)kLkWarps * kLkRing * 1024 + (size_t)(I >> 8) * kLkRowBlock * sizeof(float);
+    const size_t lk_smem = 256 + (size_t)32 * I + (size_t)kLkWarps * kLkRing * 1024 + (size_t)(I >> 8) * kLkRowBlock * sizeof(float);
     if (I <= kLkMaxIn && lk_smem <= max_smem) {
         cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(gemv_lutk_kernel), 12, max_smem);
         if (e != cudaSuccess) return e;

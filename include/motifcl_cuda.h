@@ -57,6 +57,11 @@ int mcl_cuda_upload(mcl_cuda_ctx* ctx, void* dst, const void* src_host, size_t b
 int mcl_cuda_download(mcl_cuda_ctx* ctx, void* dst_host, const void* src, size_t bytes);
 /* Number of kernels this library has launched on the context so far. */
 uint64_t mcl_cuda_launch_count(mcl_cuda_ctx* ctx);
+/* Bytes of device memory the context's internal workspace holds (grow-only scratch of the entry points: the row tile
+ * of grad_w of the fused update, operand planes, split-K partial sums).  It is how a caller checks the memory-native
+ * property MotifCL gates on (tests/test_memory_truth_gate.cpp:30-126: the fused update may allocate less than a
+ * quarter of a dense fp32 weight). */
+size_t mcl_cuda_workspace_bytes(mcl_cuda_ctx* ctx);
 
 /* ---- batch recording: replaces VulkanRuntime::batch_begin / batch_end, which wrap a training
  * step into one command-buffer submit (include/motifcl/runtime/vulkan_backend.hpp:174-178;

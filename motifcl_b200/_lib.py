@@ -64,6 +64,8 @@ def lib() -> C.CDLL:
         L.mcl_cuda_sm_count.argtypes = [vp]
         L.mcl_cuda_launch_count.argtypes = [vp]
         L.mcl_cuda_launch_count.restype = C.c_uint64
+        L.mcl_cuda_workspace_bytes.argtypes = [vp]
+        L.mcl_cuda_workspace_bytes.restype = C.c_size_t
         L.mcl_cuda_finish.argtypes = [vp]
         L.mcl_cuda_alloc.argtypes = [vp, sz, C.POINTER(vp)]
         L.mcl_cuda_free.argtypes = [vp, vp]

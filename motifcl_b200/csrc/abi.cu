@@ -292,6 +292,7 @@ const char* mcl_cuda_last_error(mcl_cuda_ctx* ctx) { return ctx ? ctx->error.c_s
 const char* mcl_cuda_device_name(mcl_cuda_ctx* ctx) { return ctx ? ctx->name.c_str() : ""; }
 int mcl_cuda_sm_count(mcl_cuda_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
 uint64_t mcl_cuda_launch_count(mcl_cuda_ctx* ctx) { return ctx ? ctx->launches : 0; }
+size_t mcl_cuda_workspace_bytes(mcl_cuda_ctx* ctx) { return ctx ? ctx->ws_bytes : 0; }
 
 int mcl_cuda_batch_begin(mcl_cuda_ctx* ctx) {
     MCL_NEED_CTX(ctx);

@@ -104,6 +104,11 @@ class Context:
     def launch_count(self) -> int:
         return int(self._lib.mcl_cuda_launch_count(self._ctx))
 
+    @property
+    def workspace_bytes(self) -> int:
+        """Device bytes held by the context's internal grow-only workspace."""
+        return int(self._lib.mcl_cuda_workspace_bytes(self._ctx))
+
     def finish(self):
         self._check(self._lib.mcl_cuda_finish(self._ctx))
 

@@ -475,6 +475,39 @@ def test_linear_step_matches_separate_calls_and_oracle(ctx, orc, mode):
         assert np.array_equal(st.cpu().numpy(), e[0])
 
 
+@pytest.mark.parametrize("D,N", [(256, 64), (1024, 32), (2048, 64)])
+def test_memory_native_update_allocates_less_than_a_quarter_of_a_dense_weight(orc, D, N):
+    """MotifCL's memory gate (tests/test_memory_truth_gate.cpp:30-126: D = 256, N = 64) on a context of its own: the
+    fused update may allocate less than a quarter of a dense fp32 [D, D] weight, where the dense path needs at least a
+    half (here: the whole gradient, which the CALLER of mcl_cuda_counter_update_dense allocates).  The result is still
+    the checker's, byte for byte (CUDA-core products: k ascending like the reference's sums)."""
+    from motifcl_b200 import Context
+    rng = np.random.default_rng(D + N)
+    C = 11
+    hy = dict(lr=3e-3, lr_scale=0.0, rms_beta=0.9, rms_eps=1e-3, seed=4242)
+    state = synth.counters(C, 9, D, D).reshape(-1)
+    scale = rng.uniform(0.02, 0.2, D).astype(np.float32)
+    v = rng.uniform(0.0, 1e-3, D).astype(np.float32)
+    x = rng.standard_normal((N, D)).astype(np.float32)
+    dy = (rng.standard_normal((N, D)) * 0.02).astype(np.float32)
+    own = Context.on_torch_stream(0)
+    try:
+        own.set_gemm_mode("exact")
+        assert own.workspace_bytes == 0
+        st, sc, vv = _t(state), _t(scale), _t(v)
+        own.counter_update_fused(st, sc, vv, _t(dy), _t(x), None, C, D, D, N, hy["lr"], hy["lr_scale"], hy["rms_beta"],
+                                 hy["rms_eps"], hy["seed"])
+        own.finish()
+        dense_weight = D * D * 4
+        print(f"D = {D}: workspace {own.workspace_bytes} bytes = {own.workspace_bytes / dense_weight:.3f} of a dense weight")
+        assert 0 < own.workspace_bytes < dense_weight // 4
+        e = orc.update_fused(state, scale, v, dy, x, C, hy["lr"], hy["lr_scale"], hy["rms_beta"], hy["rms_eps"], hy["seed"])
+        assert np.array_equal(st.cpu().numpy(), e[0])
+        assert np.array_equal(_bits(sc.cpu().numpy()), _bits(e[1])) and np.array_equal(_bits(vv.cpu().numpy()), _bits(e[2]))
+    finally:
+        own.close()
+
+
 def test_tensor_core_fused_update_flip_rate(ctx, orc):
     """Memory-native update with grad_w formed on tensor cores: grad_w differs from the fp32
     reference sum in its last bits, so a few stochastic roundings may fall the other way.  The

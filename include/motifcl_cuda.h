@@ -50,6 +50,7 @@ void mcl_cuda_destroy(mcl_cuda_ctx* ctx);
 const char* mcl_cuda_last_error(mcl_cuda_ctx* ctx);   /* ctx may be NULL */
 const char* mcl_cuda_device_name(mcl_cuda_ctx* ctx);
 int mcl_cuda_sm_count(mcl_cuda_ctx* ctx);
+size_t mcl_cuda_device_memory_bytes(mcl_cuda_ctx* ctx);   /* total device memory: what an OpenCL seam reports as CL_DEVICE_GLOBAL_MEM_SIZE */
 int mcl_cuda_finish(mcl_cuda_ctx* ctx);
 int mcl_cuda_alloc(mcl_cuda_ctx* ctx, size_t bytes, void** out_dptr);
 int mcl_cuda_free(mcl_cuda_ctx* ctx, void* dptr);
@@ -272,6 +273,16 @@ int mcl_cuda_rmsnorm_backward_x(mcl_cuda_ctx* ctx, const float* x, const float* 
 int mcl_cuda_rmsnorm_backward_weight(mcl_cuda_ctx* ctx, const float* x, const float* grad_out, float* row_inv_scratch,
                                      float* grad_weight, size_t rows, size_t cols, float eps);
 int mcl_cuda_swiglu(mcl_cuda_ctx* ctx, const float* packed, float* out, size_t rows, size_t hidden);
+/* Mean squared error as MotifCL's OpenCL backend computes it: replaces the kernels mse_loss_partial_f32,
+ * mean_reduce_f32 and mse_backward_f32 (kernels/loss.cl:1-43) behind mse_loss / mse_backward_op
+ * (src/ops/loss.cpp:21-95).  partial holds ceil(n / 256) floats: the sum of squared differences of each chunk of 256
+ * elements, added left to right; mean_reduce adds `count` partial sums (256 strided lanes, then a 128..1 tree) and
+ * divides by `denominator` (0 gives 0); mse_backward writes grad_out[0] * 2 * (pred - target) / n.  The orders of
+ * summation are the reference's, so the loss is the same float. */
+int mcl_cuda_mse_loss_partial(mcl_cuda_ctx* ctx, const float* pred, const float* target, float* partial, size_t n);
+int mcl_cuda_mean_reduce(mcl_cuda_ctx* ctx, const float* partial, float* out, size_t count, size_t denominator);
+int mcl_cuda_mse_backward(mcl_cuda_ctx* ctx, const float* pred, const float* target, const float* grad_out,
+                          float* grad_pred, size_t n);
 int mcl_cuda_swiglu_backward(mcl_cuda_ctx* ctx, const float* packed, const float* grad_out, float* grad_packed,
                              size_t rows, size_t hidden);
 int mcl_cuda_softmax_cross_entropy(mcl_cuda_ctx* ctx, const float* logits, const int32_t* targets, float* partial,

@@ -62,6 +62,8 @@ def lib() -> C.CDLL:
         L.mcl_cuda_device_name.argtypes = [vp]
         L.mcl_cuda_device_name.restype = C.c_char_p
         L.mcl_cuda_sm_count.argtypes = [vp]
+        L.mcl_cuda_device_memory_bytes.argtypes = [vp]
+        L.mcl_cuda_device_memory_bytes.restype = C.c_size_t
         L.mcl_cuda_launch_count.argtypes = [vp]
         L.mcl_cuda_launch_count.restype = C.c_uint64
         L.mcl_cuda_workspace_bytes.argtypes = [vp]
@@ -98,6 +100,9 @@ def lib() -> C.CDLL:
         L.mcl_cuda_rmsnorm_backward_x.argtypes = [vp, vp, vp, vp, vp, sz, sz, f]
         L.mcl_cuda_rmsnorm_backward_weight.argtypes = [vp, vp, vp, vp, vp, sz, sz, f]
         L.mcl_cuda_swiglu.argtypes = [vp, vp, vp, sz, sz]
+        L.mcl_cuda_mse_loss_partial.argtypes = [vp, vp, vp, vp, sz]
+        L.mcl_cuda_mean_reduce.argtypes = [vp, vp, vp, sz, sz]
+        L.mcl_cuda_mse_backward.argtypes = [vp, vp, vp, vp, vp, sz]
         L.mcl_cuda_swiglu_backward.argtypes = [vp, vp, vp, vp, sz, sz]
         L.mcl_cuda_softmax_cross_entropy.argtypes = [vp, vp, vp, vp, vp, sz, sz]
         L.mcl_cuda_softmax_cross_entropy_backward.argtypes = [vp, vp, vp, vp, vp, sz, sz]

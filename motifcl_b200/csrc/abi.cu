@@ -19,6 +19,7 @@ struct mcl_cuda_ctx {
     bool own_stream = false;
     int sm_count = 0;
     size_t max_smem = 0;
+    size_t device_mem = 0;
     std::string name;
     std::string error;
     uint64_t launches = 0;
@@ -155,6 +156,7 @@ int create_impl(int device, cudaStream_t stream, bool own, mcl_cuda_ctx** out_ct
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
     ctx->max_smem = prop.sharedMemPerBlockOptin;
+    ctx->device_mem = prop.totalGlobalMem;
     ctx->name = prop.name;
     DeviceGuard guard(device);
     if (own) {
@@ -291,6 +293,7 @@ void mcl_cuda_destroy(mcl_cuda_ctx* ctx) {
 const char* mcl_cuda_last_error(mcl_cuda_ctx* ctx) { return ctx ? ctx->error.c_str() : g_error.c_str(); }
 const char* mcl_cuda_device_name(mcl_cuda_ctx* ctx) { return ctx ? ctx->name.c_str() : ""; }
 int mcl_cuda_sm_count(mcl_cuda_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
+size_t mcl_cuda_device_memory_bytes(mcl_cuda_ctx* ctx) { return ctx ? ctx->device_mem : 0; }
 uint64_t mcl_cuda_launch_count(mcl_cuda_ctx* ctx) { return ctx ? ctx->launches : 0; }
 size_t mcl_cuda_workspace_bytes(mcl_cuda_ctx* ctx) { return ctx ? ctx->ws_bytes : 0; }
 
@@ -1229,6 +1232,40 @@ int mcl_cuda_rmsnorm_backward_weight(mcl_cuda_ctx* ctx, const float* x, const fl
     DeviceGuard guard(ctx->device);
     MCL_LAUNCH(ctx, op, mcl::launch_rmsnorm_backward_weight(x, grad_out, row_inv_scratch, grad_weight, rows, (int)cols, eps, ctx->sm_count, ctx->stream));
     ctx->launches += 1;     // the row pass and the column pass
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_mse_loss_partial(mcl_cuda_ctx* ctx, const float* pred, const float* target, float* partial, size_t n) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "mse_loss_partial";
+    if (n == 0 || n > 0x7fffffffull) return fail(ctx, MCL_CUDA_EINVAL, "mse_loss_partial needs 0 < n < 2^31");
+    MCL_TRY(check_ptr(ctx, op, "pred", pred, 4));
+    MCL_TRY(check_ptr(ctx, op, "target", target, 4));
+    MCL_TRY(check_ptr(ctx, op, "partial", partial, 4));
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, op, mcl::launch_mse_loss_partial(pred, target, partial, n, ctx->stream));
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_mean_reduce(mcl_cuda_ctx* ctx, const float* partial, float* out, size_t count, size_t denominator) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "mean_reduce";
+    if (count > 0x7fffffffull || denominator > 0x7fffffffull) return fail(ctx, MCL_CUDA_EINVAL, "mean_reduce counts exceed 2^31");
+    MCL_TRY(check_ptr(ctx, op, "partial", partial, 4));
+    MCL_TRY(check_ptr(ctx, op, "out", out, 4));
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, op, mcl::launch_mean_reduce(partial, out, (int)count, (int)denominator, ctx->stream));
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_mse_backward(mcl_cuda_ctx* ctx, const float* pred, const float* target, const float* grad_out,
+                          float* grad_pred, size_t n) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "mse_backward";
+    if (n == 0 || n > 0x7fffffffull) return fail(ctx, MCL_CUDA_EINVAL, "mse_backward needs 0 < n < 2^31");
+    MCL_TRY(check_ptr(ctx, op, "pred", pred, 4));
+    MCL_TRY(check_ptr(ctx, op, "target", target, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_out", grad_out, 4));
+    MCL_TRY(check_ptr(ctx, op, "grad_pred", grad_pred, 4));
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, op, mcl::launch_mse_backward(pred, target, grad_out, grad_pred, n, ctx->stream));
     return MCL_CUDA_OK;
 }
 int mcl_cuda_swiglu(mcl_cuda_ctx* ctx, const float* packed, float* out, size_t rows, size_t hidden) {

@@ -164,6 +164,10 @@ cudaError_t launch_rmsnorm_backward_x(const float* x, const float* w, const floa
                                       float eps, int sm_count, cudaStream_t stream);
 cudaError_t launch_rmsnorm_backward_weight(const float* x, const float* dy, float* row_inv, float* dw, size_t rows,
                                            int cols, float eps, int sm_count, cudaStream_t stream);
+cudaError_t launch_mse_loss_partial(const float* pred, const float* target, float* partial, size_t n, cudaStream_t stream);
+cudaError_t launch_mean_reduce(const float* partial, float* out, int count, int denominator, cudaStream_t stream);
+cudaError_t launch_mse_backward(const float* pred, const float* target, const float* grad_out, float* grad_pred, size_t n,
+                                cudaStream_t stream);
 cudaError_t launch_swiglu(const float* packed, float* out, size_t rows, int hidden, int sm_count, cudaStream_t stream);
 cudaError_t launch_swiglu_backward(const float* packed, const float* dy, float* dpacked, size_t rows, int hidden,
                                    int sm_count, cudaStream_t stream);

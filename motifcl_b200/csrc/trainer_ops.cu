@@ -614,4 +614,60 @@ cudaError_t launch_gqa_backward(const float* q, const float* k, const float* v, 
     return run_bgemm(t, batch, stream);
 }
 
+// ---- mean squared error: the three kernels of MotifCL's OpenCL loss (kernels/loss.cl:1-43, src/ops/loss.cpp:21-95) ----
+// The summation orders are the reference's own, so the loss is the same float: a partial sum per chunk of 256 elements,
+// left to right; then 256 lanes that stride over the partial sums, a 128..1 tree, and one division.
+namespace {
+__global__ void mse_partial_kernel(const float* __restrict__ pred, const float* __restrict__ target,
+                                   float* __restrict__ partial, long long n, long long chunks) {
+    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= chunks) return;
+    const long long start = g * 256;
+    float acc = 0.0f;
+    for (int i = 0; i < 256; ++i) {
+        const long long idx = start + i;
+        if (idx < n) {
+            const float d = __fsub_rn(pred[idx], target[idx]);
+            acc = __fadd_rn(acc, __fmul_rn(d, d));
+        }
+    }
+    partial[g] = acc;
+}
+__global__ void __launch_bounds__(256) mean_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                                          int count, int denominator) {
+    __shared__ float scratch[256];
+    const int lid = threadIdx.x;
+    float acc = 0.0f;
+    for (int i = lid; i < count; i += 256) acc = __fadd_rn(acc, partial[i]);
+    scratch[lid] = acc;
+    __syncthreads();
+    for (int stride = 128; stride > 0; stride >>= 1) {
+        if (lid < stride) scratch[lid] = __fadd_rn(scratch[lid], scratch[lid + stride]);
+        __syncthreads();
+    }
+    if (lid == 0) out[0] = denominator > 0 ? __fdiv_rn(scratch[0], (float)denominator) : 0.0f;
+}
+__global__ void mse_backward_kernel(const float* __restrict__ pred, const float* __restrict__ target,
+                                    const float* __restrict__ grad_out, float* __restrict__ grad_pred, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n)
+        grad_pred[i] = __fdiv_rn(__fmul_rn(__fmul_rn(grad_out[0], 2.0f), __fsub_rn(pred[i], target[i])), (float)n);
+}
+}  // namespace
+
+cudaError_t launch_mse_loss_partial(const float* pred, const float* target, float* partial, size_t n, cudaStream_t stream) {
+    const long long chunks = (long long)((n + 255) / 256);
+    mse_partial_kernel<<<(unsigned)((chunks + 127) / 128), 128, 0, stream>>>(pred, target, partial, (long long)n, chunks);
+    return cudaGetLastError();
+}
+cudaError_t launch_mean_reduce(const float* partial, float* out, int count, int denominator, cudaStream_t stream) {
+    mean_reduce_kernel<<<1, 256, 0, stream>>>(partial, out, count, denominator);
+    return cudaGetLastError();
+}
+cudaError_t launch_mse_backward(const float* pred, const float* target, const float* grad_out, float* grad_pred, size_t n,
+                                cudaStream_t stream) {
+    mse_backward_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(pred, target, grad_out, grad_pred, (long long)n);
+    return cudaGetLastError();
+}
+
 }  // namespace mcl

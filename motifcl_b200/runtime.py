@@ -228,6 +228,14 @@ class Context:
         self._check(self._lib.mcl_cuda_rmsnorm_backward_weight(self._ctx, _ptr(x), _ptr(grad_out), _ptr(row_inv),
                                                                _ptr(grad_weight), rows, cols, eps))
 
+    def mse_loss(self, pred, target, partial, out, n):
+        """mean((pred - target)^2) with MotifCL's OpenCL summation order; partial: ceil(n / 256) floats."""
+        self._check(self._lib.mcl_cuda_mse_loss_partial(self._ctx, _ptr(pred), _ptr(target), _ptr(partial), n))
+        self._check(self._lib.mcl_cuda_mean_reduce(self._ctx, _ptr(partial), _ptr(out), (n + 255) // 256, n))
+
+    def mse_backward(self, pred, target, grad_out, grad_pred, n):
+        self._check(self._lib.mcl_cuda_mse_backward(self._ctx, _ptr(pred), _ptr(target), _ptr(grad_out), _ptr(grad_pred), n))
+
     def swiglu(self, packed, out, rows, hidden):
         self._check(self._lib.mcl_cuda_swiglu(self._ctx, _ptr(packed), _ptr(out), rows, hidden))
 

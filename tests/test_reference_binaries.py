@@ -45,6 +45,32 @@ def test_reference_binary_passes_on_the_cuda_backend(name):
     assert "PASS" in r.stdout and "FAIL" not in r.stdout
 
 
+CL_BINARIES = ["cl/test_counter_state", "cl/test_memory_truth_gate"]
+CL_ENV = {"MOTIFCL_KERNEL_DIR": os.path.join(ROOT, "motifcl_b200", "adapter", "cl_sources")}
+
+
+@pytest.mark.parametrize("name", CL_BINARIES)
+def test_reference_opencl_binary_skips_without_a_device(name):
+    import motifcl_b200 as mb
+    if mb.lib().mcl_cuda_device_count() > 0:
+        pytest.skip("a CUDA device is present")
+    r = _run_env(name, CL_ENV)
+    assert r.returncode == 77 and "no opencl platforms" in (r.stdout + r.stderr).lower()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", CL_BINARIES)
+def test_reference_opencl_binary_passes_through_the_opencl_seam(name):
+    """MotifCL's OpenCL-only counter tests, unmodified, with motifcl_b200/adapter/cuda_opencl_shim.cpp in the place of
+    libOpenCL.  tests/test_counter_state.cpp: 800 steps of forward + mse_loss + backward on a 16 x 16 layer recover a
+    ternary teacher (final mse <= 5e-3, ternary accuracy >= 0.9; the input has no requires_grad).
+    tests/test_memory_truth_gate.cpp: the memory-native update allocates less than a quarter of a dense weight while
+    the dense apply_update_seed path allocates at least half; grad_x from the packed state equals decode + matmul
+    within 1e-4.  Both exit 0 on success and print the reason otherwise."""
+    r = _run_env(name, CL_ENV)
+    assert r.returncode == 0, r.stdout + r.stderr
+
+
 def _run_env(name, env, timeout=600):
     path = os.path.join(BUILD, name)
     if not os.path.isfile(path):

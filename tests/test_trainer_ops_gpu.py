@@ -313,3 +313,45 @@ def test_reference_known_answer_inputs_for_rmsnorm_swiglu_add(ctx):
     ctx.eltwise(0, t(a), t(b), out, 4)
     ctx.finish()
     assert np.abs(out.cpu().numpy() - (np.float32(a) + np.float32(b))).max() <= 1e-6
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [1, 255, 256, 4096, 70001])
+def test_mse_loss_and_backward_follow_the_opencl_kernels_order(ctx, n):
+    """MotifCL kernels/loss.cl:1-43: chunk sums of 256 elements left to right, 256 strided lanes over the chunk sums, a
+    128..1 tree, one division: restated here in float32 with numpy, and the result must be the same float."""
+    rng = np.random.default_rng(n)
+    pred = rng.standard_normal(n).astype(np.float32)
+    target = rng.standard_normal(n).astype(np.float32)
+    chunks = (n + 255) // 256
+    partial = np.zeros(chunks, np.float32)
+    for g in range(chunks):
+        acc = np.float32(0.0)
+        for i in range(g * 256, min(n, g * 256 + 256)):
+            d = np.float32(pred[i] - target[i])
+            acc = np.float32(acc + np.float32(d * d))
+        partial[g] = acc
+    scratch = np.zeros(256, np.float32)
+    for lid in range(256):
+        acc = np.float32(0.0)
+        for i in range(lid, chunks, 256):
+            acc = np.float32(acc + partial[i])
+        scratch[lid] = acc
+    stride = 128
+    while stride > 0:
+        scratch[:stride] = (scratch[:stride] + scratch[stride:2 * stride]).astype(np.float32)
+        stride >>= 1
+    want = np.float32(scratch[0] / np.float32(n))
+    dev = torch.device("cuda:0")
+    p_d, t_d = torch.from_numpy(pred).to(dev), torch.from_numpy(target).to(dev)
+    part_d = torch.zeros(chunks, dtype=torch.float32, device=dev)
+    out_d = torch.zeros(1, dtype=torch.float32, device=dev)
+    ctx.mse_loss(p_d, t_d, part_d, out_d, n)
+    assert np.array_equal(part_d.cpu().numpy().view(np.uint32), partial.view(np.uint32))
+    assert out_d.cpu().numpy().view(np.uint32)[0] == want.view(np.uint32)
+    g_out = torch.tensor([0.75], dtype=torch.float32, device=dev)
+    g_d = torch.empty(n, dtype=torch.float32, device=dev)
+    ctx.mse_backward(p_d, t_d, g_out, g_d, n)
+    want_g = ((np.float32(0.75) * np.float32(2.0)) * (pred - target).astype(np.float32)).astype(np.float32) / np.float32(n)
+    assert np.array_equal(g_d.cpu().numpy().view(np.uint32), want_g.astype(np.float32).view(np.uint32))
+

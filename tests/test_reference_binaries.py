@@ -45,7 +45,8 @@ def test_reference_binary_passes_on_the_cuda_backend(name):
     assert "PASS" in r.stdout and "FAIL" not in r.stdout
 
 
-CL_BINARIES = ["cl/test_counter_state", "cl/test_memory_truth_gate"]
+CL_BINARIES = ["cl/test_counter_state", "cl/test_memory_truth_gate", "cl/test_buffer", "cl/test_tensor",
+               "cl/test_backend_lifetime"]
 CL_ENV = {"MOTIFCL_KERNEL_DIR": os.path.join(ROOT, "motifcl_b200", "adapter", "cl_sources")}
 
 
@@ -66,7 +67,8 @@ def test_reference_opencl_binary_passes_through_the_opencl_seam(name):
     ternary teacher (final mse <= 5e-3, ternary accuracy >= 0.9; the input has no requires_grad).
     tests/test_memory_truth_gate.cpp: the memory-native update allocates less than a quarter of a dense weight while
     the dense apply_update_seed path allocates at least half; grad_x from the packed state equals decode + matmul
-    within 1e-4.  Both exit 0 on success and print the reason otherwise."""
+    within 1e-4.  tests/test_buffer.cpp, test_tensor.cpp, test_backend_lifetime.cpp: upload / download round trip,
+    Tensor::ones (fill_f32), a tensor that outlives its backend.  All exit 0 on success and print the reason otherwise."""
     r = _run_env(name, CL_ENV)
     assert r.returncode == 0, r.stdout + r.stderr
 

@@ -236,7 +236,7 @@ def test_ternary_gemv_vs_oracle(ctx, orc, M, O, I):
     assert rel_l2(y.cpu().numpy(), orc.forward(x, st, scale, 11, O)) <= 1e-5
 
 
-@pytest.mark.parametrize("O,I", [(203, 1024), (33, 4096), (2380, 2048),       # one table for the whole row, ragged row groups
+@pytest.mark.parametrize("O,I", [(203, 1024), (33, 4096), (2380, 2048), (64, 256), (500, 3840), (3000, 1280),   # one table for the whole row
                                  (5000, 8192), (100, 6144), (257, 14336)])     # sliced tables, ticket reduction
 def test_single_row_gemv_table_kernels_vs_oracle(ctx, orc, O, I):
     """One activation row on the table look-up kernels: row counts that are no multiple of 16 or 256, every field

@@ -270,6 +270,18 @@ cl_int release(T* obj) {
     if (--obj->refs == 0) delete obj;
     return CL_SUCCESS;
 }
+// queues, buffers, programs and kernels keep their context alive (OpenCL's own rule), so the order in which a caller
+// lets go of them does not matter
+template <class T>
+cl_int release_child(T* obj) {
+    if (!obj) return CL_INVALID_VALUE;
+    if (--obj->refs == 0) {
+        _cl_context* c = obj->context;
+        delete obj;
+        release(c);
+    }
+    return CL_SUCCESS;
+}
 
 }  // namespace
 
@@ -347,10 +359,11 @@ cl_command_queue clCreateCommandQueue(cl_context c, cl_device_id, cl_command_que
     if (!c) { if (err) *err = CL_INVALID_CONTEXT; return nullptr; }
     auto* q = new _cl_command_queue;
     q->context = c;
+    ++c->refs;
     if (err) *err = CL_SUCCESS;
     return q;
 }
-cl_int clReleaseCommandQueue(cl_command_queue q) { return release(q); }
+cl_int clReleaseCommandQueue(cl_command_queue q) { return release_child(q); }
 
 cl_mem clCreateBuffer(cl_context c, cl_mem_flags flags, size_t size, void* host_ptr, cl_int* err) {
     if (!c || size == 0) { if (err) *err = c ? CL_INVALID_VALUE : CL_INVALID_CONTEXT; return nullptr; }
@@ -365,6 +378,7 @@ cl_mem clCreateBuffer(cl_context c, cl_mem_flags flags, size_t size, void* host_
     }
     auto* m = new _cl_mem;
     m->context = c; m->dptr = static_cast<char*>(d); m->size = size;
+    ++c->refs;
     if (err) *err = CL_SUCCESS;
     return m;
 }
@@ -378,6 +392,7 @@ cl_mem clCreateSubBuffer(cl_mem parent, cl_mem_flags, cl_buffer_create_type type
     auto* m = new _cl_mem;
     m->context = parent->context; m->dptr = parent->dptr + region->origin; m->size = region->size; m->parent = parent;
     ++parent->refs;
+    ++m->context->refs;
     if (err) *err = CL_SUCCESS;
     return m;
 }
@@ -385,9 +400,11 @@ cl_int clRetainMemObject(cl_mem m) { if (!m) return CL_INVALID_MEM_OBJECT; ++m->
 cl_int clReleaseMemObject(cl_mem m) {
     if (!m) return CL_INVALID_MEM_OBJECT;
     if (--m->refs == 0) {
+        _cl_context* c = m->context;
         if (m->parent) clReleaseMemObject(m->parent);
-        else mcl_cuda_free(m->context->ctx, m->dptr);      // ordered after the work already enqueued
+        else mcl_cuda_free(c->ctx, m->dptr);      // ordered after the work already enqueued
         delete m;
+        release(c);
     }
     return CL_SUCCESS;
 }
@@ -411,6 +428,7 @@ cl_program clCreateProgramWithSource(cl_context c, cl_uint, const char**, const 
     if (!c) { if (err) *err = CL_INVALID_CONTEXT; return nullptr; }
     auto* p = new _cl_program;      // the text is not compiled: kernels are looked up by name in kKernels
     p->context = c;
+    ++c->refs;
     if (err) *err = CL_SUCCESS;
     return p;
 }
@@ -421,7 +439,7 @@ cl_int clGetProgramBuildInfo(cl_program, cl_device_id, cl_program_build_info nam
     if (name == CL_PROGRAM_BUILD_LOG || name == CL_PROGRAM_BUILD_OPTIONS) return put_string("", size, value, size_ret);
     return CL_INVALID_VALUE;
 }
-cl_int clReleaseProgram(cl_program p) { return release(p); }
+cl_int clReleaseProgram(cl_program p) { return release_child(p); }
 
 cl_kernel clCreateKernel(cl_program p, const char* name, cl_int* err) {
     if (!p || !name) { if (err) *err = CL_INVALID_PROGRAM; return nullptr; }
@@ -429,6 +447,7 @@ cl_kernel clCreateKernel(cl_program p, const char* name, cl_int* err) {
         if (std::strcmp(e.name, name) == 0) {
             auto* k = new _cl_kernel;
             k->context = p->context; k->id = e.id; k->name = name; k->args.resize(e.nargs);
+            ++k->context->refs;
             if (err) *err = CL_SUCCESS;
             return k;
         }
@@ -437,7 +456,7 @@ cl_kernel clCreateKernel(cl_program p, const char* name, cl_int* err) {
     return nullptr;
 }
 cl_int clRetainKernel(cl_kernel k) { if (!k) return CL_INVALID_KERNEL; ++k->refs; return CL_SUCCESS; }
-cl_int clReleaseKernel(cl_kernel k) { return release(k); }
+cl_int clReleaseKernel(cl_kernel k) { return release_child(k); }
 
 cl_int clSetKernelArg(cl_kernel k, cl_uint index, size_t size, const void* value) {
     if (!k) return CL_INVALID_KERNEL;

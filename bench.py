@@ -471,9 +471,11 @@ def run_trainer15m(args):
 
 
 def run_gemv_tp(args):
-    """--micro gemvtp:M[:LAYERS]  the decode-GEMV sweep with the weights sharded over the ranks of the job
-    (q, w1, w3 split by output features; o, w2 split by input features + one all-reduce each): what a
-    tensor-parallel decoder does per token.  Run under torchrun; with one rank it is the plain sweep."""
+    """--micro gemvtp:M[:LAYERS[:nccl]]  the decode-GEMV sweep with the weights sharded over the ranks of the job
+    (q, w1, w3 split by output features; o, w2 split by input features + one sum over the ranks each): what a
+    tensor-parallel decoder does per token.  The sums run as the library's one-shot peer kernel (motifcl_b200.peer;
+    the sweep is then one recorded batch per rank); `:nccl` uses NCCL all-reduces instead, launched eagerly.  Run
+    under torchrun; with one rank it is the plain sweep."""
     import torch
     import torch.distributed as dist
     from motifcl_b200 import Context, gemv_tp
@@ -489,7 +491,10 @@ def run_gemv_tp(args):
     _, shape, *rest = args.micro.split(":")
     M = int(shape)
     layers = int(rest[0]) if rest else 32
+    use_nccl = len(rest) > 1 and rest[1] == "nccl"
     dim, ffn = 4096, 14336
+    from motifcl_b200.peer import PeerReducer
+    red = None if (use_nccl or world == 1) else PeerReducer(ctx, M * dim)
     g = torch.Generator(device=dev).manual_seed(1234)          # every rank draws the same full matrices
     rnd = lambda O, I: torch.randint(-2 ** 31, 2 ** 31 - 1, (O, I // 16), dtype=torch.int32, device=dev, generator=g)
     sc = lambda O: torch.full((O,), 0.05, device=dev)
@@ -511,8 +516,23 @@ def run_gemv_tp(args):
     def sweep():
         for q, o, mlp in blocks:
             q(fn, x, yq)
-            o(fn, xo, yo)
-            mlp(fn, x, h1, h3, ym)
+            o(fn, xo, yo, reducer=red)
+            mlp(fn, x, h1, h3, ym, reducer=red, gate=False)
+
+    parity = None
+    if red is not None:
+        # the peer sum against NCCL's, on the first o layer and the first FFN
+        q0, o0, mlp0 = blocks[0]
+        o0(fn, xo, yo, reducer=red)
+        mlp0(fn, x, h1, h3, ym, reducer=red, gate=False)
+        ctx.finish()
+        a_o, a_m = yo.clone(), ym.clone()
+        o0(fn, xo, yo)
+        mlp0(fn, x, h1, h3, ym, gate=False)
+        torch.cuda.synchronize()
+        err = max(float((a_o - yo).abs().max() / yo.abs().max()), float((a_m - ym).abs().max() / ym.abs().max()))
+        parity = {"peer_sum_vs_nccl_max_rel": err, "ok": err <= 1e-6}
+        assert parity["ok"], parity
 
     def timed(steps, warm):
         for _ in range(warm):
@@ -534,27 +554,37 @@ def run_gemv_tp(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         return ms
-    # one recorded batch per sweep on a single rank; with several ranks the sweep is launched eagerly: a batch is a stream
-    # capture of the context's stream, and torch's NCCL collectives run on the process group's own stream behind event
-    # hand-offs, which must not be captured by this library's thread-local capture
+    # One recorded batch per sweep when no collective library call is inside it (one rank, or the peer kernel, whose
+    # call counter lives in device memory: an even number of sums per sweep keeps the two partial areas alternating
+    # across replays).  With NCCL all-reduces the sweep is launched eagerly: a batch is a stream capture of the context's
+    # stream, and torch's NCCL collectives run on the process group's own stream behind event hand-offs, which must not
+    # be captured by this library's thread-local capture.  Every rank takes the same path: the ranks agree on whether
+    # recording worked before any of them replays.
     recorded = False
-    try:
-        if world > 1:
-            raise RuntimeError("several ranks")
-        sweep()
-        ctx.finish()
-        ctx.batch_begin()
+    if not (use_nccl and world > 1):
+        batch = None
         try:
             sweep()
-        finally:
-            batch = ctx.batch_end()
-        eager_sweep, sweep = sweep, batch.launch
-        sweep()
-        ctx.finish()
-        recorded = True
-    except Exception as exc:      # noqa: BLE001
-        if world == 1:
+            ctx.finish()
+            ctx.batch_begin()
+            try:
+                sweep()
+            finally:
+                batch = ctx.batch_end()
+        except Exception as exc:      # noqa: BLE001
             print(f"[rank {rank}] recording refused ({exc}); timing eager launches", file=sys.stderr)
+            batch = None
+        if red is not None:
+            red.seq = 2 * layers        # the sums that really ran so far (the recorded ones did not): same on every rank
+        ok = torch.tensor([1 if batch is not None else 0], device=dev)
+        if world > 1:
+            torch.cuda.synchronize()
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 1:
+            sweep = batch.launch
+            sweep()
+            ctx.finish()
+            recorded = True
     with ClockSampler(local) as clk:
         ms = timed(args.steps, max(args.warmup, 3))
     hbm_peak, _, peak_kind = measured_peaks()
@@ -565,7 +595,10 @@ def run_gemv_tp(args):
                           "weight_bytes": nbytes, "achieved": nbytes / ms / 1e6, "unit": "GB/s (all ranks)",
                           "peak": hbm_peak * world, "frac": nbytes / ms / 1e6 / (hbm_peak * world),
                           "peak_kind": peak_kind, "all_reduces_per_sweep": 2 * layers if world > 1 else 0,
-                          "recorded_batch": recorded, "clocks": clk.summary(), "gpu_launches": ctx.launch_count}))
+                          "recorded_batch": recorded, "sum": "nccl" if (use_nccl and world > 1) else ("peer kernel" if world > 1 else None),
+                          "parity": parity, "clocks": clk.summary(), "gpu_launches": ctx.launch_count}))
+    if red is not None:
+        red.close()
     if world > 1:
         dist.destroy_process_group()
 

@@ -98,6 +98,28 @@ int mcl_cuda_lane_fork(mcl_cuda_ctx* ctx, mcl_cuda_ctx* lane);
 int mcl_cuda_lane_join(mcl_cuda_ctx* ctx, mcl_cuda_ctx* lane);
 void mcl_cuda_batch_destroy(mcl_cuda_batch* batch);
 
+/* ---- one-shot sum over the GPUs of a node (no reference counterpart: the reference has no multi-device code).
+ * For the [M, out] partial results of a row-sharded decode GEMV.  Every rank holds, in memory that all ranks have
+ * mapped, a flag area of 64 uint32 words (zero before the first call; words 0..world-1 are written by the peers, word
+ * 32 counts this rank's calls) and two partial buffers `parity_stride` floats apart; peer_data[r] / peer_flags[r]
+ * are THIS process's addresses of rank r's buffers and flags.  A call sums the n floats that every rank has written
+ * into its buffer `parity` (0 or 1; alternate it from call to call) by earlier work of its stream, in rank order
+ * (every rank gets the same bits), into `out`.  All ranks make the same sequence of calls; the call number lives in
+ * device memory, so a recorded batch that contains such calls can be replayed.  Ranks meet through the flag words:
+ * plain peer stores and loads, a wait of at most 2 s, after which the call's results are invalid and the next
+ * mcl_cuda_finish reports it. ---- */
+int mcl_cuda_peer_allreduce_f32(mcl_cuda_ctx* ctx, const void* const* peer_data, void* const* peer_flags, int rank,
+                                int world, size_t n, size_t parity_stride, int parity, float* out);
+/* Memory that the other ranks of the node can map (CUDA IPC; one process per GPU): create makes a zero-filled buffer
+ * and the 64-byte handle to send to the peers (by any host channel), open maps a peer's buffer into this process (peer
+ * access is enabled on first use), close unmaps it, destroy frees the own buffer.  The owner must outlive the mappings:
+ * peers close before the owner destroys (a barrier between the two on the host). */
+#define MCL_CUDA_IPC_HANDLE_BYTES 64
+int mcl_cuda_peer_buffer_create(mcl_cuda_ctx* ctx, size_t bytes, void** out_dptr, unsigned char* handle64);
+int mcl_cuda_peer_buffer_open(mcl_cuda_ctx* ctx, const unsigned char* handle64, void** out_dptr);
+int mcl_cuda_peer_buffer_close(mcl_cuda_ctx* ctx, void* dptr);
+int mcl_cuda_peer_buffer_destroy(mcl_cuda_ctx* ctx, void* dptr);
+
 /* ---- decode: replaces run_vulkan_compact_counter_decode_weight
  * (include/motifcl/runtime/vulkan_backend.hpp:713-719; kernels/compact_counter.cl:39-55).
  * weight[out,in] = scale[row] * t. ---- */

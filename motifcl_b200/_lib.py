@@ -101,6 +101,11 @@ def lib() -> C.CDLL:
         L.mcl_cuda_rmsnorm_backward_weight.argtypes = [vp, vp, vp, vp, vp, sz, sz, f]
         L.mcl_cuda_swiglu.argtypes = [vp, vp, vp, sz, sz]
         L.mcl_cuda_mse_loss_partial.argtypes = [vp, vp, vp, vp, sz]
+        L.mcl_cuda_peer_allreduce_f32.argtypes = [vp, C.POINTER(vp), C.POINTER(vp), C.c_int, C.c_int, sz, sz, C.c_int, vp]
+        L.mcl_cuda_peer_buffer_create.argtypes = [vp, sz, C.POINTER(vp), C.c_char_p]
+        L.mcl_cuda_peer_buffer_open.argtypes = [vp, C.c_char_p, C.POINTER(vp)]
+        L.mcl_cuda_peer_buffer_close.argtypes = [vp, vp]
+        L.mcl_cuda_peer_buffer_destroy.argtypes = [vp, vp]
         L.mcl_cuda_mean_reduce.argtypes = [vp, vp, vp, sz, sz]
         L.mcl_cuda_mse_backward.argtypes = [vp, vp, vp, vp, vp, sz]
         L.mcl_cuda_swiglu_backward.argtypes = [vp, vp, vp, vp, sz, sz]

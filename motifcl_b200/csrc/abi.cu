@@ -206,6 +206,7 @@ int check_device_error(mcl_cuda_ctx* ctx) {
             case 14: who = "MMA lane (accumulator never drained)"; break;
             case 16: case 17: who = "work-item queue (scheduler lane and its readers lost step)"; break;
             case 21: who = "wide-row counter update (a row slot was never marked ready or released)"; break;
+            case 31: who = "peer all-reduce (a rank never announced its partial result)"; break;
             default: who = "epilogue (accumulator never completed)"; break;
         }
         return fail(ctx, MCL_CUDA_ECUDA, std::string("a kernel gave up a bounded wait: ") + who + " [code " +
@@ -1474,6 +1475,81 @@ int mcl_cuda_adam_update(mcl_cuda_ctx* ctx, float* param, const float* grad, flo
     DeviceGuard guard(ctx->device);
     MCL_LAUNCH(ctx, op, mcl::launch_adam(param, grad, m, v, elements, lr, beta1, beta2, eps, weight_decay, c1, c2, ctx->sm_count,
                                          ctx->stream));
+    return MCL_CUDA_OK;
+}
+
+int mcl_cuda_peer_buffer_create(mcl_cuda_ctx* ctx, size_t bytes, void** out_dptr, unsigned char* handle64) {
+    MCL_NEED_CTX(ctx);
+    MCL_NOT_RECORDING(ctx, "peer_buffer_create");
+    if (!out_dptr || !handle64 || bytes == 0) return fail(ctx, MCL_CUDA_EINVAL, "peer_buffer_create: null argument or zero size");
+    static_assert(sizeof(cudaIpcMemHandle_t) == MCL_CUDA_IPC_HANDLE_BYTES, "IPC handle size");
+    DeviceGuard guard(ctx->device);
+    void* d = nullptr;
+    // plain cudaMalloc: memory of the stream-ordered pool cannot be exported to other processes
+    cudaError_t e = cudaMalloc(&d, bytes);
+    if (e != cudaSuccess) return fail_cuda(ctx, "peer_buffer_create (cudaMalloc)", e);
+    e = cudaMemset(d, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, d);
+    if (e != cudaSuccess) { cudaFree(d); return fail_cuda(ctx, "peer_buffer_create (export)", e); }
+    std::memcpy(handle64, &h, sizeof(h));
+    *out_dptr = d;
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_peer_buffer_open(mcl_cuda_ctx* ctx, const unsigned char* handle64, void** out_dptr) {
+    MCL_NEED_CTX(ctx);
+    MCL_NOT_RECORDING(ctx, "peer_buffer_open");
+    if (!out_dptr || !handle64) return fail(ctx, MCL_CUDA_EINVAL, "peer_buffer_open: null argument");
+    DeviceGuard guard(ctx->device);
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle64, sizeof(h));
+    void* d = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&d, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail_cuda(ctx, "peer_buffer_open", e);
+    *out_dptr = d;
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_peer_buffer_close(mcl_cuda_ctx* ctx, void* dptr) {
+    MCL_NEED_CTX(ctx);
+    if (!dptr) return MCL_CUDA_OK;
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess) e = cudaIpcCloseMemHandle(dptr);
+    if (e != cudaSuccess) return fail_cuda(ctx, "peer_buffer_close", e);
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_peer_buffer_destroy(mcl_cuda_ctx* ctx, void* dptr) {
+    MCL_NEED_CTX(ctx);
+    if (!dptr) return MCL_CUDA_OK;
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess) e = cudaFree(dptr);
+    if (e != cudaSuccess) return fail_cuda(ctx, "peer_buffer_destroy", e);
+    return MCL_CUDA_OK;
+}
+int mcl_cuda_peer_allreduce_f32(mcl_cuda_ctx* ctx, const void* const* peer_data, void* const* peer_flags, int rank,
+                                int world, size_t n, size_t parity_stride, int parity, float* out) {
+    MCL_NEED_CTX(ctx);
+    const char* op = "peer allreduce";
+    if (world < 1 || world > mcl::kPeerMaxWorld || rank < 0 || rank >= world)
+        return fail(ctx, MCL_CUDA_EINVAL, "peer allreduce serves 1 to 8 ranks of one node");
+    if (parity != 0 && parity != 1) return fail(ctx, MCL_CUDA_EINVAL, "peer allreduce: parity is 0 or 1");
+    if (n == 0 || n % 4 != 0 || parity_stride % 4 != 0 || n > parity_stride || n > 0x7fffffffull)
+        return fail(ctx, MCL_CUDA_EINVAL, "peer allreduce needs n and parity_stride in multiples of 4 floats, n <= parity_stride");
+    if (!peer_data || !peer_flags) return fail(ctx, MCL_CUDA_EINVAL, "peer allreduce: null pointer tables");
+    MCL_TRY(check_ptr(ctx, op, "out", out, 16));
+    mcl::PeerTable tab{};
+    for (int r = 0; r < world; ++r) {
+        if (!peer_data[r] || !peer_flags[r] || reinterpret_cast<uintptr_t>(peer_data[r]) % 16 != 0 ||
+            reinterpret_cast<uintptr_t>(peer_flags[r]) % 4 != 0)
+            return fail(ctx, MCL_CUDA_EINVAL, "peer allreduce: every rank's data must be 16-byte and its flags 4-byte aligned");
+        tab.data[r] = static_cast<const float*>(peer_data[r]);
+        tab.flags[r] = static_cast<uint32_t*>(peer_flags[r]);
+    }
+    tab.parity_stride4 = parity_stride / 4;
+    tab.rank = rank; tab.world = world;
+    DeviceGuard guard(ctx->device);
+    MCL_LAUNCH(ctx, op, mcl::launch_peer_allreduce(tab, n, parity, out, ctx->err_word, ctx->stream));
     return MCL_CUDA_OK;
 }
 

@@ -146,6 +146,19 @@ cudaError_t launch_ternary_gemv(const float* x, const uint32_t* packed2, const f
                                 cudaStream_t stream);
 
 
+// peer_reduce.cu -- one-shot sum of a small vector over the GPUs of a node (peer loads, bounded flag wait)
+constexpr int kPeerMaxWorld = 8;
+constexpr int kPeerErrCode = 31;
+constexpr int kPeerFlagWords = 64;        // a rank's flag area: one word per rank, then the call counter
+constexpr int kPeerCounterWord = 32;
+struct PeerTable {
+    const float* data[kPeerMaxWorld];     // every rank's partial buffers (two parities, parity_stride4 float4 apart)
+    uint32_t* flags[kPeerMaxWorld];       // every rank's flag words: flags[r][s] = last partial number rank s announced to rank r
+    size_t parity_stride4;
+    int rank, world;
+};
+cudaError_t launch_peer_allreduce(const PeerTable& tab, size_t n, int parity, float* out, int* err_word, cudaStream_t stream);
+
 // gemv_tc.cu -- the same GEMV as integer tensor-core MMA on digit-split activations
 bool gemv_tc_supported(int M, int in_features, int out_features);
 size_t gemv_tc_workspace_bytes(int M, int in_features, int out_features);

@@ -63,14 +63,21 @@ class RowParallelGemv:
         self.packed2 = packed2_full[:, self.c0 // 16:(self.c0 + self.cols) // 16].contiguous()
         self.scale = scale_full.clone()
 
-    def __call__(self, gemv_fn, x_shard: torch.Tensor, y: torch.Tensor, group=None):
+    def __call__(self, gemv_fn, x_shard: torch.Tensor, y: torch.Tensor, group=None, reducer=None):
         """x_shard[M, cols] = this rank's input features (what a column-parallel layer before it
-        produced); y[M, O] = the full result on every rank."""
+        produced); y[M, O] = the full result on every rank.  With a `reducer` (peer.PeerReducer) the
+        partial result is written into its shared buffer and summed by one kernel per rank instead of a
+        collective call."""
+        M = x_shard.shape[0]
+        part = reducer.partial(M * self.O).view(M, self.O) if reducer is not None else y
         if self.cols > 0:
-            gemv_fn(x_shard, self.packed2, self.scale, y, x_shard.shape[0], self.cols, self.O)
+            gemv_fn(x_shard, self.packed2, self.scale, part, M, self.cols, self.O)
         else:
-            y.zero_()
-        _sum_over_ranks(y, group)
+            part.zero_()
+        if reducer is not None:
+            reducer.allreduce(y, M * self.O)
+        else:
+            _sum_over_ranks(y, group)
         return y
 
 
@@ -88,15 +95,21 @@ class TensorParallelMlp:
         self.w2 = w2[:, self.c0 // 16:(self.c0 + self.cols) // 16].contiguous()
         self.s2 = s2.clone()
 
-    def __call__(self, gemv_fn, x, h1, h3, y, group=None):
-        """x[M, dim] -> y[M, dim]; h1, h3: scratch [M, cols]."""
+    def __call__(self, gemv_fn, x, h1, h3, y, group=None, reducer=None, gate=True):
+        """x[M, dim] -> y[M, dim]; h1, h3: scratch [M, cols].  gate=False leaves the elementwise gate out (a sweep
+        that times the matrix products alone).  reducer: see RowParallelGemv."""
         M = x.shape[0]
+        part = reducer.partial(M * self.dim).view(M, self.dim) if reducer is not None else y
         if self.cols > 0:
             gemv_fn(x, self.w1, self.s1, h1, M, self.dim, self.cols)
             gemv_fn(x, self.w3, self.s3, h3, M, self.dim, self.cols)
-            h1.copy_(torch.nn.functional.silu(h1) * h3)
-            gemv_fn(h1, self.w2, self.s2, y, M, self.cols, self.dim)
+            if gate:
+                h1.copy_(torch.nn.functional.silu(h1) * h3)
+            gemv_fn(h1, self.w2, self.s2, part, M, self.cols, self.dim)
         else:
-            y.zero_()
-        _sum_over_ranks(y, group)
+            part.zero_()
+        if reducer is not None:
+            reducer.allreduce(y, M * self.dim)
+        else:
+            _sum_over_ranks(y, group)
         return y

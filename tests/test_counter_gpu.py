@@ -785,3 +785,46 @@ def test_workspace_growth_is_refused_while_a_recorded_batch_is_alive(orc):
         c2.finish()
     finally:
         c2.close()
+
+
+
+def test_peer_allreduce_of_one_rank_copies_its_partial(ctx):
+    """mcl_cuda_peer_allreduce_f32 with a single rank: the hand-shake is with itself and the sum is the partial.  Both
+    parities, several calls in a row."""
+    from motifcl_b200.peer import PeerReducer
+    red = PeerReducer(ctx, 4096)
+    try:
+        out = torch.zeros(4096, dtype=torch.float32, device=DEV)
+        for k in range(5):
+            n = 4096 if k % 2 == 0 else 1024
+            src = torch.randn(n, device=DEV)
+            red.partial(n).copy_(src)
+            red.allreduce(out, n)
+            ctx.finish()
+            assert torch.equal(out[:n], src)
+    finally:
+        red.close()
+
+
+def test_peer_allreduce_gives_up_when_a_rank_never_arrives(ctx):
+    """A table that names a second rank whose flag nobody writes: the kernel's wait runs out (2 s), the context reports
+    code 31 at the next finish, and the context stays usable."""
+    import ctypes as C
+    from motifcl_b200.peer import PeerReducer, FLAG_WORDS
+    red = PeerReducer(ctx, 1024)
+    try:
+        vp = C.c_void_p * 2
+        flags = vp(red._own, red._own + 192)                 # "rank 1": spare words of the flag area; nobody signals for it
+        data = vp(red._own + FLAG_WORDS * 4, red._own + FLAG_WORDS * 4)
+        out = torch.zeros(1024, dtype=torch.float32, device=DEV)
+        ctx._check(ctx._lib.mcl_cuda_peer_allreduce_f32(ctx._ctx, data, flags, 0, 2, 1024, 1024, 1, C.c_void_p(out.data_ptr())))     # parity 1
+        with pytest.raises(RuntimeError, match="peer all-reduce"):
+            ctx.finish()
+        red.seq = 1                                           # the failed call took number 1 and parity 1
+        red.partial(1024).fill_(2.0)
+        red.allreduce(out, 1024)
+        ctx.finish()
+        assert torch.all(out == 2.0)
+    finally:
+        red.close()
+

@@ -14,7 +14,7 @@
 // Two partial buffers alternate (the caller's `parity`): a rank may run ahead into the next GEMV while a peer still
 // reads the last partial, and by the time a buffer comes round again every peer has passed the hand-shake after its
 // last read.  All ranks must make the same sequence of calls.  One CTA: the vectors are 16 to 256 KB.
-// No multicast, no load from a peer before its flag says the data is there, no wait without a limit.
+// Plain loads and stores only; no load from a peer before its flag says the data is there; no wait without a limit.
 #include "kernels.h"
 
 namespace mcl {

@@ -45,14 +45,24 @@ class PeerReducer:
             mine = torch.frombuffer(bytearray(handle.raw), dtype=torch.uint8).to(dev)
             every = [torch.empty(64, dtype=torch.uint8, device=dev) for _ in range(self.world)]
             dist.all_gather(every, mine, group=group)
+            failure = None
             for r in range(self.world):
                 if r == self.rank:
                     continue
                 p = C.c_void_p()
-                ctx._check(lib.mcl_cuda_peer_buffer_open(h, bytes(every[r].cpu().numpy().tobytes()), C.byref(p)))
+                try:
+                    ctx._check(lib.mcl_cuda_peer_buffer_open(h, bytes(every[r].cpu().numpy().tobytes()), C.byref(p)))
+                except Exception as exc:      # noqa: BLE001  -- reported below, once every rank knows
+                    failure = exc
+                    break
                 self._opened.append(p.value)
                 ptrs[r] = p.value
-            dist.barrier(group)
+            # the ranks agree on the outcome, so that a rank that could not map a peer does not leave the others waiting
+            ok = torch.tensor([0 if failure else 1], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) == 0:
+                self.close()
+                raise RuntimeError(f"peer buffers could not be mapped on every rank ({failure})")
         vp = C.c_void_p * self.world
         self._flags = vp(*ptrs)
         self._data = vp(*[p + FLAG_WORDS * 4 for p in ptrs])
